@@ -1,0 +1,132 @@
+/*
+ * llnvfp4 - C ABI of the B200 (sm_100a) NVFP4 inference path.
+ *
+ * Every entry point takes plain device pointers, extents and a CUDA stream handle, returns
+ * 0 on success or a negative LLNV_E_* code, never throws and never aborts.  After a failure
+ * llnv_last_error() returns a thread-local, human readable message.  The caller owns and
+ * allocates every buffer; unless an entry point says otherwise the library allocates nothing.
+ *
+ * Each declaration cites the interface of the reference implementation (NVlabs/LongLive,
+ * paths relative to its repository root) that it stands in for.
+ */
+#ifndef LLNVFP4_H_
+#define LLNVFP4_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* llnv_stream_t; /* a cudaStream_t */
+
+enum {
+  LLNV_OK = 0,
+  LLNV_E_INVALID = -1,   /* bad argument: null pointer, shape, alignment, unsupported option */
+  LLNV_E_CUDA = -2,      /* a CUDA runtime / driver call failed */
+  LLNV_E_TIMEOUT = -3,   /* a bounded device-side wait gave up (reported by llnv_check_status) */
+  LLNV_E_UNSUPPORTED = -4
+};
+
+/* Scale-selection rule ids; same numbering as ScaleRule.cuda_id() in
+ * fouroversix/src/fouroversix/utils.py:113-122. */
+enum {
+  LLNV_RULE_STATIC_6 = 0,
+  LLNV_RULE_STATIC_4 = 1,
+  LLNV_RULE_MAE = 2,
+  LLNV_RULE_MSE = 3,
+  LLNV_RULE_ABS_MAX = 4
+};
+
+/* Output element type codes; same numbering as utils/kernel/kv_dequant.py:18-25. */
+enum { LLNV_DTYPE_BF16 = 0, LLNV_DTYPE_FP16 = 1, LLNV_DTYPE_FP32 = 2 };
+
+/* Which of the reference's dequantize roundings to follow (they can differ in the last bit):
+ *  FUSED   (v*s) * (amax * fp32(1/(e2m1_max*e4m3_max)))   utils/kernel/kv_dequant_cuda.cu:95-101,216
+ *  PYTORCH ((v*s) * amax) / (e2m1_max*e4m3_max)           fouroversix/src/fouroversix/quantize/quantized_tensor.py:187-209
+ *  TRITON  (v*s) * (amax / (e2m1_max*e4m3_max))           utils/quant.py:756-766 */
+enum { LLNV_DEQ_FUSED = 0, LLNV_DEQ_PYTORCH = 1, LLNV_DEQ_TRITON = 2 };
+
+int llnv_version(void);
+const char* llnv_last_error(void);
+
+/* Reads and clears the device-side status word that kernels with bounded waits write when a
+ * wait gives up.  Synchronises `stream`.  Returns LLNV_OK or LLNV_E_TIMEOUT. */
+int llnv_check_status(llnv_stream_t stream);
+
+/* max|x| of a bf16 matrix [M, K] with row stride ldx (elements) into *amax (device fp32).
+ * Stands in for the tensor-amax half of fp4_quant_prologue_kernel
+ * (fouroversix/src/fouroversix/csrc/include/fp4_quant_kernel.h:31-229).  *amax is overwritten. */
+int llnv_amax_bf16(const void* x, int64_t M, int64_t K, int64_t ldx, float* amax, llnv_stream_t stream);
+
+/* bf16 [M, K] -> NVFP4.  Stands in for torch.ops.fouroversix.quantize_to_fp4 with
+ * is_nvfp4=1, is_rtn=1, no RHT, 1-D blocks, no transpose
+ * (fouroversix/src/fouroversix/csrc/bindings.cpp:28, csrc/quantize/fp4_quant.cu:99-239);
+ * results follow the reference's PyTorch quantizer bit for bit
+ * (fouroversix/src/fouroversix/quantize/pytorch/reference.py:242-368).
+ *   K % 64 == 0.  Mp = M rounded up to 128.
+ *   codes: uint8 [Mp, K/2], low nibble = even column.  Rows M..Mp-1 are written as zeros.
+ *   sf:    e4m3 bytes, Mp*K/16 of them, in the 128x4 swizzled layout
+ *          (fouroversix/src/fouroversix/quantize/utils.py:88-96).
+ *   amax:  device fp32 scalar.  amax_given == 0: computed here (overwritten);
+ *          amax_given == 1: read as the tensor scale (reference.py:244 `x_amax`).
+ *   rule:  LLNV_RULE_*. */
+int llnv_quantize_nvfp4(const void* x, int64_t M, int64_t K, int64_t ldx, int rule,
+                        void* codes, void* sf, float* amax, int amax_given, llnv_stream_t stream);
+
+/* Dequantize `num_blocks` KV-cache blocks, each an NVFP4 matrix [rows_padded, 128] holding
+ * block_token_size*num_heads logical rows (token-major, head-minor), into one contiguous
+ * tensor [1, num_blocks*block_token_size, num_heads, 128] of dtype_code.
+ * Stands in for torch.ops.longlive_kernels.dequantize_kv_cache_fp4
+ * (utils/kernel/kv_dequant.cpp:14, utils/kernel/kv_dequant_cuda.cu:148-244).
+ * codes/sf/amax are HOST arrays of `num_blocks` DEVICE pointers (passed to the kernel as
+ * launch parameters: no pointer-table upload, no synchronisation). */
+int llnv_kv_dequant(const void* const* codes, const void* const* sf, const float* const* amax,
+                    int num_blocks, int num_heads, int block_token_size, int dtype_code,
+                    float e2m1_max, float e4m3_max, int rounding, void* out, llnv_stream_t stream);
+
+/* General NVFP4 -> bf16/fp16/fp32 matrix dequantize ([rows, cols] logical, codes [rows_padded, cols_padded/2]).
+ * Stands in for QuantizedTensor.dequantize (fouroversix/src/fouroversix/quantize/quantized_tensor.py:184-214). */
+int llnv_dequantize_nvfp4(const void* codes, const void* sf, const float* amax, int64_t rows, int64_t cols,
+                          int64_t cols_padded, int dtype_code, float e2m1_max, float e4m3_max, int rounding,
+                          void* out, int64_t ldo, llnv_stream_t stream);
+
+/* Fused epilogue of the W4A4 GEMM.  All pointers are device pointers and optional (NULL = skip).
+ * With everything NULL/0 the GEMM writes bf16(alpha * acc), which is what the reference's
+ * CUTLASS kernel produces.  The chain follows the reference's rounding points
+ * (fouroversix/src/fouroversix/model/modules/linear.py:73-74, wan_5b/modules/causal_model.py:889,919):
+ *   y  = bf16(alpha * acc)
+ *   y  = bf16(y + bias[n])                         if bias
+ *   y  = bf16(gelu_tanh(y))                        if act == 1
+ *   y  = bf16(residual[m,n] + bf16(y * gate[f,n])) if residual (gate NULL -> y added as is),
+ *        f = m / frame_rows
+ *   out_amax = max(out_amax, |y|)                  if out_amax (atomic, caller zeroes it)
+ */
+typedef struct {
+  const float* alpha;     /* device scalar; NULL -> amax_a*amax_b/(6*Ea*6*Eb) from the rules */
+  const void* bias;       /* bf16 [N] */
+  int32_t act;            /* 0 none, 1 GELU(tanh) */
+  const void* residual;   /* bf16 [M, ldr] */
+  int64_t ldr;
+  const void* gate;       /* bf16 [frames, gate_stride] */
+  int64_t gate_stride;
+  int32_t frame_rows;     /* rows per frame for the gate lookup */
+  float* out_amax;        /* fp32 scalar, atomic max of |out| */
+} llnv_epilogue_t;
+
+/* D[M, N] = epilogue(alpha * A[M, K] * B[N, K]^T), A and B NVFP4 (codes [rows_padded, K/2],
+ * swizzled e4m3 scales), fp32 accumulation on tcgen05 block-scaled tensor cores, bf16 output
+ * with row stride ldd.  Stands in for
+ * torch.ops.fouroversix.gemm_nvfp4nvfp4_accum_fp32_out_bf16_tnt
+ * (fouroversix/src/fouroversix/csrc/bindings.cpp:31, csrc/fp4_gemm.cu:40-154) together with the
+ * alpha computation of fouroversix/src/fouroversix/matmul/cutlass/backend.py:81-90.
+ *   M: logical rows written (A holds ceil(M/128)*128 rows); N % 128 == 0; K % 256 == 0. */
+int llnv_gemm_nvfp4(const void* a_codes, const void* a_sf, const float* a_amax, int a_rule,
+                    const void* b_codes, const void* b_sf, const float* b_amax, int b_rule,
+                    int64_t M, int64_t N, int64_t K, const llnv_epilogue_t* epilogue,
+                    void* d, int64_t ldd, llnv_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLNVFP4_H_ */

@@ -1,0 +1,60 @@
+"""ctypes binding of ``libllnvfp4.so``.  There is no fallback: a missing library is an error."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libllnvfp4.so")
+
+# names declared in include/llnvfp4.h
+EXPORTS = [
+    "llnv_version", "llnv_last_error", "llnv_check_status", "llnv_amax_bf16", "llnv_quantize_nvfp4",
+    "llnv_kv_dequant", "llnv_dequantize_nvfp4", "llnv_gemm_nvfp4",
+]
+
+
+class Epilogue(C.Structure):
+    """Mirror of ``llnv_epilogue_t``."""
+    _fields_ = [
+        ("alpha", C.c_void_p), ("bias", C.c_void_p), ("act", C.c_int32), ("residual", C.c_void_p),
+        ("ldr", C.c_int64), ("gate", C.c_void_p), ("gate_stride", C.c_int64), ("frame_rows", C.c_int32),
+        ("out_amax", C.c_void_p),
+    ]
+
+
+class LibraryMissing(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise LibraryMissing(
+                f"{LIB_PATH} is missing: build it with `python -m longlive_b200.build` "
+                "(there is no CPU or PyTorch fallback for the NVFP4 kernels)")
+        l = C.CDLL(LIB_PATH)
+        l.llnv_last_error.restype = C.c_char_p
+        p, i64, i32, f32 = C.c_void_p, C.c_int64, C.c_int, C.c_float
+        l.llnv_check_status.argtypes = [p]
+        l.llnv_amax_bf16.argtypes = [p, i64, i64, i64, p, p]
+        l.llnv_quantize_nvfp4.argtypes = [p, i64, i64, i64, i32, p, p, p, i32, p]
+        l.llnv_kv_dequant.argtypes = [p, p, p, i32, i32, i32, i32, f32, f32, i32, p, p]
+        l.llnv_dequantize_nvfp4.argtypes = [p, p, p, i64, i64, i64, i32, f32, f32, i32, p, i64, p]
+        l.llnv_gemm_nvfp4.argtypes = [p, p, p, i32, p, p, p, i32, i64, i64, i64, p, p, i64, p]
+        for name in EXPORTS:
+            getattr(l, name)
+        _lib = l
+    return _lib
+
+
+def check(rc: int, exc=RuntimeError) -> None:
+    if rc != 0:
+        msg = lib().llnv_last_error().decode("utf-8", "replace")
+        if rc == -1:
+            raise ValueError(msg) if exc is RuntimeError else exc(msg)
+        raise exc(f"llnvfp4 error {rc}: {msg}")

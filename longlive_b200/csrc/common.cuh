@@ -1,0 +1,96 @@
+// Shared host/device helpers of the llnvfp4 library (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/llnvfp4.h"
+
+namespace llnv {
+
+// ---- error reporting -------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+
+#define LLNV_REQUIRE(cond, ...)          \
+  do {                                   \
+    if (!(cond)) {                       \
+      ::llnv::set_error(__VA_ARGS__);    \
+      return LLNV_E_INVALID;             \
+    }                                    \
+  } while (0)
+
+#define LLNV_CUDA(call)                                     \
+  do {                                                      \
+    cudaError_t e__ = (call);                               \
+    if (e__ != cudaSuccess) return ::llnv::cuda_fail(e__, #call); \
+  } while (0)
+
+inline int launch_status(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, what);
+  return LLNV_OK;
+}
+
+// Device status word written by kernels whose bounded waits give up.
+unsigned int* device_status_word();   // lazily allocated per device (never freed)
+
+// SM count of the current device (cached).
+int sm_count();
+
+// ---- scale rule constants -----------------------------------------------------------------
+__host__ __device__ inline float rule_e2m1_max(int rule) { return rule == LLNV_RULE_STATIC_4 ? 4.f : 6.f; }
+__host__ __device__ inline float rule_e4m3_max(int rule) {
+  return (rule == LLNV_RULE_STATIC_6 || rule == LLNV_RULE_STATIC_4) ? 448.f : 256.f;
+}
+
+// ---- device helpers -------------------------------------------------------------------------
+#ifdef __CUDACC__
+
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+
+// fp32 -> bf16 bits, round to nearest even (finite inputs).
+__device__ __forceinline__ uint32_t f2bf(float f) {
+  return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(f));
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) { return f2bf(lo) | (f2bf(hi) << 16); }
+// round an fp32 value to bf16 precision, keep it in fp32
+__device__ __forceinline__ float round_bf16(float f) { return __uint_as_float(f2bf(f) << 16); }
+
+// e4m3 byte -> fp32 (exact)
+__device__ __forceinline__ float e4m3_to_float(uint32_t b) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)(b & 0xFF), __NV_E4M3);
+  return __half2float(*reinterpret_cast<__half*>(&h));
+}
+// fp32 -> e4m3 byte, round to nearest even (inputs here never exceed 448)
+__device__ __forceinline__ uint32_t float_to_e4m3(float f) {
+  return (uint32_t)__nv_cvt_float_to_fp8(f, __NV_SATFINITE, __NV_E4M3);
+}
+
+// Offset of scale (row r, scale column c) in the 128x4-swizzled layout; cols = scale columns per row.
+__host__ __device__ __forceinline__ int64_t sf_offset(int64_t r, int64_t c, int64_t cols) {
+  int64_t tile = (r >> 7) * (cols >> 2) + (c >> 2);
+  return tile * 512 + (r & 31) * 16 + ((r & 127) >> 5) * 4 + (c & 3);
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+  return v;
+}
+
+// atomic max for non-negative floats (bit pattern order == value order)
+__device__ __forceinline__ void atomic_max_nonneg(float* addr, float v) {
+  atomicMax(reinterpret_cast<int*>(addr), __float_as_int(v));
+}
+
+#endif  // __CUDACC__
+
+}  // namespace llnv

@@ -1,0 +1,375 @@
+// W4A4 GEMM on tcgen05 block-scaled tensor cores (kind::mxf4nvf4, E2M1 operands, UE4M3 scale per
+// 16 elements, fp32 accumulators in tensor memory) with a fused epilogue.
+//
+//   D[M, N] = epilogue(alpha * A[M, K] * B[N, K]^T)
+//
+// One persistent CTA per SM, 6 warps:
+//   warp 0      TMA producer: per 256-element K block it loads the A tile (128 rows x 128 bytes of
+//               packed codes), the B tile (BN rows x 128 bytes) with the 128-byte swizzle, and the
+//               scale factors of both tiles (already stored as 512-byte 128x4 atoms, so a tile's
+//               scales are contiguous runs fetched with untiled bulk copies).
+//   warp 1      MMA issuer (one elected lane): copies the scale atoms shared -> tensor memory with
+//               tcgen05.cp, then issues four K=64 MMAs per stage; tcgen05.commit releases the
+//               stage to the producer and, after the last K block, hands the accumulator to the
+//               epilogue.  Warp 1 also owns the TMEM allocation.
+//   warps 2-5   epilogue: tcgen05.ld of the fp32 accumulator (32 lanes x 32 columns per load),
+//               alpha / bias / GELU / gate*y + residual / amax, bf16 stores.
+// BN = 128 keeps two accumulators in tensor memory so the epilogue of a tile overlaps the main
+// loop of the next one; BN = 256 has one accumulator (2 x 256 columns + scales exceed the 512
+// columns) but halves the shared-memory traffic per flop.
+//
+// Every mbarrier wait is bounded (see sm100.cuh); no CTA waits on another CTA.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace llnv {
+namespace {
+
+using namespace sm100;
+
+constexpr int BM = 128;
+constexpr int BK_BYTES = 128;            // 256 E2M1 elements
+constexpr int kThreads = 192;
+constexpr uint32_t kTmemCols = 512;
+
+struct GemmParams {
+  const uint8_t* sfa;
+  const uint8_t* sfb;
+  const float* a_amax;
+  const float* b_amax;
+  float alpha_denom;       // 6*Ea*6*Eb
+  int64_t M, N, K;
+  llnv_epilogue_t epi;
+  __nv_bfloat16* d;
+  int64_t ldd;
+  unsigned int* status;
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr int kAcc = BN == 128 ? 2 : 1;
+  static constexpr int kStages = BN == 128 ? 6 : 4;
+  static constexpr uint32_t kABytes = BM * BK_BYTES;
+  static constexpr uint32_t kBBytes = BN * BK_BYTES;
+  static constexpr uint32_t kSfaBytes = 2048;
+  static constexpr uint32_t kSfbBytes = BN * 16;
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+  static constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024;
+  static constexpr uint32_t kSfaCol = kAcc * BN;          // first TMEM column of the A scales
+  static constexpr uint32_t kSfbCol = kSfaCol + 16;       // 4 MMAs x 4 columns
+  static_assert(kStageBytes % 1024 == 0, "stage must keep 1024-byte alignment");
+  static_assert(kSfbCol + 4 * (BN / 32) <= kTmemCols, "tensor memory overflow");
+};
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  const float inner = k0 * (x + k1 * x * x * x);
+  return 0.5f * x * (1.f + tanhf(inner));
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  using C = Cfg<BN>;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+  uint64_t* empty_bar = full_bar + C::kStages;
+  uint64_t* tfull_bar = empty_bar + C::kStages;
+  uint64_t* tempty_bar = tfull_bar + C::kAcc;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + C::kAcc);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int num_m = (int)((p.M + BM - 1) / BM);
+  const int num_n = (int)(p.N / BN);
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (int)(p.K / 256);
+  const int64_t k_atoms = p.K / 64;       // 512-byte scale atoms per 128-row tile
+
+  if ((smem_u32(smem) & 1023u) != 0) {    // swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0 && p.status && atomicCAS(p.status, 0u, 2u) == 0u) p.status[1] = 900u;
+    return;
+  }
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < C::kStages; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < C::kAcc; ++i) {
+      mbar_init(&tfull_bar[i], 1);
+      mbar_init(&tempty_bar[i], 4);
+    }
+    *abort_flag = 0u;
+    fence_barrier_init();
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        const int mt = tile % num_m, nt = tile / num_m;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 100u);
+          uint8_t* st = smem + stage * C::kStageBytes;
+          mbar_arrive_expect_tx(&full_bar[stage], C::kStageBytes);
+          tma_load_2d(st, &tmA, kb * BK_BYTES, mt * BM, &full_bar[stage]);
+          tma_load_2d(st + C::kABytes, &tmB, kb * BK_BYTES, nt * BN, &full_bar[stage]);
+          bulk_load(st + C::kABytes + C::kBBytes, p.sfa + ((int64_t)mt * k_atoms + kb * 4) * 512, 2048, &full_bar[stage]);
+#pragma unroll
+          for (int h = 0; h < BN / 128; ++h)
+            bulk_load(st + C::kABytes + C::kBBytes + C::kSfaBytes + h * 2048,
+                      p.sfb + (((int64_t)nt * (BN / 128) + h) * k_atoms + kb * 4) * 512, 2048, &full_bar[stage]);
+          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc_nvf4(BM, BN);
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_flag, p.status, 200u);
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 201u);
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * C::kStageBytes);
+          const uint32_t b_addr = a_addr + C::kABytes;
+          const uint32_t sfa_addr = b_addr + C::kBBytes;
+          const uint32_t sfb_addr = sfa_addr + C::kSfaBytes;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            tmem_cp_sf(tmem_base + C::kSfaCol + 4 * g, make_sf_desc(sfa_addr + g * 512));
+#pragma unroll
+            for (int h = 0; h < BN / 128; ++h)
+              tmem_cp_sf(tmem_base + C::kSfbCol + (BN / 32) * g + 4 * h, make_sf_desc(sfb_addr + h * 2048 + g * 512));
+          }
+          const uint64_t a_desc = make_kmajor_sw128_desc(a_addr);
+          const uint64_t b_desc = make_kmajor_sw128_desc(b_addr);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            // 64 E2M1 elements = 32 bytes further along K inside the 128-byte swizzled row
+            mma_nvf4(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_base + C::kSfaCol + 4 * k,
+                     tmem_base + C::kSfbCol + (BN / 32) * k, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[stage]);
+          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+        }
+        tc_commit(&tfull_bar[acc]);
+        if (++acc == C::kAcc) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;                           // TMEM lane quarter this warp may access
+    float alpha;
+    if (p.epi.alpha) alpha = __ldg(p.epi.alpha);
+    else alpha = __fdiv_rn(__fmul_rn(__ldg(p.a_amax), __ldg(p.b_amax)), p.alpha_denom);
+    const uint16_t* bias = reinterpret_cast<const uint16_t*>(p.epi.bias);
+    const uint16_t* resid = reinterpret_cast<const uint16_t*>(p.epi.residual);
+    const uint16_t* gate = reinterpret_cast<const uint16_t*>(p.epi.gate);
+    float local_amax = 0.f;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      const int mt = tile % num_m, nt = tile / num_m;
+      mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, 300u);
+      tc_fence_after();
+      const int64_t row = (int64_t)mt * BM + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint16_t* grow = nullptr;
+      if (gate && row_ok) grow = gate + (row / p.epi.frame_rows) * p.epi.gate_stride;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c0, r);
+        tmem_ld_wait();
+        if (c0 + 32 == BN) {
+          // accumulator fully read: hand it back to the MMA warp before the math and the stores
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+        }
+        if (row_ok) {
+          const int64_t col = (int64_t)nt * BN + c0;
+          uint32_t outw[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float y[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int64_t n = col + 2 * j + h;
+              float v = round_bf16(__fmul_rn(alpha, __uint_as_float(r[2 * j + h])));
+              if (bias) v = round_bf16(v + __uint_as_float((uint32_t)__ldg(bias + n) << 16));
+              if (p.epi.act == 1) v = round_bf16(gelu_tanh(v));
+              if (resid) {
+                float t = v;
+                if (grow) t = round_bf16(v * __uint_as_float((uint32_t)__ldg(grow + n) << 16));
+                v = round_bf16(__uint_as_float((uint32_t)__ldg(resid + row * p.epi.ldr + n) << 16) + t);
+              }
+              local_amax = fmaxf(local_amax, fabsf(v));
+              y[h] = v;
+            }
+            outw[j] = pack_bf16x2(y[0], y[1]);
+          }
+          uint4* dst = reinterpret_cast<uint4*>(p.d + row * p.ldd + col);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) dst[j] = make_uint4(outw[4 * j], outw[4 * j + 1], outw[4 * j + 2], outw[4 * j + 3]);
+        }
+      }
+      if (++acc == C::kAcc) { acc = 0; acc_phase ^= 1u; }
+    }
+    if (p.epi.out_amax) {
+      local_amax = warp_max(local_amax);
+      if (lane == 0 && local_amax > 0.f) atomic_max_nonneg(p.epi.out_amax, local_amax);
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // a wait gave up: give copies that may still be in flight time to land before shared memory
+    // and tensor memory are released
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+
+struct MapKey {
+  const void* ptr;
+  uint64_t rows, row_bytes;
+  uint32_t box_rows;
+  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && row_bytes == o.row_bytes && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = std::hash<const void*>()(k.ptr);
+    h ^= std::hash<uint64_t>()(k.rows * 1315423911ull + k.row_bytes * 2654435761ull + k.box_rows) + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
+    return h;
+  }
+};
+
+std::mutex g_map_mu;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+int g_forced_bn = 0;
+
+int get_codes_map(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
+  MapKey key{ptr, rows, row_bytes, box_rows};
+  std::lock_guard<std::mutex> lock(g_map_mu);
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) {
+    *out = it->second;
+    return LLNV_OK;
+  }
+  CUtensorMap m;
+  int rc = make_tensor_map_2d(&m, ptr, rows, row_bytes, row_bytes, box_rows, BK_BYTES, 3);
+  if (rc != LLNV_OK) return rc;
+  if (g_maps.size() > 8192) g_maps.clear();
+  g_maps.emplace(key, m);
+  *out = m;
+  return LLNV_OK;
+}
+
+template <int BN>
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream) {
+  static bool attr_set[64] = {};
+  int dev = 0;
+  LLNV_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    LLNV_CUDA(cudaFuncSetAttribute(gemm_nvfp4_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<BN>::kSmemBytes));
+    attr_set[dev] = true;
+  }
+  const int64_t tiles = ((p.M + BM - 1) / BM) * (p.N / BN);
+  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+  gemm_nvfp4_kernel<BN><<<grid, kThreads, Cfg<BN>::kSmemBytes, stream>>>(tmA, tmB, p);
+  return launch_status("gemm_nvfp4_kernel");
+}
+
+}  // namespace
+}  // namespace llnv
+
+using namespace llnv;
+
+// Test/benchmark hook: force the N tile (128 or 256); 0 restores the automatic choice.
+extern "C" int llnv_gemm_nvfp4_force_tile_n(int bn) {
+  LLNV_REQUIRE(bn == 0 || bn == 128 || bn == 256, "llnv_gemm_nvfp4_force_tile_n: tile must be 0, 128 or 256");
+  g_forced_bn = bn;
+  return LLNV_OK;
+}
+
+extern "C" int llnv_gemm_nvfp4(const void* a_codes, const void* a_sf, const float* a_amax, int a_rule, const void* b_codes,
+                               const void* b_sf, const float* b_amax, int b_rule, int64_t M, int64_t N, int64_t K,
+                               const llnv_epilogue_t* epilogue, void* d, int64_t ldd, llnv_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  LLNV_REQUIRE(a_codes && a_sf && b_codes && b_sf && d, "llnv_gemm_nvfp4: null pointer");
+  LLNV_REQUIRE(M >= 0 && N > 0 && K > 0, "llnv_gemm_nvfp4: bad shape M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
+  LLNV_REQUIRE(N % 128 == 0, "llnv_gemm_nvfp4: N must be a multiple of 128 (got %lld)", (long long)N);
+  LLNV_REQUIRE(K % 256 == 0, "llnv_gemm_nvfp4: K must be a multiple of 256 (got %lld)", (long long)K);
+  LLNV_REQUIRE(ldd >= N && ldd % 8 == 0 && ((uintptr_t)d & 15) == 0, "llnv_gemm_nvfp4: d must be 16-byte aligned with ldd a multiple of 8");
+  LLNV_REQUIRE(((uintptr_t)a_sf & 15) == 0 && ((uintptr_t)b_sf & 15) == 0, "llnv_gemm_nvfp4: scale arrays must be 16-byte aligned");
+  LLNV_REQUIRE(a_rule >= 0 && a_rule <= 4 && b_rule >= 0 && b_rule <= 4, "llnv_gemm_nvfp4: unknown scale rule");
+  llnv_epilogue_t epi;
+  memset(&epi, 0, sizeof(epi));
+  if (epilogue) epi = *epilogue;
+  LLNV_REQUIRE(epi.alpha || (a_amax && b_amax), "llnv_gemm_nvfp4: need alpha or both amax pointers");
+  LLNV_REQUIRE(epi.act == 0 || epi.act == 1, "llnv_gemm_nvfp4: unknown activation %d", epi.act);
+  if (epi.residual) LLNV_REQUIRE(epi.ldr >= N, "llnv_gemm_nvfp4: residual row stride smaller than N");
+  if (epi.gate) LLNV_REQUIRE(epi.residual && epi.frame_rows > 0 && epi.gate_stride >= N, "llnv_gemm_nvfp4: gate needs residual, frame_rows > 0 and gate_stride >= N");
+  if (M == 0) return LLNV_OK;
+
+  int bn = (N % 256 == 0) ? 256 : 128;
+  if (g_forced_bn == 128) bn = 128;
+  if (g_forced_bn == 256 && N % 256 == 0) bn = 256;
+
+  const uint64_t mp = (uint64_t)((M + 127) / 128 * 128);
+  CUtensorMap tmA, tmB;
+  int rc = get_codes_map(&tmA, a_codes, mp, (uint64_t)K / 2, BM);
+  if (rc != LLNV_OK) return rc;
+  rc = get_codes_map(&tmB, b_codes, (uint64_t)N, (uint64_t)K / 2, (uint32_t)bn);
+  if (rc != LLNV_OK) return rc;
+
+  GemmParams p;
+  p.sfa = (const uint8_t*)a_sf;
+  p.sfb = (const uint8_t*)b_sf;
+  p.a_amax = a_amax;
+  p.b_amax = b_amax;
+  p.alpha_denom = rule_e2m1_max(a_rule) * rule_e4m3_max(a_rule) * rule_e2m1_max(b_rule) * rule_e4m3_max(b_rule);
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.epi = epi;
+  p.d = (__nv_bfloat16*)d;
+  p.ldd = ldd;
+  p.status = device_status_word();
+  return bn == 256 ? launch<256>(tmA, tmB, p, stream) : launch<128>(tmA, tmB, p, stream);
+}

@@ -1,0 +1,143 @@
+"""torch.Tensor-level wrappers around the C-ABI entry points (device pointers in, nothing
+allocated by the library).  These are the only functions that touch ctypes."""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+
+_DTYPE_CODES = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+DEQ_FUSED, DEQ_PYTORCH, DEQ_TRITON = 0, 1, 2
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not isinstance(t, torch.Tensor) or t.device.type != "cuda":
+        raise ValueError(f"{name} must be a CUDA tensor (the NVFP4 path has no CPU implementation)")
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        msg = _lib.lib().llnv_last_error().decode("utf-8", "replace")
+        raise RuntimeError(f"llnvfp4 error {rc}: {msg}")
+
+
+def padded_rows(m: int) -> int:
+    return (m + 127) // 128 * 128
+
+
+def amax_bf16(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    _require_cuda(x, "x")
+    assert x.dim() == 2 and x.dtype == torch.bfloat16 and x.stride(1) == 1
+    if out is None:
+        out = torch.empty(1, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _check(_lib.lib().llnv_amax_bf16(x.data_ptr(), x.shape[0], x.shape[1], x.stride(0), out.data_ptr(), _stream(x)))
+    return out
+
+
+def quantize_nvfp4(x: torch.Tensor, rule_id: int, amax: torch.Tensor | None = None, codes=None, sf=None,
+                   amax_given: bool | None = None):
+    """bf16 [M, K] (K % 64 == 0, unit column stride) -> (codes [Mp, K/2] u8, sf [Mp*K/16] e4m3, amax [1] f32).
+
+    ``amax`` is the fp32 tensor-scale buffer.  With ``amax_given`` (default: true when a buffer is
+    passed) it is read as the scale; otherwise it is computed on the device into that buffer (or a
+    new one).  ``codes`` / ``sf`` may be preallocated slot buffers (KV cache) written in place.
+    """
+    _require_cuda(x, "x")
+    if x.dim() != 2 or x.dtype != torch.bfloat16:
+        raise RuntimeError("quantize_nvfp4 expects a 2-D bfloat16 tensor")
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    m, k = x.shape
+    mp = padded_rows(m)
+    if codes is None:
+        codes = torch.empty((mp, k // 2), dtype=torch.uint8, device=x.device)
+    if sf is None:
+        sf = torch.empty(mp * k // 16, dtype=torch.float8_e4m3fn, device=x.device)
+    given = (amax is not None) if amax_given is None else bool(amax_given)
+    if amax is None:
+        if given:
+            raise ValueError("amax_given needs an amax tensor")
+        amax = torch.empty(1, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _check(_lib.lib().llnv_quantize_nvfp4(x.data_ptr(), m, k, x.stride(0), rule_id, codes.data_ptr(), sf.data_ptr(),
+                                              amax.data_ptr(), 1 if given else 0, _stream(x)))
+    return codes, sf, amax
+
+
+def dequantize_nvfp4(codes, sf, amax, rows, cols, cols_padded, dtype, e2m1_max, e4m3_max, rounding=DEQ_PYTORCH):
+    _require_cuda(codes, "codes")
+    out = torch.empty((rows, cols), dtype=dtype, device=codes.device)
+    with torch.cuda.device(codes.device):
+        _check(_lib.lib().llnv_dequantize_nvfp4(codes.data_ptr(), sf.data_ptr(), amax.data_ptr(), rows, cols, cols_padded,
+                                                _DTYPE_CODES[dtype], float(e2m1_max), float(e4m3_max), rounding,
+                                                out.data_ptr(), out.stride(0), _stream(codes)))
+    return out
+
+
+def kv_dequant(values, scale_factors, amax, num_heads, block_token_size, dtype, e2m1_max, e4m3_max,
+               rounding=DEQ_FUSED, out=None):
+    n = len(values)
+    if n == 0:
+        raise RuntimeError("values must contain at least one cache block")
+    if not (len(scale_factors) == n and len(amax) == n):
+        raise RuntimeError("values, scale_factors and amax must have the same length")
+    _require_cuda(values[0], "values")
+    dev = values[0].device
+    if dtype not in _DTYPE_CODES:
+        raise ValueError(f"Unsupported fused KV dequant dtype: {dtype}")
+    for v, s, a in zip(values, scale_factors, amax):
+        if v.dtype != torch.uint8 or v.dim() != 2 or v.shape[1] != 64:
+            raise RuntimeError("KV dequant expects uint8 values of shape [rows_padded, 64] (head_dim 128)")
+        if v.shape[0] < num_heads * block_token_size or v.shape[0] % 128 != 0:
+            raise RuntimeError("values rows must be padded to a multiple of 128 and cover the block")
+        if a.dtype != torch.float32:
+            raise RuntimeError("amax tensors must be float32")
+        if v.device != dev or s.device != dev or a.device != dev:
+            raise RuntimeError("all KV block tensors must be on the same device")
+        if not (v.is_contiguous() and s.is_contiguous() and a.is_contiguous()):
+            raise RuntimeError("KV block tensors must be contiguous")
+    if out is None:
+        out = torch.empty((1, n * block_token_size, num_heads, 128), dtype=dtype, device=dev)
+    arr = C.c_void_p * n
+    cp = arr(*[v.data_ptr() for v in values])
+    sp = arr(*[s.data_ptr() for s in scale_factors])
+    ap = arr(*[a.data_ptr() for a in amax])
+    with torch.cuda.device(dev):
+        _check(_lib.lib().llnv_kv_dequant(cp, sp, ap, n, num_heads, block_token_size, _DTYPE_CODES[dtype],
+                                          float(e2m1_max), float(e4m3_max), rounding, out.data_ptr(), _stream(values[0])))
+    return out
+
+
+def gemm_nvfp4(a_codes, a_sf, a_amax, a_rule, b_codes, b_sf, b_amax, b_rule, m, n, k, *, out=None, alpha=None,
+               bias=None, act=0, residual=None, gate=None, frame_rows=0, out_amax=None):
+    """``epilogue(alpha * A @ B^T)`` -> bf16 [m, n]; see ``llnv_gemm_nvfp4`` in include/llnvfp4.h."""
+    _require_cuda(a_codes, "a_codes")
+    dev = a_codes.device
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    epi = _lib.Epilogue()
+    epi.alpha = alpha.data_ptr() if alpha is not None else None
+    epi.bias = bias.data_ptr() if bias is not None else None
+    epi.act = int(act)
+    if residual is not None:
+        epi.residual = residual.data_ptr()
+        epi.ldr = residual.stride(0)
+    if gate is not None:
+        epi.gate = gate.data_ptr()
+        epi.gate_stride = gate.stride(0)
+        epi.frame_rows = int(frame_rows)
+    epi.out_amax = out_amax.data_ptr() if out_amax is not None else None
+    with torch.cuda.device(dev):
+        _check(_lib.lib().llnv_gemm_nvfp4(a_codes.data_ptr(), a_sf.data_ptr(),
+                                          a_amax.data_ptr() if a_amax is not None else None, a_rule,
+                                          b_codes.data_ptr(), b_sf.data_ptr(),
+                                          b_amax.data_ptr() if b_amax is not None else None, b_rule,
+                                          m, n, k, C.byref(epi), out.data_ptr(), out.stride(0), _stream(a_codes)))
+    return out

@@ -1,0 +1,158 @@
+"""CUDA quantizer / dequantize parity: bit-exact against the numpy oracle and the golden
+fixtures generated from the reference."""
+import hashlib
+
+import numpy as np
+import pytest
+import torch
+
+import longlive_b200 as L
+from longlive_b200 import ops
+from oracle import nvfp4_oracle as O
+from tests import util
+
+pytestmark = pytest.mark.gpu
+RULES = ["static_6", "static_4", "mae", "mse", "abs_max"]
+
+
+def sha(a):
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+@pytest.mark.parametrize("case", ["edge", "randn", "zeros"])
+@pytest.mark.parametrize("rule", RULES)
+def test_quantize_matches_reference_fixtures(golden, case, rule):
+    g = golden("quantize_small.npz")
+    x = util.bf16_np_to_torch(g[f"{case}_x"])
+    q = L.quantize_to_fp4(x, L.QuantizationConfig(scale_rule=rule))
+    assert q.padded_shape == tuple(g[f"{case}_{rule}_padded"])
+    assert float(q.amax.item()) == float(g[f"{case}_{rule}_amax"])
+    assert np.array_equal(util.u8(q.scale_factors), g[f"{case}_{rule}_sf"])
+    assert np.array_equal(q.values.cpu().numpy(), g[f"{case}_{rule}_codes"])
+    for dtype, key in ((torch.float32, "deq_f32"), (torch.bfloat16, "deq_bf16")):
+        d = q.dequantize(dtype)
+        if dtype == torch.float32:
+            assert np.array_equal(d.cpu().numpy().view(np.uint32), g[f"{case}_{rule}_{key}"].view(np.uint32))
+        else:
+            assert np.array_equal(util.torch_bf16_bits(d), g[f"{case}_{rule}_{key}"])
+
+
+@pytest.mark.parametrize("rule", RULES)
+def test_quantize_ragged_columns(golden, rule):
+    g = golden("quantize_small.npz")          # [130, 320]: columns padded to 384 by the frontend
+    x = util.bf16_np_to_torch(g["ragged_x"])
+    q = L.quantize_to_fp4(x, L.QuantizationConfig(scale_rule=rule))
+    assert q.original_shape == (130, 320) and q.padded_shape == (256, 384)
+    assert np.array_equal(util.u8(q.scale_factors), g[f"ragged_{rule}_sf"])
+    assert np.array_equal(q.values.cpu().numpy(), g[f"ragged_{rule}_codes"])
+    assert np.array_equal(util.torch_bf16_bits(q.dequantize(torch.bfloat16)), g[f"ragged_{rule}_deq_bf16"])
+
+
+def test_quantize_config1_activation_and_weight(golden):
+    g = golden("config1_linear.npz")
+    torch.manual_seed(0)
+    M, K, N = 2640, 3072, 3072
+    x = torch.randn(M, K)
+    x = torch.where(torch.rand(M, K) < 0.001, x * 20, x).bfloat16()
+    w = (torch.randn(N, K) * 0.02).bfloat16()
+    assert sha(util.torch_bf16_bits(x)) == str(g["x_sha"])
+    xq = L.quantize_to_fp4(x.cuda())
+    wq = L.quantize_to_fp4(w.cuda())
+    assert float(xq.amax.item()) == float(g["x_amax"]) and float(wq.amax.item()) == float(g["w_amax"])
+    assert sha(xq.values.cpu().numpy()) == str(g["x_codes_sha"])
+    assert sha(util.u8(xq.scale_factors)) == str(g["x_sf_sha"])
+    assert sha(wq.values.cpu().numpy()) == str(g["w_codes_sha"])
+    assert sha(util.u8(wq.scale_factors)) == str(g["w_sf_sha"])
+
+
+@pytest.mark.parametrize("shape", [(1, 64), (127, 128), (129, 192), (512, 14336), (880, 3072)])
+def test_quantize_vs_oracle_shapes(shape):
+    x = util.config_activation(*shape, seed=shape[0])
+    q = L.quantize_to_fp4(x.cuda())
+    codes, sf, amax = O.quantize_nvfp4(x.float().numpy(), "mse")
+    assert float(q.amax.item()) == float(amax)
+    assert np.array_equal(util.u8(q.scale_factors), sf)
+    assert np.array_equal(q.values.cpu().numpy(), codes)
+
+
+def test_quantize_given_amax_and_strided_input():
+    x = util.config_activation(256, 512, seed=5)
+    big = torch.zeros(256, 1024, dtype=torch.bfloat16)
+    big[:, 256:768] = x
+    view = big.cuda()[:, 256:768]
+    amax = torch.tensor([37.5], dtype=torch.float32, device="cuda")
+    q = L.quantize_to_fp4(view, L.QuantizationConfig(scale_rule="mse"), amax=amax)
+    codes, sf, _ = O.quantize_nvfp4(x.float().numpy(), "mse", amax=np.float32(37.5))
+    assert np.array_equal(q.values.cpu().numpy(), codes) and np.array_equal(util.u8(q.scale_factors), sf)
+
+
+def test_quantize_properties_full_size():
+    """Size-independent checks on the largest benchmark activation (10560 x 14336)."""
+    m, k = 10560, 14336
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(m, k, generator=g, device="cuda", dtype=torch.float32).bfloat16()
+    q = L.quantize_to_fp4(x)
+    assert float(q.amax.item()) == float(x.abs().max().item())
+    d = q.dequantize(torch.float32)
+    rel = ((d - x.float()).norm() / x.float().norm()).item()
+    assert rel < 0.12                                    # NVFP4 4-over-6 on gaussian data: ~9 %
+    # idempotence: quantizing the dequantized tensor with the same amax reproduces codes and scales
+    q2 = L.quantize_to_fp4(d.bfloat16(), amax=q.amax)
+    d2 = q2.dequantize(torch.float32)
+    assert ((d2 - d.bfloat16().float()).abs().max() <= d.abs().max() * 0.07).item()
+    # padding rows are zero codes / zero scales
+    assert q.values.shape[0] == 10624 and int(q.values[m:].max().item()) == 0
+
+
+def test_kv_dequant_matches_oracle_and_fixture(golden):
+    g = golden("kv_small.npz")
+    codes = torch.from_numpy(g["codes"]).cuda()
+    sf = torch.from_numpy(g["sf"]).cuda().view(torch.float8_e4m3fn)
+    amax = torch.tensor([float(g["amax"])], dtype=torch.float32, device="cuda")
+    T, H = 48, 4
+    qt = L.QuantizedTensor(codes, sf, amax, "nvfp4", (T * H, 128), "mse")
+    out = ops.kv_dequant([codes], [sf], [amax], H, T, torch.bfloat16, 6, 256, ops.DEQ_PYTORCH)
+    assert np.array_equal(util.torch_bf16_bits(out[0]), g["deq_bf16"])
+    blocks = []
+    for i in range(3):
+        k = torch.randn(T * H, 128, generator=torch.Generator().manual_seed(40 + i)).bfloat16() * (i + 1)
+        blocks.append(L.quantize_to_fp4(k.cuda()))
+    fused = L.dequantize_kv_cache(blocks + [qt], 4, H, T, torch.bfloat16, "cuda")
+    assert fused.shape == (1, 4 * T, H, 128)
+    ref = O.dequantize_kv_cache([(b.values.cpu().numpy(), util.u8(b.scale_factors), np.float32(b.amax.item()))
+                                 for b in blocks + [qt]], H, T, "mse", O.DEQ_FUSED_CUDA)
+    assert np.array_equal(util.torch_bf16_bits(fused), O.bf16_bits(ref))
+    for dt in (torch.float16, torch.float32):
+        o = L.dequantize_kv_cache(blocks, 3, H, T, dt, "cuda")
+        r32 = O.dequantize_kv_cache([(b.values.cpu().numpy(), util.u8(b.scale_factors), np.float32(b.amax.item()))
+                                     for b in blocks], H, T, "mse", O.DEQ_FUSED_CUDA)
+        assert o.dtype == dt and o.shape == (1, 3 * T, H, 128)
+
+
+def test_kv_slot_helpers():
+    T, H = 16, 8
+    k = torch.randn(T * H, 128, generator=torch.Generator().manual_seed(2)).bfloat16().cuda()
+    slot = L.quantize_to_fp4(torch.zeros_like(k))
+    ptrs = (slot.values.data_ptr(), slot.scale_factors.data_ptr(), slot.amax.data_ptr())
+    src = L.quantize_to_fp4(k)
+    L.copy_quantized_into(slot, src)
+    assert torch.equal(slot.values, src.values) and torch.equal(slot.amax, src.amax)
+    assert ptrs == (slot.values.data_ptr(), slot.scale_factors.data_ptr(), slot.amax.data_ptr())
+    clone = L.clone_quantized_tensor(slot)
+    assert clone.values.data_ptr() != slot.values.data_ptr() and torch.equal(clone.values, slot.values)
+    # in-place quantize into the slot (no staging copy)
+    k2 = (k * 3).contiguous()
+    L.quantize_to_fp4(k2, out=slot)
+    ref = L.quantize_to_fp4(k2)
+    assert torch.equal(slot.values, ref.values) and torch.equal(slot.amax, ref.amax)
+    assert torch.equal(slot.scale_factors.view(torch.uint8), ref.scale_factors.view(torch.uint8))
+    ks = L.k_smooth(k.view(1, T, H, 128))
+    assert np.array_equal(util.torch_bf16_bits(ks), O.bf16_bits(O.k_smooth(k.view(1, T, H, 128).float().cpu().numpy())))
+
+
+def test_c_abi_error_reporting():
+    x = torch.zeros(128, 96, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="multiple of 64"):
+        ops.quantize_nvfp4(x, 3)
+    with pytest.raises(RuntimeError, match="at least one cache block"):
+        ops.kv_dequant([], [], [], 4, 4, torch.bfloat16, 6, 256)
