@@ -1,0 +1,353 @@
+#!/usr/bin/env python
+"""Benchmark of the NVFP4 hot path: the W4A4 GEMM shape sweep of one Wan2.2-5B-shaped DiT block.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+Workload (seeded synthetic tensors with the benchmark's shapes and value distributions):
+q/k/v/o and cross-attention q/o 3072->3072, cross-attention k/v over 512 text tokens, FFN
+3072->14336->3072, for M in {880, 2640, 10560} tokens; activations ~N(0,1) with 0.1 % entries
+x20, weights ~N(0, 0.02), both quantized to NVFP4 with the 4-over-6 MSE rule.
+
+One "step" is one pass over all 30 GEMMs of the sweep.
+  value  W4A4 GEMM TFLOP/s (2*M*N*K with the logical M) with NVFP4 operands resident in HBM,
+         timed with CUDA events around each step, L2 flushed between steps, max over ranks.
+  e2e    the same FLOPs through the public Linear path from HOST buffers: pinned bf16
+         activations -> device, quantize, GEMM + bias, result -> host, all inside the timed region.
+With --gpus N every rank runs the sweep on its own token shard (tokens are sharded across
+ranks for every Linear; there is no collective on this path): weak scaling.
+
+--impl reference times the CPU restatement of the reference's dequantize-then-matmul path
+(oracle/, numpy) on the host cores for the same metric, on a bounded sample of the workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+DIM, FFN, TEXT = 3072, 14336, 512
+M_SWEEP = (880, 2640, 10560)
+
+
+def sweep_shapes(m_values=M_SWEEP):
+    """(name, M, N, K) of every GEMM of the sweep."""
+    shapes = []
+    for m in m_values:
+        for name in ("self_attn.q", "self_attn.k", "self_attn.v", "self_attn.o", "cross_attn.q", "cross_attn.o"):
+            shapes.append((name, m, DIM, DIM))
+        shapes.append(("cross_attn.k", TEXT, DIM, DIM))
+        shapes.append(("cross_attn.v", TEXT, DIM, DIM))
+        shapes.append(("ffn.0", m, FFN, DIM))
+        shapes.append(("ffn.2", m, DIM, FFN))
+    return shapes
+
+
+def flops_of(shapes) -> float:
+    return float(sum(2.0 * m * n * k for _, m, n, k in shapes))
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(prefix="clocks_", suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(self.gpu)],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    smax.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            # the loop is busy for most samples; use the upper half to skip idle gaps between steps
+            out["sm_mhz"] = statistics.median(sm)
+            out["sm_max_mhz"] = max(smax)
+            out["samples"] = len(sm)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm (oracle port): dequantize-then-fp32-matmul on the host cores
+# ---------------------------------------------------------------------------------------------
+
+def cpu_port_tflops(sample_shapes, repeats: int = 1):
+    """Times oracle.fp4_matmul (the reference's PyTorch matmul backend restated in numpy) on
+    pre-quantized operands; returns (TFLOP/s, seconds, description)."""
+    import numpy as np
+
+    from oracle import nvfp4_oracle as O
+
+    rng = np.random.default_rng(0)
+    ops_ = []
+    for name, m, n, k in sample_shapes:
+        x = rng.standard_normal((m, k), dtype=np.float32)
+        x = np.where(rng.random((m, k)) < 0.001, x * 20, x).astype(np.float32)
+        w = (rng.standard_normal((n, k), dtype=np.float32) * 0.02).astype(np.float32)
+        # quantization of the operands is not part of the GEMM metric: use the static rule (one pass)
+        ops_.append((O.quantize_nvfp4(O.bf16_round(x), "static_6"), O.quantize_nvfp4(O.bf16_round(w), "static_6"), (m, k), (n, k)))
+    t0 = time.perf_counter()
+    for _ in range(repeats):
+        for xq, wq, xs, ws in ops_:
+            O.fp4_matmul(xq, wq, xs, ws, "static_6", "static_6")
+    dt = time.perf_counter() - t0
+    fl = flops_of(sample_shapes) * repeats
+    return fl / dt / 1e12, dt, "; ".join(f"{n} {m}x{nn}x{k}" for n, m, nn, k in sample_shapes)
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample = [s for s in sweep_shapes((880,)) if s[0] in ("self_attn.q", "cross_attn.k", "ffn.0")]
+    for _ in range(max(0, min(args.warmup, 1))):
+        cpu_port_tflops(sample[:1])
+    vals, secs = [], []
+    for _ in range(max(1, min(args.steps, 5))):
+        v, dt, desc = cpu_port_tflops(sample)
+        vals.append(v)
+        secs.append(dt)
+    value = statistics.mean(vals)
+    cores = os.cpu_count() or 1
+    line = {
+        "impl": "reference", "metric": "w4a4_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": len(vals), "warmup": min(args.warmup, 1), "ms_per_step": statistics.mean(secs) * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4 (dequantized to f32 on the CPU)",
+        "data": "synthetic",
+        "config": {"workload": "DiT-block W4A4 GEMM sweep (3072/14336, M in {880,2640,10560}); CPU arm runs a bounded sample",
+                   "l2": "n/a (CPU)"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                         "sample": f"numpy restatement of the reference's dequantize-then-fp32-matmul backend on: {desc}"},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    import longlive_b200 as L
+    from longlive_b200 import _lib, ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.lib()
+
+    shapes = sweep_shapes()
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+
+    def activation(m, k):
+        x = torch.randn(m, k, generator=gen, device=dev)
+        mask = torch.rand(m, k, generator=gen, device=dev) < 0.001
+        return torch.where(mask, x * 20, x).bfloat16()
+
+    cfg = L.QuantizationConfig(scale_rule="mse")
+    weights = {}
+    for name, m, n, k in shapes:
+        if (name, n, k) not in weights:
+            w = (torch.randn(n, k, generator=gen, device=dev) * 0.02).bfloat16()
+            weights[(name, n, k)] = (L.quantize_to_fp4(w, cfg), torch.zeros(n, dtype=torch.bfloat16, device=dev))
+            del w
+    acts = {}
+    for name, m, n, k in shapes:
+        if (m, k) not in acts:
+            acts[(m, k)] = L.quantize_to_fp4(activation(m, k), cfg)
+    outs = {}
+    for name, m, n, k in shapes:
+        if (m, n) not in outs:
+            outs[(m, n)] = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+
+    def gemm_step():
+        for name, m, n, k in shapes:
+            xq = acts[(m, k)]
+            wq, _ = weights[(name, n, k)]
+            ops.gemm_nvfp4(xq.values, xq.scale_factors, xq.amax, 3, wq.values, wq.scale_factors, wq.amax, 3, m, n, k,
+                           out=outs[(m, n)])
+
+    def sync_all():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+
+    for _ in range(max(args.warmup, 3)):
+        flush.fill_(1)
+        gemm_step()
+    sync_all()
+    assert lib.llnv_check_status(None) == 0, lib.llnv_last_error()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    sync_all()
+    wall0 = time.perf_counter()
+    for i in range(args.steps):
+        flush.fill_(i & 0xFF)          # evict the 126 MB L2 (not timed)
+        starts[i].record()
+        gemm_step()
+        ends[i].record()
+    sync_all()
+    wall = time.perf_counter() - wall0
+    step_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+    total_ms = sum(step_ms)
+    if world > 1:
+        t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    fl_step = flops_of(shapes)
+    value = fl_step * world / (ms_per_step * 1e-3) / 1e12
+    assert lib.llnv_check_status(None) == 0, lib.llnv_last_error()
+
+    # ---- end to end through the public Linear path, host buffers -------------------------------
+    e2e_steps = max(1, min(args.steps, 3))
+    host_in = {}
+    for name, m, n, k in shapes:
+        if (m, k) not in host_in:
+            host_in[(m, k)] = torch.randn(m, k, dtype=torch.bfloat16).pin_memory()
+    host_out = {}
+    for name, m, n, k in shapes:
+        if (m, n) not in host_out:
+            host_out[(m, n)] = torch.empty(m, n, dtype=torch.bfloat16).pin_memory()
+    h2d = sum(m * k * 2 for _, m, n, k in shapes)
+    d2h = sum(m * n * 2 for _, m, n, k in shapes)
+
+    def e2e_step():
+        for name, m, n, k in shapes:
+            x = host_in[(m, k)].to(dev, non_blocking=True)
+            wq, bias = weights[(name, n, k)]
+            y = L.fp4_matmul(L.quantize_to_fp4(x, cfg), wq, bias=bias)
+            host_out[(m, n)].copy_(y, non_blocking=True)
+
+    e2e_step()
+    sync_all()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    sync_all()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_value = fl_step * world / e2e_s / 1e12
+    clocks = sampler.stop() if rank == 0 else {}
+
+    if rank == 0:
+        peaks = load_peaks()
+        fp4_peak = 4.0 * peaks["bf16_tflops"]
+        per_gpu = value / world
+        line = {
+            "metric": "w4a4_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3 block scale, f32 accumulate, bf16 out)", "data": "synthetic",
+            "config": {"workload": "DiT-block W4A4 GEMM sweep: q/k/v/o + cross q/o 3072x3072, cross k/v M=512, FFN 3072<->14336; "
+                                   "M in {880,2640,10560}; 30 GEMMs per step",
+                       "flops_per_step": fl_step, "l2": "flushed between timed steps (256 MiB write)",
+                       "parallelism": f"tokens sharded over {world} rank(s), no collective"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps, "ms_per_step": e2e_s * 1e3},
+            "gpu_launches": len(shapes) * args.steps,
+            "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": fp4_peak, "unit": "TFLOP/s",
+                         "frac": per_gpu / fp4_peak, "traffic": None,
+                         "peak_note": f"4 x {peaks['source']} dense bf16 burst peak ({peaks['bf16_tflops']} TFLOP/s); "
+                                      "no FP4 entry is measured; nominal dense FP4 is 9000",
+                         "kernel": "gemm_nvfp4_kernel", "frac_of_nominal_9pf": per_gpu / 9000.0},
+            "wall_s_timed_region": wall,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            sample = [s for s in sweep_shapes((880,)) if s[0] in ("self_attn.q", "cross_attn.k", "ffn.0")]
+            v, dt, desc = cpu_port_tflops(sample)
+            line["cpu_baseline"] = {"value": v, "unit": "TFLOP/s", "cores": os.cpu_count() or 1, "kind": "port",
+                                    "sample": f"numpy restatement of the reference's dequantize-then-fp32-matmul backend, "
+                                              f"{dt:.1f} s on: {desc}"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -19,10 +19,13 @@ from tests import util
 pytestmark = pytest.mark.gpu
 
 
-def check_close(d: torch.Tensor, ref: np.ndarray, k: int):
+def check_close(d: torch.Tensor, ref: np.ndarray, k: int, mag: np.ndarray | None = None):
+    """`mag` is the magnitude the ulp tolerance refers to (the GEMM result before a bias or
+    residual is added - cancellation otherwise shrinks |ref| but not the rounding error)."""
     d = d.float().cpu().numpy()
-    scale = np.abs(ref).mean() + 1e-12
-    tol = np.abs(ref) * 2.0 ** -6 + k * 2.0 ** -24 * scale + 1e-30
+    mag = np.abs(ref) if mag is None else mag
+    scale = mag.mean() + 1e-12
+    tol = mag * 2.0 ** -6 + k * 2.0 ** -24 * scale + 1e-30
     bad = np.abs(d - ref) > tol
     assert not bad.any(), f"{bad.sum()} / {bad.size} outside tolerance; max abs diff {np.abs(d - ref).max()}"
     rel = np.linalg.norm(d - ref) / (np.linalg.norm(ref) + 1e-30)
@@ -97,8 +100,10 @@ def test_linear_module_with_bias_matches_oracle():
     y = ql(x.cuda())
     assert y.shape == (1, 300, 768)
     wq = O.quantize_nvfp4(w_np, "mse")
-    ref = O.linear_forward(x[0].float().numpy(), wq, (768, 512), lin.bias.data.float().cpu().numpy())
-    check_close(y[0], ref, 512)
+    bias_np = lin.bias.data.float().cpu().numpy()
+    ref = O.linear_forward(x[0].float().numpy(), wq, (768, 512), bias_np)
+    nobias = O.linear_forward(x[0].float().numpy(), wq, (768, 512))
+    check_close(y[0], ref, 512, mag=np.abs(nobias) + np.abs(bias_np)[None, :])
 
 
 def test_gemm_fused_epilogue_matches_unfused_chain():
