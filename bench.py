@@ -335,14 +335,81 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
+def run_kernel_case(spec: str, iters: int):
+    """Run one kernel on one shape a few times (used for ncu captures and quick timing):
+    gemm:MxNxK[:tile]   quantize:MxK[:rule]   kvdequant:BLOCKSxTOKENSxHEADS"""
+    import torch
+
+    import longlive_b200 as L
+    from longlive_b200 import _lib, ops
+
+    lib = _lib.lib()
+    kind, _, rest = spec.partition(":")
+    dims, _, opt = rest.partition(":")
+    d = [int(v) for v in dims.split("x")]
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    gen = torch.Generator(device=dev).manual_seed(0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    if kind == "gemm":
+        m, n, k = d
+        xq = L.quantize_to_fp4(torch.randn(m, k, generator=gen, device=dev).bfloat16())
+        wq = L.quantize_to_fp4((torch.randn(n, k, generator=gen, device=dev) * 0.02).bfloat16())
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+        if opt:
+            lib.llnv_gemm_nvfp4_force_tile_n(int(opt))
+        fn = lambda: ops.gemm_nvfp4(xq.values, xq.scale_factors, xq.amax, 3, wq.values, wq.scale_factors, wq.amax, 3,
+                                    m, n, k, out=out)
+        work, unit = 2.0 * m * n * k / 1e12, "TFLOP/s"
+    elif kind == "quantize":
+        m, k = d
+        x = torch.randn(m, k, generator=gen, device=dev).bfloat16()
+        rule = L.ScaleRule(opt or "mse").cuda_id()
+        mp = ops.padded_rows(m)
+        codes = torch.empty(mp, k // 2, dtype=torch.uint8, device=dev)
+        sf = torch.empty(mp * k // 16, dtype=torch.float8_e4m3fn, device=dev)
+        amax = torch.empty(1, dtype=torch.float32, device=dev)
+        fn = lambda: ops.quantize_nvfp4(x, rule, amax, codes, sf, amax_given=False)
+        work, unit = 2.5625 * m * k / 1e9, "GB/s"
+    elif kind == "kvdequant":
+        blocks, tokens, heads = d
+        qs = [L.quantize_to_fp4(torch.randn(tokens * heads, 128, generator=gen, device=dev).bfloat16()) for _ in range(blocks)]
+        out = torch.empty(1, blocks * tokens, heads, 128, dtype=torch.bfloat16, device=dev)
+        fn = lambda: L.dequantize_kv_cache(qs, blocks, heads, tokens, torch.bfloat16, dev, out=out)
+        work, unit = blocks * tokens * heads * 128 * (0.5 + 1 / 16 + 2) / 1e9, "GB/s"
+    else:
+        raise SystemExit(f"unknown kernel case {spec}")
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for i in range(iters):
+        flush.fill_(i)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    assert lib.llnv_check_status(None) == 0, lib.llnv_last_error()
+    med = statistics.median(times)
+    print(json.dumps({"kernel_case": spec, "iters": iters, "median_us": med * 1e3, "min_us": min(times) * 1e3,
+                      "rate": work / (med * 1e-3), "unit": unit}))
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel-case", default=None, help="run one kernel case instead of the benchmark (see run_kernel_case)")
+    ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    if args.kernel_case:
+        run_kernel_case(args.kernel_case, args.iters)
+        return
     if args.impl == "reference":
         run_reference_arm(args)
     else:

@@ -48,40 +48,59 @@ struct GemmParams {
   __nv_bfloat16* d;
   int64_t ldd;
   unsigned int* status;
+  int debug;               // timing experiments only: bit0 skip scale copies, bit1 one MMA per stage, bit2 skip stores
 };
 
 template <int BN>
 struct Cfg {
   static constexpr int kAcc = BN == 128 ? 2 : 1;
-  static constexpr int kStages = BN == 128 ? 6 : 4;
+  static constexpr int kStages = BN == 128 ? 5 : 3;
   static constexpr uint32_t kABytes = BM * BK_BYTES;
   static constexpr uint32_t kBBytes = BN * BK_BYTES;
   static constexpr uint32_t kSfaBytes = 2048;
   static constexpr uint32_t kSfbBytes = BN * 16;
   static constexpr uint32_t kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-  static constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024;
+  // epilogue staging: per epilogue warp two buffers of 32 rows x 64 bf16 columns (128-byte rows,
+  // 128-byte swizzle) that TMA stores drain; the same buffers receive the residual tile first
+  static constexpr uint32_t kStagingBytes = 4 * 2 * 4096;
+  static constexpr uint32_t kStagingOff = kStages * kStageBytes;
+  static constexpr uint32_t kBarOff = kStagingOff + kStagingBytes;
+  static constexpr uint32_t kSmemBytes = kBarOff + 1024;
   static constexpr uint32_t kSfaCol = kAcc * BN;          // first TMEM column of the A scales
   static constexpr uint32_t kSfbCol = kSfaCol + 16;       // 4 MMAs x 4 columns
   static_assert(kStageBytes % 1024 == 0, "stage must keep 1024-byte alignment");
   static_assert(kSfbCol + 4 * (BN / 32) <= kTmemCols, "tensor memory overflow");
 };
 
-__device__ __forceinline__ float gelu_tanh(float x) {
-  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-  const float inner = k0 * (x + k1 * x * x * x);
-  return 0.5f * x * (1.f + tanhf(inner));
+// GELU, tanh form: 0.5 x (1 + tanh(u)) = x / (1 + exp(-2u)), u = sqrt(2/pi) (x + 0.044715 x^3)
+// two fp32 -> packed bf16x2 (one conversion instruction, round to nearest even)
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-template <int BN>
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  const float u = k0 * (x + k1 * x * x * x);
+  return __fdividef(x, 1.f + __expf(-2.f * u));
+}
+
+// epilogue variants (compile-time, so that the plain path stays a handful of instructions per
+// element and the whole epilogue fits the instruction cache)
+constexpr int kEpiBias = 1, kEpiGelu = 2, kEpiRes = 4;
+
+template <int BN, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmR, const GemmParams p) {
   using C = Cfg<BN>;
   extern __shared__ __align__(1024) uint8_t smem[];
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::kBarOff);
   uint64_t* empty_bar = full_bar + C::kStages;
   uint64_t* tfull_bar = empty_bar + C::kStages;
   uint64_t* tempty_bar = tfull_bar + C::kAcc;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + C::kAcc);
+  uint64_t* res_bar = tempty_bar + C::kAcc;                 // [4 warps][2 buffers]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_bar + 8);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -107,10 +126,12 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       mbar_init(&tfull_bar[i], 1);
       mbar_init(&tempty_bar[i], 4);
     }
+    for (int i = 0; i < 8; ++i) mbar_init(&res_bar[i], 1);
     *abort_flag = 0u;
     fence_barrier_init();
     prefetch_tensormap(&tmA);
     prefetch_tensormap(&tmB);
+    prefetch_tensormap(&tmD);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -160,17 +181,19 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           const uint32_t b_addr = a_addr + C::kABytes;
           const uint32_t sfa_addr = b_addr + C::kBBytes;
           const uint32_t sfb_addr = sfa_addr + C::kSfaBytes;
+          if (!(p.debug & 1) || kb == 0) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            tmem_cp_sf(tmem_base + C::kSfaCol + 4 * g, make_sf_desc(sfa_addr + g * 512));
+            for (int g = 0; g < 4; ++g) {
+              tmem_cp_sf(tmem_base + C::kSfaCol + 4 * g, make_sf_desc(sfa_addr + g * 512));
 #pragma unroll
-            for (int h = 0; h < BN / 128; ++h)
-              tmem_cp_sf(tmem_base + C::kSfbCol + (BN / 32) * g + 4 * h, make_sf_desc(sfb_addr + h * 2048 + g * 512));
+              for (int h = 0; h < BN / 128; ++h)
+                tmem_cp_sf(tmem_base + C::kSfbCol + (BN / 32) * g + 4 * h, make_sf_desc(sfb_addr + h * 2048 + g * 512));
+            }
           }
           const uint64_t a_desc = make_kmajor_sw128_desc(a_addr);
           const uint64_t b_desc = make_kmajor_sw128_desc(b_addr);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
+          for (int k = 0; k < ((p.debug & 2) ? 1 : 4); ++k) {
             // 64 E2M1 elements = 32 bytes further along K inside the 128-byte swizzled row
             mma_nvf4(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_base + C::kSfaCol + 4 * k,
                      tmem_base + C::kSfbCol + (BN / 32) * k, (kb | k) != 0 ? 1u : 0u);
@@ -189,59 +212,122 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if (p.epi.alpha) alpha = __ldg(p.epi.alpha);
     else alpha = __fdiv_rn(__fmul_rn(__ldg(p.a_amax), __ldg(p.b_amax)), p.alpha_denom);
     const uint16_t* bias = reinterpret_cast<const uint16_t*>(p.epi.bias);
-    const uint16_t* resid = reinterpret_cast<const uint16_t*>(p.epi.residual);
+    constexpr bool has_res = (EPI & kEpiRes) != 0;
     const uint16_t* gate = reinterpret_cast<const uint16_t*>(p.epi.gate);
+    uint8_t* my_stage = smem + C::kStagingOff + q * 8192;
+    uint64_t* my_res_bar = res_bar + q * 2;
+    uint32_t res_phase = 0u;                          // bit b = parity to wait for on buffer b
     float local_amax = 0.f;
     int acc = 0;
     uint32_t acc_phase = 0;
+    uint32_t chunk = 0;                               // running chunk counter -> staging buffer
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       const int mt = tile % num_m, nt = tile / num_m;
-      mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, 300u);
-      tc_fence_after();
-      const int64_t row = (int64_t)mt * BM + q * 32 + lane;
+      const int row0 = mt * BM + q * 32;              // first row of this warp
+      const int64_t row = (int64_t)row0 + lane;
       const bool row_ok = row < p.M;
       const uint16_t* grow = nullptr;
       if (gate && row_ok) grow = gate + (row / p.epi.frame_rows) * p.epi.gate_stride;
+      // residual tile of the first chunk can be fetched while the main loop is still running
+      if (has_res && row0 < p.M) {
+        const uint32_t b0 = chunk & 1u;
+        if (lane == 0) {
+          bulk_wait_read<1>();                        // the store that used this buffer two chunks ago has read it
+          mbar_arrive_expect_tx(&my_res_bar[b0], 4096);
+          tma_load_2d(my_stage + b0 * 4096, &tmR, nt * BN, row0, &my_res_bar[b0]);
+        }
+      }
+      mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, 300u);
+      tc_fence_after();
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c0, r);
+      for (int c0 = 0; c0 < BN; c0 += 64, ++chunk) {
+        const uint32_t b = chunk & 1u;
+        uint8_t* buf = my_stage + b * 4096;
+        uint32_t r[2][32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c0, r[0]);
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c0 + 32, r[1]);
         tmem_ld_wait();
-        if (c0 + 32 == BN) {
+        if (c0 + 64 == BN) {
           // accumulator fully read: hand it back to the MMA warp before the math and the stores
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&tempty_bar[acc]);
         }
-        if (row_ok) {
-          const int64_t col = (int64_t)nt * BN + c0;
-          uint32_t outw[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            float y[2];
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              const int64_t n = col + 2 * j + h;
-              float v = round_bf16(__fmul_rn(alpha, __uint_as_float(r[2 * j + h])));
-              if (bias) v = round_bf16(v + __uint_as_float((uint32_t)__ldg(bias + n) << 16));
-              if (p.epi.act == 1) v = round_bf16(gelu_tanh(v));
-              if (resid) {
-                float t = v;
-                if (grow) t = round_bf16(v * __uint_as_float((uint32_t)__ldg(grow + n) << 16));
-                v = round_bf16(__uint_as_float((uint32_t)__ldg(resid + row * p.epi.ldr + n) << 16) + t);
-              }
-              local_amax = fmaxf(local_amax, fabsf(v));
-              y[h] = v;
+        if (row0 < p.M && !(p.debug & 4)) {
+          if (has_res) {
+            // prefetch the residual of the next chunk of this tile into the other buffer
+            if (c0 + 64 < BN && lane == 0) {
+              bulk_wait_read<0>();
+              mbar_arrive_expect_tx(&my_res_bar[b ^ 1u], 4096);
+              tma_load_2d(my_stage + (b ^ 1u) * 4096, &tmR, nt * BN + c0 + 64, row0, &my_res_bar[b ^ 1u]);
             }
-            outw[j] = pack_bf16x2(y[0], y[1]);
+            mbar_wait(&my_res_bar[b], (res_phase >> b) & 1u, abort_flag, p.status, 301u);
+            res_phase ^= 1u << b;
+          } else {
+            if (lane == 0) bulk_wait_read<1>();       // buffer b was last used two chunks ago
+            __syncwarp();
           }
-          uint4* dst = reinterpret_cast<uint4*>(p.d + row * p.ldd + col);
+          const int64_t col = (int64_t)nt * BN + c0;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) dst[j] = make_uint4(outw[4 * j], outw[4 * j + 1], outw[4 * j + 2], outw[4 * j + 3]);
+          for (int v8 = 0; v8 < 8; ++v8) {            // 8 columns (16 bytes) at a time
+            uint4* slot = reinterpret_cast<uint4*>(buf + lane * 128 + ((v8 ^ (lane & 7)) << 4));
+            float y[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const int cc = v8 * 8 + e;              // column inside the 64-column chunk
+              y[e] = __fmul_rn(alpha, __uint_as_float(r[cc >> 5][cc & 31]));
+            }
+            if (EPI != 0 || p.epi.out_amax) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) y[e] = round_bf16(y[e]);
+            }
+            if (EPI & kEpiBias) {
+              const uint4 bv = __ldg(reinterpret_cast<const uint4*>(bias + col + v8 * 8));
+              const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                y[e] = round_bf16(y[e] + ((e & 1) ? bf16_hi(bw[e >> 1]) : bf16_lo(bw[e >> 1])));
+            }
+            if (EPI & kEpiGelu) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) y[e] = round_bf16(gelu_tanh(y[e]));
+            }
+            if (has_res) {
+              const uint4 rv = *slot;
+              const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+              if (grow) {
+                const uint4 gv = __ldg(reinterpret_cast<const uint4*>(grow + col + v8 * 8));
+                const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  y[e] = round_bf16(y[e] * ((e & 1) ? bf16_hi(gw[e >> 1]) : bf16_lo(gw[e >> 1])));
+              }
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                y[e] = round_bf16(((e & 1) ? bf16_hi(rw[e >> 1]) : bf16_lo(rw[e >> 1])) + y[e]);
+            }
+            if (p.epi.out_amax && row_ok) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) local_amax = fmaxf(local_amax, fabsf(y[e]));
+            }
+            uint4 ov;
+            ov.x = pack2(y[0], y[1]);
+            ov.y = pack2(y[2], y[3]);
+            ov.z = pack2(y[4], y[5]);
+            ov.w = pack2(y[6], y[7]);
+            *slot = ov;
+          }
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0 && !(p.debug & 8)) {
+            tma_store_2d(&tmD, buf, (int)col, row0);  // rows beyond M are clipped by the tensor map
+            bulk_commit();
+          }
         }
       }
       if (++acc == C::kAcc) { acc = 0; acc_phase ^= 1u; }
     }
+    if (lane == 0) bulk_wait<0>();
     if (p.epi.out_amax) {
       local_amax = warp_max(local_amax);
       if (lane == 0 && local_amax > 0.f) atomic_max_nonneg(p.epi.out_amax, local_amax);
@@ -282,6 +368,7 @@ struct MapKeyHash {
 std::mutex g_map_mu;
 std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
 int g_forced_bn = 0;
+int g_debug = 0;
 
 int get_codes_map(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
   MapKey key{ptr, rows, row_bytes, box_rows};
@@ -300,18 +387,37 @@ int get_codes_map(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t row
   return LLNV_OK;
 }
 
-template <int BN>
-int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream) {
+int get_out_map(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t pitch) {
+  // keyed with a marker in box_rows so that it cannot collide with a codes map
+  MapKey key{ptr, rows, cols * 2 + (pitch << 20), 0x80000000u | 32u};
+  std::lock_guard<std::mutex> lock(g_map_mu);
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) {
+    *out = it->second;
+    return LLNV_OK;
+  }
+  CUtensorMap m;
+  int rc = make_tensor_map_2d_bf16(&m, ptr, rows, cols, pitch, 32, 64, 3);
+  if (rc != LLNV_OK) return rc;
+  if (g_maps.size() > 8192) g_maps.clear();
+  g_maps.emplace(key, m);
+  *out = m;
+  return LLNV_OK;
+}
+
+template <int BN, int EPI>
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD, const CUtensorMap& tmR,
+           const GemmParams& p, cudaStream_t stream) {
   static bool attr_set[64] = {};
   int dev = 0;
   LLNV_CUDA(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    LLNV_CUDA(cudaFuncSetAttribute(gemm_nvfp4_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<BN>::kSmemBytes));
+    LLNV_CUDA(cudaFuncSetAttribute(gemm_nvfp4_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<BN>::kSmemBytes));
     attr_set[dev] = true;
   }
   const int64_t tiles = ((p.M + BM - 1) / BM) * (p.N / BN);
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  gemm_nvfp4_kernel<BN><<<grid, kThreads, Cfg<BN>::kSmemBytes, stream>>>(tmA, tmB, p);
+  gemm_nvfp4_kernel<BN, EPI><<<grid, kThreads, Cfg<BN>::kSmemBytes, stream>>>(tmA, tmB, tmD, tmR, p);
   return launch_status("gemm_nvfp4_kernel");
 }
 
@@ -324,6 +430,12 @@ using namespace llnv;
 extern "C" int llnv_gemm_nvfp4_force_tile_n(int bn) {
   LLNV_REQUIRE(bn == 0 || bn == 128 || bn == 256, "llnv_gemm_nvfp4_force_tile_n: tile must be 0, 128 or 256");
   g_forced_bn = bn;
+  return LLNV_OK;
+}
+
+// Timing experiments only (results become wrong): see GemmParams::debug.
+extern "C" int llnv_gemm_nvfp4_debug(int flags) {
+  g_debug = flags;
   return LLNV_OK;
 }
 
@@ -344,6 +456,8 @@ extern "C" int llnv_gemm_nvfp4(const void* a_codes, const void* a_sf, const floa
   LLNV_REQUIRE(epi.alpha || (a_amax && b_amax), "llnv_gemm_nvfp4: need alpha or both amax pointers");
   LLNV_REQUIRE(epi.act == 0 || epi.act == 1, "llnv_gemm_nvfp4: unknown activation %d", epi.act);
   if (epi.residual) LLNV_REQUIRE(epi.ldr >= N, "llnv_gemm_nvfp4: residual row stride smaller than N");
+  if (epi.bias) LLNV_REQUIRE(((uintptr_t)epi.bias & 15) == 0, "llnv_gemm_nvfp4: bias must be 16-byte aligned");
+  if (epi.gate) LLNV_REQUIRE(((uintptr_t)epi.gate & 15) == 0 && epi.gate_stride % 8 == 0, "llnv_gemm_nvfp4: gate must be 16-byte aligned with a stride that is a multiple of 8");
   if (epi.gate) LLNV_REQUIRE(epi.residual && epi.frame_rows > 0 && epi.gate_stride >= N, "llnv_gemm_nvfp4: gate needs residual, frame_rows > 0 and gate_stride >= N");
   if (M == 0) return LLNV_OK;
 
@@ -371,5 +485,31 @@ extern "C" int llnv_gemm_nvfp4(const void* a_codes, const void* a_sf, const floa
   p.d = (__nv_bfloat16*)d;
   p.ldd = ldd;
   p.status = device_status_word();
-  return bn == 256 ? launch<256>(tmA, tmB, p, stream) : launch<128>(tmA, tmB, p, stream);
+  p.debug = g_debug;
+  CUtensorMap tmD, tmR;
+  rc = get_out_map(&tmD, d, (uint64_t)M, (uint64_t)N, (uint64_t)ldd);
+  if (rc != LLNV_OK) return rc;
+  tmR = tmD;
+  if (epi.residual) {
+    LLNV_REQUIRE(((uintptr_t)epi.residual & 15) == 0 && epi.ldr % 8 == 0, "llnv_gemm_nvfp4: residual must be 16-byte aligned with ldr a multiple of 8");
+    rc = get_out_map(&tmR, epi.residual, (uint64_t)M, (uint64_t)N, (uint64_t)epi.ldr);
+    if (rc != LLNV_OK) return rc;
+  }
+  const int variant = (epi.bias ? kEpiBias : 0) | (epi.act == 1 ? kEpiGelu : 0) | (epi.residual ? kEpiRes : 0);
+#define LLNV_GEMM_CASE(V)                                                                   \
+  case V:                                                                                   \
+    return bn == 256 ? launch<256, V>(tmA, tmB, tmD, tmR, p, stream) : launch<128, V>(tmA, tmB, tmD, tmR, p, stream);
+  switch (variant) {
+    LLNV_GEMM_CASE(0)
+    LLNV_GEMM_CASE(1)
+    LLNV_GEMM_CASE(2)
+    LLNV_GEMM_CASE(3)
+    LLNV_GEMM_CASE(4)
+    LLNV_GEMM_CASE(5)
+    LLNV_GEMM_CASE(6)
+    LLNV_GEMM_CASE(7)
+  }
+#undef LLNV_GEMM_CASE
+  set_error("llnv_gemm_nvfp4: internal dispatch error");
+  return LLNV_E_INVALID;
 }
