@@ -74,6 +74,27 @@ int llnv_amax_bf16(const void* x, int64_t M, int64_t K, int64_t ldx, float* amax
 int llnv_quantize_nvfp4(const void* x, int64_t M, int64_t K, int64_t ldx, int rule,
                         void* codes, void* sf, float* amax, int amax_given, llnv_stream_t stream);
 
+/* adaLN modulation fused into the quantizer: y = LayerNorm(x) (no affine, eps) -> bf16 ->
+ * * bf16(1 + scale[f]) -> bf16 -> + shift[f] -> bf16, f = row / frame_rows, then y is quantized as by
+ * llnv_quantize_nvfp4 (amax computed here).  Stands in for adaln_modulate_triton
+ * (utils/adaln_triton.py:36-126; call sites wan_5b/modules/causal_model.py:867-873, 908-914)
+ * followed by the activation quantize of the next Linear
+ * (fouroversix/src/fouroversix/model/modules/linear.py:45-46); y itself is written only when
+ * y_out != NULL.
+ *   x: bf16 [M, C], C % 64 == 0, C <= 4096.  scale/shift: bf16 [frames, mod_stride].
+ *   add_one: 1 -> multiply by (1 + scale) (adaln_triton.py:74-78), 0 -> by scale.
+ *   row_stats: caller-provided scratch of 2*M floats (mean and 1/std of every row). */
+int llnv_adaln_quantize_nvfp4(const void* x, int64_t M, int64_t C, int64_t ldx, const void* scale, const void* shift,
+                              int64_t mod_stride, int frame_rows, float eps, int add_one, int rule, void* codes,
+                              void* sf, float* amax, void* y_out, int64_t ldy, float* row_stats, llnv_stream_t stream);
+
+/* LayerNorm with affine weight/bias (bf16 [C]) fused into the quantizer: y = bf16(LN(x)*w + b).
+ * Stands in for the cross-attention input norm (`norm3`, wan_5b/modules/causal_model.py:817-819, 906;
+ * wan_5b/modules/model.py:101-111) followed by the quantize of cross_attn.q.  Same buffers as above. */
+int llnv_layernorm_quantize_nvfp4(const void* x, int64_t M, int64_t C, int64_t ldx, const void* weight, const void* bias,
+                                  float eps, int rule, void* codes, void* sf, float* amax, void* y_out, int64_t ldy,
+                                  float* row_stats, llnv_stream_t stream);
+
 /* Dequantize `num_blocks` KV-cache blocks, each an NVFP4 matrix [rows_padded, 128] holding
  * block_token_size*num_heads logical rows (token-major, head-minor), into one contiguous
  * tensor [1, num_blocks*block_token_size, num_heads, 128] of dtype_code.
@@ -125,6 +146,12 @@ int llnv_gemm_nvfp4(const void* a_codes, const void* a_sf, const float* a_amax, 
                     const void* b_codes, const void* b_sf, const float* b_amax, int b_rule,
                     int64_t M, int64_t N, int64_t K, const llnv_epilogue_t* epilogue,
                     void* d, int64_t ldd, llnv_stream_t stream);
+
+/* Test / benchmark hooks (no counterpart in the reference). */
+int llnv_gemm_nvfp4_force_tile_n(int bn);       /* 0 = automatic, 128 or 256 */
+int llnv_gemm_nvfp4_debug(int flags);           /* timing experiments; results become wrong when non-zero */
+int llnv_selftest_div_const(int divisor, uint32_t first_bits, uint64_t count, unsigned long long* mismatches,
+                            llnv_stream_t stream);
 
 #ifdef __cplusplus
 }

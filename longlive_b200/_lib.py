@@ -10,7 +10,8 @@ LIB_PATH = os.path.join(_PKG, "libllnvfp4.so")
 # names declared in include/llnvfp4.h
 EXPORTS = [
     "llnv_version", "llnv_last_error", "llnv_check_status", "llnv_amax_bf16", "llnv_quantize_nvfp4",
-    "llnv_kv_dequant", "llnv_dequantize_nvfp4", "llnv_gemm_nvfp4",
+    "llnv_kv_dequant", "llnv_dequantize_nvfp4", "llnv_gemm_nvfp4", "llnv_adaln_quantize_nvfp4",
+    "llnv_layernorm_quantize_nvfp4", "llnv_gemm_nvfp4_force_tile_n", "llnv_gemm_nvfp4_debug", "llnv_selftest_div_const",
 ]
 
 
@@ -46,6 +47,11 @@ def lib() -> C.CDLL:
         l.llnv_kv_dequant.argtypes = [p, p, p, i32, i32, i32, i32, f32, f32, i32, p, p]
         l.llnv_dequantize_nvfp4.argtypes = [p, p, p, i64, i64, i64, i32, f32, f32, i32, p, i64, p]
         l.llnv_gemm_nvfp4.argtypes = [p, p, p, i32, p, p, p, i32, i64, i64, i64, p, p, i64, p]
+        l.llnv_adaln_quantize_nvfp4.argtypes = [p, i64, i64, i64, p, p, i64, i32, f32, i32, i32, p, p, p, p, i64, p, p]
+        l.llnv_layernorm_quantize_nvfp4.argtypes = [p, i64, i64, i64, p, p, f32, i32, p, p, p, p, i64, p, p]
+        l.llnv_gemm_nvfp4_force_tile_n.argtypes = [i32]
+        l.llnv_gemm_nvfp4_debug.argtypes = [i32]
+        l.llnv_selftest_div_const.argtypes = [i32, C.c_uint32, C.c_uint64, p, p]
         for name in EXPORTS:
             getattr(l, name)
         _lib = l

@@ -71,6 +71,58 @@ def quantize_nvfp4(x: torch.Tensor, rule_id: int, amax: torch.Tensor | None = No
     return codes, sf, amax
 
 
+def _quant_outputs(x, m, c, codes, sf, amax):
+    mp = padded_rows(m)
+    if codes is None:
+        codes = torch.empty((mp, c // 2), dtype=torch.uint8, device=x.device)
+    if sf is None:
+        sf = torch.empty(mp * c // 16, dtype=torch.float8_e4m3fn, device=x.device)
+    if amax is None:
+        amax = torch.empty(1, dtype=torch.float32, device=x.device)
+    return codes, sf, amax
+
+
+def adaln_quantize_nvfp4(x, scale, shift, frame_rows, rule_id, eps=1e-6, add_one=True, *, want_y=False, codes=None,
+                         sf=None, amax=None, row_stats=None):
+    """LayerNorm(no affine) -> (1 + scale[f]) * x + shift[f] (bf16 rounding points of the reference)
+    fused with the NVFP4 quantize of the result.  x: bf16 [M, C]; scale/shift: bf16 [F, C] views
+    (row stride free).  Returns (codes, sf, amax, y or None)."""
+    _require_cuda(x, "x")
+    if x.dim() != 2 or x.dtype != torch.bfloat16 or x.stride(1) != 1:
+        raise RuntimeError("adaln_quantize_nvfp4 expects a 2-D bfloat16 tensor with unit column stride")
+    if scale.dim() != 2 or shift.dim() != 2 or scale.stride(1) != 1 or shift.stride(1) != 1 or scale.stride(0) != shift.stride(0):
+        raise RuntimeError("scale and shift must be [frames, C] views with the same row stride")
+    m, c = x.shape
+    codes, sf, amax = _quant_outputs(x, m, c, codes, sf, amax)
+    if row_stats is None:
+        row_stats = torch.empty(2 * max(m, 1), dtype=torch.float32, device=x.device)
+    y = torch.empty((m, c), dtype=torch.bfloat16, device=x.device) if want_y else None
+    with torch.cuda.device(x.device):
+        _check(_lib.lib().llnv_adaln_quantize_nvfp4(
+            x.data_ptr(), m, c, x.stride(0), scale.data_ptr(), shift.data_ptr(), scale.stride(0), int(frame_rows), float(eps),
+            1 if add_one else 0, rule_id, codes.data_ptr(), sf.data_ptr(), amax.data_ptr(),
+            y.data_ptr() if y is not None else None, c, row_stats.data_ptr(), _stream(x)))
+    return codes, sf, amax, y
+
+
+def layernorm_quantize_nvfp4(x, weight, bias, rule_id, eps=1e-6, *, want_y=False, codes=None, sf=None, amax=None,
+                             row_stats=None):
+    """Affine LayerNorm fused with the NVFP4 quantize of its output.  Returns (codes, sf, amax, y or None)."""
+    _require_cuda(x, "x")
+    if x.dim() != 2 or x.dtype != torch.bfloat16 or x.stride(1) != 1:
+        raise RuntimeError("layernorm_quantize_nvfp4 expects a 2-D bfloat16 tensor with unit column stride")
+    m, c = x.shape
+    codes, sf, amax = _quant_outputs(x, m, c, codes, sf, amax)
+    if row_stats is None:
+        row_stats = torch.empty(2 * max(m, 1), dtype=torch.float32, device=x.device)
+    y = torch.empty((m, c), dtype=torch.bfloat16, device=x.device) if want_y else None
+    with torch.cuda.device(x.device):
+        _check(_lib.lib().llnv_layernorm_quantize_nvfp4(
+            x.data_ptr(), m, c, x.stride(0), weight.data_ptr(), bias.data_ptr(), float(eps), rule_id, codes.data_ptr(),
+            sf.data_ptr(), amax.data_ptr(), y.data_ptr() if y is not None else None, c, row_stats.data_ptr(), _stream(x)))
+    return codes, sf, amax, y
+
+
 def dequantize_nvfp4(codes, sf, amax, rows, cols, cols_padded, dtype, e2m1_max, e4m3_max, rounding=DEQ_PYTORCH):
     _require_cuda(codes, "codes")
     out = torch.empty((rows, cols), dtype=dtype, device=codes.device)

@@ -468,6 +468,19 @@ def adaln_modulate(x: np.ndarray, scale: np.ndarray, shift: np.ndarray, frame_se
     return bf16_round((prod + shift.astype(f32)[frame]).astype(f32))
 
 
+def layer_norm_affine(x: np.ndarray, weight: np.ndarray, bias: np.ndarray, eps: float = 1e-6) -> np.ndarray:
+    """nn.LayerNorm with elementwise affine on a bf16 tensor: fp32 statistics and affine, one
+    rounding to bf16 at the end.  wan_5b/modules/model.py:101-111 (``WanLayerNorm`` with
+    ``elementwise_affine=True``, the cross-attention ``norm3``)."""
+    xf = x.astype(f32)
+    c = xf.shape[-1]
+    mean = (xf.sum(axis=-1, keepdims=True, dtype=np.float64) / c).astype(f32)
+    xc = (xf - mean).astype(f32)
+    var = ((xc * xc).astype(f32).sum(axis=-1, keepdims=True, dtype=np.float64) / c).astype(f32)
+    rstd = (f32(1) / np.sqrt((var + f32(eps)).astype(f32))).astype(f32)
+    return bf16_round(((xc * rstd).astype(f32) * weight.astype(f32) + bias.astype(f32)).astype(f32))
+
+
 def attention(q: np.ndarray, k: np.ndarray, v: np.ndarray) -> np.ndarray:
     """softmax(q k^T / sqrt(D)) v per head, non-causal, fp32 math, bf16 result.
 

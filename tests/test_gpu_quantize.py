@@ -156,3 +156,23 @@ def test_c_abi_error_reporting():
         ops.quantize_nvfp4(x, 3)
     with pytest.raises(RuntimeError, match="at least one cache block"):
         ops.kv_dequant([], [], [], 4, 4, torch.bfloat16, 6, 256)
+
+
+def test_exact_division():
+    """The quantizer's multiply-and-correct division by 6 and by 1536 must agree with IEEE division
+    for every finite fp32 value whose magnitude is at least 2^-100 (the fast path never sees
+    smaller operands); checked exhaustively over those bit patterns, both signs."""
+    import ctypes
+    from longlive_b200 import _lib
+    lib = _lib.lib()
+    counter = torch.zeros(1, dtype=torch.int64, device="cuda")
+    lo_bits = (127 - 100) << 23                      # 2^-100
+    hi_bits = 0x7F800000                             # +inf (excluded by the kernel)
+    for divisor in (6, 1536):
+        for sign in (0, 0x80000000):
+            counter.zero_()
+            rc = lib.llnv_selftest_div_const(divisor, ctypes.c_uint32(sign | lo_bits), ctypes.c_uint64(hi_bits - lo_bits),
+                                             counter.data_ptr(), None)
+            assert rc == 0
+            torch.cuda.synchronize()
+            assert int(counter.item()) == 0, (divisor, sign, int(counter.item()))
