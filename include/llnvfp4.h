@@ -88,6 +88,24 @@ int llnv_adaln_quantize_nvfp4(const void* x, int64_t M, int64_t C, int64_t ldx, 
                               int64_t mod_stride, int frame_rows, float eps, int add_one, int rule, void* codes,
                               void* sf, float* amax, void* y_out, int64_t ldy, float* row_stats, llnv_stream_t stream);
 
+/* Same operation and results as llnv_adaln_quantize_nvfp4 for callers that cannot allocate device
+ * memory where they call it (a server that owns all device memory through its own arena, a
+ * latency-critical loop that must not take cudaMalloc's device-wide synchronisation).  It has no
+ * counterpart in the reference.  The row-statistics scratch is a fixed array inside the library
+ * image, so the call performs no cudaMalloc / cudaFree and uses no allocating library routine;
+ * inputs and outputs are still the caller's buffers.
+ *   - M must not exceed llnv_static_max_rows() (16384 rows, 128 KiB per GPU, held until exit);
+ *     larger M fails with LLNV_E_INVALID and a message naming the limit.
+ *   - All calls on a GPU share the array and it keeps the previous call's contents; nothing in it
+ *     needs to start at zero.  Calls that can overlap on the same GPU race: issue them on one stream.
+ *   - The first call on each device resolves the array's device address (one-time set-up outside
+ *     the stream); make it at start-up, before any stream capture begins. */
+int llnv_adaln_quantize_nvfp4_static(const void* x, int64_t M, int64_t C, int64_t ldx, const void* scale,
+                                     const void* shift, int64_t mod_stride, int frame_rows, float eps, int add_one,
+                                     int rule, void* codes, void* sf, float* amax, void* y_out, int64_t ldy,
+                                     llnv_stream_t stream);
+int64_t llnv_static_max_rows(void);
+
 /* LayerNorm with affine weight/bias (bf16 [C]) fused into the quantizer: y = bf16(LN(x)*w + b).
  * Stands in for the cross-attention input norm (`norm3`, wan_5b/modules/causal_model.py:817-819, 906;
  * wan_5b/modules/model.py:101-111) followed by the quantize of cross_attn.q.  Same buffers as above. */
