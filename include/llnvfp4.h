@@ -113,6 +113,18 @@ int llnv_layernorm_quantize_nvfp4(const void* x, int64_t M, int64_t C, int64_t l
                                   float eps, int rule, void* codes, void* sf, float* amax, void* y_out, int64_t ldy,
                                   float* row_stats, llnv_stream_t stream);
 
+/* Q / K prologue of the chunk attention: RMSNorm over all C channels (weight != NULL), 3-D RoPE on
+ * interleaved pairs of every 128-channel head (cos/sin != NULL, fp32 [S, 64] per token), and
+ * optionally the smoothed copy `out - mean over the head` plus max|out|.
+ * Stands in for WanRMSNorm (wan_5b/modules/model.py:82-98; call site
+ * wan_5b/modules/causal_model.py:363-365), rope_apply_triton (utils/rope_triton.py:94-135; call
+ * site causal_model.py:479-486) and k_smooth (utils/quant.py:797-798; call sites
+ * causal_model.py:568, 631).  x, out, out_smooth: bf16 [S, C] with row strides ldx/ldo/lds;
+ * amax_out: fp32 scalar that is overwritten (the tensor scale for the KV-cache write of `out`). */
+int llnv_rmsnorm_rope(const void* x, int64_t S, int64_t C, int64_t ldx, const void* weight, float eps,
+                      const float* cos, const float* sin, void* out, int64_t ldo, void* out_smooth, int64_t lds,
+                      float* amax_out, llnv_stream_t stream);
+
 /* Dequantize `num_blocks` KV-cache blocks, each an NVFP4 matrix [rows_padded, 128] holding
  * block_token_size*num_heads logical rows (token-major, head-minor), into one contiguous
  * tensor [1, num_blocks*block_token_size, num_heads, 128] of dtype_code.

@@ -1,0 +1,143 @@
+// RMSNorm over the full channel dimension -> per-head 3-D RoPE -> (optionally) k_smooth and the
+// amax of the rotated tensor, in one pass: the Q / K prologue of the chunk attention and of the
+// KV-cache write.
+//
+//   y   = bf16(bf16(x * rsqrt(mean(x^2) + eps)) * weight)          wan_5b/modules/model.py:82-98
+//   out = bf16(rotate pairs (2d, 2d+1) of every head by (cos, sin)[token, d])  utils/rope_triton.py:36-81
+//   out_smooth = bf16(out - bf16(mean over the head's channels))   utils/quant.py:797-798
+//   amax = max |out|  (tensor scale of the NVFP4 cache block the rotated keys are written to)
+//
+// One warp per token row: a lane holds 16-byte vectors v = lane + 32*i; vector v covers channels
+// 8v..8v+7, i.e. four rotation pairs of head v/16, so a head's 128 channels live in 16 adjacent
+// lanes and the per-head mean is a 4-step shuffle reduction.
+#include "common.cuh"
+
+namespace llnv {
+namespace {
+
+constexpr int kMaxVec = 16;      // C <= 4096
+
+__global__ void __launch_bounds__(256) rmsnorm_rope_kernel(const uint16_t* __restrict__ x, int64_t S, int64_t C, int64_t ldx,
+                                                           const uint16_t* __restrict__ weight, float eps,
+                                                           const float* __restrict__ cosv, const float* __restrict__ sinv,
+                                                           uint16_t* __restrict__ out, int64_t ldo,
+                                                           uint16_t* __restrict__ out_smooth, int64_t lds,
+                                                           float* __restrict__ amax_out) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 8 + warp;
+  float wmax = 0.f;
+  if (row < S) {
+    const int nvec = (int)(C >> 3);
+    uint4 v[kMaxVec];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+      const int idx = lane + 32 * i;
+      if (idx < nvec) {
+        v[i] = __ldg(reinterpret_cast<const uint4*>(x + row * ldx) + idx);
+        const uint32_t w4[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float a = bf16_lo(w4[j]), b = bf16_hi(w4[j]);
+          ss += a * a + b * b;
+        }
+      }
+    }
+    float rinv = 1.f;
+    if (weight) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+      rinv = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)C), eps)));
+    }
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+      const int idx = lane + 32 * i;
+      if (idx >= nvec) continue;          // uniform per (i, lane half): C is a multiple of 128 so 16-lane groups stay whole
+      uint32_t w4[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+      float y[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        y[2 * j] = bf16_lo(w4[j]);
+        y[2 * j + 1] = bf16_hi(w4[j]);
+      }
+      if (weight) {
+        const uint4 wv = __ldg(reinterpret_cast<const uint4*>(weight) + idx);
+        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float g = (e & 1) ? bf16_hi(ww[e >> 1]) : bf16_lo(ww[e >> 1]);
+          y[e] = round_bf16(__fmul_rn(round_bf16(__fmul_rn(y[e], rinv)), g));
+        }
+      }
+      if (cosv) {
+        const int pair0 = (idx & 15) * 4;                         // first rotation pair of this vector inside its head
+        const float4 c4 = __ldg(reinterpret_cast<const float4*>(cosv + row * 64 + pair0));
+        const float4 s4 = __ldg(reinterpret_cast<const float4*>(sinv + row * 64 + pair0));
+        const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          const float a = y[2 * p], b = y[2 * p + 1];
+          y[2 * p] = round_bf16(__fsub_rn(__fmul_rn(a, cc[p]), __fmul_rn(b, sn[p])));
+          y[2 * p + 1] = round_bf16(__fadd_rn(__fmul_rn(a, sn[p]), __fmul_rn(b, cc[p])));
+        }
+      }
+      float hsum = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        wmax = fmaxf(wmax, fabsf(y[e]));
+        hsum += y[e];
+      }
+      uint4 o;
+      o.x = pack_bf16x2(y[0], y[1]); o.y = pack_bf16x2(y[2], y[3]);
+      o.z = pack_bf16x2(y[4], y[5]); o.w = pack_bf16x2(y[6], y[7]);
+      reinterpret_cast<uint4*>(out + row * ldo)[idx] = o;
+      if (out_smooth) {
+#pragma unroll
+        for (int sft = 8; sft > 0; sft >>= 1) hsum += __shfl_xor_sync(0xFFFFFFFFu, hsum, sft, 16);
+        const float mean = round_bf16(hsum * (1.f / 128.f));
+        uint4 s;
+        s.x = pack_bf16x2(__fsub_rn(y[0], mean), __fsub_rn(y[1], mean));
+        s.y = pack_bf16x2(__fsub_rn(y[2], mean), __fsub_rn(y[3], mean));
+        s.z = pack_bf16x2(__fsub_rn(y[4], mean), __fsub_rn(y[5], mean));
+        s.w = pack_bf16x2(__fsub_rn(y[6], mean), __fsub_rn(y[7], mean));
+        reinterpret_cast<uint4*>(out_smooth + row * lds)[idx] = s;
+      }
+    }
+  }
+  if (amax_out) {
+    wmax = warp_max(wmax);
+    __shared__ float smax[8];
+    if (lane == 0) smax[warp] = wmax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float m = smax[0];
+#pragma unroll
+      for (int i = 1; i < 8; ++i) m = fmaxf(m, smax[i]);
+      if (m > 0.f) atomic_max_nonneg(amax_out, m);
+    }
+  }
+}
+
+}  // namespace
+}  // namespace llnv
+
+using namespace llnv;
+
+extern "C" int llnv_rmsnorm_rope(const void* x, int64_t S, int64_t C, int64_t ldx, const void* weight, float eps,
+                                 const float* cos, const float* sin, void* out, int64_t ldo, void* out_smooth, int64_t lds,
+                                 float* amax_out, llnv_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  LLNV_REQUIRE(x && out, "llnv_rmsnorm_rope: null pointer");
+  LLNV_REQUIRE((cos == nullptr) == (sin == nullptr), "llnv_rmsnorm_rope: cos and sin must be given together");
+  LLNV_REQUIRE(S >= 0 && C > 0 && C % 128 == 0 && C <= 4096, "llnv_rmsnorm_rope: C must be a multiple of 128 (head_dim 128) and at most 4096 (got %lld)", (long long)C);
+  LLNV_REQUIRE(ldx >= C && ldx % 8 == 0 && ldo >= C && ldo % 8 == 0, "llnv_rmsnorm_rope: row strides must be >= C and multiples of 8");
+  LLNV_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)weight & 15) == 0 && ((uintptr_t)cos & 15) == 0 &&
+                   ((uintptr_t)sin & 15) == 0,
+               "llnv_rmsnorm_rope: pointers must be 16-byte aligned");
+  if (out_smooth) LLNV_REQUIRE(lds >= C && lds % 8 == 0 && ((uintptr_t)out_smooth & 15) == 0, "llnv_rmsnorm_rope: out_smooth must be 16-byte aligned with a row stride that is a multiple of 8");
+  if (amax_out) LLNV_CUDA(cudaMemsetAsync(amax_out, 0, sizeof(float), stream));
+  if (S == 0) return LLNV_OK;
+  rmsnorm_rope_kernel<<<(unsigned)((S + 7) / 8), 256, 0, stream>>>((const uint16_t*)x, S, C, ldx, (const uint16_t*)weight, eps, cos, sin,
+                                                                  (uint16_t*)out, ldo, (uint16_t*)out_smooth, lds, amax_out);
+  return launch_status("rmsnorm_rope_kernel");
+}

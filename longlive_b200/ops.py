@@ -123,6 +123,32 @@ def layernorm_quantize_nvfp4(x, weight, bias, rule_id, eps=1e-6, *, want_y=False
     return codes, sf, amax, y
 
 
+def rmsnorm_rope(x, weight=None, cos=None, sin=None, eps=1e-6, *, out=None, out_smooth=None, want_smooth=False,
+                 amax_out=None, want_amax=False):
+    """RMSNorm (if ``weight``) -> per-head RoPE (if ``cos``/``sin``, fp32 [S, 64]) on bf16 [S, C];
+    optionally the k_smooth copy and max|out|.  Returns (out, out_smooth or None, amax or None)."""
+    _require_cuda(x, "x")
+    if x.dim() != 2 or x.dtype != torch.bfloat16 or x.stride(1) != 1:
+        raise RuntimeError("rmsnorm_rope expects a 2-D bfloat16 tensor with unit column stride")
+    s, c = x.shape
+    if out is None:
+        out = torch.empty((s, c), dtype=torch.bfloat16, device=x.device)
+    if out_smooth is None and want_smooth:
+        out_smooth = torch.empty((s, c), dtype=torch.bfloat16, device=x.device)
+    if amax_out is None and want_amax:
+        amax_out = torch.empty(1, dtype=torch.float32, device=x.device)
+    if cos is not None and (cos.dtype != torch.float32 or cos.shape != (s, 64) or not cos.is_contiguous() or not sin.is_contiguous()):
+        raise RuntimeError("cos/sin must be contiguous float32 [S, 64]")
+    with torch.cuda.device(x.device):
+        _check(_lib.lib().llnv_rmsnorm_rope(
+            x.data_ptr(), s, c, x.stride(0), weight.data_ptr() if weight is not None else None, float(eps),
+            cos.data_ptr() if cos is not None else None, sin.data_ptr() if sin is not None else None,
+            out.data_ptr(), out.stride(0), out_smooth.data_ptr() if out_smooth is not None else None,
+            out_smooth.stride(0) if out_smooth is not None else 0,
+            amax_out.data_ptr() if amax_out is not None else None, _stream(x)))
+    return out, out_smooth, amax_out
+
+
 def dequantize_nvfp4(codes, sf, amax, rows, cols, cols_padded, dtype, e2m1_max, e4m3_max, rounding=DEQ_PYTORCH):
     _require_cuda(codes, "codes")
     out = torch.empty((rows, cols), dtype=dtype, device=codes.device)
