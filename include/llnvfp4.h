@@ -142,6 +142,18 @@ int llnv_dequantize_nvfp4(const void* codes, const void* sf, const float* amax, 
                           int64_t cols_padded, int dtype_code, float e2m1_max, float e4m3_max, int rounding,
                           void* out, int64_t ldo, llnv_stream_t stream);
 
+/* Non-causal attention of a query chunk over a key/value window: out[q,h,:] =
+ * softmax_k(q[q,h,:].k[k,h,:] * scale) v[k,h,:], head_dim 128, bf16 tensors laid out
+ * [tokens, heads*128] with row strides ldq/ldk/ldv/ldo (elements), fp32 softmax, bf16 P.V on
+ * tcgen05 tensor cores.  Stands in for attention() -> flash_attn_varlen_func as called on the
+ * sink + local window (wan_5b/modules/attention.py:241-254, 260-290; call site
+ * wan_5b/modules/causal_model.py:781) and on the text context (causal_model.py:197-295).
+ * The window is one contiguous K and one contiguous V tensor: dequantized cache blocks followed by
+ * the current chunk (llnv_kv_dequant and llnv_rmsnorm_rope / the V GEMM write straight into it). */
+int llnv_attention_bf16(const void* q, int64_t Lq, int64_t ldq, const void* k, const void* v, int64_t Lk,
+                        int64_t ldk, int64_t ldv, int heads, float scale, void* out, int64_t ldo,
+                        llnv_stream_t stream);
+
 /* Fused epilogue of the W4A4 GEMM.  All pointers are device pointers and optional (NULL = skip).
  * With everything NULL/0 the GEMM writes bf16(alpha * acc), which is what the reference's
  * CUTLASS kernel produces.  The chain follows the reference's rounding points

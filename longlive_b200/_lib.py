@@ -12,7 +12,7 @@ EXPORTS = [
     "llnv_version", "llnv_last_error", "llnv_check_status", "llnv_amax_bf16", "llnv_quantize_nvfp4",
     "llnv_kv_dequant", "llnv_dequantize_nvfp4", "llnv_gemm_nvfp4", "llnv_adaln_quantize_nvfp4",
     "llnv_layernorm_quantize_nvfp4", "llnv_gemm_nvfp4_force_tile_n", "llnv_gemm_nvfp4_debug", "llnv_selftest_div_const",
-    "llnv_adaln_quantize_nvfp4_static", "llnv_static_max_rows", "llnv_rmsnorm_rope",
+    "llnv_adaln_quantize_nvfp4_static", "llnv_static_max_rows", "llnv_rmsnorm_rope", "llnv_attention_bf16",
 ]
 
 
@@ -55,6 +55,7 @@ def lib() -> C.CDLL:
         l.llnv_selftest_div_const.argtypes = [i32, C.c_uint32, C.c_uint64, p, p]
         l.llnv_adaln_quantize_nvfp4_static.argtypes = [p, i64, i64, i64, p, p, i64, i32, f32, i32, i32, p, p, p, p, i64, p]
         l.llnv_static_max_rows.restype = C.c_int64
+        l.llnv_attention_bf16.argtypes = [p, i64, i64, p, p, i64, i64, i64, i32, f32, p, i64, p]
         l.llnv_rmsnorm_rope.argtypes = [p, i64, i64, i64, p, f32, p, p, p, i64, p, i64, p, p]
         for name in EXPORTS:
             getattr(l, name)

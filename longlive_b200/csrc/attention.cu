@@ -1,0 +1,343 @@
+// Non-causal attention of a query chunk over a key/value window, bf16 in / bf16 out, fp32
+// softmax, on tcgen05 tensor cores (kind::f16) with the score and output accumulators in tensor
+// memory.  head_dim = 128.
+//
+//   O[q, h, :] = softmax_k( Q[q, h, :] . K[k, h, :] * scale ) V[k, h, :]
+//
+// One CTA per (128-query tile, head), 6 warps:
+//   warp 0     TMA producer: the Q tile once, then K and V tiles of 128 keys (two 64-channel halves
+//              each, 128-byte swizzle), two stages.
+//   warp 1     MMA issuer / TMEM owner.  S_j = Q K_j^T (8 MMAs, K = 16 channels each, both operands
+//              K-major from shared memory) into one of two score buffers; O += P_j V_j (8 MMAs,
+//              K = 16 keys each; P read from tensor memory, V MN-major from shared memory).
+//              Issue order  S_0, S_1, { PV_j, S_{j+2} }  keeps the tensor pipe busy while the
+//              softmax of tile j runs.
+//   warps 2-5  softmax: thread = query row.  Reads S_j with tcgen05.ld, keeps the running row
+//              maximum and sum, writes P_j as packed bf16 over the first 64 columns of the same
+//              score buffer (tcgen05.st).  The output accumulator is rescaled lazily: only when
+//              a row maximum grows by more than 2^8 is O multiplied by exp2(m_old - m_new), so in
+//              steady state O is touched only by the tensor pipe.  After the last tile the same
+//              warps normalise O and store it through swizzled shared memory with TMA.
+// All mbarrier waits are bounded (sm100.cuh).
+#include <cuda.h>
+
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace llnv {
+namespace {
+
+using namespace sm100;
+
+constexpr int kD = 128;            // head dim
+constexpr int kBQ = 128;           // queries per CTA
+constexpr int kBK = 128;           // keys per tile
+constexpr int kStages = 2;
+constexpr uint32_t kHalfBytes = 128 * 128;        // 128 rows x 64 bf16
+constexpr uint32_t kTileBytes = 2 * kHalfBytes;   // 32 KiB
+constexpr uint32_t kQOff = 0;
+constexpr uint32_t kKOff = kTileBytes;
+constexpr uint32_t kVOff = kKOff + kStages * kTileBytes;
+constexpr uint32_t kBarOff = kVOff + kStages * kTileBytes;
+constexpr uint32_t kSmemBytes = kBarOff + 1024;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kSCol0 = 0, kSCol1 = 128, kOCol = 256;
+constexpr int kThreads = 192;
+
+struct AttnParams {
+  int64_t Lq, Lk;
+  int heads;
+  float scale_log2;            // scale * log2(e)
+  unsigned int* status;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const AttnParams p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* q_full = reinterpret_cast<uint64_t*>(smem + kBarOff);
+  uint64_t* k_full = q_full + 1;
+  uint64_t* k_empty = k_full + kStages;
+  uint64_t* v_full = k_empty + kStages;
+  uint64_t* v_empty = v_full + kStages;
+  uint64_t* s_full = v_empty + kStages;        // [2]
+  uint64_t* p_ready = s_full + 2;              // [2]
+  uint64_t* pv_done = p_ready + 2;             // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = blockIdx.x, head = blockIdx.y;
+  const int nt = (int)((p.Lk + kBK - 1) / kBK);
+
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0 && p.status && atomicCAS(p.status, 0u, 2u) == 0u) p.status[1] = 901u;
+    return;
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_ready[i], 4);
+    }
+    mbar_init(pv_done, 1);
+    *abort_flag = 0u;
+    fence_barrier_init();
+    prefetch_tensormap(&tmQ);
+    prefetch_tensormap(&tmK);
+    prefetch_tensormap(&tmV);
+    prefetch_tensormap(&tmO);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      const int col = head * kD;
+      mbar_arrive_expect_tx(q_full, kTileBytes);
+      tma_load_2d(smem + kQOff, &tmQ, col, qt * kBQ, q_full);
+      tma_load_2d(smem + kQOff + kHalfBytes, &tmQ, col + 64, qt * kBQ, q_full);
+      for (int j = 0; j < nt; ++j) {
+        const int s = j % kStages;
+        const uint32_t ph = (uint32_t)((j / kStages) & 1);
+        mbar_wait(&k_empty[s], ph ^ 1u, abort_flag, p.status, 100u);
+        mbar_arrive_expect_tx(&k_full[s], kTileBytes);
+        tma_load_2d(smem + kKOff + s * kTileBytes, &tmK, col, j * kBK, &k_full[s]);
+        tma_load_2d(smem + kKOff + s * kTileBytes + kHalfBytes, &tmK, col + 64, j * kBK, &k_full[s]);
+        mbar_wait(&v_empty[s], ph ^ 1u, abort_flag, p.status, 101u);
+        mbar_arrive_expect_tx(&v_full[s], kTileBytes);
+        tma_load_2d(smem + kVOff + s * kTileBytes, &tmV, col, j * kBK, &v_full[s]);
+        tma_load_2d(smem + kVOff + s * kTileBytes + kHalfBytes, &tmV, col + 64, j * kBK, &v_full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc_qk = make_idesc_bf16(kBQ, kBK, 0, 0);     // A, B K-major
+      constexpr uint32_t idesc_pv = make_idesc_bf16(kBQ, kD, 0, 1);      // B (V) MN-major
+      const uint32_t q_addr = smem_u32(smem + kQOff);
+
+      auto issue_qk = [&](int t) {
+        const int s = t % kStages;
+        mbar_wait(&k_full[s], (uint32_t)((t / kStages) & 1), abort_flag, p.status, 200u);
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(smem + kKOff + s * kTileBytes);
+        const uint32_t d_tmem = tmem_base + ((t & 1) ? kSCol1 : kSCol0);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          // 16 channels per MMA: 32 bytes along the swizzled 128-byte row, second half after 4 steps
+          const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
+          mma_f16_ss(d_tmem, make_kmajor_sw128_desc(q_addr + off), make_kmajor_sw128_desc(k_addr + off), idesc_qk, ks != 0);
+        }
+        tc_commit(&k_empty[s]);
+        tc_commit(&s_full[t & 1]);
+      };
+
+      mbar_wait(q_full, 0u, abort_flag, p.status, 201u);
+      issue_qk(0);
+      if (nt > 1) issue_qk(1);
+      for (int j = 0; j < nt; ++j) {
+        const int s = j % kStages;
+        const uint32_t ph = (uint32_t)((j / kStages) & 1);
+        mbar_wait(&p_ready[j & 1], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 202u);
+        mbar_wait(&v_full[s], ph, abort_flag, p.status, 203u);
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(smem + kVOff + s * kTileBytes);
+        const uint32_t p_tmem = tmem_base + ((j & 1) ? kSCol1 : kSCol0);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          // 16 keys per MMA: P columns 8*ks..8*ks+7 (two bf16 per column), V rows 16*ks.. (2048 bytes apart)
+          // V is MN-major: 64 channels contiguous per key row, the second 64 channels one half-tile further
+          const uint64_t v_desc = make_smem_desc(v_addr + ks * 2048, kHalfBytes, 1024, 2);
+          mma_f16_ts(tmem_base + kOCol, p_tmem + 8 * ks, v_desc, idesc_pv, (j | ks) != 0);
+        }
+        tc_commit(&v_empty[s]);
+        tc_commit(pv_done);
+        if (j + 2 < nt) issue_qk(j + 2);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue
+    const int q = warp & 3;
+    const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+    const float c = p.scale_log2;
+    float m = -INFINITY;          // running maximum of raw scores used as the exponent offset
+    float l = 0.f;                // running sum of exp
+    for (int j = 0; j < nt; ++j) {
+      const uint32_t s_tmem = tmem_base + lane_base + ((j & 1) ? kSCol1 : kSCol0);
+      mbar_wait(&s_full[j & 1], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 300u);
+      tc_fence_after();
+      uint32_t sr[4][32];
+#pragma unroll
+      for (int g = 0; g < 4; ++g) tmem_ld32(s_tmem + 32 * g, sr[g]);
+      tmem_ld_wait();
+      const int valid = (int)min((int64_t)kBK, p.Lk - (int64_t)j * kBK);
+      float mt = -INFINITY;
+#pragma unroll
+      for (int g = 0; g < 4; ++g)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float sv = __uint_as_float(sr[g][i]);
+          if (g * 32 + i >= valid) sv = -INFINITY;
+          sr[g][i] = __float_as_uint(sv);
+          mt = fmaxf(mt, sv);
+        }
+      // lazy rescale: keep the old offset unless this tile's maximum exceeds it by more than 2^8
+      const bool grow = (mt - m) * c > 8.f;           // also true for the first tile (m = -inf)
+      if (__any_sync(0xFFFFFFFFu, grow && j > 0)) {
+        // all PV products issued so far must have landed in O before it is rescaled
+        mbar_wait(pv_done, (uint32_t)((j - 1) & 1), abort_flag, p.status, 301u);
+        tc_fence_after();
+        const float m_new = grow ? mt : m;
+        const float alpha = ex2((m - m_new) * c);
+        l *= alpha;
+        m = m_new;
+#pragma unroll 1
+        for (int g = 0; g < 4; ++g) {
+          uint32_t o[32];
+          tmem_ld32(tmem_base + lane_base + kOCol + 32 * g, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(tmem_base + lane_base + kOCol + 32 * g, o);
+        }
+        tmem_st_wait();
+      } else if (grow) {
+        m = mt;                                        // first tile: nothing accumulated yet
+      }
+      const float mc = m * c;
+      float rs = 0.f;
+      uint32_t pk[64];
+#pragma unroll
+      for (int g = 0; g < 4; ++g)
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = ex2(__fmaf_rn(__uint_as_float(sr[g][i]), c, -mc));
+          const float p1 = ex2(__fmaf_rn(__uint_as_float(sr[g][i + 1]), c, -mc));
+          rs += p0 + p1;
+          const __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
+          pk[(g * 32 + i) >> 1] = *reinterpret_cast<const uint32_t*>(&b2);
+        }
+      l += rs;
+      {
+        uint32_t(&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pk[0]);
+        uint32_t(&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pk[32]);
+        tmem_st32(s_tmem, lo);
+        tmem_st32(s_tmem + 32, hi);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_ready[j & 1]);
+    }
+    // ---- epilogue: O / l -> bf16 -> swizzled staging (the Q tile's shared memory) -> TMA store
+    mbar_wait(pv_done, (uint32_t)((nt - 1) & 1), abort_flag, p.status, 302u);
+    tc_fence_after();
+    const float inv_l = 1.f / l;
+    const int row0 = qt * kBQ + q * 32;
+#pragma unroll 1
+    for (int half = 0; half < 2; ++half) {
+      uint32_t o[2][32];
+      tmem_ld32(tmem_base + lane_base + kOCol + 64 * half, o[0]);
+      tmem_ld32(tmem_base + lane_base + kOCol + 64 * half + 32, o[1]);
+      tmem_ld_wait();
+      uint8_t* buf = smem + kQOff + half * kHalfBytes + q * 4096;      // 32 rows x 128 bytes
+#pragma unroll
+      for (int v8 = 0; v8 < 8; ++v8) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int cc = v8 * 8 + 2 * e;
+          const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(o[cc >> 5][cc & 31]) * inv_l,
+                                                          __uint_as_float(o[(cc + 1) >> 5][(cc + 1) & 31]) * inv_l);
+          w[e] = *reinterpret_cast<const uint32_t*>(&b2);
+        }
+        *reinterpret_cast<uint4*>(buf + lane * 128 + ((v8 ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0 && row0 < p.Lq) {
+        tma_store_2d(&tmO, buf, head * kD + half * 64, row0);
+        bulk_commit();
+      }
+    }
+    if (lane == 0) bulk_wait<0>();
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace
+}  // namespace llnv
+
+using namespace llnv;
+
+extern "C" int llnv_attention_bf16(const void* q, int64_t Lq, int64_t ldq, const void* k, const void* v, int64_t Lk,
+                                   int64_t ldk, int64_t ldv, int heads, float scale, void* out, int64_t ldo,
+                                   llnv_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  LLNV_REQUIRE(q && k && v && out, "llnv_attention_bf16: null pointer");
+  LLNV_REQUIRE(Lq >= 0 && Lk > 0 && heads > 0, "llnv_attention_bf16: need Lq >= 0, Lk > 0, heads > 0 (Lq=%lld Lk=%lld heads=%d)",
+               (long long)Lq, (long long)Lk, heads);
+  const int64_t C = (int64_t)heads * kD;
+  LLNV_REQUIRE(ldq >= C && ldk >= C && ldv >= C && ldo >= C && ldq % 8 == 0 && ldk % 8 == 0 && ldv % 8 == 0 && ldo % 8 == 0,
+               "llnv_attention_bf16: row strides must be >= heads*128 and multiples of 8");
+  LLNV_REQUIRE(((uintptr_t)q & 15) == 0 && ((uintptr_t)k & 15) == 0 && ((uintptr_t)v & 15) == 0 && ((uintptr_t)out & 15) == 0,
+               "llnv_attention_bf16: pointers must be 16-byte aligned");
+  LLNV_REQUIRE(heads <= 65535, "llnv_attention_bf16: too many heads");
+  if (Lq == 0) return LLNV_OK;
+  CUtensorMap tmQ, tmK, tmV, tmO;
+  int rc = cached_tensor_map(&tmQ, 1, q, (uint64_t)Lq, (uint64_t)C, (uint64_t)ldq, 128, 64, 3);
+  if (rc != LLNV_OK) return rc;
+  rc = cached_tensor_map(&tmK, 1, k, (uint64_t)Lk, (uint64_t)C, (uint64_t)ldk, 128, 64, 3);
+  if (rc != LLNV_OK) return rc;
+  rc = cached_tensor_map(&tmV, 1, v, (uint64_t)Lk, (uint64_t)C, (uint64_t)ldv, 128, 64, 3);
+  if (rc != LLNV_OK) return rc;
+  rc = cached_tensor_map(&tmO, 1, out, (uint64_t)Lq, (uint64_t)C, (uint64_t)ldo, 32, 64, 3);
+  if (rc != LLNV_OK) return rc;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  LLNV_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    LLNV_CUDA(cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+    attr_set[dev] = true;
+  }
+  AttnParams p;
+  p.Lq = Lq;
+  p.Lk = Lk;
+  p.heads = heads;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = device_status_word();
+  dim3 grid((unsigned)((Lq + kBQ - 1) / kBQ), (unsigned)heads);
+  attention_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmQ, tmK, tmV, tmO, p);
+  return launch_status("attention_kernel");
+}

@@ -21,9 +21,6 @@
 // Every mbarrier wait is bounded (see sm100.cuh); no CTA waits on another CTA.
 #include <cuda.h>
 
-#include <mutex>
-#include <unordered_map>
-
 #include "common.cuh"
 #include "sm100.cuh"
 
@@ -351,58 +348,15 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
 // ---- host side ------------------------------------------------------------------------------
 
-struct MapKey {
-  const void* ptr;
-  uint64_t rows, row_bytes;
-  uint32_t box_rows;
-  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && row_bytes == o.row_bytes && box_rows == o.box_rows; }
-};
-struct MapKeyHash {
-  size_t operator()(const MapKey& k) const {
-    size_t h = std::hash<const void*>()(k.ptr);
-    h ^= std::hash<uint64_t>()(k.rows * 1315423911ull + k.row_bytes * 2654435761ull + k.box_rows) + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
-    return h;
-  }
-};
-
-std::mutex g_map_mu;
-std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
 int g_forced_bn = 0;
 int g_debug = 0;
 
 int get_codes_map(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
-  MapKey key{ptr, rows, row_bytes, box_rows};
-  std::lock_guard<std::mutex> lock(g_map_mu);
-  auto it = g_maps.find(key);
-  if (it != g_maps.end()) {
-    *out = it->second;
-    return LLNV_OK;
-  }
-  CUtensorMap m;
-  int rc = make_tensor_map_2d(&m, ptr, rows, row_bytes, row_bytes, box_rows, BK_BYTES, 3);
-  if (rc != LLNV_OK) return rc;
-  if (g_maps.size() > 8192) g_maps.clear();
-  g_maps.emplace(key, m);
-  *out = m;
-  return LLNV_OK;
+  return cached_tensor_map(out, 0, ptr, rows, row_bytes, row_bytes, box_rows, BK_BYTES, 3);
 }
 
 int get_out_map(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t pitch) {
-  // keyed with a marker in box_rows so that it cannot collide with a codes map
-  MapKey key{ptr, rows, cols * 2 + (pitch << 20), 0x80000000u | 32u};
-  std::lock_guard<std::mutex> lock(g_map_mu);
-  auto it = g_maps.find(key);
-  if (it != g_maps.end()) {
-    *out = it->second;
-    return LLNV_OK;
-  }
-  CUtensorMap m;
-  int rc = make_tensor_map_2d_bf16(&m, ptr, rows, cols, pitch, 32, 64, 3);
-  if (rc != LLNV_OK) return rc;
-  if (g_maps.size() > 8192) g_maps.clear();
-  g_maps.emplace(key, m);
-  *out = m;
-  return LLNV_OK;
+  return cached_tensor_map(out, 1, ptr, rows, cols, pitch, 32, 64, 3);
 }
 
 template <int BN, int EPI>

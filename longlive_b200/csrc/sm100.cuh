@@ -243,4 +243,9 @@ int make_tensor_map_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64
 int make_tensor_map_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_elems,
                             uint32_t box_rows, uint32_t box_cols, int swizzle);
 
+// Cached variants (key: pointer, extents, box, swizzle).  kind 0: byte tensor (cols = row bytes,
+// pitch in bytes), kind 1: bf16 tensor (cols and pitch in elements).
+int cached_tensor_map(CUtensorMap* out, int kind, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch,
+                      uint32_t box_rows, uint32_t box_cols, int swizzle);
+
 }  // namespace llnv

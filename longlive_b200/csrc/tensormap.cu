@@ -3,6 +3,7 @@
 #include <cuda.h>
 
 #include <mutex>
+#include <unordered_map>
 
 #include "common.cuh"
 #include "sm100.cuh"
@@ -67,6 +68,49 @@ int make_tensor_map_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64
 int make_tensor_map_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_elems,
                             uint32_t box_rows, uint32_t box_cols, int swizzle) {
   return encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, rows, cols, pitch_elems * 2, box_rows, box_cols, swizzle);
+}
+
+// ---- small cache: encoding a tensor map costs a few microseconds of host time ----------------
+namespace {
+struct MapKey {
+  const void* ptr;
+  uint64_t rows, cols, pitch;
+  uint32_t box_rows, box_cols;
+  int kind, swizzle;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && pitch == o.pitch && box_rows == o.box_rows &&
+           box_cols == o.box_cols && kind == o.kind && swizzle == o.swizzle;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    uint64_t h = (uint64_t)(uintptr_t)k.ptr * 0x9e3779b97f4a7c15ull;
+    h ^= k.rows * 1315423911ull + k.cols * 2654435761ull + k.pitch * 40503ull + k.box_rows * 97ull + k.box_cols * 13ull +
+         (uint64_t)k.kind * 7ull + (uint64_t)k.swizzle;
+    return (size_t)(h ^ (h >> 29));
+  }
+};
+std::mutex g_map_mu;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+}  // namespace
+
+int cached_tensor_map(CUtensorMap* out, int kind, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch,
+                      uint32_t box_rows, uint32_t box_cols, int swizzle) {
+  MapKey key{base, rows, cols, pitch, box_rows, box_cols, kind, swizzle};
+  std::lock_guard<std::mutex> lock(g_map_mu);
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) {
+    *out = it->second;
+    return LLNV_OK;
+  }
+  CUtensorMap m;
+  int rc = kind == 0 ? make_tensor_map_2d(&m, base, rows, cols, pitch, box_rows, box_cols, swizzle)
+                     : make_tensor_map_2d_bf16(&m, base, rows, cols, pitch, box_rows, box_cols, swizzle);
+  if (rc != LLNV_OK) return rc;
+  if (g_maps.size() > 8192) g_maps.clear();
+  g_maps.emplace(key, m);
+  *out = m;
+  return LLNV_OK;
 }
 
 }  // namespace llnv

@@ -149,6 +149,26 @@ def rmsnorm_rope(x, weight=None, cos=None, sin=None, eps=1e-6, *, out=None, out_
     return out, out_smooth, amax_out
 
 
+def attention_bf16(q, k, v, heads, scale=None, out=None):
+    """softmax(q k^T * scale) v per head, non-causal.  q: bf16 [Lq, heads*128]; k, v: bf16 [Lk, heads*128]
+    (row strides free, unit column stride).  Returns bf16 [Lq, heads*128]."""
+    _require_cuda(q, "q")
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        if t.dim() != 2 or t.dtype != torch.bfloat16 or t.stride(1) != 1 or t.shape[1] != heads * 128:
+            raise RuntimeError(f"{name} must be bfloat16 [tokens, heads*128] with unit column stride")
+    if k.shape[0] != v.shape[0]:
+        raise RuntimeError("k and v must have the same number of tokens")
+    if out is None:
+        out = torch.empty((q.shape[0], heads * 128), dtype=torch.bfloat16, device=q.device)
+    if scale is None:
+        scale = 128 ** -0.5
+    with torch.cuda.device(q.device):
+        _check(_lib.lib().llnv_attention_bf16(q.data_ptr(), q.shape[0], q.stride(0), k.data_ptr(), v.data_ptr(), k.shape[0],
+                                              k.stride(0), v.stride(0), heads, float(scale), out.data_ptr(), out.stride(0),
+                                              _stream(q)))
+    return out
+
+
 def dequantize_nvfp4(codes, sf, amax, rows, cols, cols_padded, dtype, e2m1_max, e4m3_max, rounding=DEQ_PYTORCH):
     _require_cuda(codes, "codes")
     out = torch.empty((rows, cols), dtype=dtype, device=codes.device)

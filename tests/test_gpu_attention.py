@@ -1,0 +1,90 @@
+"""Chunk attention parity against the oracle (fp32 softmax(QK^T/sqrt(d))V, bf16 result).
+
+Tolerance: the kernel multiplies bf16-rounded probabilities with V on the tensor cores and uses a
+hardware exp2, the oracle works in fp32 throughout; results are compared after the bf16 output
+rounding with relative Frobenius error <= 1e-2 and |diff| <= 2^-6 |ref| + 2^-7 mean|ref|."""
+import numpy as np
+import pytest
+import torch
+
+import longlive_b200 as L
+from longlive_b200 import _lib, ops
+from oracle import nvfp4_oracle as O
+from tests import util
+
+pytestmark = pytest.mark.gpu
+
+
+def check(got, ref):
+    got = got.float().cpu().numpy().reshape(ref.shape)
+    rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
+    assert rel <= 1e-2, rel
+    tol = np.abs(ref) * 2.0 ** -6 + 2.0 ** -7 * np.abs(ref).mean()
+    frac = (np.abs(got - ref) > tol).mean()
+    assert frac < 2e-3, frac
+
+
+@pytest.mark.parametrize("lq,lk,heads,sigma", [(128, 128, 1, 1.0), (200, 300, 2, 1.0), (256, 1320, 3, 1.0), (130, 77, 2, 3.0), (384, 640, 2, 0.2)])
+def test_attention_vs_oracle(lq, lk, heads, sigma):
+    g = torch.Generator().manual_seed(lq + lk)
+    q = (torch.randn(lq, heads, 128, generator=g) * sigma).bfloat16()
+    k = (torch.randn(lk, heads, 128, generator=g) * sigma).bfloat16()
+    v = torch.randn(lk, heads, 128, generator=g).bfloat16()
+    out = ops.attention_bf16(q.reshape(lq, -1).cuda(), k.reshape(lk, -1).cuda(), v.reshape(lk, -1).cuda(), heads)
+    torch.cuda.synchronize()
+    assert _lib.lib().llnv_check_status(None) == 0, _lib.lib().llnv_last_error()
+    ref = O.attention(q.float().numpy(), k.float().numpy(), v.float().numpy())
+    check(out, ref.reshape(lq, -1))
+
+
+def test_attention_growing_maxima_exercise_lazy_rescale():
+    """Keys whose scores keep growing tile after tile force the deferred rescale of the output."""
+    lq, lk, heads = 128, 1024, 1
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(lq, heads, 128, generator=g).bfloat16()
+    k = torch.randn(lk, heads, 128, generator=g)
+    ramp = torch.linspace(0.2, 6.0, lk).view(lk, 1, 1)
+    k = (k * ramp).bfloat16()
+    v = torch.randn(lk, heads, 128, generator=g).bfloat16()
+    out = ops.attention_bf16(q.reshape(lq, -1).cuda(), k.reshape(lk, -1).cuda(), v.reshape(lk, -1).cuda(), heads)
+    check(out, O.attention(q.float().numpy(), k.float().numpy(), v.float().numpy()).reshape(lq, -1))
+
+
+def test_attention_matches_reference_fixture(golden):
+    g = golden("elementwise_small.npz")
+    q = util.bf16_np_to_torch(g["att_q"])[0]
+    k = util.bf16_np_to_torch(g["att_k"])[0]
+    v = util.bf16_np_to_torch(g["att_v"])[0]
+    heads = q.shape[1]
+    out = ops.attention_bf16(q.reshape(q.shape[0], -1), k.reshape(k.shape[0], -1), v.reshape(v.shape[0], -1), heads)
+    check(out, O.bf16_from_bits(g["att_y"])[0].reshape(q.shape[0], -1))
+
+
+def test_window_attention_with_nvfp4_cache():
+    """The reference's quantized-cache attention: dequantized NVFP4 blocks (un-smoothed keys) followed by
+    the current chunk with k_smooth-ed keys (wan_5b/modules/causal_model.py:628-652, 781)."""
+    heads, T, blocks, lq = 2, 96, 2, 96
+    g = torch.Generator().manual_seed(11)
+    cache_k = [torch.randn(T * heads, 128, generator=g).bfloat16() for _ in range(blocks)]
+    cache_v = [torch.randn(T * heads, 128, generator=g).bfloat16() for _ in range(blocks)]
+    q = torch.randn(lq, heads, 128, generator=g).bfloat16()
+    k_new = torch.randn(lq, heads, 128, generator=g).bfloat16()
+    v_new = torch.randn(lq, heads, 128, generator=g).bfloat16()
+    kq = [L.quantize_to_fp4(t.cuda()) for t in cache_k]
+    vq = [L.quantize_to_fp4(t.cuda()) for t in cache_v]
+    lk = blocks * T + lq
+    win_k = torch.empty(lk, heads * 128, dtype=torch.bfloat16, device="cuda")
+    win_v = torch.empty_like(win_k)
+    L.dequantize_kv_cache(kq, blocks, heads, T, torch.bfloat16, "cuda", out=win_k[: blocks * T].view(1, blocks * T, heads, 128))
+    L.dequantize_kv_cache(vq, blocks, heads, T, torch.bfloat16, "cuda", out=win_v[: blocks * T].view(1, blocks * T, heads, 128))
+    # current chunk: smoothed keys and values written straight into the window tail
+    ops.rmsnorm_rope(k_new.reshape(lq, -1).cuda(), out=torch.empty(lq, heads * 128, dtype=torch.bfloat16, device="cuda"),
+                     out_smooth=win_k[blocks * T:])
+    win_v[blocks * T:] = v_new.reshape(lq, -1).cuda()
+    out = ops.attention_bf16(q.reshape(lq, -1).cuda(), win_k, win_v, heads)
+
+    def trip(qt):
+        return qt.values.cpu().numpy(), util.u8(qt.scale_factors), np.float32(qt.amax.item())
+    ref = O.window_attention(q.float().numpy(), k_new.float().numpy(), v_new.float().numpy(),
+                             [trip(t) for t in kq], [trip(t) for t in vq], heads, T)
+    check(out, ref.reshape(lq, -1))
