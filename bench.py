@@ -337,7 +337,7 @@ def run_gpu_arm(args):
 
 def run_kernel_case(spec: str, iters: int):
     """Run one kernel on one shape a few times (used for ncu captures and quick timing):
-    gemm:MxNxK[:tile]   quantize:MxK[:rule]   kvdequant:BLOCKSxTOKENSxHEADS"""
+    gemm:MxNxK[:tile]   quantize:MxK[:rule]   kvdequant:BLOCKSxTOKENSxHEADS   attention:LQxLKxHEADS   ropenorm:TOKENSxHEADS"""
     import torch
 
     import longlive_b200 as L
@@ -377,6 +377,25 @@ def run_kernel_case(spec: str, iters: int):
         out = torch.empty(1, blocks * tokens, heads, 128, dtype=torch.bfloat16, device=dev)
         fn = lambda: L.dequantize_kv_cache(qs, blocks, heads, tokens, torch.bfloat16, dev, out=out)
         work, unit = blocks * tokens * heads * 128 * (0.5 + 1 / 16 + 2) / 1e9, "GB/s"
+    elif kind == "attention":
+        lq, lk, heads = d
+        q = torch.randn(lq, heads * 128, generator=gen, device=dev).bfloat16()
+        k = torch.randn(lk, heads * 128, generator=gen, device=dev).bfloat16()
+        v = torch.randn(lk, heads * 128, generator=gen, device=dev).bfloat16()
+        out = torch.empty_like(q)
+        fn = lambda: ops.attention_bf16(q, k, v, heads, out=out)
+        work, unit = 4.0 * lq * lk * heads * 128 / 1e12, "TFLOP/s"
+    elif kind == "ropenorm":
+        s_, heads = d
+        x = torch.randn(s_, heads * 128, generator=gen, device=dev).bfloat16()
+        w = torch.ones(heads * 128, device=dev).bfloat16()
+        cos = torch.rand(s_, 64, generator=gen, device=dev)
+        sin = torch.rand(s_, 64, generator=gen, device=dev)
+        out = torch.empty_like(x)
+        sm = torch.empty_like(x)
+        amax = torch.empty(1, dtype=torch.float32, device=dev)
+        fn = lambda: ops.rmsnorm_rope(x, w, cos, sin, out=out, out_smooth=sm, amax_out=amax)
+        work, unit = s_ * heads * 128 * 6 / 1e9, "GB/s"
     else:
         raise SystemExit(f"unknown kernel case {spec}")
     for _ in range(3):

@@ -88,6 +88,18 @@ int llnv_adaln_quantize_nvfp4(const void* x, int64_t M, int64_t C, int64_t ldx, 
                               int64_t mod_stride, int frame_rows, float eps, int add_one, int rule, void* codes,
                               void* sf, float* amax, void* y_out, int64_t ldy, float* row_stats, llnv_stream_t stream);
 
+/* Extended forms for token-sharded (sequence-parallel) use: `row_offset` is added to the row index
+ * before the frame lookup, and `phase` splits the call so that the tensor amax can be max-reduced
+ * across ranks in between: 0 = everything, 1 = row statistics + amax only, 2 = quantize only
+ * (reads amax and row_stats as phase 1 left them). */
+int llnv_adaln_quantize_nvfp4_ex(const void* x, int64_t M, int64_t C, int64_t ldx, const void* scale, const void* shift,
+                                 int64_t mod_stride, int frame_rows, float eps, int add_one, int rule, void* codes,
+                                 void* sf, float* amax, void* y_out, int64_t ldy, float* row_stats, int64_t row_offset,
+                                 int phase, llnv_stream_t stream);
+int llnv_layernorm_quantize_nvfp4_ex(const void* x, int64_t M, int64_t C, int64_t ldx, const void* weight, const void* bias,
+                                     float eps, int rule, void* codes, void* sf, float* amax, void* y_out, int64_t ldy,
+                                     float* row_stats, int phase, llnv_stream_t stream);
+
 /* Same operation and results as llnv_adaln_quantize_nvfp4 for callers that cannot allocate device
  * memory where they call it (a server that owns all device memory through its own arena, a
  * latency-critical loop that must not take cudaMalloc's device-wide synchronisation).  It has no
@@ -162,7 +174,7 @@ int llnv_attention_bf16(const void* q, int64_t Lq, int64_t ldq, const void* k, c
  *   y  = bf16(y + bias[n])                         if bias
  *   y  = bf16(gelu_tanh(y))                        if act == 1
  *   y  = bf16(residual[m,n] + bf16(y * gate[f,n])) if residual (gate NULL -> y added as is),
- *        f = m / frame_rows
+ *        f = (m + row_offset) / frame_rows
  *   out_amax = max(out_amax, |y|)                  if out_amax (atomic, caller zeroes it)
  */
 typedef struct {
@@ -175,6 +187,7 @@ typedef struct {
   int64_t gate_stride;
   int32_t frame_rows;     /* rows per frame for the gate lookup */
   float* out_amax;        /* fp32 scalar, atomic max of |out| */
+  int32_t row_offset;     /* added to m before the gate's frame lookup (token shards) */
 } llnv_epilogue_t;
 
 /* D[M, N] = epilogue(alpha * A[M, K] * B[N, K]^T), A and B NVFP4 (codes [rows_padded, K/2],

@@ -12,7 +12,7 @@ EXPORTS = [
     "llnv_version", "llnv_last_error", "llnv_check_status", "llnv_amax_bf16", "llnv_quantize_nvfp4",
     "llnv_kv_dequant", "llnv_dequantize_nvfp4", "llnv_gemm_nvfp4", "llnv_adaln_quantize_nvfp4",
     "llnv_layernorm_quantize_nvfp4", "llnv_gemm_nvfp4_force_tile_n", "llnv_gemm_nvfp4_debug", "llnv_selftest_div_const",
-    "llnv_adaln_quantize_nvfp4_static", "llnv_static_max_rows", "llnv_rmsnorm_rope", "llnv_attention_bf16",
+    "llnv_adaln_quantize_nvfp4_static", "llnv_static_max_rows", "llnv_rmsnorm_rope", "llnv_attention_bf16", "llnv_adaln_quantize_nvfp4_ex", "llnv_layernorm_quantize_nvfp4_ex",
 ]
 
 
@@ -21,7 +21,7 @@ class Epilogue(C.Structure):
     _fields_ = [
         ("alpha", C.c_void_p), ("bias", C.c_void_p), ("act", C.c_int32), ("residual", C.c_void_p),
         ("ldr", C.c_int64), ("gate", C.c_void_p), ("gate_stride", C.c_int64), ("frame_rows", C.c_int32),
-        ("out_amax", C.c_void_p),
+        ("out_amax", C.c_void_p), ("row_offset", C.c_int32),
     ]
 
 
@@ -56,6 +56,8 @@ def lib() -> C.CDLL:
         l.llnv_adaln_quantize_nvfp4_static.argtypes = [p, i64, i64, i64, p, p, i64, i32, f32, i32, i32, p, p, p, p, i64, p]
         l.llnv_static_max_rows.restype = C.c_int64
         l.llnv_attention_bf16.argtypes = [p, i64, i64, p, p, i64, i64, i64, i32, f32, p, i64, p]
+        l.llnv_adaln_quantize_nvfp4_ex.argtypes = [p, i64, i64, i64, p, p, i64, i32, f32, i32, i32, p, p, p, p, i64, p, i64, i32, p]
+        l.llnv_layernorm_quantize_nvfp4_ex.argtypes = [p, i64, i64, i64, p, p, f32, i32, p, p, p, p, i64, p, i32, p]
         l.llnv_rmsnorm_rope.argtypes = [p, i64, i64, i64, p, f32, p, p, p, i64, p, i64, p, p]
         for name in EXPORTS:
             getattr(l, name)

@@ -46,9 +46,12 @@ int sm_count();
 
 // LayerNorm-family transform fused into the quantizer (quantize.cu).  mode: 1 = adaLN modulation,
 // 2 = affine LayerNorm.  row_stats is a scratch array of 2*M floats; nothing is allocated.
+// row_offset shifts the frame lookup (token shards); phase 0 = statistics + amax + quantize,
+// 1 = statistics + amax only, 2 = quantize only (amax and row_stats as left by phase 1).
 int ln_quantize_impl(int mode, const void* x, int64_t M, int64_t C, int64_t ldx, const void* p0, const void* p1,
                      int64_t mod_stride, int frame_rows, float eps, int add_one, int rule, void* codes, void* sf,
-                     float* amax, void* y_out, int64_t ldy, float* row_stats, cudaStream_t stream, const char* who);
+                     float* amax, void* y_out, int64_t ldy, float* row_stats, cudaStream_t stream, const char* who,
+                     int64_t row_offset, int phase);
 
 // ---- scale rule constants -----------------------------------------------------------------
 __host__ __device__ inline float rule_e2m1_max(int rule) { return rule == LLNV_RULE_STATIC_4 ? 4.f : 6.f; }

@@ -224,7 +224,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const int64_t row = (int64_t)row0 + lane;
       const bool row_ok = row < p.M;
       const uint16_t* grow = nullptr;
-      if (gate && row_ok) grow = gate + (row / p.epi.frame_rows) * p.epi.gate_stride;
+      if (gate && row_ok) grow = gate + ((row + p.epi.row_offset) / p.epi.frame_rows) * p.epi.gate_stride;
       // residual tile of the first chunk can be fetched while the main loop is still running
       if (has_res && row0 < p.M) {
         const uint32_t b0 = chunk & 1u;

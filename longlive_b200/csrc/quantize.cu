@@ -272,13 +272,14 @@ struct Prologue {
   int64_t stride;
   int frame_rows;
   int add_one;
+  int64_t row_offset;          // added to the row index before the frame lookup (token shards)
 };
 
 template <int MODE>
 __device__ __forceinline__ void transform_block(uint32_t (&w)[8], const Prologue& pr, int64_t row, int64_t col) {
   if (MODE == kPlain) return;
   const float mean = __ldg(pr.row_stats + 2 * row), rstd = __ldg(pr.row_stats + 2 * row + 1);
-  const int64_t prow = MODE == kAdaLN ? (row / pr.frame_rows) * pr.stride : 0;
+  const int64_t prow = MODE == kAdaLN ? ((row + pr.row_offset) / pr.frame_rows) * pr.stride : 0;
   const uint4* a4 = reinterpret_cast<const uint4*>(pr.p0 + prow + col);
   const uint4* b4 = reinterpret_cast<const uint4*>(pr.p1 + prow + col);
   const uint4 a0 = __ldg(a4), a1 = __ldg(a4 + 1), b0 = __ldg(b4), b1 = __ldg(b4 + 1);
@@ -425,7 +426,7 @@ __global__ void __launch_bounds__(256) ln_stats_amax_kernel(const uint16_t* __re
       row_stats[2 * row] = mean;
       row_stats[2 * row + 1] = rstd;
     }
-    const int64_t prow = MODE == kAdaLN ? (row / pr.frame_rows) * pr.stride : 0;
+    const int64_t prow = MODE == kAdaLN ? ((row + pr.row_offset) / pr.frame_rows) * pr.stride : 0;
 #pragma unroll
     for (int i = 0; i < kMaxVec; ++i) {
       const int idx = lane + 32 * i;
@@ -500,7 +501,8 @@ int launch_quantize(int rule, dim3 grid, cudaStream_t stream, const uint16_t* x,
 // Shared by the allocation-free entry point in static_scratch.cu.
 int ln_quantize_impl(int mode, const void* x, int64_t M, int64_t C, int64_t ldx, const void* p0, const void* p1,
                      int64_t mod_stride, int frame_rows, float eps, int add_one, int rule, void* codes, void* sf,
-                     float* amax, void* y_out, int64_t ldy, float* row_stats, cudaStream_t stream, const char* who) {
+                     float* amax, void* y_out, int64_t ldy, float* row_stats, cudaStream_t stream, const char* who,
+                     int64_t row_offset, int phase) {
   LLNV_REQUIRE(x && p0 && p1 && codes && sf && amax && row_stats, "%s: null pointer", who);
   LLNV_REQUIRE(mode == kAdaLN || mode == kAffineLN, "%s: unknown mode %d", who, mode);
   LLNV_REQUIRE(M >= 0 && C > 0 && C % 64 == 0 && C <= 4096, "%s: C must be a multiple of 64 and at most 4096 (got %lld)", who, (long long)C);
@@ -511,7 +513,8 @@ int ln_quantize_impl(int mode, const void* x, int64_t M, int64_t C, int64_t ldx,
                "%s: x, scale/weight and shift/bias must be 16-byte aligned, codes 8-byte, sf 4-byte, row_stats 8-byte", who);
   if (mode == kAdaLN) LLNV_REQUIRE(frame_rows > 0 && mod_stride >= C && mod_stride % 8 == 0, "%s: frame_rows must be positive and the modulation stride a multiple of 8 that is >= C", who);
   if (y_out) LLNV_REQUIRE(ldy >= C && ldy % 8 == 0 && ((uintptr_t)y_out & 15) == 0, "%s: y_out must be 16-byte aligned with ldy a multiple of 8", who);
-  LLNV_CUDA(cudaMemsetAsync(amax, 0, sizeof(float), stream));
+  LLNV_REQUIRE(phase >= 0 && phase <= 2 && row_offset >= 0, "%s: phase must be 0, 1 or 2 and row_offset non-negative", who);
+  if (phase != 2) LLNV_CUDA(cudaMemsetAsync(amax, 0, sizeof(float), stream));
   if (M == 0) return LLNV_OK;
   Prologue pr;
   pr.row_stats = row_stats;
@@ -520,11 +523,15 @@ int ln_quantize_impl(int mode, const void* x, int64_t M, int64_t C, int64_t ldx,
   pr.stride = mod_stride;
   pr.frame_rows = frame_rows > 0 ? frame_rows : 1;
   pr.add_one = add_one;
+  pr.row_offset = row_offset;
   const unsigned sblocks = (unsigned)((M + 7) / 8);
-  if (mode == kAdaLN) ln_stats_amax_kernel<kAdaLN><<<sblocks, 256, 0, stream>>>((const uint16_t*)x, M, C, ldx, eps, pr, row_stats, amax);
-  else ln_stats_amax_kernel<kAffineLN><<<sblocks, 256, 0, stream>>>((const uint16_t*)x, M, C, ldx, eps, pr, row_stats, amax);
-  int rc = launch_status("ln_stats_amax_kernel");
-  if (rc != LLNV_OK) return rc;
+  if (phase != 2) {
+    if (mode == kAdaLN) ln_stats_amax_kernel<kAdaLN><<<sblocks, 256, 0, stream>>>((const uint16_t*)x, M, C, ldx, eps, pr, row_stats, amax);
+    else ln_stats_amax_kernel<kAffineLN><<<sblocks, 256, 0, stream>>>((const uint16_t*)x, M, C, ldx, eps, pr, row_stats, amax);
+    int rc = launch_status("ln_stats_amax_kernel");
+    if (rc != LLNV_OK) return rc;
+  }
+  if (phase == 1) return LLNV_OK;
   const int64_t mp = (M + 127) / 128 * 128;
   LLNV_REQUIRE(mp / 128 <= 65535, "%s: too many rows (%lld)", who, (long long)M);
   dim3 grid((unsigned)((C + 127) / 128), (unsigned)(mp / 128));
@@ -582,14 +589,29 @@ extern "C" int llnv_adaln_quantize_nvfp4(const void* x, int64_t M, int64_t C, in
                                          void* sf, float* amax, void* y_out, int64_t ldy, float* row_stats,
                                          llnv_stream_t stream) {
   return ln_quantize_impl(kAdaLN, x, M, C, ldx, scale, shift, mod_stride, frame_rows, eps, add_one, rule, codes, sf, amax,
-                          y_out, ldy, row_stats, (cudaStream_t)stream, "llnv_adaln_quantize_nvfp4");
+                          y_out, ldy, row_stats, (cudaStream_t)stream, "llnv_adaln_quantize_nvfp4", 0, 0);
+}
+
+extern "C" int llnv_adaln_quantize_nvfp4_ex(const void* x, int64_t M, int64_t C, int64_t ldx, const void* scale, const void* shift,
+                                            int64_t mod_stride, int frame_rows, float eps, int add_one, int rule, void* codes,
+                                            void* sf, float* amax, void* y_out, int64_t ldy, float* row_stats,
+                                            int64_t row_offset, int phase, llnv_stream_t stream) {
+  return ln_quantize_impl(kAdaLN, x, M, C, ldx, scale, shift, mod_stride, frame_rows, eps, add_one, rule, codes, sf, amax,
+                          y_out, ldy, row_stats, (cudaStream_t)stream, "llnv_adaln_quantize_nvfp4_ex", row_offset, phase);
+}
+
+extern "C" int llnv_layernorm_quantize_nvfp4_ex(const void* x, int64_t M, int64_t C, int64_t ldx, const void* weight,
+                                                const void* bias, float eps, int rule, void* codes, void* sf, float* amax,
+                                                void* y_out, int64_t ldy, float* row_stats, int phase, llnv_stream_t stream) {
+  return ln_quantize_impl(kAffineLN, x, M, C, ldx, weight, bias, 0, 1, eps, 0, rule, codes, sf, amax, y_out, ldy, row_stats,
+                          (cudaStream_t)stream, "llnv_layernorm_quantize_nvfp4_ex", 0, phase);
 }
 
 extern "C" int llnv_layernorm_quantize_nvfp4(const void* x, int64_t M, int64_t C, int64_t ldx, const void* weight,
                                              const void* bias, float eps, int rule, void* codes, void* sf, float* amax,
                                              void* y_out, int64_t ldy, float* row_stats, llnv_stream_t stream) {
   return ln_quantize_impl(kAffineLN, x, M, C, ldx, weight, bias, 0, 1, eps, 0, rule, codes, sf, amax, y_out, ldy, row_stats,
-                          (cudaStream_t)stream, "llnv_layernorm_quantize_nvfp4");
+                          (cudaStream_t)stream, "llnv_layernorm_quantize_nvfp4", 0, 0);
 }
 
 // Test hook: number of fp32 bit patterns in [first_bits, first_bits + count) for which the

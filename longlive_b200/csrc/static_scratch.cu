@@ -71,5 +71,5 @@ extern "C" int llnv_adaln_quantize_nvfp4_static(const void* x, int64_t M, int64_
   const int rc = static_row_stats(&row_stats);
   if (rc != LLNV_OK) return rc;
   return ln_quantize_impl(1, x, M, C, ldx, scale, shift, mod_stride, frame_rows, eps, add_one, rule, codes, sf, amax, y_out,
-                          ldy, row_stats, (cudaStream_t)stream, "llnv_adaln_quantize_nvfp4_static");
+                          ldy, row_stats, (cudaStream_t)stream, "llnv_adaln_quantize_nvfp4_static", 0, 0);
 }

@@ -1,0 +1,394 @@
+"""Causal DiT block stack on the NVFP4 kernels: the caller side of the hot path.
+
+Mirrors the inference forward of the reference's causal Wan2.2-5B-shaped DiT block
+(wan_5b/modules/causal_model.py:829-930 block, :327-791 self-attention with the rolling NVFP4 KV
+cache, :197-295 cross-attention, :1371-1483 cache update) as a sequence of C-ABI calls on
+persistent buffers: no per-call allocation, no host synchronisation, cache roll by permuting a
+block table instead of copying slots.  Random-init weights of the reference's shapes; patch
+embedding, time/text MLPs and the head are plain bf16 torch ops (outside the hot path).
+
+Per block and forward (S tokens of the chunk, window = cached blocks + current chunk):
+  adaLN(e0,e1)+quantize -> q,k,v GEMMs(+bias; v also emits its amax and lands in the V window)
+  -> RMSNorm+RoPE (q) / RMSNorm+RoPE+k_smooth+amax (k, smoothed copy lands in the K window)
+  -> NVFP4 cache blocks dequantized into the window -> attention -> quantize -> o GEMM(+bias,
+  gate e2, residual) -> LayerNorm+quantize -> cross q GEMM -> RMSNorm -> attention over the text
+  K/V -> quantize -> o GEMM(+bias, residual) -> adaLN(e3,e4)+quantize -> FFN GEMM(+bias, GELU, amax)
+  -> quantize (amax given) -> FFN GEMM(+bias, gate e5, residual); then the rotated keys and the
+  values of the chunk are quantized straight into the current cache block.
+
+Sequence parallelism (``sp_group``): tokens are sharded for everything except self-attention,
+where heads are sharded; see ``longlive_b200/sp.py``.  With ``sync_amax`` every per-tensor amax is
+MAX-reduced over the group so that codes and scales equal the single-GPU run bit for bit.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from . import ops, sp
+from .enums import ScaleRule
+from .quantize import QuantizationConfig, QuantizedTensor, quantize_to_fp4
+
+MSE = ScaleRule.mse.cuda_id()
+
+
+@dataclass
+class DiTConfig:
+    dim: int = 3072
+    ffn_dim: int = 14336
+    heads: int = 24
+    layers: int = 30
+    text_len: int = 512
+    text_dim: int = 4096
+    freq_dim: int = 256
+    grid_h: int = 22                 # post-patch latent grid (44 x 80 latent, patch 1x2x2)
+    grid_w: int = 40
+    frames_per_chunk: int = 3
+    window_frames: int = 15          # sink + local window, current chunk included
+    sink_frames: int = 3
+    in_channels: int = 48
+    eps: float = 1e-6
+
+    @property
+    def frame_tokens(self) -> int:
+        return self.grid_h * self.grid_w
+
+    @property
+    def chunk_tokens(self) -> int:
+        return self.frames_per_chunk * self.frame_tokens
+
+    @property
+    def max_blocks(self) -> int:
+        return self.window_frames // self.frames_per_chunk
+
+    @property
+    def patch_dim(self) -> int:
+        return self.in_channels * 4
+
+
+def rope_tables(cfg: DiTConfig, start_frame: int, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """cos/sin fp32 [chunk_tokens, 64] for frames start_frame.., tokens in (f, h, w) order
+    (wan_5b/modules/model.py:29-36, wan_5b/modules/causal_model.py:156-165, 1075-1081)."""
+    d = 128
+    dims = [d - 4 * (d // 6), 2 * (d // 6), 2 * (d // 6)]
+
+    def ang(pos, dim):
+        inv = 1.0 / torch.pow(10000.0, torch.arange(0, dim, 2, dtype=torch.float64) / dim)
+        return torch.outer(pos.to(torch.float64), inv)
+
+    f, h, w = cfg.frames_per_chunk, cfg.grid_h, cfg.grid_w
+    at = ang(torch.arange(start_frame, start_frame + f), dims[0])
+    ah = ang(torch.arange(h), dims[1])
+    aw = ang(torch.arange(w), dims[2])
+    full = torch.cat([at[:, None, None, :].expand(f, h, w, -1), ah[None, :, None, :].expand(f, h, w, -1),
+                      aw[None, None, :, :].expand(f, h, w, -1)], dim=-1).reshape(f * h * w, d // 2)
+    return full.cos().float().to(device).contiguous(), full.sin().float().to(device).contiguous()
+
+
+class _Linear:
+    """An NVFP4 weight [out, in] quantized once (4-over-6 MSE) plus its bf16 bias."""
+
+    def __init__(self, out_f: int, in_f: int, gen, device, std: float = 0.02):
+        w = (torch.randn(out_f, in_f, generator=gen, device=device) * std).bfloat16()
+        self.q: QuantizedTensor = quantize_to_fp4(w, QuantizationConfig(scale_rule="mse"))
+        self.bias = (torch.randn(out_f, generator=gen, device=device) * 0.02).bfloat16()
+        self.out_f, self.in_f = out_f, in_f
+        self.weight_bf16 = None
+
+    def keep_master(self, w):
+        self.weight_bf16 = w
+
+
+class _Act:
+    """A reusable NVFP4 activation buffer (codes / scales / amax) for up to ``rows`` x ``cols``."""
+
+    def __init__(self, rows: int, cols: int, device):
+        mp = ops.padded_rows(rows)
+        self.codes = torch.zeros((mp, cols // 2), dtype=torch.uint8, device=device)
+        self.sf = torch.zeros(mp * cols // 16, dtype=torch.float8_e4m3fn, device=device)
+        self.amax = torch.zeros(1, dtype=torch.float32, device=device)
+        self.rows, self.cols = rows, cols
+
+
+class Block:
+    def __init__(self, cfg: DiTConfig, gen, device):
+        c, f = cfg.dim, cfg.ffn_dim
+        self.q, self.k, self.v, self.o = (_Linear(c, c, gen, device) for _ in range(4))
+        self.cq, self.ck, self.cv, self.co = (_Linear(c, c, gen, device) for _ in range(4))
+        self.ffn0, self.ffn2 = _Linear(f, c, gen, device), _Linear(c, f, gen, device)
+        ones = lambda: (1 + 0.05 * torch.randn(c, generator=gen, device=device)).bfloat16()
+        self.norm_q, self.norm_k, self.cnorm_q, self.cnorm_k = ones(), ones(), ones(), ones()
+        self.norm3_w, self.norm3_b = ones(), (0.02 * torch.randn(c, generator=gen, device=device)).bfloat16()
+        self.modulation = (torch.randn(1, 6, c, generator=gen, device=device) / math.sqrt(c)).bfloat16()
+
+
+class KVCache:
+    """Per layer ``max_blocks`` NVFP4 slots for K and V, each [block_tokens * local_heads, 128].
+
+    ``order[layer]`` lists slot indices from oldest to newest; the last entry is the block of the
+    current chunk.  Rolling (wan_5b/modules/causal_model.py:1396-1411) permutes this table."""
+
+    def __init__(self, cfg: DiTConfig, local_heads: int, device):
+        rows = cfg.chunk_tokens * local_heads
+        mp = ops.padded_rows(rows)
+        mk = lambda: QuantizedTensor(torch.zeros((mp, 64), dtype=torch.uint8, device=device),
+                                     torch.zeros(mp * 8, dtype=torch.float8_e4m3fn, device=device),
+                                     torch.zeros(1, dtype=torch.float32, device=device), "nvfp4", (rows, 128), "mse", (mp, 128))
+        self.k = [[mk() for _ in range(cfg.max_blocks)] for _ in range(cfg.layers)]
+        self.v = [[mk() for _ in range(cfg.max_blocks)] for _ in range(cfg.layers)]
+        self.order = list(range(cfg.max_blocks))
+        self.filled = 0                       # number of valid blocks, current chunk included
+        self.cfg = cfg
+
+    def begin_chunk(self) -> None:
+        """Make room for a new chunk: grow until full, then evict the oldest non-sink block."""
+        cfg = self.cfg
+        if self.filled < cfg.max_blocks:
+            self.filled += 1
+            return
+        sink_blocks = cfg.sink_frames // cfg.frames_per_chunk
+        victim = self.order.pop(sink_blocks)
+        self.order.append(victim)
+
+    def past_slots(self) -> list[int]:
+        return self.order[: self.filled - 1]
+
+    def current_slot(self) -> int:
+        return self.order[self.filled - 1]
+
+    def bytes(self) -> int:
+        return sum(t.values.numel() + t.scale_factors.numel() + 4 for layer in self.k + self.v for t in layer)
+
+
+class CausalDiT:
+    def __init__(self, cfg: DiTConfig | None = None, device="cuda", seed: int = 0, sp_group=None, sync_amax: bool = True,
+                 cache_text_kv: bool = True):
+        self.cfg = cfg = cfg or DiTConfig()
+        self.device = torch.device(device)
+        self.group = sp_group
+        self.rank, self.P = sp.world(sp_group)
+        self.sync_amax = sync_amax and self.P > 1
+        self.cache_text_kv = cache_text_kv
+        assert cfg.chunk_tokens % self.P == 0 and cfg.heads % self.P == 0, "tokens and heads must divide by the SP size"
+        gen = torch.Generator(device=self.device).manual_seed(seed)          # same weights on every rank
+        self.blocks = [Block(cfg, gen, self.device) for _ in range(cfg.layers)]
+        c = cfg.dim
+        lin = lambda o, i: ((torch.randn(o, i, generator=gen, device=self.device) * 0.02).bfloat16(),
+                            torch.zeros(o, dtype=torch.bfloat16, device=self.device))
+        self.patch_w, self.patch_b = lin(c, cfg.patch_dim)
+        self.time_w0, self.time_b0 = lin(c, cfg.freq_dim)
+        self.time_w1, self.time_b1 = lin(c, c)
+        self.tproj_w, self.tproj_b = lin(6 * c, c)
+        self.text_w0, self.text_b0 = lin(c, cfg.text_dim)
+        self.text_w1, self.text_b1 = lin(c, c)
+        self.head_w, self.head_b = lin(cfg.patch_dim, c)
+        self.head_mod = (torch.randn(1, 2, c, generator=gen, device=self.device) / math.sqrt(c)).bfloat16()
+
+        S, Sl = cfg.chunk_tokens, cfg.chunk_tokens // self.P
+        Hl = cfg.heads // self.P
+        self.S, self.Sl, self.Hl, self.Cl = S, Sl, Hl, Hl * 128
+        dev = self.device
+        bf = lambda *shape: torch.empty(shape, dtype=torch.bfloat16, device=dev)
+        self.act_c = _Act(Sl, c, dev)            # activations with `dim` columns
+        self.act_f = _Act(Sl, cfg.ffn_dim, dev)  # FFN hidden
+        self.act_t = _Act(cfg.text_len, c, dev)  # text context
+        self.row_stats = torch.empty(2 * Sl, dtype=torch.float32, device=dev)
+        self.q_buf, self.k_buf, self.v_buf = bf(Sl, c), bf(Sl, c), bf(Sl, c)
+        self.q_rot, self.k_rot, self.k_smooth = bf(Sl, c), bf(Sl, c), bf(Sl, c)
+        self.attn_out = bf(S, self.Cl)
+        self.attn_seq = bf(Sl, c)
+        self.x_a, self.x_b, self.x1, self.x2 = bf(Sl, c), bf(Sl, c), bf(Sl, c), bf(Sl, c)
+        self.hidden = bf(Sl, cfg.ffn_dim)
+        self.cq_buf, self.cq_n = bf(Sl, c), bf(Sl, c)
+        self.ck_buf, self.cv_buf, self.ck_n = bf(cfg.text_len, c), bf(cfg.text_len, c), bf(cfg.text_len, c)
+        self.cattn = bf(Sl, c)
+        Lk = cfg.window_frames * cfg.frame_tokens
+        self.win_k, self.win_v = bf(Lk, self.Cl), bf(Lk, self.Cl)
+        self.k_amax = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.v_amax = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.h_amax = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.text_kv: list | None = None
+        self.cache = KVCache(cfg, Hl, dev)
+
+    # ---- helpers ----------------------------------------------------------------------------
+    def _gemm(self, a: _Act, rows: int, lin: _Linear, out, **epi):
+        act = a
+        return ops.gemm_nvfp4(act.codes, act.sf, act.amax, MSE, lin.q.values, lin.q.scale_factors, lin.q.amax, MSE,
+                              rows, lin.out_f, lin.in_f, out=out, bias=lin.bias, **epi)
+
+    def _quantize(self, x, act: _Act, amax_given: bool = False):
+        if self.sync_amax and not amax_given:
+            ops.amax_bf16(x, act.amax)
+            sp.allreduce_max_(act.amax, self.group)
+            amax_given = True
+        ops.quantize_nvfp4(x, MSE, act.amax, act.codes, act.sf, amax_given=amax_given)
+
+    def _adaln_quantize(self, x, scale, shift, act: _Act):
+        cfg = self.cfg
+        kw = dict(codes=act.codes, sf=act.sf, amax=act.amax, row_stats=self.row_stats, row_offset=self.rank * self.Sl)
+        if self.sync_amax:
+            ops.adaln_quantize_nvfp4(x, scale, shift, cfg.frame_tokens, MSE, cfg.eps, phase=1, **kw)
+            sp.allreduce_max_(act.amax, self.group)
+            ops.adaln_quantize_nvfp4(x, scale, shift, cfg.frame_tokens, MSE, cfg.eps, phase=2, **kw)
+        else:
+            ops.adaln_quantize_nvfp4(x, scale, shift, cfg.frame_tokens, MSE, cfg.eps, **kw)
+
+    def _ln_quantize(self, x, w, b, act: _Act):
+        kw = dict(codes=act.codes, sf=act.sf, amax=act.amax, row_stats=self.row_stats)
+        if self.sync_amax:
+            ops.layernorm_quantize_nvfp4(x, w, b, MSE, self.cfg.eps, phase=1, **kw)
+            sp.allreduce_max_(act.amax, self.group)
+            ops.layernorm_quantize_nvfp4(x, w, b, MSE, self.cfg.eps, phase=2, **kw)
+        else:
+            ops.layernorm_quantize_nvfp4(x, w, b, MSE, self.cfg.eps, **kw)
+
+    # ---- text context -------------------------------------------------------------------------
+    def encode_text(self, ctx_raw: torch.Tensor) -> torch.Tensor:
+        """[text_len, text_dim] -> [text_len, dim] (text_embedding MLP, wan_5b/modules/causal_model.py:1568-1573)."""
+        h = torch.nn.functional.gelu(torch.nn.functional.linear(ctx_raw, self.text_w0, self.text_b0), approximate="tanh")
+        self.text_kv = None
+        return torch.nn.functional.linear(h, self.text_w1, self.text_b1).contiguous()
+
+    def _text_kv(self, layer: int, blk: Block, ctx: torch.Tensor):
+        """Cross-attention K (RMS-normed) and V of the text context.  The reference recomputes them on
+        every call (causal_model.py:229-235); they depend only on the prompt, so they are cached."""
+        if self.cache_text_kv and self.text_kv is not None and self.text_kv[layer] is not None:
+            return self.text_kv[layer]
+        cfg = self.cfg
+        if layer == 0 or not self.cache_text_kv:
+            ops.quantize_nvfp4(ctx, MSE, self.act_t.amax, self.act_t.codes, self.act_t.sf, amax_given=False)
+        k = self._gemm(self.act_t, cfg.text_len, blk.ck, None if self.cache_text_kv else self.ck_buf)
+        v = self._gemm(self.act_t, cfg.text_len, blk.cv, None if self.cache_text_kv else self.cv_buf)
+        kn, _, _ = ops.rmsnorm_rope(k, blk.cnorm_k, eps=cfg.eps, out=None if self.cache_text_kv else self.ck_n)
+        if self.cache_text_kv:
+            if self.text_kv is None:
+                self.text_kv = [None] * cfg.layers
+            self.text_kv[layer] = (kn, v)
+        return kn, v
+
+    # ---- one block ----------------------------------------------------------------------------
+    def block_forward(self, li: int, x: torch.Tensor, x_out: torch.Tensor, e: torch.Tensor, ctx, cos, sin):
+        """x: [Sl, dim] bf16 (my tokens); e: [F, 6, dim] (block modulation + time projection); returns x_out."""
+        cfg, blk, cache = self.cfg, self.blocks[li], self.cache
+        Sl, S, ft = self.Sl, self.S, cfg.frame_tokens
+        roff = self.rank * Sl
+        # -- self attention
+        self._adaln_quantize(x, e[:, 1], e[:, 0], self.act_c)
+        self._gemm(self.act_c, Sl, blk.q, self.q_buf)
+        self._gemm(self.act_c, Sl, blk.k, self.k_buf)
+        n_past = len(cache.past_slots())
+        T = cfg.chunk_tokens
+        if self.P == 1:
+            v_dst = self.win_v[n_past * T:(n_past + 1) * T]
+            ks_dst = self.win_k[n_past * T:(n_past + 1) * T]
+        else:
+            v_dst, ks_dst = self.v_buf, self.k_smooth
+        self.v_amax.zero_()
+        self._gemm(self.act_c, Sl, blk.v, v_dst, out_amax=self.v_amax)
+        ops.rmsnorm_rope(x=self.q_buf, weight=blk.norm_q, cos=cos, sin=sin, eps=cfg.eps, out=self.q_rot)
+        ops.rmsnorm_rope(x=self.k_buf, weight=blk.norm_k, cos=cos, sin=sin, eps=cfg.eps, out=self.k_rot, out_smooth=ks_dst,
+                         amax_out=self.k_amax)
+        if self.P > 1:
+            if self.sync_amax:
+                sp.allreduce_max_(self.k_amax, self.group)
+                sp.allreduce_max_(self.v_amax, self.group)
+            q_h, ks_h, kr_h, v_h = sp.seq_to_head_many([self.q_rot, self.k_smooth, self.k_rot, self.v_buf], self.group)
+            self.win_k[n_past * T:(n_past + 1) * T].copy_(ks_h)
+            self.win_v[n_past * T:(n_past + 1) * T].copy_(v_h)
+            k_for_cache, v_for_cache = kr_h, v_h
+        else:
+            q_h, k_for_cache, v_for_cache = self.q_rot, self.k_rot, v_dst
+        if n_past:
+            slots = cache.past_slots()
+            ops.kv_dequant([cache.k[li][s].values for s in slots], [cache.k[li][s].scale_factors for s in slots],
+                           [cache.k[li][s].amax for s in slots], self.Hl, T, torch.bfloat16, 6, 256, ops.DEQ_FUSED,
+                           out=self.win_k[: n_past * T])
+            ops.kv_dequant([cache.v[li][s].values for s in slots], [cache.v[li][s].scale_factors for s in slots],
+                           [cache.v[li][s].amax for s in slots], self.Hl, T, torch.bfloat16, 6, 256, ops.DEQ_FUSED,
+                           out=self.win_v[: n_past * T])
+        lk = (n_past + 1) * T
+        ops.attention_bf16(q_h, self.win_k[:lk], self.win_v[:lk], self.Hl, out=self.attn_out)
+        # cache write: rotated (un-smoothed) keys and values of the chunk, straight into the slot
+        cur = cache.current_slot()
+        ck, cv = cache.k[li][cur], cache.v[li][cur]
+        ck.amax.copy_(self.k_amax)
+        cv.amax.copy_(self.v_amax)
+        ops.quantize_nvfp4(k_for_cache.reshape(S * self.Hl, 128), MSE, ck.amax, ck.values, ck.scale_factors, amax_given=True)
+        ops.quantize_nvfp4(v_for_cache.reshape(S * self.Hl, 128), MSE, cv.amax, cv.values, cv.scale_factors, amax_given=True)
+        attn = sp.head_to_seq(self.attn_out, self.group, out=self.attn_seq) if self.P > 1 else self.attn_out
+        self._quantize(attn, self.act_c)
+        x1, x2 = self.x1, self.x2
+        self._gemm(self.act_c, Sl, blk.o, x1, residual=x, gate=e[:, 2], frame_rows=ft, row_offset=roff)
+        # -- cross attention
+        self._ln_quantize(x1, blk.norm3_w, blk.norm3_b, self.act_c)
+        self._gemm(self.act_c, Sl, blk.cq, self.cq_buf)
+        ops.rmsnorm_rope(self.cq_buf, blk.cnorm_q, eps=cfg.eps, out=self.cq_n)
+        kn, v = self._text_kv(li, blk, ctx)
+        ops.attention_bf16(self.cq_n, kn, v, cfg.heads, out=self.cattn)
+        self._quantize(self.cattn, self.act_c)
+        self._gemm(self.act_c, Sl, blk.co, x2, residual=x1)
+        # -- FFN
+        self._adaln_quantize(x2, e[:, 4], e[:, 3], self.act_c)
+        self.h_amax.zero_()
+        self._gemm(self.act_c, Sl, blk.ffn0, self.hidden, act=1, out_amax=self.h_amax)
+        if self.sync_amax:
+            sp.allreduce_max_(self.h_amax, self.group)
+        self.act_f.amax.copy_(self.h_amax)
+        ops.quantize_nvfp4(self.hidden, MSE, self.act_f.amax, self.act_f.codes, self.act_f.sf, amax_given=True)
+        self._gemm(self.act_f, Sl, blk.ffn2, x_out, residual=x2, gate=e[:, 5], frame_rows=ft, row_offset=roff)
+        return x_out
+
+    # ---- whole model ----------------------------------------------------------------------------
+    def time_embed(self, t: torch.Tensor):
+        """t: [F] timesteps -> (e [F, dim], e0 [F, 6, dim]) (causal_model.py:1561-1564)."""
+        cfg = self.cfg
+        half = cfg.freq_dim // 2
+        freqs = torch.pow(10000.0, -torch.arange(half, device=self.device, dtype=torch.float64) / half)
+        ang = t.to(torch.float64)[:, None] * freqs[None]
+        emb = torch.cat([ang.cos(), ang.sin()], dim=1).to(torch.bfloat16)
+        lin = torch.nn.functional.linear
+        e = lin(torch.nn.functional.silu(lin(emb, self.time_w0, self.time_b0)), self.time_w1, self.time_b1)
+        e0 = lin(torch.nn.functional.silu(e), self.tproj_w, self.tproj_b).view(-1, 6, cfg.dim)
+        return e, e0
+
+    def forward(self, latent_tokens: torch.Tensor, t: torch.Tensor, ctx: torch.Tensor, start_frame: int) -> torch.Tensor:
+        """latent_tokens: [Sl, patch_dim] (my token shard of the patchified chunk) -> [Sl, patch_dim]."""
+        cfg = self.cfg
+        x = torch.nn.functional.linear(latent_tokens, self.patch_w, self.patch_b)
+        self.x_a.copy_(x)
+        e, e0 = self.time_embed(t)
+        cos, sin = rope_tables(cfg, start_frame, self.device)
+        if self.P > 1:
+            cos = cos[self.rank * self.Sl:(self.rank + 1) * self.Sl].contiguous()
+            sin = sin[self.rank * self.Sl:(self.rank + 1) * self.Sl].contiguous()
+        cur, nxt = self.x_a, self.x_b
+        for li, blk in enumerate(self.blocks):
+            em = (blk.modulation + e0).contiguous()                    # [F, 6, dim], causal_model.py:863
+            self.block_forward(li, cur, nxt, em, ctx, cos, sin)
+            cur, nxt = nxt, cur
+        # head: LayerNorm, modulate with (head.modulation + e), project (causal_model.py:1648)
+        hm = (self.head_mod + e.unsqueeze(1)).float()                   # [F, 2, dim]
+        frame = (torch.arange(self.Sl, device=self.device) + self.rank * self.Sl) // cfg.frame_tokens
+        xn = torch.nn.functional.layer_norm(cur.float(), (cfg.dim,), eps=cfg.eps)
+        y = (xn * (1 + hm[frame, 1]) + hm[frame, 0]).bfloat16()
+        return torch.nn.functional.linear(y, self.head_w, self.head_b)
+
+    def run_chunk(self, latent_tokens: torch.Tensor, ctx: torch.Tensor, chunk_index: int,
+                  timesteps=(999, 937, 833, 624)) -> torch.Tensor:
+        """One AR chunk: 4 denoising forwards + 1 clean re-cache forward
+        (pipeline/causal_diffusion_inference.py:567-647).  The scheduler update between steps is a
+        plain flow-matching Euler step (the UniPC solver is outside the hot path)."""
+        cfg = self.cfg
+        self.cache.begin_chunk()
+        start_frame = chunk_index * cfg.frames_per_chunk
+        x_t = latent_tokens
+        F = cfg.frames_per_chunk
+        sig = [t / 1000.0 for t in timesteps] + [0.0]
+        for i, t in enumerate(timesteps):
+            tt = torch.full((F,), float(t), device=self.device)
+            flow = self.forward(x_t, tt, ctx, start_frame)
+            x_t = (x_t.float() + (sig[i + 1] - sig[i]) * flow.float()).bfloat16()
+        self.forward(x_t, torch.zeros(F, device=self.device), ctx, start_frame)
+        return x_t

@@ -83,7 +83,7 @@ def _quant_outputs(x, m, c, codes, sf, amax):
 
 
 def adaln_quantize_nvfp4(x, scale, shift, frame_rows, rule_id, eps=1e-6, add_one=True, *, want_y=False, codes=None,
-                         sf=None, amax=None, row_stats=None):
+                         sf=None, amax=None, row_stats=None, row_offset=0, phase=0):
     """LayerNorm(no affine) -> (1 + scale[f]) * x + shift[f] (bf16 rounding points of the reference)
     fused with the NVFP4 quantize of the result.  x: bf16 [M, C]; scale/shift: bf16 [F, C] views
     (row stride free).  Returns (codes, sf, amax, y or None)."""
@@ -98,15 +98,15 @@ def adaln_quantize_nvfp4(x, scale, shift, frame_rows, rule_id, eps=1e-6, add_one
         row_stats = torch.empty(2 * max(m, 1), dtype=torch.float32, device=x.device)
     y = torch.empty((m, c), dtype=torch.bfloat16, device=x.device) if want_y else None
     with torch.cuda.device(x.device):
-        _check(_lib.lib().llnv_adaln_quantize_nvfp4(
+        _check(_lib.lib().llnv_adaln_quantize_nvfp4_ex(
             x.data_ptr(), m, c, x.stride(0), scale.data_ptr(), shift.data_ptr(), scale.stride(0), int(frame_rows), float(eps),
             1 if add_one else 0, rule_id, codes.data_ptr(), sf.data_ptr(), amax.data_ptr(),
-            y.data_ptr() if y is not None else None, c, row_stats.data_ptr(), _stream(x)))
+            y.data_ptr() if y is not None else None, c, row_stats.data_ptr(), int(row_offset), int(phase), _stream(x)))
     return codes, sf, amax, y
 
 
 def layernorm_quantize_nvfp4(x, weight, bias, rule_id, eps=1e-6, *, want_y=False, codes=None, sf=None, amax=None,
-                             row_stats=None):
+                             row_stats=None, phase=0):
     """Affine LayerNorm fused with the NVFP4 quantize of its output.  Returns (codes, sf, amax, y or None)."""
     _require_cuda(x, "x")
     if x.dim() != 2 or x.dtype != torch.bfloat16 or x.stride(1) != 1:
@@ -117,9 +117,10 @@ def layernorm_quantize_nvfp4(x, weight, bias, rule_id, eps=1e-6, *, want_y=False
         row_stats = torch.empty(2 * max(m, 1), dtype=torch.float32, device=x.device)
     y = torch.empty((m, c), dtype=torch.bfloat16, device=x.device) if want_y else None
     with torch.cuda.device(x.device):
-        _check(_lib.lib().llnv_layernorm_quantize_nvfp4(
+        _check(_lib.lib().llnv_layernorm_quantize_nvfp4_ex(
             x.data_ptr(), m, c, x.stride(0), weight.data_ptr(), bias.data_ptr(), float(eps), rule_id, codes.data_ptr(),
-            sf.data_ptr(), amax.data_ptr(), y.data_ptr() if y is not None else None, c, row_stats.data_ptr(), _stream(x)))
+            sf.data_ptr(), amax.data_ptr(), y.data_ptr() if y is not None else None, c, row_stats.data_ptr(), int(phase),
+            _stream(x)))
     return codes, sf, amax, y
 
 
@@ -214,7 +215,7 @@ def kv_dequant(values, scale_factors, amax, num_heads, block_token_size, dtype, 
 
 
 def gemm_nvfp4(a_codes, a_sf, a_amax, a_rule, b_codes, b_sf, b_amax, b_rule, m, n, k, *, out=None, alpha=None,
-               bias=None, act=0, residual=None, gate=None, frame_rows=0, out_amax=None):
+               bias=None, act=0, residual=None, gate=None, frame_rows=0, out_amax=None, row_offset=0):
     """``epilogue(alpha * A @ B^T)`` -> bf16 [m, n]; see ``llnv_gemm_nvfp4`` in include/llnvfp4.h."""
     _require_cuda(a_codes, "a_codes")
     dev = a_codes.device
@@ -231,6 +232,7 @@ def gemm_nvfp4(a_codes, a_sf, a_amax, a_rule, b_codes, b_sf, b_amax, b_rule, m, 
         epi.gate = gate.data_ptr()
         epi.gate_stride = gate.stride(0)
         epi.frame_rows = int(frame_rows)
+        epi.row_offset = int(row_offset)
     epi.out_amax = out_amax.data_ptr() if out_amax is not None else None
     with torch.cuda.device(dev):
         _check(_lib.lib().llnv_gemm_nvfp4(a_codes.data_ptr(), a_sf.data_ptr(),

@@ -1,0 +1,92 @@
+"""One causal DiT block (and two consecutive chunks through the rolling NVFP4 cache) against the
+CPU oracle composition, on a reduced configuration (dim 256, 2 heads, FFN 512, 24 tokens/frame).
+
+Tolerance: every stage matches its oracle to within a bf16 ulp, but a one-ulp difference ahead of
+a quantizer can flip an E2M1 code (a ~6 % change of that element), so block outputs are compared
+with a relative Frobenius error <= 3e-2 and <= 1 % of elements outside 8 bf16 ulps + 2^-5 mean|ref|."""
+import numpy as np
+import pytest
+import torch
+
+from longlive_b200 import dit, ops
+from oracle import dit_oracle as DO
+from oracle import nvfp4_oracle as O
+from tests import util
+
+pytestmark = pytest.mark.gpu
+
+CFG = dict(dim=256, ffn_dim=512, heads=2, layers=1, text_len=128, text_dim=64, freq_dim=32, grid_h=4, grid_w=6,
+           frames_per_chunk=3, window_frames=9, sink_frames=3, in_channels=4)
+
+
+def trip(qt):
+    return qt.values.cpu().numpy(), util.u8(qt.scale_factors), np.float32(qt.amax.item())
+
+
+def params_of(blk, ffn_dim):
+    f = lambda t: t.float().cpu().numpy()
+    p = {"ffn_dim": ffn_dim}
+    for name in ("q", "k", "v", "o", "cq", "ck", "cv", "co", "ffn0", "ffn2"):
+        lin = getattr(blk, name)
+        p[name] = trip(lin.q)
+        p[name + "_b"] = f(lin.bias)
+    for name in ("norm_q", "norm_k", "cnorm_q", "cnorm_k", "norm3_w", "norm3_b"):
+        p[name] = f(getattr(blk, name))
+    return p
+
+
+def close(got, ref, rel_tol=3e-2):
+    got = got.float().cpu().numpy().reshape(ref.shape)
+    rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
+    assert rel <= rel_tol, rel
+    tol = np.abs(ref) * 2.0 ** -4 + 2.0 ** -5 * np.abs(ref).mean()
+    assert (np.abs(got - ref) > tol).mean() < 0.01
+
+
+def test_block_and_cache_roll_vs_oracle():
+    cfg = dit.DiTConfig(**CFG)
+    model = dit.CausalDiT(cfg, seed=3)
+    blk = model.blocks[0]
+    p = params_of(blk, cfg.ffn_dim)
+    g = torch.Generator().manual_seed(5)
+    S, C, F = cfg.chunk_tokens, cfg.dim, cfg.frames_per_chunk
+    ctx = torch.randn(cfg.text_len, C, generator=g).bfloat16()
+    ctx_kn, ctx_v = DO.text_kv(ctx.float().numpy(), p, cfg.heads)
+    past_k, past_v = [], []
+    for chunk in range(4):                       # window of 3 blocks: the 4th chunk evicts the first non-sink block
+        x = (torch.randn(S, C, generator=g) * 1.5).bfloat16()
+        e = (blk.modulation.cpu() + torch.randn(F, 6, C, generator=g).bfloat16() * 0.3).contiguous()
+        cos, sin = dit.rope_tables(cfg, chunk * F, "cuda")
+        model.cache.begin_chunk()
+        out = model.block_forward(0, x.cuda(), model.x_b, e.cuda(), ctx.cuda(), cos, sin)
+        torch.cuda.synchronize()
+        ref, nk, nv = DO.block_forward(x.float().numpy(), e.float().numpy(), p, ctx_kn, ctx_v, cos.cpu().numpy(),
+                                       sin.cpu().numpy(), past_k, past_v, cfg.heads, cfg.frame_tokens, cfg.chunk_tokens)
+        close(out, ref)
+        # the cache block written by the kernels dequantizes to (nearly) what the oracle's block holds
+        cur = model.cache.current_slot()
+        got_k = ops.kv_dequant([model.cache.k[0][cur].values], [model.cache.k[0][cur].scale_factors],
+                               [model.cache.k[0][cur].amax], cfg.heads, S, torch.bfloat16, 6, 256)
+        ref_k = O.dequantize_kv_cache([nk], cfg.heads, S)
+        close(got_k, ref_k, rel_tol=2e-2)
+        # oracle-side cache bookkeeping: sink block + the newest (max_blocks - 2) blocks + current
+        past_k.append(nk)
+        past_v.append(nv)
+        if len(past_k) > cfg.max_blocks - 1:
+            del past_k[1], past_v[1]
+    assert model.cache.order != list(range(cfg.max_blocks))     # the block table was permuted, no slot copies
+
+
+def test_full_model_chunk_runs_and_fills_cache():
+    cfg = dit.DiTConfig(**{**CFG, "layers": 2})
+    model = dit.CausalDiT(cfg, seed=1)
+    g = torch.Generator().manual_seed(2)
+    ctx = model.encode_text(torch.randn(cfg.text_len, cfg.text_dim, generator=g).bfloat16().cuda())
+    for chunk in range(2):
+        lat = torch.randn(cfg.chunk_tokens, cfg.patch_dim, generator=g).bfloat16().cuda()
+        x = model.run_chunk(lat, ctx, chunk)
+        assert x.shape == lat.shape and torch.isfinite(x.float()).all()
+    assert model.cache.filled == 2
+    for layer in range(cfg.layers):
+        for slot in model.cache.order[:2]:
+            assert float(model.cache.k[layer][slot].amax.item()) > 0 and int(model.cache.k[layer][slot].values.max().item()) > 0
