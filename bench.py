@@ -301,6 +301,12 @@ def run_gpu_arm(args):
     e2e_value = fl_step * world / e2e_s / 1e12
     clocks = sampler.stop() if rank == 0 else {}
 
+    dit_chunk = None
+    if not args.no_dit:
+        del flush
+        torch.cuda.empty_cache()
+        dit_chunk = bench_dit_chunk(dev, rank, world, dist.group.WORLD if world > 1 else None, args.chunk_steps)
+
     if rank == 0:
         peaks = load_peaks()
         fp4_peak = 4.0 * peaks["bf16_tflops"]
@@ -324,6 +330,8 @@ def run_gpu_arm(args):
                          "kernel": "gemm_nvfp4_kernel", "frac_of_nominal_9pf": per_gpu / 9000.0},
             "wall_s_timed_region": wall,
         }
+        if dit_chunk is not None:
+            line["dit_chunk"] = dit_chunk
         if world == 1 and not args.no_cpu_baseline:
             sample = [s for s in sweep_shapes((880,)) if s[0] in ("self_attn.q", "cross_attn.k", "ffn.0")]
             v, dt, desc = cpu_port_tflops(sample)
@@ -333,6 +341,55 @@ def run_gpu_arm(args):
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def bench_dit_chunk(dev, rank, world, group, steps: int):
+    """Second headline of the benchmark: one AR chunk (3 latent frames, 4 denoising forwards + 1
+    clean re-cache forward) of the 30-layer random-init Wan2.2-5B-shaped causal DiT with NVFP4
+    W4A4 linears and the NVFP4 KV cache in steady state (full 15-frame window).  With N > 1 ranks
+    the chunk is sequence-parallel over the N GPUs (tokens sharded, heads sharded inside
+    self-attention, NCCL all-to-all at the attention boundary): strong scaling.  DiT only (no T5,
+    no VAE); video fps = 4 * 3 latent frames / chunk time."""
+    import torch
+    import torch.distributed as dist
+
+    from longlive_b200 import _lib, dit
+
+    cfg = dit.DiTConfig()
+    model = dit.CausalDiT(cfg, device=dev, seed=0, sp_group=group, sync_amax=True)
+    gen = torch.Generator(device=dev).manual_seed(7)
+    ctx = model.encode_text(torch.randn(cfg.text_len, cfg.text_dim, generator=gen, device=dev).bfloat16())
+    lat_full = torch.randn(cfg.chunk_tokens, cfg.patch_dim, generator=gen, device=dev).bfloat16()
+    sl = cfg.chunk_tokens // world
+    lat = lat_full[rank * sl:(rank + 1) * sl].contiguous()
+    chunk = 0
+    for _ in range(cfg.max_blocks + 1):            # fill the window, then one more chunk to reach the rolling state
+        model.run_chunk(lat, ctx, chunk)
+        chunk += 1
+    torch.cuda.synchronize(dev)
+    if world > 1:
+        dist.barrier()
+    times = []
+    for _ in range(steps):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        model.run_chunk(lat, ctx, chunk)
+        e.record()
+        torch.cuda.synchronize(dev)
+        times.append(s.elapsed_time(e))
+        chunk += 1
+    assert _lib.lib().llnv_check_status(None) == 0, _lib.lib().llnv_last_error()
+    ms = statistics.median(times)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return {"metric": "dit_chunk_video_fps", "value": 12.0 / (ms * 1e-3), "unit": "frames/s", "latent_fps": 3.0 / (ms * 1e-3),
+            "ms_per_chunk": ms, "chunks_timed": steps, "layers": cfg.layers, "forwards_per_chunk": 5,
+            "window_tokens": cfg.window_frames * cfg.frame_tokens, "chunk_tokens": cfg.chunk_tokens,
+            "parallelism": f"sequence-parallel over {world} GPU(s)" if world > 1 else "single GPU",
+            "amax_sync": world > 1, "scaling": "strong", "kv_cache_bytes_per_rank": model.cache.bytes(),
+            "data": "synthetic, random-init weights"}
 
 
 def run_kernel_case(spec: str, iters: int):
@@ -425,6 +482,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-dit", action="store_true", help="skip the 30-layer DiT chunk measurement")
+    ap.add_argument("--chunk-steps", type=int, default=3)
     args = ap.parse_args()
     if args.kernel_case:
         run_kernel_case(args.kernel_case, args.iters)
