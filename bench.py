@@ -324,7 +324,11 @@ def run_gpu_arm(args):
                     "steps": e2e_steps, "ms_per_step": e2e_s * 1e3},
             "gpu_launches": len(shapes) * args.steps,
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": fp4_peak, "unit": "TFLOP/s",
-                         "frac": per_gpu / fp4_peak, "traffic": None,
+                         "frac": per_gpu / fp4_peak,
+                         "traffic": 53.5e6, "traffic_case": "dram read+write of one captured launch, M=2640 N=14336 K=3072 "
+                                                            "(profiles/gemm_nvfp4_kernel__2640x14336x3072.md); algorithmic "
+                                                            "operand+output bytes of that launch: 105 MB, of which 52 MB of output "
+                                                            "stay dirty in L2",
                          "peak_note": f"4 x {peaks['source']} dense bf16 burst peak ({peaks['bf16_tflops']} TFLOP/s); "
                                       "no FP4 entry is measured; nominal dense FP4 is 9000",
                          "kernel": "gemm_nvfp4_kernel", "frac_of_nominal_9pf": per_gpu / 9000.0},
