@@ -4,20 +4,23 @@
 //
 //   O[q, h, :] = softmax_k( Q[q, h, :] . K[k, h, :] * scale ) V[k, h, :]
 //
-// One CTA per (128-query tile, head), 6 warps:
-//   warp 0     TMA producer: the Q tile once, then K and V tiles of 128 keys (two 64-channel halves
-//              each, 128-byte swizzle), two stages.
-//   warp 1     MMA issuer / TMEM owner.  S_j = Q K_j^T (8 MMAs, K = 16 channels each, both operands
-//              K-major from shared memory) into one of two score buffers; O += P_j V_j (8 MMAs,
-//              K = 16 keys each; P read from tensor memory, V MN-major from shared memory).
-//              Issue order  S_0, S_1, { PV_j, S_{j+2} }  keeps the tensor pipe busy while the
-//              softmax of tile j runs.
-//   warps 2-5  softmax: thread = query row.  Reads S_j with tcgen05.ld, keeps the running row
-//              maximum and sum, writes P_j as packed bf16 over the first 64 columns of the same
-//              score buffer (tcgen05.st).  The output accumulator is rescaled lazily: only when
-//              a row maximum grows by more than 2^8 is O multiplied by exp2(m_old - m_new), so in
-//              steady state O is touched only by the tensor pipe.  After the last tile the same
-//              warps normalise O and store it through swizzled shared memory with TMA.
+// One CTA per (256-query tile, head), 10 warps.  The tile is processed as two independent
+// 128-query halves that share the K/V tiles; each half has its own score / output accumulator
+// (S_h, O_h: 4 x 128 columns = the whole tensor memory) and its own softmax warpgroup, so that
+// the tensor pipe works on one half while the other half is in its softmax:
+//   warp 0     TMA producer: both Q halves once, then K and V tiles of 128 keys (two 64-channel
+//              halves each, 128-byte swizzle), two stages.
+//   warp 1     MMA issuer / TMEM owner.  S_h = Q_h K_j^T (8 MMAs, K = 16 channels, operands K-major
+//              in shared memory); O_h += P_h V_j (8 MMAs, K = 16 keys; P read from tensor memory
+//              where it overwrote S_h, V MN-major in shared memory).  Issue order per key tile:
+//              PV_a(j), S_a(j+1), PV_b(j), S_b(j+1).
+//   warps 2-5  softmax of half a, warps 6-9 softmax of half b: thread = query row.  Reads S with
+//              tcgen05.ld, keeps the running row maximum and sum, writes P as packed bf16 over the
+//              first 64 columns of the score buffer (tcgen05.st).  The output accumulator is
+//              rescaled lazily: only when a row maximum grows by more than 2^8 is O multiplied by
+//              exp2(m_old - m_new), so in steady state O is touched only by the tensor pipe.
+//              After the last tile the same warps normalise O and store it through swizzled
+//              shared memory (the Q tile's buffer) with TMA.
 // All mbarrier waits are bounded (sm100.cuh).
 #include <cuda.h>
 
@@ -30,19 +33,20 @@ namespace {
 using namespace sm100;
 
 constexpr int kD = 128;            // head dim
-constexpr int kBQ = 128;           // queries per CTA
+constexpr int kBQ = 256;           // queries per CTA (two halves of 128)
+constexpr int kHQ = 128;           // queries per half
 constexpr int kBK = 128;           // keys per tile
 constexpr int kStages = 2;
 constexpr uint32_t kHalfBytes = 128 * 128;        // 128 rows x 64 bf16
 constexpr uint32_t kTileBytes = 2 * kHalfBytes;   // 32 KiB
 constexpr uint32_t kQOff = 0;
-constexpr uint32_t kKOff = kTileBytes;
+constexpr uint32_t kKOff = 2 * kTileBytes;
 constexpr uint32_t kVOff = kKOff + kStages * kTileBytes;
 constexpr uint32_t kBarOff = kVOff + kStages * kTileBytes;
 constexpr uint32_t kSmemBytes = kBarOff + 1024;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kSCol0 = 0, kSCol1 = 128, kOCol = 256;
-constexpr int kThreads = 192;
+constexpr uint32_t kSCol = 0, kOCol = 256;      // S_h at kSCol + 128 h, O_h at kOCol + 128 h
+constexpr int kThreads = 320;
 
 struct AttnParams {
   int64_t Lq, Lk;
@@ -51,12 +55,18 @@ struct AttnParams {
   unsigned int* status;
 };
 
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 
+// 10 warps put three warps on some schedulers, whose 16 K-register files then allow 168 registers per thread
 __global__ void __launch_bounds__(kThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const AttnParams p) {
@@ -66,15 +76,16 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* k_empty = k_full + kStages;
   uint64_t* v_full = k_empty + kStages;
   uint64_t* v_empty = v_full + kStages;
-  uint64_t* s_full = v_empty + kStages;        // [2]
-  uint64_t* p_ready = s_full + 2;              // [2]
-  uint64_t* pv_done = p_ready + 2;             // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
+  uint64_t* s_full = v_empty + kStages;        // [2 halves]
+  uint64_t* p_ready = s_full + 2;              // [2 halves]
+  uint64_t* pv_done = p_ready + 2;             // [2 halves]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qt = blockIdx.x, head = blockIdx.y;
   const int nt = (int)((p.Lk + kBK - 1) / kBK);
+  const int n_half = ((int64_t)qt * kBQ + kHQ < p.Lq) ? 2 : 1;     // the second half may lie entirely beyond Lq
 
   if ((smem_u32(smem) & 1023u) != 0) {
     if (threadIdx.x == 0 && p.status && atomicCAS(p.status, 0u, 2u) == 0u) p.status[1] = 901u;
@@ -91,8 +102,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
       mbar_init(&p_ready[i], 4);
+      mbar_init(&pv_done[i], 1);
     }
-    mbar_init(pv_done, 1);
     *abort_flag = 0u;
     fence_barrier_init();
     prefetch_tensormap(&tmQ);
@@ -113,9 +124,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
       const int col = head * kD;
-      mbar_arrive_expect_tx(q_full, kTileBytes);
-      tma_load_2d(smem + kQOff, &tmQ, col, qt * kBQ, q_full);
-      tma_load_2d(smem + kQOff + kHalfBytes, &tmQ, col + 64, qt * kBQ, q_full);
+      mbar_arrive_expect_tx(q_full, n_half * kTileBytes);
+      for (int h = 0; h < n_half; ++h) {
+        tma_load_2d(smem + kQOff + h * kTileBytes, &tmQ, col, qt * kBQ + h * kHQ, q_full);
+        tma_load_2d(smem + kQOff + h * kTileBytes + kHalfBytes, &tmQ, col + 64, qt * kBQ + h * kHQ, q_full);
+      }
       for (int j = 0; j < nt; ++j) {
         const int s = j % kStages;
         const uint32_t ph = (uint32_t)((j / kStages) & 1);
@@ -132,80 +145,97 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (elect_one()) {
-      constexpr uint32_t idesc_qk = make_idesc_bf16(kBQ, kBK, 0, 0);     // A, B K-major
-      constexpr uint32_t idesc_pv = make_idesc_bf16(kBQ, kD, 0, 1);      // B (V) MN-major
-      const uint32_t q_addr = smem_u32(smem + kQOff);
+      constexpr uint32_t idesc_qk = make_idesc_bf16(kHQ, kBK, 0, 0);     // A, B K-major
+      constexpr uint32_t idesc_pv = make_idesc_bf16(kHQ, kD, 0, 1);      // B (V) MN-major
 
-      auto issue_qk = [&](int t) {
+      auto issue_qk = [&](int t, int h) {
         const int s = t % kStages;
-        mbar_wait(&k_full[s], (uint32_t)((t / kStages) & 1), abort_flag, p.status, 200u);
-        tc_fence_after();
+        const uint32_t q_addr = smem_u32(smem + kQOff + h * kTileBytes);
         const uint32_t k_addr = smem_u32(smem + kKOff + s * kTileBytes);
-        const uint32_t d_tmem = tmem_base + ((t & 1) ? kSCol1 : kSCol0);
+        const uint32_t d_tmem = tmem_base + kSCol + 128 * h;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           // 16 channels per MMA: 32 bytes along the swizzled 128-byte row, second half after 4 steps
           const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
           mma_f16_ss(d_tmem, make_kmajor_sw128_desc(q_addr + off), make_kmajor_sw128_desc(k_addr + off), idesc_qk, ks != 0);
         }
-        tc_commit(&k_empty[s]);
-        tc_commit(&s_full[t & 1]);
+        tc_commit(&s_full[h]);
+        if (h == n_half - 1) tc_commit(&k_empty[s]);
       };
 
       mbar_wait(q_full, 0u, abort_flag, p.status, 201u);
-      issue_qk(0);
-      if (nt > 1) issue_qk(1);
+      mbar_wait(&k_full[0], 0u, abort_flag, p.status, 200u);
+      tc_fence_after();
+      for (int h = 0; h < n_half; ++h) issue_qk(0, h);
       for (int j = 0; j < nt; ++j) {
         const int s = j % kStages;
         const uint32_t ph = (uint32_t)((j / kStages) & 1);
-        mbar_wait(&p_ready[j & 1], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 202u);
         mbar_wait(&v_full[s], ph, abort_flag, p.status, 203u);
-        tc_fence_after();
         const uint32_t v_addr = smem_u32(smem + kVOff + s * kTileBytes);
-        const uint32_t p_tmem = tmem_base + ((j & 1) ? kSCol1 : kSCol0);
+        for (int h = 0; h < n_half; ++h) {
+          mbar_wait(&p_ready[h], (uint32_t)(j & 1), abort_flag, p.status, 202u);
+          tc_fence_after();
+          const uint32_t p_tmem = tmem_base + kSCol + 128 * h;
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          // 16 keys per MMA: P columns 8*ks..8*ks+7 (two bf16 per column), V rows 16*ks.. (2048 bytes apart)
-          // V is MN-major: 64 channels contiguous per key row, the second 64 channels one half-tile further
-          const uint64_t v_desc = make_smem_desc(v_addr + ks * 2048, kHalfBytes, 1024, 2);
-          mma_f16_ts(tmem_base + kOCol, p_tmem + 8 * ks, v_desc, idesc_pv, (j | ks) != 0);
+          for (int ks = 0; ks < 8; ++ks) {
+            // 16 keys per MMA: P columns 8*ks..8*ks+7 (two bf16 per column), V rows 16*ks.. (2048 bytes apart)
+            // V is MN-major: 64 channels contiguous per key row, the second 64 channels one half-tile further
+            const uint64_t v_desc = make_smem_desc(v_addr + ks * 2048, kHalfBytes, 1024, 2);
+            mma_f16_ts(tmem_base + kOCol + 128 * h, p_tmem + 8 * ks, v_desc, idesc_pv, (j | ks) != 0);
+          }
+          tc_commit(&pv_done[h]);
+          if (h == n_half - 1) tc_commit(&v_empty[s]);
+          if (j + 1 < nt) {
+            if (h == 0) {
+              mbar_wait(&k_full[(j + 1) % kStages], (uint32_t)(((j + 1) / kStages) & 1), abort_flag, p.status, 204u);
+              tc_fence_after();
+            }
+            issue_qk(j + 1, h);
+          }
         }
-        tc_commit(&v_empty[s]);
-        tc_commit(pv_done);
-        if (j + 2 < nt) issue_qk(j + 2);
       }
     }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
     const int q = warp & 3;
+    const int half = warp >= 6 ? 1 : 0;
     const uint32_t lane_base = (uint32_t)(q * 32) << 16;
     const float c = p.scale_log2;
+    if (half < n_half) {
     float m = -INFINITY;          // running maximum of raw scores used as the exponent offset
     float l = 0.f;                // running sum of exp
     for (int j = 0; j < nt; ++j) {
-      const uint32_t s_tmem = tmem_base + lane_base + ((j & 1) ? kSCol1 : kSCol0);
-      mbar_wait(&s_full[j & 1], (uint32_t)((j >> 1) & 1), abort_flag, p.status, 300u);
+      const uint32_t s_tmem = tmem_base + lane_base + kSCol + 128 * half;
+      mbar_wait(&s_full[half], (uint32_t)(j & 1), abort_flag, p.status, 300u);
       tc_fence_after();
       uint32_t sr[4][32];
 #pragma unroll
       for (int g = 0; g < 4; ++g) tmem_ld32(s_tmem + 32 * g, sr[g]);
       tmem_ld_wait();
       const int valid = (int)min((int64_t)kBK, p.Lk - (int64_t)j * kBK);
-      float mt = -INFINITY;
+      if (valid < kBK) {                               // only the last key tile can be ragged
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int nv = valid - 32 * g;                // valid columns of this group of 32
+          const uint32_t keep = nv >= 32 ? 0xFFFFFFFFu : (nv <= 0 ? 0u : ((1u << nv) - 1u));
+#pragma unroll
+          for (int i = 0; i < 32; ++i) sr[g][i] = ((keep >> i) & 1u) ? sr[g][i] : 0xFF800000u;      // -inf
+        }
+      }
+      // row maximum with eight independent chains
+      float mx[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mx[i] = -INFINITY;
 #pragma unroll
       for (int g = 0; g < 4; ++g)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float sv = __uint_as_float(sr[g][i]);
-          if (g * 32 + i >= valid) sv = -INFINITY;
-          sr[g][i] = __float_as_uint(sv);
-          mt = fmaxf(mt, sv);
-        }
+        for (int i = 0; i < 32; ++i) mx[i & 7] = fmaxf(mx[i & 7], __uint_as_float(sr[g][i]));
+      const float mt = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
       // lazy rescale: keep the old offset unless this tile's maximum exceeds it by more than 2^8
       const bool grow = (mt - m) * c > 8.f;           // also true for the first tile (m = -inf)
       if (__any_sync(0xFFFFFFFFu, grow && j > 0)) {
         // all PV products issued so far must have landed in O before it is rescaled
-        mbar_wait(pv_done, (uint32_t)((j - 1) & 1), abort_flag, p.status, 301u);
+        mbar_wait(&pv_done[half], (uint32_t)((j - 1) & 1), abort_flag, p.status, 301u);
         tc_fence_after();
         const float m_new = grow ? mt : m;
         const float alpha = ex2((m - m_new) * c);
@@ -214,53 +244,50 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll 1
         for (int g = 0; g < 4; ++g) {
           uint32_t o[32];
-          tmem_ld32(tmem_base + lane_base + kOCol + 32 * g, o);
+          tmem_ld32(tmem_base + lane_base + kOCol + 128 * half + 32 * g, o);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st32(tmem_base + lane_base + kOCol + 32 * g, o);
+          tmem_st32(tmem_base + lane_base + kOCol + 128 * half + 32 * g, o);
         }
         tmem_st_wait();
       } else if (grow) {
         m = mt;                                        // first tile: nothing accumulated yet
       }
       const float mc = m * c;
-      float rs = 0.f;
-      uint32_t pk[64];
+      float rsum[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t pk0[32], pk1[32];
 #pragma unroll
       for (int g = 0; g < 4; ++g)
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           const float p0 = ex2(__fmaf_rn(__uint_as_float(sr[g][i]), c, -mc));
           const float p1 = ex2(__fmaf_rn(__uint_as_float(sr[g][i + 1]), c, -mc));
-          rs += p0 + p1;
-          const __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
-          pk[(g * 32 + i) >> 1] = *reinterpret_cast<const uint32_t*>(&b2);
+          rsum[(i >> 1) & 3] += p0 + p1;
+          const uint32_t packed = pack2(p0, p1);
+          if (g < 2) pk0[(g * 32 + i) >> 1] = packed; else pk1[((g - 2) * 32 + i) >> 1] = packed;
         }
+      const float rs = (rsum[0] + rsum[1]) + (rsum[2] + rsum[3]);
       l += rs;
-      {
-        uint32_t(&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pk[0]);
-        uint32_t(&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pk[32]);
-        tmem_st32(s_tmem, lo);
-        tmem_st32(s_tmem + 32, hi);
-      }
+      tmem_st32(s_tmem, pk0);
+      tmem_st32(s_tmem + 32, pk1);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_ready[j & 1]);
+      if (lane == 0) mbar_arrive(&p_ready[half]);
     }
     // ---- epilogue: O / l -> bf16 -> swizzled staging (the Q tile's shared memory) -> TMA store
-    mbar_wait(pv_done, (uint32_t)((nt - 1) & 1), abort_flag, p.status, 302u);
+    mbar_wait(&pv_done[half], (uint32_t)((nt - 1) & 1), abort_flag, p.status, 302u);
     tc_fence_after();
     const float inv_l = 1.f / l;
-    const int row0 = qt * kBQ + q * 32;
+    const int row0 = qt * kBQ + half * kHQ + q * 32;
 #pragma unroll 1
-    for (int half = 0; half < 2; ++half) {
+    for (int dh = 0; dh < 2; ++dh) {
       uint32_t o[2][32];
-      tmem_ld32(tmem_base + lane_base + kOCol + 64 * half, o[0]);
-      tmem_ld32(tmem_base + lane_base + kOCol + 64 * half + 32, o[1]);
+      tmem_ld32(tmem_base + lane_base + kOCol + 128 * half + 64 * dh, o[0]);
+      tmem_ld32(tmem_base + lane_base + kOCol + 128 * half + 64 * dh + 32, o[1]);
       tmem_ld_wait();
-      uint8_t* buf = smem + kQOff + half * kHalfBytes + q * 4096;      // 32 rows x 128 bytes
+      uint8_t* buf = smem + kQOff + half * kTileBytes + dh * kHalfBytes + q * 4096;      // 32 rows x 128 bytes
 #pragma unroll
       for (int v8 = 0; v8 < 8; ++v8) {
         uint32_t w[4];
@@ -276,11 +303,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       fence_proxy_async();
       __syncwarp();
       if (lane == 0 && row0 < p.Lq) {
-        tma_store_2d(&tmO, buf, head * kD + half * 64, row0);
+        tma_store_2d(&tmO, buf, head * kD + dh * 64, row0);
         bulk_commit();
       }
     }
     if (lane == 0) bulk_wait<0>();
+    }
   }
 
   // ---------------------------------------------------------------------- teardown
