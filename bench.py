@@ -273,6 +273,7 @@ def run_gpu_arm(args):
     for name, m, n, k in shapes:
         if (m, k) not in host_in:
             host_in[(m, k)] = torch.randn(m, k, dtype=torch.bfloat16).pin_memory()
+    torch.cuda.current_stream(dev).synchronize()
     host_out = {}
     for name, m, n, k in shapes:
         if (m, n) not in host_out:
@@ -280,12 +281,32 @@ def run_gpu_arm(args):
     h2d = sum(m * k * 2 for _, m, n, k in shapes)
     d2h = sum(m * n * 2 for _, m, n, k in shapes)
 
+    # Three streams: host->device copies, quantize + GEMM, device->host copies, chained with events so
+    # that the copies of neighbouring GEMMs overlap the compute (PCIe is full duplex).
+    st_in, st_cmp, st_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    dev_in = [torch.empty(m, k, dtype=torch.bfloat16, device=dev) for _, m, n, k in shapes]
+    dev_out = [torch.empty(m, n, dtype=torch.bfloat16, device=dev) for _, m, n, k in shapes]
+    step_done = torch.cuda.Event()
+
     def e2e_step():
-        for name, m, n, k in shapes:
-            x = host_in[(m, k)].to(dev, non_blocking=True)
-            wq, bias = weights[(name, n, k)]
-            y = L.fp4_matmul(L.quantize_to_fp4(x, cfg), wq, bias=bias)
-            host_out[(m, n)].copy_(y, non_blocking=True)
+        st_in.wait_event(step_done)                    # buffers of the previous step are free again
+        st_cmp.wait_event(step_done)
+        for i, (name, m, n, k) in enumerate(shapes):
+            with torch.cuda.stream(st_in):
+                dev_in[i].copy_(host_in[(m, k)], non_blocking=True)
+                ev_in = torch.cuda.Event()
+                ev_in.record(st_in)
+            with torch.cuda.stream(st_cmp):
+                st_cmp.wait_event(ev_in)
+                wq, bias = weights[(name, n, k)]
+                L.fp4_matmul(L.quantize_to_fp4(dev_in[i], cfg), wq, bias=bias, out=dev_out[i])
+                ev_c = torch.cuda.Event()
+                ev_c.record(st_cmp)
+            with torch.cuda.stream(st_out):
+                st_out.wait_event(ev_c)
+                host_out[(m, n)].copy_(dev_out[i], non_blocking=True)
+        step_done.record(st_out)
+        torch.cuda.current_stream(dev).wait_event(step_done)
 
     e2e_step()
     sync_all()
