@@ -1,0 +1,103 @@
+// Pieces shared by the 1-CTA and the 2-CTA W4A4 GEMM kernels: launch parameters, epilogue math.
+#pragma once
+
+#include <cuda.h>
+
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace llnv {
+namespace gemm {
+
+struct GemmParams {
+  const uint8_t* sfa;
+  const uint8_t* sfb;
+  const float* a_amax;
+  const float* b_amax;
+  float alpha_denom;       // 6*Ea*6*Eb
+  int64_t M, N, K;
+  llnv_epilogue_t epi;
+  __nv_bfloat16* d;
+  int64_t ldd;
+  unsigned int* status;
+  int debug;               // timing experiments only: bit0 skip scale copies, bit1 one MMA per stage, bit2 skip stores
+};
+
+// two fp32 -> packed bf16x2 (one conversion instruction, round to nearest even)
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  const float u = k0 * (x + k1 * x * x * x);
+  return __fdividef(x, 1.f + __expf(-2.f * u));
+}
+
+// epilogue variants (compile-time, so that the plain path stays a handful of instructions per
+// element and the whole epilogue fits the instruction cache)
+constexpr int kEpiBias = 1, kEpiGelu = 2, kEpiRes = 4;
+
+// Epilogue of one 64-column chunk of one accumulator row per thread: r holds the fp32 accumulators
+// (columns col .. col+63 of this thread's row), the result is written as bf16 into the warp's
+// swizzled staging buffer `buf` (32 rows x 128 bytes; with a residual the buffer holds the residual
+// tile on entry).  grow: this row's gate vector or nullptr.
+template <int EPI>
+__device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[2][32], float alpha, const uint16_t* __restrict__ bias,
+                                               const uint16_t* __restrict__ grow, int64_t col, uint8_t* buf, int lane,
+                                               bool want_amax, bool row_ok, float& local_amax) {
+  constexpr bool has_res = (EPI & kEpiRes) != 0;
+#pragma unroll
+  for (int v8 = 0; v8 < 8; ++v8) {    // 8 columns (16 bytes) at a time
+    uint4* slot = reinterpret_cast<uint4*>(buf + lane * 128 + ((v8 ^ (lane & 7)) << 4));
+    float y[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int cc = v8 * 8 + e;      // column inside the 64-column chunk
+      y[e] = __fmul_rn(alpha, __uint_as_float(r[cc >> 5][cc & 31]));
+    }
+    if (EPI != 0 || want_amax) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) y[e] = round_bf16(y[e]);
+    }
+    if (EPI & kEpiBias) {
+      const uint4 bv = __ldg(reinterpret_cast<const uint4*>(bias + col + v8 * 8));
+      const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        y[e] = round_bf16(y[e] + ((e & 1) ? bf16_hi(bw[e >> 1]) : bf16_lo(bw[e >> 1])));
+    }
+    if (EPI & kEpiGelu) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) y[e] = round_bf16(gelu_tanh(y[e]));
+    }
+    if (has_res) {
+      const uint4 rv = *slot;
+      const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+      if (grow) {
+        const uint4 gv = __ldg(reinterpret_cast<const uint4*>(grow + col + v8 * 8));
+        const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          y[e] = round_bf16(y[e] * ((e & 1) ? bf16_hi(gw[e >> 1]) : bf16_lo(gw[e >> 1])));
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        y[e] = round_bf16(((e & 1) ? bf16_hi(rw[e >> 1]) : bf16_lo(rw[e >> 1])) + y[e]);
+    }
+    if (want_amax && row_ok) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) local_amax = fmaxf(local_amax, fabsf(y[e]));
+    }
+    uint4 ov;
+    ov.x = pack2(y[0], y[1]);
+    ov.y = pack2(y[2], y[3]);
+    ov.z = pack2(y[4], y[5]);
+    ov.w = pack2(y[6], y[7]);
+    *slot = ov;
+  }
+}
+
+}  // namespace gemm
+}  // namespace llnv

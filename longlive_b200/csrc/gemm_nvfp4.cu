@@ -21,32 +21,18 @@
 // Every mbarrier wait is bounded (see sm100.cuh); no CTA waits on another CTA.
 #include <cuda.h>
 
-#include "common.cuh"
-#include "sm100.cuh"
+#include "gemm_common.cuh"
 
 namespace llnv {
 namespace {
 
 using namespace sm100;
+using namespace gemm;
 
 constexpr int BM = 128;
 constexpr int BK_BYTES = 128;            // 256 E2M1 elements
 constexpr int kThreads = 192;
 constexpr uint32_t kTmemCols = 512;
-
-struct GemmParams {
-  const uint8_t* sfa;
-  const uint8_t* sfb;
-  const float* a_amax;
-  const float* b_amax;
-  float alpha_denom;       // 6*Ea*6*Eb
-  int64_t M, N, K;
-  llnv_epilogue_t epi;
-  __nv_bfloat16* d;
-  int64_t ldd;
-  unsigned int* status;
-  int debug;               // timing experiments only: bit0 skip scale copies, bit1 one MMA per stage, bit2 skip stores
-};
 
 template <int BN>
 struct Cfg {
@@ -70,22 +56,6 @@ struct Cfg {
 };
 
 // GELU, tanh form: 0.5 x (1 + tanh(u)) = x / (1 + exp(-2u)), u = sqrt(2/pi) (x + 0.044715 x^3)
-// two fp32 -> packed bf16x2 (one conversion instruction, round to nearest even)
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<const uint32_t*>(&v);
-}
-
-__device__ __forceinline__ float gelu_tanh(float x) {
-  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-  const float u = k0 * (x + k1 * x * x * x);
-  return __fdividef(x, 1.f + __expf(-2.f * u));
-}
-
-// epilogue variants (compile-time, so that the plain path stays a handful of instructions per
-// element and the whole epilogue fits the instruction cache)
-constexpr int kEpiBias = 1, kEpiGelu = 2, kEpiRes = 4;
-
 template <int BN, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -265,55 +235,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             __syncwarp();
           }
           const int64_t col = (int64_t)nt * BN + c0;
-#pragma unroll
-          for (int v8 = 0; v8 < 8; ++v8) {            // 8 columns (16 bytes) at a time
-            uint4* slot = reinterpret_cast<uint4*>(buf + lane * 128 + ((v8 ^ (lane & 7)) << 4));
-            float y[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const int cc = v8 * 8 + e;              // column inside the 64-column chunk
-              y[e] = __fmul_rn(alpha, __uint_as_float(r[cc >> 5][cc & 31]));
-            }
-            if (EPI != 0 || p.epi.out_amax) {
-#pragma unroll
-              for (int e = 0; e < 8; ++e) y[e] = round_bf16(y[e]);
-            }
-            if (EPI & kEpiBias) {
-              const uint4 bv = __ldg(reinterpret_cast<const uint4*>(bias + col + v8 * 8));
-              const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
-#pragma unroll
-              for (int e = 0; e < 8; ++e)
-                y[e] = round_bf16(y[e] + ((e & 1) ? bf16_hi(bw[e >> 1]) : bf16_lo(bw[e >> 1])));
-            }
-            if (EPI & kEpiGelu) {
-#pragma unroll
-              for (int e = 0; e < 8; ++e) y[e] = round_bf16(gelu_tanh(y[e]));
-            }
-            if (has_res) {
-              const uint4 rv = *slot;
-              const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
-              if (grow) {
-                const uint4 gv = __ldg(reinterpret_cast<const uint4*>(grow + col + v8 * 8));
-                const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
-#pragma unroll
-                for (int e = 0; e < 8; ++e)
-                  y[e] = round_bf16(y[e] * ((e & 1) ? bf16_hi(gw[e >> 1]) : bf16_lo(gw[e >> 1])));
-              }
-#pragma unroll
-              for (int e = 0; e < 8; ++e)
-                y[e] = round_bf16(((e & 1) ? bf16_hi(rw[e >> 1]) : bf16_lo(rw[e >> 1])) + y[e]);
-            }
-            if (p.epi.out_amax && row_ok) {
-#pragma unroll
-              for (int e = 0; e < 8; ++e) local_amax = fmaxf(local_amax, fabsf(y[e]));
-            }
-            uint4 ov;
-            ov.x = pack2(y[0], y[1]);
-            ov.y = pack2(y[2], y[3]);
-            ov.z = pack2(y[4], y[5]);
-            ov.w = pack2(y[6], y[7]);
-            *slot = ov;
-          }
+          epilogue_chunk<EPI>(r, alpha, bias, grow, col, buf, lane, p.epi.out_amax != nullptr, row_ok, local_amax);
           fence_proxy_async();
           __syncwarp();
           if (lane == 0 && !(p.debug & 8)) {
@@ -376,13 +298,17 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tm
 }
 
 }  // namespace
+
+int gemm_nvfp4_pair(const void* a_codes, const void* a_sf, const void* b_codes, const void* b_sf, const gemm::GemmParams& p,
+                    const CUtensorMap& tmD, const CUtensorMap& tmR, int variant, cudaStream_t stream);
 }  // namespace llnv
 
 using namespace llnv;
 
-// Test/benchmark hook: force the N tile (128 or 256); 0 restores the automatic choice.
+// Test/benchmark hook: force the kernel: 128 / 256 = one CTA per tile with that N tile, 2 = CTA pairs
+// (256 x 256 tile per pair); 0 restores the automatic choice.
 extern "C" int llnv_gemm_nvfp4_force_tile_n(int bn) {
-  LLNV_REQUIRE(bn == 0 || bn == 128 || bn == 256, "llnv_gemm_nvfp4_force_tile_n: tile must be 0, 128 or 256");
+  LLNV_REQUIRE(bn == 0 || bn == 2 || bn == 128 || bn == 256, "llnv_gemm_nvfp4_force_tile_n: tile must be 0, 2, 128 or 256");
   g_forced_bn = bn;
   return LLNV_OK;
 }
@@ -450,6 +376,7 @@ extern "C" int llnv_gemm_nvfp4(const void* a_codes, const void* a_sf, const floa
     if (rc != LLNV_OK) return rc;
   }
   const int variant = (epi.bias ? kEpiBias : 0) | (epi.act == 1 ? kEpiGelu : 0) | (epi.residual ? kEpiRes : 0);
+  if (g_forced_bn == 2 && N % 256 == 0) return gemm_nvfp4_pair(a_codes, a_sf, b_codes, b_sf, p, tmD, tmR, variant, stream);
 #define LLNV_GEMM_CASE(V)                                                                   \
   case V:                                                                                   \
     return bn == 256 ? launch<256, V>(tmA, tmB, tmD, tmR, p, stream) : launch<128, V>(tmA, tmB, tmD, tmR, p, stream);

@@ -38,7 +38,7 @@ def oracle_matmul(xq, wq, m, n, k):
     return a @ b.T
 
 
-@pytest.mark.parametrize("tile_n", [128, 256])
+@pytest.mark.parametrize("tile_n", [128, 256, 2])     # 2 = CTA-pair kernel (256 x 256 tile per pair)
 @pytest.mark.parametrize("m,n,k", [(128, 256, 256), (200, 256, 512), (880, 512, 3072), (130, 1024, 1024), (512, 3072, 3072)])
 def test_gemm_matches_oracle(m, n, k, tile_n):
     _lib.lib().llnv_gemm_nvfp4_force_tile_n(tile_n)
@@ -134,6 +134,33 @@ def test_gemm_fused_epilogue_matches_unfused_chain():
     # residual without gate
     y = ops.gemm_nvfp4(*args, residual=resid)
     assert torch.equal(y, resid + base)
+
+
+def test_pair_kernel_fused_epilogues_match_single_cta_kernel():
+    m, n, k, frames = 700, 512, 1024, 2
+    x = util.config_activation(m, k, seed=11).cuda()
+    w = util.config_weight(n, k, seed=12).cuda()
+    xq, wq = L.quantize_to_fp4(x), L.quantize_to_fp4(w)
+    g = torch.Generator().manual_seed(6)
+    bias = torch.randn(n, generator=g).bfloat16().cuda()
+    resid = torch.randn(m, n, generator=g).bfloat16().cuda()
+    gate = torch.randn(frames, n, generator=g).bfloat16().cuda()
+    args = (xq.values, xq.scale_factors, xq.amax, 3, wq.values, wq.scale_factors, wq.amax, 3, m, n, k)
+    lib = _lib.lib()
+    outs = {}
+    for tile in (256, 2):
+        lib.llnv_gemm_nvfp4_force_tile_n(tile)
+        try:
+            a1 = torch.zeros(1, dtype=torch.float32, device="cuda")
+            a2 = torch.zeros(1, dtype=torch.float32, device="cuda")
+            outs[tile] = (ops.gemm_nvfp4(*args), ops.gemm_nvfp4(*args, bias=bias, act=1, out_amax=a1),
+                          ops.gemm_nvfp4(*args, bias=bias, residual=resid, gate=gate, frame_rows=m // frames, out_amax=a2), a1, a2)
+        finally:
+            lib.llnv_gemm_nvfp4_force_tile_n(0)
+    torch.cuda.synchronize()
+    assert lib.llnv_check_status(None) == 0, lib.llnv_last_error()
+    for a, b in zip(outs[256], outs[2]):
+        assert torch.equal(a, b)
 
 
 def test_gemm_rejects_bad_shapes():
