@@ -110,7 +110,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         const int mt = tile % num_m, nt = tile / num_m;
         const int a_row = mt * 256 + (int)rank * 128;
         for (int kb = 0; kb < num_kb; ++kb) {
-          mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 100u);
+          mbar_spin(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 100u);
           uint8_t* st = smem + stage * kStageBytes;
           // the leader posts the byte count of both CTAs' loads of this stage
           if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * kStageBytes);
@@ -139,7 +139,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         const uint32_t b0 = use % kAccBufs, b1 = (use + 1) % kAccBufs;
         const uint32_t ph0 = (use / kAccBufs) & 1u, ph1 = ((use + 1) / kAccBufs) & 1u;
         for (int kb = 0; kb < num_kb; ++kb) {
-          mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 201u);
+          mbar_spin(&full_bar[stage], phase, abort_flag, p.status, 201u);
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + stage * kStageBytes);
           const uint32_t b_addr = a_addr + kABytes;

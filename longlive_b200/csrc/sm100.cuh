@@ -65,6 +65,36 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded busy-poll (no hardware suspend between polls): lowest wake-up latency, for the single
+// threads that drive the load and MMA pipelines.  Same give-up protocol as mbar_wait.
+__device__ __forceinline__ bool mbar_spin(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, unsigned int* status,
+                                          uint32_t where) {
+  if (*abort_flag) return false;
+  for (uint32_t i = 0; i < (kMaxPolls << 4); ++i) {
+    if (mbar_test_wait(bar, parity)) return true;
+    if ((i & 4095u) == 4095u && *abort_flag) return false;
+  }
+  *abort_flag = 1u;
+  if (status && atomicCAS(status, 0u, 1u) == 0u) {
+    status[1] = where;
+    status[2] = blockIdx.x;
+    status[3] = kMaxPolls;
+  }
+  return false;
+}
+
 // Bounded wait.  `abort_flag` lives in shared memory; `status` is the device status word
 // (4 x u32: code, where, block, polls).  Returns false when the wait gave up or was skipped.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
