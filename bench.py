@@ -326,7 +326,13 @@ def run_gpu_arm(args):
     if not args.no_dit:
         del flush
         torch.cuda.empty_cache()
-        dit_chunk = bench_dit_chunk(dev, rank, world, dist.group.WORLD if world > 1 else None, args.chunk_steps)
+        grp = dist.group.WORLD if world > 1 else None
+        dit_chunk = bench_dit_chunk(dev, rank, world, grp, args.chunk_steps)
+        if world > 1:
+            # same run with per-shard tensor scales (no amax all-reduces): valid NVFP4, but codes differ from the 1-GPU run
+            torch.cuda.empty_cache()
+            local = bench_dit_chunk(dev, rank, world, grp, args.chunk_steps, sync_amax=False)
+            dit_chunk["per_shard_amax"] = {"value": local["value"], "ms_per_chunk": local["ms_per_chunk"]}
 
     if rank == 0:
         peaks = load_peaks()
@@ -368,7 +374,7 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
-def bench_dit_chunk(dev, rank, world, group, steps: int):
+def bench_dit_chunk(dev, rank, world, group, steps: int, sync_amax: bool = True):
     """Second headline of the benchmark: one AR chunk (3 latent frames, 4 denoising forwards + 1
     clean re-cache forward) of the 30-layer random-init Wan2.2-5B-shaped causal DiT with NVFP4
     W4A4 linears and the NVFP4 KV cache in steady state (full 15-frame window).  With N > 1 ranks
@@ -381,7 +387,7 @@ def bench_dit_chunk(dev, rank, world, group, steps: int):
     from longlive_b200 import _lib, dit
 
     cfg = dit.DiTConfig()
-    model = dit.CausalDiT(cfg, device=dev, seed=0, sp_group=group, sync_amax=True)
+    model = dit.CausalDiT(cfg, device=dev, seed=0, sp_group=group, sync_amax=sync_amax)
     gen = torch.Generator(device=dev).manual_seed(7)
     ctx = model.encode_text(torch.randn(cfg.text_len, cfg.text_dim, generator=gen, device=dev).bfloat16())
     lat_full = torch.randn(cfg.chunk_tokens, cfg.patch_dim, generator=gen, device=dev).bfloat16()
@@ -413,7 +419,7 @@ def bench_dit_chunk(dev, rank, world, group, steps: int):
             "ms_per_chunk": ms, "chunks_timed": steps, "layers": cfg.layers, "forwards_per_chunk": 5,
             "window_tokens": cfg.window_frames * cfg.frame_tokens, "chunk_tokens": cfg.chunk_tokens,
             "parallelism": f"sequence-parallel over {world} GPU(s)" if world > 1 else "single GPU",
-            "amax_sync": world > 1, "scaling": "strong", "kv_cache_bytes_per_rank": model.cache.bytes(),
+            "amax_sync": bool(world > 1 and sync_amax), "scaling": "strong", "kv_cache_bytes_per_rank": model.cache.bytes(),
             "data": "synthetic, random-init weights"}
 
 

@@ -69,7 +69,18 @@ __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w 
 __device__ __forceinline__ uint32_t f2bf(float f) {
   return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(f));
 }
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) { return f2bf(lo) | (f2bf(hi) << 16); }
+// two fp32 -> packed bf16x2 with ONE paired conversion (the scalar conversion issues on the slow
+// special-function pipe; the paired form does not)
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&p);
+}
+// round two fp32 values to bf16 precision in place (kept in fp32)
+__device__ __forceinline__ void round_bf16x2(float& a, float& b) {
+  const uint32_t p = pack_bf16x2(a, b);
+  a = __uint_as_float(p << 16);
+  b = __uint_as_float(p & 0xFFFF0000u);
+}
 // round an fp32 value to bf16 precision, keep it in fp32
 __device__ __forceinline__ float round_bf16(float f) { return __uint_as_float(f2bf(f) << 16); }
 

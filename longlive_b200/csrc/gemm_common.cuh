@@ -59,18 +59,25 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[2][32], float
     }
     if (EPI != 0 || want_amax) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) y[e] = round_bf16(y[e]);
+      for (int e = 0; e < 8; e += 2) round_bf16x2(y[e], y[e + 1]);
     }
     if (EPI & kEpiBias) {
       const uint4 bv = __ldg(reinterpret_cast<const uint4*>(bias + col + v8 * 8));
       const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
-      for (int e = 0; e < 8; ++e)
-        y[e] = round_bf16(y[e] + ((e & 1) ? bf16_hi(bw[e >> 1]) : bf16_lo(bw[e >> 1])));
+      for (int e = 0; e < 8; e += 2) {
+        y[e] = y[e] + bf16_lo(bw[e >> 1]);
+        y[e + 1] = y[e + 1] + bf16_hi(bw[e >> 1]);
+        round_bf16x2(y[e], y[e + 1]);
+      }
     }
     if (EPI & kEpiGelu) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) y[e] = round_bf16(gelu_tanh(y[e]));
+      for (int e = 0; e < 8; e += 2) {
+        y[e] = gelu_tanh(y[e]);
+        y[e + 1] = gelu_tanh(y[e + 1]);
+        round_bf16x2(y[e], y[e + 1]);
+      }
     }
     if (has_res) {
       const uint4 rv = *slot;
@@ -79,12 +86,18 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[2][32], float
         const uint4 gv = __ldg(reinterpret_cast<const uint4*>(grow + col + v8 * 8));
         const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
 #pragma unroll
-        for (int e = 0; e < 8; ++e)
-          y[e] = round_bf16(y[e] * ((e & 1) ? bf16_hi(gw[e >> 1]) : bf16_lo(gw[e >> 1])));
+        for (int e = 0; e < 8; e += 2) {
+          y[e] = y[e] * bf16_lo(gw[e >> 1]);
+          y[e + 1] = y[e + 1] * bf16_hi(gw[e >> 1]);
+          round_bf16x2(y[e], y[e + 1]);
+        }
       }
 #pragma unroll
-      for (int e = 0; e < 8; ++e)
-        y[e] = round_bf16(((e & 1) ? bf16_hi(rw[e >> 1]) : bf16_lo(rw[e >> 1])) + y[e]);
+      for (int e = 0; e < 8; e += 2) {
+        y[e] = bf16_lo(rw[e >> 1]) + y[e];
+        y[e + 1] = bf16_hi(rw[e >> 1]) + y[e + 1];
+        round_bf16x2(y[e], y[e + 1]);
+      }
     }
     if (want_amax && row_ok) {
 #pragma unroll

@@ -288,18 +288,25 @@ __device__ __forceinline__ void transform_block(uint32_t (&w)[8], const Prologue
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     float y[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const float xv = h ? bf16_hi(w[j]) : bf16_lo(w[j]);
-      const float av = h ? bf16_hi(aw[j]) : bf16_lo(aw[j]);
-      const float bv = h ? bf16_hi(bw[j]) : bf16_lo(bw[j]);
-      const float xn = __fmul_rn(__fsub_rn(xv, mean), rstd);
-      if (MODE == kAdaLN) {
-        const float sc = pr.add_one ? round_bf16(__fadd_rn(av, 1.f)) : av;
-        y[h] = __fadd_rn(round_bf16(__fmul_rn(round_bf16(xn), sc)), bv);
-      } else {
-        y[h] = __fmaf_rn(xn, av, bv);
+    const float a0f = bf16_lo(aw[j]), a1f = bf16_hi(aw[j]);
+    const float b0f = bf16_lo(bw[j]), b1f = bf16_hi(bw[j]);
+    float xn0 = __fmul_rn(__fsub_rn(bf16_lo(w[j]), mean), rstd);
+    float xn1 = __fmul_rn(__fsub_rn(bf16_hi(w[j]), mean), rstd);
+    if (MODE == kAdaLN) {
+      float s0 = a0f, s1 = a1f;
+      if (pr.add_one) {
+        s0 = __fadd_rn(a0f, 1.f);
+        s1 = __fadd_rn(a1f, 1.f);
+        round_bf16x2(s0, s1);
       }
+      round_bf16x2(xn0, xn1);
+      float m0 = __fmul_rn(xn0, s0), m1 = __fmul_rn(xn1, s1);
+      round_bf16x2(m0, m1);
+      y[0] = __fadd_rn(m0, b0f);
+      y[1] = __fadd_rn(m1, b1f);
+    } else {
+      y[0] = __fmaf_rn(xn0, a0f, b0f);
+      y[1] = __fmaf_rn(xn1, a1f, b1f);
     }
     w[j] = pack_bf16x2(y[0], y[1]);
   }
@@ -390,6 +397,25 @@ __global__ void __launch_bounds__(256) ln_stats_amax_kernel(const uint16_t* __re
   constexpr int kMaxVec = 16;                 // up to 16 x 8 elements per lane -> C <= 4096
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * 8 + warp;
+  // The modulation / affine vectors are shared by the rows of a CTA (8 consecutive rows touch at
+  // most two frames): stage them in shared memory once instead of loading them, dependently, in
+  // every step of the per-row loop.
+  __shared__ uint4 pa_sh[2][4096 / 8];
+  __shared__ uint4 pb_sh[2][4096 / 8];
+  const int nvec_all = (int)(C >> 3);
+  const int64_t first_row = (int64_t)blockIdx.x * 8;
+  const int64_t last_row = min(first_row + 7, M - 1);
+  const int64_t f0 = MODE == kAdaLN ? (first_row + pr.row_offset) / pr.frame_rows : 0;
+  const int64_t f1 = MODE == kAdaLN ? (last_row + pr.row_offset) / pr.frame_rows : 0;
+  for (int i = threadIdx.x; i < nvec_all; i += blockDim.x) {
+    pa_sh[0][i] = __ldg(reinterpret_cast<const uint4*>(pr.p0 + f0 * pr.stride) + i);
+    pb_sh[0][i] = __ldg(reinterpret_cast<const uint4*>(pr.p1 + f0 * pr.stride) + i);
+    if (f1 != f0) {
+      pa_sh[1][i] = __ldg(reinterpret_cast<const uint4*>(pr.p0 + f1 * pr.stride) + i);
+      pb_sh[1][i] = __ldg(reinterpret_cast<const uint4*>(pr.p1 + f1 * pr.stride) + i);
+    }
+  }
+  __syncthreads();
   float wmax = 0.f;
   if (row < M) {
     const int nvec = (int)(C >> 3);           // 16-byte vectors per row
@@ -426,33 +452,41 @@ __global__ void __launch_bounds__(256) ln_stats_amax_kernel(const uint16_t* __re
       row_stats[2 * row] = mean;
       row_stats[2 * row + 1] = rstd;
     }
-    const int64_t prow = MODE == kAdaLN ? ((row + pr.row_offset) / pr.frame_rows) * pr.stride : 0;
+    const int fsel = (MODE == kAdaLN && (row + pr.row_offset) / pr.frame_rows != f0) ? 1 : 0;
 #pragma unroll
     for (int i = 0; i < kMaxVec; ++i) {
       const int idx = lane + 32 * i;
       if (idx < nvec) {
-        const uint4 a4 = __ldg(reinterpret_cast<const uint4*>(pr.p0 + prow) + idx);
-        const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(pr.p1 + prow) + idx);
+        const uint4 a4 = pa_sh[fsel][idx];
+        const uint4 b4 = pb_sh[fsel][idx];
         const uint32_t ws[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
         const uint32_t aw[4] = {a4.x, a4.y, a4.z, a4.w};
         const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const float xv = h ? bf16_hi(ws[j]) : bf16_lo(ws[j]);
-            const float av = h ? bf16_hi(aw[j]) : bf16_lo(aw[j]);
-            const float bv = h ? bf16_hi(bw[j]) : bf16_lo(bw[j]);
-            const float xn = __fmul_rn(__fsub_rn(xv, mean), rstd);
-            float y;
-            if (MODE == kAdaLN) {
-              const float sc = pr.add_one ? round_bf16(__fadd_rn(av, 1.f)) : av;
-              y = __fadd_rn(round_bf16(__fmul_rn(round_bf16(xn), sc)), bv);
-            } else {
-              y = __fmaf_rn(xn, av, bv);
+          const float a0f = bf16_lo(aw[j]), a1f = bf16_hi(aw[j]);
+          const float b0f = bf16_lo(bw[j]), b1f = bf16_hi(bw[j]);
+          float xn0 = __fmul_rn(__fsub_rn(bf16_lo(ws[j]), mean), rstd);
+          float xn1 = __fmul_rn(__fsub_rn(bf16_hi(ws[j]), mean), rstd);
+          float y0, y1;
+          if (MODE == kAdaLN) {
+            float s0 = a0f, s1 = a1f;
+            if (pr.add_one) {
+              s0 = __fadd_rn(a0f, 1.f);
+              s1 = __fadd_rn(a1f, 1.f);
+              round_bf16x2(s0, s1);
             }
-            wmax = fmaxf(wmax, fabsf(round_bf16(y)));
+            round_bf16x2(xn0, xn1);
+            float m0 = __fmul_rn(xn0, s0), m1 = __fmul_rn(xn1, s1);
+            round_bf16x2(m0, m1);
+            y0 = __fadd_rn(m0, b0f);
+            y1 = __fadd_rn(m1, b1f);
+          } else {
+            y0 = __fmaf_rn(xn0, a0f, b0f);
+            y1 = __fmaf_rn(xn1, a1f, b1f);
           }
+          round_bf16x2(y0, y1);
+          wmax = fmaxf(wmax, fmaxf(fabsf(y0), fabsf(y1)));
         }
       }
     }

@@ -25,9 +25,25 @@ __global__ void __launch_bounds__(256) rmsnorm_rope_kernel(const uint16_t* __res
                                                            float* __restrict__ amax_out) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * 8 + warp;
+  // the norm weight is shared by all rows: one cooperative load per CTA instead of a dependent
+  // global load in every step of the per-row loop
+  __shared__ uint4 w_sh[4096 / 8];
+  const int nvec = (int)(C >> 3);
+  if (weight) {
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) w_sh[i] = __ldg(reinterpret_cast<const uint4*>(weight) + i);
+  }
+  __syncthreads();
   float wmax = 0.f;
   if (row < S) {
-    const int nvec = (int)(C >> 3);
+    // this lane needs the same 4 cos / 4 sin values in every step (pair index depends on lane only)
+    float cc[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
+    if (cosv) {
+      const int pair0 = (lane & 15) * 4;
+      const float4 c4 = __ldg(reinterpret_cast<const float4*>(cosv + row * 64 + pair0));
+      const float4 s4 = __ldg(reinterpret_cast<const float4*>(sinv + row * 64 + pair0));
+      cc[0] = c4.x; cc[1] = c4.y; cc[2] = c4.z; cc[3] = c4.w;
+      sn[0] = s4.x; sn[1] = s4.y; sn[2] = s4.z; sn[3] = s4.w;
+    }
     uint4 v[kMaxVec];
     float ss = 0.f;
 #pragma unroll
@@ -61,24 +77,26 @@ __global__ void __launch_bounds__(256) rmsnorm_rope_kernel(const uint16_t* __res
         y[2 * j + 1] = bf16_hi(w4[j]);
       }
       if (weight) {
-        const uint4 wv = __ldg(reinterpret_cast<const uint4*>(weight) + idx);
+        const uint4 wv = w_sh[idx];
         const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float g = (e & 1) ? bf16_hi(ww[e >> 1]) : bf16_lo(ww[e >> 1]);
-          y[e] = round_bf16(__fmul_rn(round_bf16(__fmul_rn(y[e], rinv)), g));
+        for (int p = 0; p < 4; ++p) {
+          float a = __fmul_rn(y[2 * p], rinv), b = __fmul_rn(y[2 * p + 1], rinv);
+          round_bf16x2(a, b);
+          a = __fmul_rn(a, bf16_lo(ww[p]));
+          b = __fmul_rn(b, bf16_hi(ww[p]));
+          round_bf16x2(a, b);
+          y[2 * p] = a;
+          y[2 * p + 1] = b;
         }
       }
       if (cosv) {
-        const int pair0 = (idx & 15) * 4;                         // first rotation pair of this vector inside its head
-        const float4 c4 = __ldg(reinterpret_cast<const float4*>(cosv + row * 64 + pair0));
-        const float4 s4 = __ldg(reinterpret_cast<const float4*>(sinv + row * 64 + pair0));
-        const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
         for (int p = 0; p < 4; ++p) {
           const float a = y[2 * p], b = y[2 * p + 1];
-          y[2 * p] = round_bf16(__fsub_rn(__fmul_rn(a, cc[p]), __fmul_rn(b, sn[p])));
-          y[2 * p + 1] = round_bf16(__fadd_rn(__fmul_rn(a, sn[p]), __fmul_rn(b, cc[p])));
+          y[2 * p] = __fsub_rn(__fmul_rn(a, cc[p]), __fmul_rn(b, sn[p]));
+          y[2 * p + 1] = __fadd_rn(__fmul_rn(a, sn[p]), __fmul_rn(b, cc[p]));
+          round_bf16x2(y[2 * p], y[2 * p + 1]);
         }
       }
       float hsum = 0.f;

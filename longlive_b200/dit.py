@@ -206,8 +206,8 @@ class CausalDiT:
         self.cattn = bf(Sl, c)
         Lk = cfg.window_frames * cfg.frame_tokens
         self.win_k, self.win_v = bf(Lk, self.Cl), bf(Lk, self.Cl)
-        self.k_amax = torch.zeros(1, dtype=torch.float32, device=dev)
-        self.v_amax = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.kv_amax = torch.zeros(2, dtype=torch.float32, device=dev)      # [k, v]: reduced with one collective
+        self.k_amax, self.v_amax = self.kv_amax[0:1], self.kv_amax[1:2]
         self.h_amax = torch.zeros(1, dtype=torch.float32, device=dev)
         self.text_kv: list | None = None
         self.cache = KVCache(cfg, Hl, dev)
@@ -292,8 +292,7 @@ class CausalDiT:
                          amax_out=self.k_amax)
         if self.P > 1:
             if self.sync_amax:
-                sp.allreduce_max_(self.k_amax, self.group)
-                sp.allreduce_max_(self.v_amax, self.group)
+                sp.allreduce_max_(self.kv_amax, self.group)
             q_h, ks_h, kr_h, v_h = sp.seq_to_head_many([self.q_rot, self.k_smooth, self.k_rot, self.v_buf], self.group)
             self.win_k[n_past * T:(n_past + 1) * T].copy_(ks_h)
             self.win_v[n_past * T:(n_past + 1) * T].copy_(v_h)

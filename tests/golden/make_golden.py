@@ -93,7 +93,7 @@ def edge_case_tensor(gen: torch.Generator) -> torch.Tensor:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the NVlabs/LongLive checkout")
     args = ap.parse_args()
     _setup(args.reference)
 
