@@ -333,6 +333,9 @@ def run_gpu_arm(args):
             torch.cuda.empty_cache()
             local = bench_dit_chunk(dev, rank, world, grp, args.chunk_steps, sync_amax=False)
             dit_chunk["per_shard_amax"] = {"value": local["value"], "ms_per_chunk": local["ms_per_chunk"]}
+        torch.cuda.empty_cache()
+        eager = bench_dit_chunk(dev, rank, world, grp, args.chunk_steps, use_graphs=False)
+        dit_chunk["eager_launches"] = {"value": eager["value"], "ms_per_chunk": eager["ms_per_chunk"]}
 
     if rank == 0:
         peaks = load_peaks()
@@ -374,7 +377,7 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
-def bench_dit_chunk(dev, rank, world, group, steps: int, sync_amax: bool = True):
+def bench_dit_chunk(dev, rank, world, group, steps: int, sync_amax: bool = True, use_graphs: bool = True):
     """Second headline of the benchmark: one AR chunk (3 latent frames, 4 denoising forwards + 1
     clean re-cache forward) of the 30-layer random-init Wan2.2-5B-shaped causal DiT with NVFP4
     W4A4 linears and the NVFP4 KV cache in steady state (full 15-frame window).  With N > 1 ranks
@@ -387,14 +390,17 @@ def bench_dit_chunk(dev, rank, world, group, steps: int, sync_amax: bool = True)
     from longlive_b200 import _lib, dit
 
     cfg = dit.DiTConfig()
-    model = dit.CausalDiT(cfg, device=dev, seed=0, sp_group=group, sync_amax=sync_amax)
+    model = dit.CausalDiT(cfg, device=dev, seed=0, sp_group=group, sync_amax=sync_amax, use_graphs=use_graphs)
     gen = torch.Generator(device=dev).manual_seed(7)
     ctx = model.encode_text(torch.randn(cfg.text_len, cfg.text_dim, generator=gen, device=dev).bfloat16())
     lat_full = torch.randn(cfg.chunk_tokens, cfg.patch_dim, generator=gen, device=dev).bfloat16()
     sl = cfg.chunk_tokens // world
     lat = lat_full[rank * sl:(rank + 1) * sl].contiguous()
     chunk = 0
-    for _ in range(cfg.max_blocks + 1):            # fill the window, then one more chunk to reach the rolling state
+    # fill the window, then one full period of the rolling block table (each of its states is
+    # captured as a CUDA graph on first use; the timed chunks below are replays)
+    period = cfg.max_blocks - cfg.sink_frames // cfg.frames_per_chunk
+    for _ in range(cfg.max_blocks + period):
         model.run_chunk(lat, ctx, chunk)
         chunk += 1
     torch.cuda.synchronize(dev)
@@ -419,7 +425,8 @@ def bench_dit_chunk(dev, rank, world, group, steps: int, sync_amax: bool = True)
             "ms_per_chunk": ms, "chunks_timed": steps, "layers": cfg.layers, "forwards_per_chunk": 5,
             "window_tokens": cfg.window_frames * cfg.frame_tokens, "chunk_tokens": cfg.chunk_tokens,
             "parallelism": f"sequence-parallel over {world} GPU(s)" if world > 1 else "single GPU",
-            "amax_sync": bool(world > 1 and sync_amax), "scaling": "strong", "kv_cache_bytes_per_rank": model.cache.bytes(),
+            "amax_sync": bool(world > 1 and sync_amax), "cuda_graphs": bool(use_graphs), "scaling": "strong",
+            "kv_cache_bytes_per_rank": model.cache.bytes(),
             "data": "synthetic, random-init weights"}
 
 

@@ -164,8 +164,9 @@ class KVCache:
 
 class CausalDiT:
     def __init__(self, cfg: DiTConfig | None = None, device="cuda", seed: int = 0, sp_group=None, sync_amax: bool = True,
-                 cache_text_kv: bool = True):
+                 cache_text_kv: bool = True, use_graphs: bool = False):
         self.cfg = cfg = cfg or DiTConfig()
+        self.use_graphs = use_graphs
         self.device = torch.device(device)
         self.group = sp_group
         self.rank, self.P = sp.world(sp_group)
@@ -211,6 +212,15 @@ class CausalDiT:
         self.h_amax = torch.zeros(1, dtype=torch.float32, device=dev)
         self.text_kv: list | None = None
         self.cache = KVCache(cfg, Hl, dev)
+        # static inputs of a forward (a captured graph reads these addresses on every replay)
+        self.g_lat = bf(Sl, cfg.patch_dim)
+        self.g_t = torch.zeros(cfg.frames_per_chunk, dtype=torch.float32, device=dev)
+        self.cos_buf = torch.empty((Sl, 64), dtype=torch.float32, device=dev)
+        self.sin_buf = torch.empty((Sl, 64), dtype=torch.float32, device=dev)
+        self._rope_frame: int | None = None
+        self._graphs: dict = {}
+        self._graph_pool = None
+        self._ran_eager = False
 
     # ---- helpers ----------------------------------------------------------------------------
     def _gemm(self, a: _Act, rows: int, lin: _Linear, out, **epi):
@@ -352,16 +362,51 @@ class CausalDiT:
         e0 = lin(torch.nn.functional.silu(e), self.tproj_w, self.tproj_b).view(-1, 6, cfg.dim)
         return e, e0
 
+    def _set_rope(self, start_frame: int) -> None:
+        if self._rope_frame == start_frame:
+            return
+        cos, sin = rope_tables(self.cfg, start_frame, self.device)
+        lo, hi = self.rank * self.Sl, (self.rank + 1) * self.Sl
+        self.cos_buf.copy_(cos[lo:hi])
+        self.sin_buf.copy_(sin[lo:hi])
+        self._rope_frame = start_frame
+
     def forward(self, latent_tokens: torch.Tensor, t: torch.Tensor, ctx: torch.Tensor, start_frame: int) -> torch.Tensor:
-        """latent_tokens: [Sl, patch_dim] (my token shard of the patchified chunk) -> [Sl, patch_dim]."""
+        """latent_tokens: [Sl, patch_dim] (my token shard of the patchified chunk) -> [Sl, patch_dim].
+
+        With ``use_graphs`` the whole forward (about a thousand launches, the collectives included)
+        is captured once per state of the KV block table and replayed afterwards: the launch sequence
+        depends only on which cache slots are past / current, every other input lives at a fixed
+        address.  The returned tensor is then the graph's output buffer: consume it before the next
+        forward.  The first forward and the chunks that still fill the window run eagerly (one-time
+        set-up such as the text K/V and the communicators must not happen inside a capture)."""
+        self._set_rope(start_frame)
+        if not self.use_graphs:
+            return self._forward_impl(latent_tokens, t, ctx)
+        self.g_lat.copy_(latent_tokens)
+        self.g_t.copy_(t)
+        key = (tuple(self.cache.order), self.cache.filled, ctx.data_ptr())
+        entry = self._graphs.get(key)
+        if entry is None:
+            if not self._ran_eager or self.cache.filled < self.cfg.max_blocks:
+                return self._forward_impl(self.g_lat, self.g_t, ctx)
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            graph = torch.cuda.CUDAGraph()
+            torch.cuda.synchronize(self.device)
+            with torch.cuda.graph(graph, pool=self._graph_pool, capture_error_mode="thread_local"):
+                out = self._forward_impl(self.g_lat, self.g_t, ctx)
+            entry = self._graphs[key] = (graph, out)
+        entry[0].replay()
+        return entry[1]
+
+    def _forward_impl(self, latent_tokens: torch.Tensor, t: torch.Tensor, ctx: torch.Tensor) -> torch.Tensor:
         cfg = self.cfg
         x = torch.nn.functional.linear(latent_tokens, self.patch_w, self.patch_b)
         self.x_a.copy_(x)
         e, e0 = self.time_embed(t)
-        cos, sin = rope_tables(cfg, start_frame, self.device)
-        if self.P > 1:
-            cos = cos[self.rank * self.Sl:(self.rank + 1) * self.Sl].contiguous()
-            sin = sin[self.rank * self.Sl:(self.rank + 1) * self.Sl].contiguous()
+        cos, sin = self.cos_buf, self.sin_buf
+        self._ran_eager = True
         cur, nxt = self.x_a, self.x_b
         for li, blk in enumerate(self.blocks):
             em = (blk.modulation + e0).contiguous()                    # [F, 6, dim], causal_model.py:863

@@ -21,7 +21,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, use_graphs=False):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
@@ -31,14 +31,14 @@ def _worker(rank, world, port, q):
     try:
         from longlive_b200 import dit
         cfg = dit.DiTConfig(**CFG)
-        par = dit.CausalDiT(cfg, device=dev, seed=4, sp_group=dist.group.WORLD, sync_amax=True)
+        par = dit.CausalDiT(cfg, device=dev, seed=4, sp_group=dist.group.WORLD, sync_amax=True, use_graphs=use_graphs)
         ref = dit.CausalDiT(cfg, device=dev, seed=4)
         g = torch.Generator(device=dev).manual_seed(9)
         ctx_raw = torch.randn(cfg.text_len, cfg.text_dim, generator=g, device=dev).bfloat16()
         ctx_p, ctx_r = par.encode_text(ctx_raw), ref.encode_text(ctx_raw)
         sl = cfg.chunk_tokens // world
         ok = True
-        for chunk in range(4):
+        for chunk in range(6 if use_graphs else 4):
             lat = torch.randn(cfg.chunk_tokens, cfg.patch_dim, generator=g, device=dev).bfloat16()
             out_r = ref.run_chunk(lat, ctx_r, chunk)
             out_p = par.run_chunk(lat[rank * sl:(rank + 1) * sl].contiguous(), ctx_p, chunk)
@@ -52,6 +52,8 @@ def _worker(rank, world, port, q):
         kr = ref.cache.k[0][cur_r].dequantize(torch.float32).view(cfg.chunk_tokens, cfg.heads, 128)
         kp = par.cache.k[0][cur_p].dequantize(torch.float32).view(cfg.chunk_tokens, hl, 128)
         ok = ok and torch.equal(kp, kr[:, rank * hl:(rank + 1) * hl])
+        if use_graphs:
+            ok = ok and len(par._graphs) == 2
         torch.cuda.synchronize()
         q.put((rank, "ok" if ok else "mismatch"))
     except Exception as exc:  # pragma: no cover
@@ -62,12 +64,13 @@ def _worker(rank, world, port, q):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_sequence_parallel_matches_single_gpu():
+@pytest.mark.parametrize("use_graphs", [False, True])
+def test_sequence_parallel_matches_single_gpu(use_graphs):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, use_graphs)) for r in range(2)]
     for p in procs:
         p.start()
     results = sorted(q.get(timeout=600) for _ in procs)
