@@ -416,6 +416,7 @@ def bench_dit_chunk(dev, rank, world, group, steps: int, sync_amax: bool = True,
         times.append(s.elapsed_time(e))
         chunk += 1
     assert _lib.lib().llnv_check_status(None) == 0, _lib.lib().llnv_last_error()
+    model.close()
     ms = statistics.median(times)
     if world > 1:
         t = torch.tensor([ms], dtype=torch.float64, device=dev)

@@ -400,6 +400,12 @@ class CausalDiT:
         entry[0].replay()
         return entry[1]
 
+    def close(self) -> None:
+        """Drop the captured graphs.  Call this before the process group is destroyed: a communicator
+        cannot be torn down while a live graph still holds its collectives."""
+        self._graphs.clear()
+        self._graph_pool = None
+
     def _forward_impl(self, latent_tokens: torch.Tensor, t: torch.Tensor, ctx: torch.Tensor) -> torch.Tensor:
         cfg = self.cfg
         x = torch.nn.functional.linear(latent_tokens, self.patch_w, self.patch_b)

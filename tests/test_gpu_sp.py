@@ -55,6 +55,7 @@ def _worker(rank, world, port, q, use_graphs=False):
         if use_graphs:
             ok = ok and len(par._graphs) == 2
         torch.cuda.synchronize()
+        par.close()
         q.put((rank, "ok" if ok else "mismatch"))
     except Exception as exc:  # pragma: no cover
         import traceback
@@ -75,5 +76,7 @@ def test_sequence_parallel_matches_single_gpu(use_graphs):
         p.start()
     results = sorted(q.get(timeout=600) for _ in procs)
     for p in procs:
-        p.join(timeout=120)
+        p.join(timeout=60)
+        if p.is_alive():
+            p.kill()
     assert results == [(0, "ok"), (1, "ok")], results
