@@ -327,14 +327,16 @@ def run_gpu_arm(args):
         del flush
         torch.cuda.empty_cache()
         grp = dist.group.WORLD if world > 1 else None
-        dit_chunk = bench_dit_chunk(dev, rank, world, grp, args.chunk_steps)
+        # Sequence-parallel ranks quantize their own token shard with its own tensor scale, as the
+        # reference's sequence-parallel path does (it has no amax exchange).  The variant with every
+        # amax MAX-reduced over the group reproduces the 1-GPU codes bit for bit and is timed beside it.
+        dit_chunk = bench_dit_chunk(dev, rank, world, grp, args.chunk_steps, sync_amax=False)
         if world > 1:
-            # same run with per-shard tensor scales (no amax all-reduces): valid NVFP4, but codes differ from the 1-GPU run
             torch.cuda.empty_cache()
-            local = bench_dit_chunk(dev, rank, world, grp, args.chunk_steps, sync_amax=False)
-            dit_chunk["per_shard_amax"] = {"value": local["value"], "ms_per_chunk": local["ms_per_chunk"]}
+            synced = bench_dit_chunk(dev, rank, world, grp, args.chunk_steps, sync_amax=True)
+            dit_chunk["bit_identical_to_1gpu_amax_allreduce"] = {"value": synced["value"], "ms_per_chunk": synced["ms_per_chunk"]}
         torch.cuda.empty_cache()
-        eager = bench_dit_chunk(dev, rank, world, grp, args.chunk_steps, use_graphs=False)
+        eager = bench_dit_chunk(dev, rank, world, grp, args.chunk_steps, sync_amax=False, use_graphs=False)
         dit_chunk["eager_launches"] = {"value": eager["value"], "ms_per_chunk": eager["ms_per_chunk"]}
 
     if rank == 0:
