@@ -166,6 +166,20 @@ int llnv_attention_bf16(const void* q, int64_t Lq, int64_t ldq, const void* k, c
                         int64_t ldk, int64_t ldv, int heads, float scale, void* out, int64_t ldo,
                         llnv_stream_t stream);
 
+/* The same attention with the key window split over `key_splits` CTAs per (256-query tile, head),
+ * for calls whose tiles alone cannot fill the device: a head shard of a sequence-parallel rank
+ * (wan_5b/distributed/sp_ulysses_inference.py:122-154 leaves heads / P heads per rank) has only
+ * ceil(Lq / 256) * heads / P tiles.  Every split attends to a contiguous range of 128-key tiles
+ * and writes unnormalised fp32 partial outputs plus (row maximum, row sum) to `workspace`; a
+ * second small kernel merges them.  key_splits = 1 is llnv_attention_bf16 (no workspace).
+ * llnv_attention_key_splits() proposes a split count for the current device (1 when the tiles
+ * already fill it); llnv_attention_workspace_bytes() is the workspace size for a split count. */
+int llnv_attention_bf16_ex(const void* q, int64_t Lq, int64_t ldq, const void* k, const void* v, int64_t Lk,
+                           int64_t ldk, int64_t ldv, int heads, float scale, void* out, int64_t ldo,
+                           int key_splits, void* workspace, int64_t workspace_bytes, llnv_stream_t stream);
+int llnv_attention_key_splits(int64_t Lq, int64_t Lk, int heads);
+int64_t llnv_attention_workspace_bytes(int64_t Lq, int heads, int key_splits);
+
 /* Fused epilogue of the W4A4 GEMM.  All pointers are device pointers and optional (NULL = skip).
  * With everything NULL/0 the GEMM writes bf16(alpha * acc), which is what the reference's
  * CUTLASS kernel produces.  The chain follows the reference's rounding points

@@ -53,6 +53,11 @@ struct AttnParams {
   int heads;
   float scale_log2;            // scale * log2(e)
   unsigned int* status;
+  // key splits: CTA z of a (query tile, head) handles a contiguous range of the key tiles and,
+  // when there is more than one split, writes its unnormalised output and (m, l) to the workspace
+  int nsplit;
+  float* part_o;               // [nsplit][Lq][heads][128] fp32
+  float* part_ml;              // [nsplit][Lq][heads][2]   fp32: exponent offset m (raw score units), sum l
 };
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
@@ -84,7 +89,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qt = blockIdx.x, head = blockIdx.y;
-  const int nt = (int)((p.Lk + kBK - 1) / kBK);
+  const int nt_all = (int)((p.Lk + kBK - 1) / kBK);
+  const int j0 = (int)((int64_t)blockIdx.z * nt_all / p.nsplit);                  // first key tile of this split
+  const int nt = (int)((int64_t)(blockIdx.z + 1) * nt_all / p.nsplit) - j0;       // >= 1: the host keeps nsplit <= nt_all
   const int n_half = ((int64_t)qt * kBQ + kHQ < p.Lq) ? 2 : 1;     // the second half may lie entirely beyond Lq
 
   if ((smem_u32(smem) & 1023u) != 0) {
@@ -134,12 +141,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t ph = (uint32_t)((j / kStages) & 1);
         mbar_wait(&k_empty[s], ph ^ 1u, abort_flag, p.status, 100u);
         mbar_arrive_expect_tx(&k_full[s], kTileBytes);
-        tma_load_2d(smem + kKOff + s * kTileBytes, &tmK, col, j * kBK, &k_full[s]);
-        tma_load_2d(smem + kKOff + s * kTileBytes + kHalfBytes, &tmK, col + 64, j * kBK, &k_full[s]);
+        tma_load_2d(smem + kKOff + s * kTileBytes, &tmK, col, (j0 + j) * kBK, &k_full[s]);
+        tma_load_2d(smem + kKOff + s * kTileBytes + kHalfBytes, &tmK, col + 64, (j0 + j) * kBK, &k_full[s]);
         mbar_wait(&v_empty[s], ph ^ 1u, abort_flag, p.status, 101u);
         mbar_arrive_expect_tx(&v_full[s], kTileBytes);
-        tma_load_2d(smem + kVOff + s * kTileBytes, &tmV, col, j * kBK, &v_full[s]);
-        tma_load_2d(smem + kVOff + s * kTileBytes + kHalfBytes, &tmV, col + 64, j * kBK, &v_full[s]);
+        tma_load_2d(smem + kVOff + s * kTileBytes, &tmV, col, (j0 + j) * kBK, &v_full[s]);
+        tma_load_2d(smem + kVOff + s * kTileBytes + kHalfBytes, &tmV, col + 64, (j0 + j) * kBK, &v_full[s]);
       }
     }
   } else if (warp == 1) {
@@ -212,7 +219,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
       for (int g = 0; g < 4; ++g) tmem_ld32(s_tmem + 32 * g, sr[g]);
       tmem_ld_wait();
-      const int valid = (int)min((int64_t)kBK, p.Lk - (int64_t)j * kBK);
+      const int valid = (int)min((int64_t)kBK, p.Lk - (int64_t)(j0 + j) * kBK);
       if (valid < kBK) {                               // only the last key tile can be ragged
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -279,8 +286,27 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // ---- epilogue: O / l -> bf16 -> swizzled staging (the Q tile's shared memory) -> TMA store
     mbar_wait(&pv_done[half], (uint32_t)((nt - 1) & 1), abort_flag, p.status, 302u);
     tc_fence_after();
-    const float inv_l = 1.f / l;
     const int row0 = qt * kBQ + half * kHQ + q * 32;
+    if (p.part_o) {
+      // one of several key splits: unnormalised fp32 output and (m, l) for the combine kernel
+      const int64_t grow = (int64_t)row0 + lane;
+      const int64_t slot = ((int64_t)blockIdx.z * p.Lq + grow) * p.heads + head;
+      float4* dst = reinterpret_cast<float4*>(p.part_o + slot * kD);
+#pragma unroll 1
+      for (int g = 0; g < 4; ++g) {
+        uint32_t o[32];
+        tmem_ld32(tmem_base + lane_base + kOCol + 128 * half + 32 * g, o);
+        tmem_ld_wait();
+        if (grow < p.Lq) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            dst[g * 8 + i] = make_float4(__uint_as_float(o[4 * i]), __uint_as_float(o[4 * i + 1]), __uint_as_float(o[4 * i + 2]),
+                                         __uint_as_float(o[4 * i + 3]));
+        }
+      }
+      if (grow < p.Lq) *reinterpret_cast<float2*>(p.part_ml + slot * 2) = make_float2(m, l);
+    } else {
+    const float inv_l = 1.f / l;
 #pragma unroll 1
     for (int dh = 0; dh < 2; ++dh) {
       uint32_t o[2][32];
@@ -309,6 +335,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     if (lane == 0) bulk_wait<0>();
     }
+    }
   }
 
   // ---------------------------------------------------------------------- teardown
@@ -324,15 +351,72 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 }
 
+// Merges the key splits: out = sum_z 2^((m_z - M) c) O_z / sum_z 2^((m_z - M) c) l_z with M = max_z m_z.
+// One warp per (query row, head); a lane owns four of the 128 channels.
+__global__ void __launch_bounds__(256) attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                                                int nsplit, int64_t Lq, int heads, float scale_log2,
+                                                                uint16_t* __restrict__ out, int64_t ldo) {
+  const int64_t unit = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);      // row * heads + head
+  const int lane = threadIdx.x & 31;
+  if (unit >= Lq * heads) return;
+  const int64_t stride = Lq * heads;
+  float mmax = -INFINITY;
+  for (int z = 0; z < nsplit; ++z) mmax = fmaxf(mmax, __ldg(part_ml + (z * stride + unit) * 2));
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float lsum = 0.f;
+  for (int z = 0; z < nsplit; ++z) {
+    const float2 ml = __ldg(reinterpret_cast<const float2*>(part_ml + (z * stride + unit) * 2));
+    const float w = exp2f((ml.x - mmax) * scale_log2);
+    const float4 o = __ldg(reinterpret_cast<const float4*>(part_o + (z * stride + unit) * kD) + lane);
+    acc.x = __fmaf_rn(w, o.x, acc.x);
+    acc.y = __fmaf_rn(w, o.y, acc.y);
+    acc.z = __fmaf_rn(w, o.z, acc.z);
+    acc.w = __fmaf_rn(w, o.w, acc.w);
+    lsum = __fmaf_rn(w, ml.y, lsum);
+  }
+  const float inv = 1.f / lsum;
+  const int64_t row = unit / heads;
+  const int head = (int)(unit % heads);
+  uint2 packed;
+  packed.x = pack2(acc.x * inv, acc.y * inv);
+  packed.y = pack2(acc.z * inv, acc.w * inv);
+  *reinterpret_cast<uint2*>(out + row * ldo + (int64_t)head * kD + lane * 4) = packed;
+}
+
 }  // namespace
 }  // namespace llnv
 
 using namespace llnv;
 
-extern "C" int llnv_attention_bf16(const void* q, int64_t Lq, int64_t ldq, const void* k, const void* v, int64_t Lk,
-                                   int64_t ldk, int64_t ldv, int heads, float scale, void* out, int64_t ldo,
-                                   llnv_stream_t stream_) {
+extern "C" int llnv_attention_key_splits(int64_t Lq, int64_t Lk, int heads) {
+  if (Lq <= 0 || Lk <= 0 || heads <= 0) return 1;
+  const int64_t ctas = ((Lq + kBQ - 1) / kBQ) * heads;
+  const int64_t nt = (Lk + kBK - 1) / kBK;
+  const int sms = sm_count();
+  if (sms <= 0 || 2 * ctas > sms) return 1;                 // the grid already fills most of the device
+  int64_t splits = sms / ctas;
+  // every split should still run a few key tiles, so that the set-up and the combine pass stay small
+  splits = splits < nt / 4 ? splits : nt / 4;
+  splits = splits < 16 ? splits : 16;
+  return (int)(splits < 1 ? 1 : splits);
+}
+
+extern "C" int64_t llnv_attention_workspace_bytes(int64_t Lq, int heads, int key_splits) {
+  if (key_splits <= 1 || Lq <= 0 || heads <= 0) return 0;
+  return (int64_t)key_splits * Lq * heads * (kD + 2) * (int64_t)sizeof(float);
+}
+
+extern "C" int llnv_attention_bf16_ex(const void* q, int64_t Lq, int64_t ldq, const void* k, const void* v, int64_t Lk,
+                                      int64_t ldk, int64_t ldv, int heads, float scale, void* out, int64_t ldo,
+                                      int key_splits, void* workspace, int64_t workspace_bytes, llnv_stream_t stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
+  LLNV_REQUIRE(key_splits >= 1 && key_splits <= 64, "llnv_attention_bf16: key_splits must be in 1..64 (got %d)", key_splits);
+  LLNV_REQUIRE(Lk <= 0 || key_splits <= (Lk + kBK - 1) / kBK, "llnv_attention_bf16: more key splits (%d) than key tiles of 128", key_splits);
+  if (key_splits > 1) {
+    LLNV_REQUIRE(workspace != nullptr && ((uintptr_t)workspace & 15) == 0 &&
+                     workspace_bytes >= llnv_attention_workspace_bytes(Lq, heads, key_splits),
+                 "llnv_attention_bf16: key splits need a 16-byte aligned workspace of llnv_attention_workspace_bytes() bytes");
+  }
   LLNV_REQUIRE(q && k && v && out, "llnv_attention_bf16: null pointer");
   LLNV_REQUIRE(Lq >= 0 && Lk > 0 && heads > 0, "llnv_attention_bf16: need Lq >= 0, Lk > 0, heads > 0 (Lq=%lld Lk=%lld heads=%d)",
                (long long)Lq, (long long)Lk, heads);
@@ -365,7 +449,21 @@ extern "C" int llnv_attention_bf16(const void* q, int64_t Lq, int64_t ldq, const
   p.heads = heads;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = device_status_word();
-  dim3 grid((unsigned)((Lq + kBQ - 1) / kBQ), (unsigned)heads);
+  p.nsplit = key_splits;
+  p.part_o = key_splits > 1 ? (float*)workspace : nullptr;
+  p.part_ml = key_splits > 1 ? (float*)workspace + (int64_t)key_splits * Lq * heads * kD : nullptr;
+  dim3 grid((unsigned)((Lq + kBQ - 1) / kBQ), (unsigned)heads, (unsigned)key_splits);
   attention_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmQ, tmK, tmV, tmO, p);
-  return launch_status("attention_kernel");
+  int st = launch_status("attention_kernel");
+  if (st != LLNV_OK || key_splits == 1) return st;
+  const int64_t units = Lq * heads;
+  attention_combine_kernel<<<(unsigned)((units + 7) / 8), 256, 0, stream>>>(p.part_o, p.part_ml, key_splits, Lq, heads, p.scale_log2,
+                                                                           (uint16_t*)out, ldo);
+  return launch_status("attention_combine_kernel");
+}
+
+extern "C" int llnv_attention_bf16(const void* q, int64_t Lq, int64_t ldq, const void* k, const void* v, int64_t Lk,
+                                   int64_t ldk, int64_t ldv, int heads, float scale, void* out, int64_t ldo,
+                                   llnv_stream_t stream) {
+  return llnv_attention_bf16_ex(q, Lq, ldq, k, v, Lk, ldk, ldv, heads, scale, out, ldo, 1, nullptr, 0, stream);
 }

@@ -88,3 +88,31 @@ def test_window_attention_with_nvfp4_cache():
     ref = O.window_attention(q.float().numpy(), k_new.float().numpy(), v_new.float().numpy(),
                              [trip(t) for t in kq], [trip(t) for t in vq], heads, T)
     check(out, ref.reshape(lq, -1))
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 5])
+def test_attention_key_splits(splits):
+    """Every split count gives the single-pass result (ragged last key tile, ragged query tile,
+    keys whose scores grow along the window so the splits end with very different maxima)."""
+    lq, lk, heads = 300, 5 * 128 + 37, 2
+    g = torch.Generator().manual_seed(17)
+    q = torch.randn(lq, heads, 128, generator=g).bfloat16()
+    k = (torch.randn(lk, heads, 128, generator=g) * torch.linspace(0.2, 2.5, lk)[:, None, None]).bfloat16()
+    v = torch.randn(lk, heads, 128, generator=g).bfloat16()
+    out = ops.attention_bf16(q.reshape(lq, -1).cuda(), k.reshape(lk, -1).cuda(), v.reshape(lk, -1).cuda(), heads, key_splits=splits)
+    torch.cuda.synchronize()
+    assert _lib.lib().llnv_check_status(None) == 0, _lib.lib().llnv_last_error()
+    ref = O.attention(q.float().numpy(), k.float().numpy(), v.float().numpy())
+    check(out, ref.reshape(lq, -1))
+
+
+def test_attention_key_split_arguments():
+    lib = _lib.lib()
+    q = torch.zeros(128, 128, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="more key splits"):
+        ops.attention_bf16(q, q, q, 1, key_splits=2)               # one key tile cannot be split
+    assert lib.llnv_attention_workspace_bytes(2640, 3, 1) == 0
+    assert lib.llnv_attention_workspace_bytes(2640, 3, 4) == 4 * 2640 * 3 * 130 * 4
+    # the full-size single-GPU call fills the device by itself; an 8-way head shard of it does not
+    assert lib.llnv_attention_key_splits(2640, 13200, 24) == 1
+    assert lib.llnv_attention_key_splits(2640, 13200, 3) > 1
