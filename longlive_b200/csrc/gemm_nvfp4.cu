@@ -342,6 +342,8 @@ extern "C" int llnv_gemm_nvfp4(const void* a_codes, const void* a_sf, const floa
   if (M == 0) return LLNV_OK;
 
   int bn = (N % 256 == 0) ? 256 : 128;
+  // few tokens (a sequence-parallel shard): 256-wide tiles would leave SMs idle, 128-wide tiles double the grid
+  if (bn == 256 && ((M + 127) / 128) * (N / 256) * 2 <= (int64_t)sm_count() + 8) bn = 128;
   if (g_forced_bn == 128) bn = 128;
   if (g_forced_bn == 256 && N % 256 == 0) bn = 256;
 
