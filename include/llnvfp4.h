@@ -172,11 +172,15 @@ int llnv_attention_bf16(const void* q, int64_t Lq, int64_t ldq, const void* k, c
  * ceil(Lq / 256) * heads / P tiles.  Every split attends to a contiguous range of 128-key tiles
  * and writes unnormalised fp32 partial outputs plus (row maximum, row sum) to `workspace`; a
  * second small kernel merges them.  key_splits = 1 is llnv_attention_bf16 (no workspace).
+ * out_amax (optional, device fp32) receives max |out| over the written elements: the tensor scale
+ * of the quantizer that follows (utils/quant.py quantize_to_fp4 on the attention output) without
+ * a separate reduction pass.
  * llnv_attention_key_splits() proposes a split count for the current device (1 when the tiles
  * already fill it); llnv_attention_workspace_bytes() is the workspace size for a split count. */
 int llnv_attention_bf16_ex(const void* q, int64_t Lq, int64_t ldq, const void* k, const void* v, int64_t Lk,
                            int64_t ldk, int64_t ldv, int heads, float scale, void* out, int64_t ldo,
-                           int key_splits, void* workspace, int64_t workspace_bytes, llnv_stream_t stream);
+                           int key_splits, void* workspace, int64_t workspace_bytes, float* out_amax,
+                           llnv_stream_t stream);
 int llnv_attention_key_splits(int64_t Lq, int64_t Lk, int heads);
 int64_t llnv_attention_workspace_bytes(int64_t Lq, int heads, int key_splits);
 

@@ -56,7 +56,7 @@ def lib() -> C.CDLL:
         l.llnv_adaln_quantize_nvfp4_static.argtypes = [p, i64, i64, i64, p, p, i64, i32, f32, i32, i32, p, p, p, p, i64, p]
         l.llnv_static_max_rows.restype = C.c_int64
         l.llnv_attention_bf16.argtypes = [p, i64, i64, p, p, i64, i64, i64, i32, f32, p, i64, p]
-        l.llnv_attention_bf16_ex.argtypes = [p, i64, i64, p, p, i64, i64, i64, i32, f32, p, i64, i32, p, i64, p]
+        l.llnv_attention_bf16_ex.argtypes = [p, i64, i64, p, p, i64, i64, i64, i32, f32, p, i64, i32, p, i64, p, p]
         l.llnv_attention_key_splits.argtypes = [i64, i64, i32]
         l.llnv_attention_workspace_bytes.argtypes = [i64, i32, i32]
         l.llnv_attention_workspace_bytes.restype = C.c_int64

@@ -58,6 +58,7 @@ struct AttnParams {
   int nsplit;
   float* part_o;               // [nsplit][Lq][heads][128] fp32
   float* part_ml;              // [nsplit][Lq][heads][2]   fp32: exponent offset m (raw score units), sum l
+  float* out_amax;             // optional: max |out| over all written elements (zeroed by the host before the launch)
 };
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
@@ -307,6 +308,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (grow < p.Lq) *reinterpret_cast<float2*>(p.part_ml + slot * 2) = make_float2(m, l);
     } else {
     const float inv_l = 1.f / l;
+    uint32_t amax2 = 0u;          // packed running max of |out| (bf16 pairs; the magnitudes compare as integers)
 #pragma unroll 1
     for (int dh = 0; dh < 2; ++dh) {
       uint32_t o[2][32];
@@ -323,6 +325,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(o[cc >> 5][cc & 31]) * inv_l,
                                                           __uint_as_float(o[(cc + 1) >> 5][(cc + 1) & 31]) * inv_l);
           w[e] = *reinterpret_cast<const uint32_t*>(&b2);
+          amax2 = __vmaxu2(amax2, w[e] & 0x7FFF7FFFu);
         }
         *reinterpret_cast<uint4*>(buf + lane * 128 + ((v8 ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
@@ -332,6 +335,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tma_store_2d(&tmO, buf, head * kD + dh * 64, row0);
         bulk_commit();
       }
+    }
+    if (p.out_amax) {
+      // rows at or beyond Lq are not written (the TMA store clips them) and must not count
+      float a = row0 + lane < p.Lq ? __uint_as_float(max(amax2 & 0xFFFFu, amax2 >> 16) << 16) : 0.f;
+      a = warp_max(a);
+      if (lane == 0 && a > 0.f) atomic_max_nonneg(p.out_amax, a);
     }
     if (lane == 0) bulk_wait<0>();
     }
@@ -355,7 +364,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 // One warp per (query row, head); a lane owns four of the 128 channels.
 __global__ void __launch_bounds__(256) attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                                 int nsplit, int64_t Lq, int heads, float scale_log2,
-                                                                uint16_t* __restrict__ out, int64_t ldo) {
+                                                                uint16_t* __restrict__ out, int64_t ldo, float* __restrict__ out_amax) {
   const int64_t unit = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);      // row * heads + head
   const int lane = threadIdx.x & 31;
   if (unit >= Lq * heads) return;
@@ -381,6 +390,11 @@ __global__ void __launch_bounds__(256) attention_combine_kernel(const float* __r
   packed.x = pack2(acc.x * inv, acc.y * inv);
   packed.y = pack2(acc.z * inv, acc.w * inv);
   *reinterpret_cast<uint2*>(out + row * ldo + (int64_t)head * kD + lane * 4) = packed;
+  if (out_amax) {
+    const uint32_t m2 = __vmaxu2(packed.x & 0x7FFF7FFFu, packed.y & 0x7FFF7FFFu);
+    const float a = warp_max(__uint_as_float(max(m2 & 0xFFFFu, m2 >> 16) << 16));
+    if (lane == 0 && a > 0.f) atomic_max_nonneg(out_amax, a);
+  }
 }
 
 }  // namespace
@@ -408,7 +422,8 @@ extern "C" int64_t llnv_attention_workspace_bytes(int64_t Lq, int heads, int key
 
 extern "C" int llnv_attention_bf16_ex(const void* q, int64_t Lq, int64_t ldq, const void* k, const void* v, int64_t Lk,
                                       int64_t ldk, int64_t ldv, int heads, float scale, void* out, int64_t ldo,
-                                      int key_splits, void* workspace, int64_t workspace_bytes, llnv_stream_t stream_) {
+                                      int key_splits, void* workspace, int64_t workspace_bytes, float* out_amax,
+                                      llnv_stream_t stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   LLNV_REQUIRE(key_splits >= 1 && key_splits <= 64, "llnv_attention_bf16: key_splits must be in 1..64 (got %d)", key_splits);
   LLNV_REQUIRE(Lk <= 0 || key_splits <= (Lk + kBK - 1) / kBK, "llnv_attention_bf16: more key splits (%d) than key tiles of 128", key_splits);
@@ -426,6 +441,7 @@ extern "C" int llnv_attention_bf16_ex(const void* q, int64_t Lq, int64_t ldq, co
   LLNV_REQUIRE(((uintptr_t)q & 15) == 0 && ((uintptr_t)k & 15) == 0 && ((uintptr_t)v & 15) == 0 && ((uintptr_t)out & 15) == 0,
                "llnv_attention_bf16: pointers must be 16-byte aligned");
   LLNV_REQUIRE(heads <= 65535, "llnv_attention_bf16: too many heads");
+  if (out_amax) LLNV_CUDA(cudaMemsetAsync(out_amax, 0, sizeof(float), stream));
   if (Lq == 0) return LLNV_OK;
   CUtensorMap tmQ, tmK, tmV, tmO;
   int rc = cached_tensor_map(&tmQ, 1, q, (uint64_t)Lq, (uint64_t)C, (uint64_t)ldq, 128, 64, 3);
@@ -452,18 +468,19 @@ extern "C" int llnv_attention_bf16_ex(const void* q, int64_t Lq, int64_t ldq, co
   p.nsplit = key_splits;
   p.part_o = key_splits > 1 ? (float*)workspace : nullptr;
   p.part_ml = key_splits > 1 ? (float*)workspace + (int64_t)key_splits * Lq * heads * kD : nullptr;
+  p.out_amax = key_splits > 1 ? nullptr : out_amax;
   dim3 grid((unsigned)((Lq + kBQ - 1) / kBQ), (unsigned)heads, (unsigned)key_splits);
   attention_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmQ, tmK, tmV, tmO, p);
   int st = launch_status("attention_kernel");
   if (st != LLNV_OK || key_splits == 1) return st;
   const int64_t units = Lq * heads;
   attention_combine_kernel<<<(unsigned)((units + 7) / 8), 256, 0, stream>>>(p.part_o, p.part_ml, key_splits, Lq, heads, p.scale_log2,
-                                                                           (uint16_t*)out, ldo);
+                                                                           (uint16_t*)out, ldo, out_amax);
   return launch_status("attention_combine_kernel");
 }
 
 extern "C" int llnv_attention_bf16(const void* q, int64_t Lq, int64_t ldq, const void* k, const void* v, int64_t Lk,
                                    int64_t ldk, int64_t ldv, int heads, float scale, void* out, int64_t ldo,
                                    llnv_stream_t stream) {
-  return llnv_attention_bf16_ex(q, Lq, ldq, k, v, Lk, ldk, ldv, heads, scale, out, ldo, 1, nullptr, 0, stream);
+  return llnv_attention_bf16_ex(q, Lq, ldq, k, v, Lk, ldk, ldv, heads, scale, out, ldo, 1, nullptr, 0, nullptr, stream);
 }

@@ -140,11 +140,13 @@ class KVCache:
         self.v = [[mk() for _ in range(cfg.max_blocks)] for _ in range(cfg.layers)]
         self.order = list(range(cfg.max_blocks))
         self.filled = 0                       # number of valid blocks, current chunk included
+        self.version = 0                      # bumped whenever the set of past blocks changes
         self.cfg = cfg
 
     def begin_chunk(self) -> None:
         """Make room for a new chunk: grow until full, then evict the oldest non-sink block."""
         cfg = self.cfg
+        self.version += 1
         if self.filled < cfg.max_blocks:
             self.filled += 1
             return
@@ -205,8 +207,14 @@ class CausalDiT:
         self.cq_buf, self.cq_n = bf(Sl, c), bf(Sl, c)
         self.ck_buf, self.cv_buf, self.ck_n = bf(cfg.text_len, c), bf(cfg.text_len, c), bf(cfg.text_len, c)
         self.cattn = bf(Sl, c)
+        # One bf16 attention window per layer.  The past blocks of a window do not change during
+        # the forwards of a chunk, so they are dequantized from the NVFP4 cache once per chunk (by the
+        # first forward after the block table moved) instead of once per forward as the reference does
+        # (causal_model.py:591-600); 2 x 81 MB per layer at full size.
         Lk = cfg.window_frames * cfg.frame_tokens
-        self.win_k, self.win_v = bf(Lk, self.Cl), bf(Lk, self.Cl)
+        self.win_k = [bf(Lk, self.Cl) for _ in range(cfg.layers)]
+        self.win_v = [bf(Lk, self.Cl) for _ in range(cfg.layers)]
+        self._window_version = -1             # cache.version whose past blocks the windows hold
         self.kv_amax = torch.zeros(2, dtype=torch.float32, device=dev)      # [k, v]: reduced with one collective
         self.k_amax, self.v_amax = self.kv_amax[0:1], self.kv_amax[1:2]
         self.h_amax = torch.zeros(1, dtype=torch.float32, device=dev)
@@ -228,11 +236,18 @@ class CausalDiT:
         return ops.gemm_nvfp4(act.codes, act.sf, act.amax, MSE, lin.q.values, lin.q.scale_factors, lin.q.amax, MSE,
                               rows, lin.out_f, lin.in_f, out=out, bias=lin.bias, **epi)
 
-    def _quantize(self, x, act: _Act, amax_given: bool = False):
-        if self.sync_amax and not amax_given:
-            ops.amax_bf16(x, act.amax)
-            sp.allreduce_max_(act.amax, self.group)
-            amax_given = True
+    def _quantize(self, x, act: _Act, amax_given: bool = False, have_local_amax: bool = False):
+        """NVFP4-quantize x into ``act``.  ``amax_given``: act.amax already holds the final tensor
+        amax.  ``have_local_amax``: act.amax holds this rank's amax of exactly the rows of x (written
+        by the producing kernel's epilogue), which only needs the group reduction, if any."""
+        if not amax_given:
+            if self.sync_amax:
+                if not have_local_amax:
+                    ops.amax_bf16(x, act.amax)
+                sp.allreduce_max_(act.amax, self.group)
+                amax_given = True
+            elif have_local_amax:
+                amax_given = True
         ops.quantize_nvfp4(x, MSE, act.amax, act.codes, act.sf, amax_given=amax_given)
 
     def _adaln_quantize(self, x, scale, shift, act: _Act):
@@ -290,9 +305,10 @@ class CausalDiT:
         self._gemm(self.act_c, Sl, blk.k, self.k_buf)
         n_past = len(cache.past_slots())
         T = cfg.chunk_tokens
+        win_k, win_v = self.win_k[li], self.win_v[li]
         if self.P == 1:
-            v_dst = self.win_v[n_past * T:(n_past + 1) * T]
-            ks_dst = self.win_k[n_past * T:(n_past + 1) * T]
+            v_dst = win_v[n_past * T:(n_past + 1) * T]
+            ks_dst = win_k[n_past * T:(n_past + 1) * T]
         else:
             v_dst, ks_dst = self.v_buf, self.k_smooth
         self.v_amax.zero_()
@@ -304,21 +320,25 @@ class CausalDiT:
             if self.sync_amax:
                 sp.allreduce_max_(self.kv_amax, self.group)
             q_h, ks_h, kr_h, v_h = sp.seq_to_head_many([self.q_rot, self.k_smooth, self.k_rot, self.v_buf], self.group)
-            self.win_k[n_past * T:(n_past + 1) * T].copy_(ks_h)
-            self.win_v[n_past * T:(n_past + 1) * T].copy_(v_h)
+            win_k[n_past * T:(n_past + 1) * T].copy_(ks_h)
+            win_v[n_past * T:(n_past + 1) * T].copy_(v_h)
             k_for_cache, v_for_cache = kr_h, v_h
         else:
             q_h, k_for_cache, v_for_cache = self.q_rot, self.k_rot, v_dst
-        if n_past:
+        if n_past and self._window_version != cache.version:
             slots = cache.past_slots()
             ops.kv_dequant([cache.k[li][s].values for s in slots], [cache.k[li][s].scale_factors for s in slots],
                            [cache.k[li][s].amax for s in slots], self.Hl, T, torch.bfloat16, 6, 256, ops.DEQ_FUSED,
-                           out=self.win_k[: n_past * T])
+                           out=win_k[: n_past * T])
             ops.kv_dequant([cache.v[li][s].values for s in slots], [cache.v[li][s].scale_factors for s in slots],
                            [cache.v[li][s].amax for s in slots], self.Hl, T, torch.bfloat16, 6, 256, ops.DEQ_FUSED,
-                           out=self.win_v[: n_past * T])
+                           out=win_v[: n_past * T])
         lk = (n_past + 1) * T
-        ops.attention_bf16(q_h, self.win_k[:lk], self.win_v[:lk], self.Hl, out=self.attn_out)
+        # The attention epilogue also produces max |out|.  Across a sequence-parallel group that is
+        # the amax of (all tokens, my heads), which bounds the (my tokens, all heads) tensor quantized
+        # after the exchange only once it is MAX-reduced, so it is used on one GPU or with sync_amax.
+        fused_amax = self.P == 1 or self.sync_amax
+        ops.attention_bf16(q_h, win_k[:lk], win_v[:lk], self.Hl, out=self.attn_out, out_amax=self.act_c.amax if fused_amax else None)
         # cache write: rotated (un-smoothed) keys and values of the chunk, straight into the slot
         cur = cache.current_slot()
         ck, cv = cache.k[li][cur], cache.v[li][cur]
@@ -327,7 +347,7 @@ class CausalDiT:
         ops.quantize_nvfp4(k_for_cache.reshape(S * self.Hl, 128), MSE, ck.amax, ck.values, ck.scale_factors, amax_given=True)
         ops.quantize_nvfp4(v_for_cache.reshape(S * self.Hl, 128), MSE, cv.amax, cv.values, cv.scale_factors, amax_given=True)
         attn = sp.head_to_seq(self.attn_out, self.group, out=self.attn_seq) if self.P > 1 else self.attn_out
-        self._quantize(attn, self.act_c)
+        self._quantize(attn, self.act_c, have_local_amax=fused_amax)
         x1, x2 = self.x1, self.x2
         self._gemm(self.act_c, Sl, blk.o, x1, residual=x, gate=e[:, 2], frame_rows=ft, row_offset=roff)
         # -- cross attention
@@ -335,8 +355,8 @@ class CausalDiT:
         self._gemm(self.act_c, Sl, blk.cq, self.cq_buf)
         ops.rmsnorm_rope(self.cq_buf, blk.cnorm_q, eps=cfg.eps, out=self.cq_n)
         kn, v = self._text_kv(li, blk, ctx)
-        ops.attention_bf16(self.cq_n, kn, v, cfg.heads, out=self.cattn)
-        self._quantize(self.cattn, self.act_c)
+        ops.attention_bf16(self.cq_n, kn, v, cfg.heads, out=self.cattn, out_amax=self.act_c.amax)
+        self._quantize(self.cattn, self.act_c, have_local_amax=True)
         self._gemm(self.act_c, Sl, blk.co, x2, residual=x1)
         # -- FFN
         self._adaln_quantize(x2, e[:, 4], e[:, 3], self.act_c)
@@ -382,14 +402,19 @@ class CausalDiT:
         set-up such as the text K/V and the communicators must not happen inside a capture)."""
         self._set_rope(start_frame)
         if not self.use_graphs:
-            return self._forward_impl(latent_tokens, t, ctx)
+            out = self._forward_impl(latent_tokens, t, ctx)
+            self._window_version = self.cache.version
+            return out
         self.g_lat.copy_(latent_tokens)
         self.g_t.copy_(t)
-        key = (tuple(self.cache.order), self.cache.filled, ctx.data_ptr())
+        fresh = self._window_version != self.cache.version        # this forward also dequantizes the past blocks
+        key = (tuple(self.cache.order), self.cache.filled, ctx.data_ptr(), fresh)
         entry = self._graphs.get(key)
         if entry is None:
             if not self._ran_eager or self.cache.filled < self.cfg.max_blocks:
-                return self._forward_impl(self.g_lat, self.g_t, ctx)
+                out = self._forward_impl(self.g_lat, self.g_t, ctx)
+                self._window_version = self.cache.version
+                return out
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
             graph = torch.cuda.CUDAGraph()
@@ -398,6 +423,7 @@ class CausalDiT:
                 out = self._forward_impl(self.g_lat, self.g_t, ctx)
             entry = self._graphs[key] = (graph, out)
         entry[0].replay()
+        self._window_version = self.cache.version
         return entry[1]
 
     def close(self) -> None:

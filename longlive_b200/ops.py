@@ -150,11 +150,11 @@ def rmsnorm_rope(x, weight=None, cos=None, sin=None, eps=1e-6, *, out=None, out_
     return out, out_smooth, amax_out
 
 
-def attention_bf16(q, k, v, heads, scale=None, out=None, key_splits=None):
+def attention_bf16(q, k, v, heads, scale=None, out=None, key_splits=None, out_amax=None):
     """softmax(q k^T * scale) v per head, non-causal.  q: bf16 [Lq, heads*128]; k, v: bf16 [Lk, heads*128]
     (row strides free, unit column stride).  Returns bf16 [Lq, heads*128].  ``key_splits`` > 1 splits
     the key window over several CTAs per query tile (default: what the library proposes for the
-    device, 1 unless the tiles alone leave most SMs idle)."""
+    device, 1 unless the tiles alone leave most SMs idle).  ``out_amax`` (fp32 [1]) receives max |out|."""
     _require_cuda(q, "q")
     for name, t in (("q", q), ("k", k), ("v", v)):
         if t.dim() != 2 or t.dtype != torch.bfloat16 or t.stride(1) != 1 or t.shape[1] != heads * 128:
@@ -175,7 +175,8 @@ def attention_bf16(q, k, v, heads, scale=None, out=None, key_splits=None):
             ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
         _check(lib.llnv_attention_bf16_ex(q.data_ptr(), q.shape[0], q.stride(0), k.data_ptr(), v.data_ptr(), k.shape[0],
                                           k.stride(0), v.stride(0), heads, float(scale), out.data_ptr(), out.stride(0),
-                                          int(key_splits), ws.data_ptr() if ws is not None else None, ws_bytes, _stream(q)))
+                                          int(key_splits), ws.data_ptr() if ws is not None else None, ws_bytes,
+                                          out_amax.data_ptr() if out_amax is not None else None, _stream(q)))
     return out
 
 

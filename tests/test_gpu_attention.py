@@ -116,3 +116,18 @@ def test_attention_key_split_arguments():
     # the full-size single-GPU call fills the device by itself; an 8-way head shard of it does not
     assert lib.llnv_attention_key_splits(2640, 13200, 24) == 1
     assert lib.llnv_attention_key_splits(2640, 13200, 3) > 1
+
+
+@pytest.mark.parametrize("lq,splits", [(300, 1), (300, 3), (256, 1)])
+def test_attention_output_amax(lq, splits):
+    """The epilogue's amax is exactly the maximum magnitude of the bf16 output (rows beyond Lq of
+    the last query tile, which are computed but never stored, do not count)."""
+    lk, heads = 4 * 128 + 5, 2
+    g = torch.Generator().manual_seed(23)
+    q = torch.randn(lq, heads * 128, generator=g).bfloat16().cuda()
+    k = torch.randn(lk, heads * 128, generator=g).bfloat16().cuda()
+    v = (torch.randn(lk, heads * 128, generator=g) * 3).bfloat16().cuda()
+    amax = torch.full((1,), 123.0, dtype=torch.float32, device="cuda")
+    out = ops.attention_bf16(q, k, v, heads, key_splits=splits, out_amax=amax)
+    torch.cuda.synchronize()
+    assert float(amax.item()) == float(out.float().abs().max().item())
