@@ -74,6 +74,15 @@ int llnv_amax_bf16(const void* x, int64_t M, int64_t K, int64_t ldx, float* amax
 int llnv_quantize_nvfp4(const void* x, int64_t M, int64_t K, int64_t ldx, int rule,
                         void* codes, void* sf, float* amax, int amax_given, llnv_stream_t stream);
 
+/* The same quantizer reading a column-sharded activation: x is [shards][M][K / shards] (row stride
+ * ldx inside a shard, shards M * ldx elements apart), which is how the head -> token exchange of
+ * sequence parallelism delivers the attention output (ulysses_head_to_seq,
+ * wan_5b/distributed/sp_ulysses_inference.py:139-154, then permutes it into [M, K]; here the
+ * quantizer reads the received layout directly).  Codes and scales are those of the [M, K] matrix.
+ * shards = 1 is llnv_quantize_nvfp4. */
+int llnv_quantize_nvfp4_ex(const void* x, int64_t M, int64_t K, int64_t ldx, int rule,
+                           void* codes, void* sf, float* amax, int amax_given, int shards, llnv_stream_t stream);
+
 /* adaLN modulation fused into the quantizer: y = LayerNorm(x) (no affine, eps) -> bf16 ->
  * * bf16(1 + scale[f]) -> bf16 -> + shift[f] -> bf16, f = row / frame_rows, then y is quantized as by
  * llnv_quantize_nvfp4 (amax computed here).  Stands in for adaln_modulate_triton
@@ -136,6 +145,14 @@ int llnv_layernorm_quantize_nvfp4(const void* x, int64_t M, int64_t C, int64_t l
 int llnv_rmsnorm_rope(const void* x, int64_t S, int64_t C, int64_t ldx, const void* weight, float eps,
                       const float* cos, const float* sin, void* out, int64_t ldo, void* out_smooth, int64_t lds,
                       float* amax_out, llnv_stream_t stream);
+
+/* The same prologue writing head-sharded outputs: out and out_smooth are [shards][S][C / shards]
+ * (row strides ldo / lds inside a shard, shards S * ldo / S * lds elements apart), the send layout
+ * of the token -> head exchange (ulysses_seq_to_head, sp_ulysses_inference.py:122-137), so that no
+ * pack copy is needed before the all-to-all.  shards = 1 is llnv_rmsnorm_rope. */
+int llnv_rmsnorm_rope_ex(const void* x, int64_t S, int64_t C, int64_t ldx, const void* weight, float eps,
+                         const float* cos, const float* sin, void* out, int64_t ldo, void* out_smooth, int64_t lds,
+                         float* amax_out, int shards, llnv_stream_t stream);
 
 /* Dequantize `num_blocks` KV-cache blocks, each an NVFP4 matrix [rows_padded, 128] holding
  * block_token_size*num_heads logical rows (token-major, head-minor), into one contiguous

@@ -273,6 +273,10 @@ struct Prologue {
   int frame_rows;
   int add_one;
   int64_t row_offset;          // added to the row index before the frame lookup (token shards)
+  // column-sharded input (kPlain): x is [K / shard_cols][M][shard_cols] with row stride ldx inside a
+  // shard and shard_stride elements between shards (the receive layout of the head -> token
+  // exchange of sequence parallelism); 0 = one plain [M][K] matrix
+  int64_t shard_cols, shard_stride;
 };
 
 template <int MODE>
@@ -331,11 +335,12 @@ __global__ void __launch_bounds__(256) quantize_nvfp4_kernel(const uint16_t* __r
   const int64_t col = (int64_t)blockIdx.x * 128 + cb * 16;
   const int64_t row_base = (int64_t)blockIdx.y * 128;
   const bool col_ok = col < K;
+  const int64_t xoff = pr.shard_cols ? (col / pr.shard_cols) * pr.shard_stride + col % pr.shard_cols : col;
 
   auto load_block = [&](int i, uint32_t (&w)[8]) {
     const int64_t r = row_base + r0 + 32 * i;
     if (col_ok && r < M) {
-      const uint4* p = reinterpret_cast<const uint4*>(x + r * ldx + col);
+      const uint4* p = reinterpret_cast<const uint4*>(x + r * ldx + xoff);
       const uint4 a = __ldg(p), b = __ldg(p + 1);
       w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
       w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
@@ -595,11 +600,19 @@ extern "C" int llnv_amax_bf16(const void* x, int64_t M, int64_t K, int64_t ldx, 
 }
 
 extern "C" int llnv_quantize_nvfp4(const void* x, int64_t M, int64_t K, int64_t ldx, int rule, void* codes, void* sf,
-                                   float* amax, int amax_given, llnv_stream_t stream_) {
+                                   float* amax, int amax_given, llnv_stream_t stream) {
+  return llnv_quantize_nvfp4_ex(x, M, K, ldx, rule, codes, sf, amax, amax_given, 1, stream);
+}
+
+extern "C" int llnv_quantize_nvfp4_ex(const void* x, int64_t M, int64_t K, int64_t ldx, int rule, void* codes, void* sf,
+                                      float* amax, int amax_given, int shards, llnv_stream_t stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   LLNV_REQUIRE(x && codes && sf && amax, "llnv_quantize_nvfp4: null pointer");
   LLNV_REQUIRE(M >= 0 && K > 0 && K % 64 == 0, "llnv_quantize_nvfp4: K must be a positive multiple of 64 (got %lld)", (long long)K);
-  LLNV_REQUIRE(ldx >= K && ldx % 8 == 0, "llnv_quantize_nvfp4: ldx must be >= K and a multiple of 8 (got %lld)", (long long)ldx);
+  LLNV_REQUIRE(shards >= 1 && K % shards == 0 && (K / shards) % 16 == 0,
+               "llnv_quantize_nvfp4: shards must divide K into multiples of 16 columns (K=%lld shards=%d)", (long long)K, shards);
+  const int64_t Ks = K / shards;
+  LLNV_REQUIRE(ldx >= Ks && ldx % 8 == 0, "llnv_quantize_nvfp4: ldx must be >= K / shards and a multiple of 8 (got %lld)", (long long)ldx);
   LLNV_REQUIRE(rule >= 0 && rule <= 4, "llnv_quantize_nvfp4: unknown scale rule %d", rule);
   LLNV_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)codes & 7) == 0 && ((uintptr_t)sf & 3) == 0,
                "llnv_quantize_nvfp4: x must be 16-byte, codes 8-byte, sf 4-byte aligned");
@@ -608,13 +621,17 @@ extern "C" int llnv_quantize_nvfp4(const void* x, int64_t M, int64_t K, int64_t 
     return LLNV_OK;
   }
   if (!amax_given) {
-    int rc = llnv_amax_bf16(x, M, K, ldx, amax, stream_);
+    int rc = llnv_amax_bf16(x, M * shards, Ks, ldx, amax, stream_);
     if (rc != LLNV_OK) return rc;
   }
   const int64_t mp = (M + 127) / 128 * 128;
   dim3 grid((unsigned)((K + 127) / 128), (unsigned)(mp / 128));
   LLNV_REQUIRE(mp / 128 <= 65535, "llnv_quantize_nvfp4: too many rows (%lld)", (long long)M);
   Prologue pr = {};
+  if (shards > 1) {
+    pr.shard_cols = Ks;
+    pr.shard_stride = M * ldx;
+  }
   return launch_quantize<kPlain>(rule, grid, stream, (const uint16_t*)x, M, K, ldx, amax, (uint8_t*)codes, (uint8_t*)sf, pr, nullptr, 0);
 }
 

@@ -22,7 +22,8 @@ __global__ void __launch_bounds__(256) rmsnorm_rope_kernel(const uint16_t* __res
                                                            const float* __restrict__ cosv, const float* __restrict__ sinv,
                                                            uint16_t* __restrict__ out, int64_t ldo,
                                                            uint16_t* __restrict__ out_smooth, int64_t lds,
-                                                           float* __restrict__ amax_out) {
+                                                           float* __restrict__ amax_out, int shard_vecs, int64_t shard_stride_o,
+                                                           int64_t shard_stride_s) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * 8 + warp;
   // the norm weight is shared by all rows: one cooperative load per CTA instead of a dependent
@@ -108,7 +109,10 @@ __global__ void __launch_bounds__(256) rmsnorm_rope_kernel(const uint16_t* __res
       uint4 o;
       o.x = pack_bf16x2(y[0], y[1]); o.y = pack_bf16x2(y[2], y[3]);
       o.z = pack_bf16x2(y[4], y[5]); o.w = pack_bf16x2(y[6], y[7]);
-      reinterpret_cast<uint4*>(out + row * ldo)[idx] = o;
+      // head-sharded outputs: 16-byte vector idx lives in shard idx / shard_vecs (a whole number of heads)
+      const int sh = shard_vecs ? idx / shard_vecs : 0;
+      const int vi = shard_vecs ? idx - sh * shard_vecs : idx;
+      reinterpret_cast<uint4*>(out + sh * shard_stride_o + row * ldo)[vi] = o;
       if (out_smooth) {
 #pragma unroll
         for (int sft = 8; sft > 0; sft >>= 1) hsum += __shfl_xor_sync(0xFFFFFFFFu, hsum, sft, 16);
@@ -118,7 +122,7 @@ __global__ void __launch_bounds__(256) rmsnorm_rope_kernel(const uint16_t* __res
         s.y = pack_bf16x2(__fsub_rn(y[2], mean), __fsub_rn(y[3], mean));
         s.z = pack_bf16x2(__fsub_rn(y[4], mean), __fsub_rn(y[5], mean));
         s.w = pack_bf16x2(__fsub_rn(y[6], mean), __fsub_rn(y[7], mean));
-        reinterpret_cast<uint4*>(out_smooth + row * lds)[idx] = s;
+        reinterpret_cast<uint4*>(out_smooth + sh * shard_stride_s + row * lds)[vi] = s;
       }
     }
   }
@@ -143,19 +147,29 @@ using namespace llnv;
 
 extern "C" int llnv_rmsnorm_rope(const void* x, int64_t S, int64_t C, int64_t ldx, const void* weight, float eps,
                                  const float* cos, const float* sin, void* out, int64_t ldo, void* out_smooth, int64_t lds,
-                                 float* amax_out, llnv_stream_t stream_) {
+                                 float* amax_out, llnv_stream_t stream) {
+  return llnv_rmsnorm_rope_ex(x, S, C, ldx, weight, eps, cos, sin, out, ldo, out_smooth, lds, amax_out, 1, stream);
+}
+
+extern "C" int llnv_rmsnorm_rope_ex(const void* x, int64_t S, int64_t C, int64_t ldx, const void* weight, float eps,
+                                    const float* cos, const float* sin, void* out, int64_t ldo, void* out_smooth, int64_t lds,
+                                    float* amax_out, int shards, llnv_stream_t stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
+  LLNV_REQUIRE(shards >= 1 && C % shards == 0 && (C / shards) % 128 == 0,
+               "llnv_rmsnorm_rope: shards must divide the channels into whole heads (C=%lld shards=%d)", (long long)C, shards);
+  const int64_t Cs = C / shards;
   LLNV_REQUIRE(x && out, "llnv_rmsnorm_rope: null pointer");
   LLNV_REQUIRE((cos == nullptr) == (sin == nullptr), "llnv_rmsnorm_rope: cos and sin must be given together");
   LLNV_REQUIRE(S >= 0 && C > 0 && C % 128 == 0 && C <= 4096, "llnv_rmsnorm_rope: C must be a multiple of 128 (head_dim 128) and at most 4096 (got %lld)", (long long)C);
-  LLNV_REQUIRE(ldx >= C && ldx % 8 == 0 && ldo >= C && ldo % 8 == 0, "llnv_rmsnorm_rope: row strides must be >= C and multiples of 8");
+  LLNV_REQUIRE(ldx >= C && ldx % 8 == 0 && ldo >= Cs && ldo % 8 == 0, "llnv_rmsnorm_rope: row strides must be >= the row width and multiples of 8");
   LLNV_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)weight & 15) == 0 && ((uintptr_t)cos & 15) == 0 &&
                    ((uintptr_t)sin & 15) == 0,
                "llnv_rmsnorm_rope: pointers must be 16-byte aligned");
-  if (out_smooth) LLNV_REQUIRE(lds >= C && lds % 8 == 0 && ((uintptr_t)out_smooth & 15) == 0, "llnv_rmsnorm_rope: out_smooth must be 16-byte aligned with a row stride that is a multiple of 8");
+  if (out_smooth) LLNV_REQUIRE(lds >= Cs && lds % 8 == 0 && ((uintptr_t)out_smooth & 15) == 0, "llnv_rmsnorm_rope: out_smooth must be 16-byte aligned with a row stride that is a multiple of 8");
   if (amax_out) LLNV_CUDA(cudaMemsetAsync(amax_out, 0, sizeof(float), stream));
   if (S == 0) return LLNV_OK;
   rmsnorm_rope_kernel<<<(unsigned)((S + 7) / 8), 256, 0, stream>>>((const uint16_t*)x, S, C, ldx, (const uint16_t*)weight, eps, cos, sin,
-                                                                  (uint16_t*)out, ldo, (uint16_t*)out_smooth, lds, amax_out);
+                                                                  (uint16_t*)out, ldo, (uint16_t*)out_smooth, lds, amax_out,
+                                                                  shards > 1 ? (int)(Cs / 8) : 0, S * ldo, S * lds);
   return launch_status("rmsnorm_rope_kernel");
 }

@@ -201,7 +201,13 @@ class CausalDiT:
         self.q_buf, self.k_buf, self.v_buf = bf(Sl, c), bf(Sl, c), bf(Sl, c)
         self.q_rot, self.k_rot, self.k_smooth = bf(Sl, c), bf(Sl, c), bf(Sl, c)
         self.attn_out = bf(S, self.Cl)
-        self.attn_seq = bf(Sl, c)
+        if self.P > 1:
+            # send / receive layouts of the two exchanges: [rank][my tokens][that rank's heads] and
+            # [all tokens][my heads]; written and read in place by the kernels on either side
+            P_, Cl_ = self.P, self.Cl
+            self.q_sh, self.kr_sh, self.ks_sh, self.v_sh = bf(P_, Sl, Cl_), bf(P_, Sl, Cl_), bf(P_, Sl, Cl_), bf(P_, Sl, Cl_)
+            self.q_h, self.kr_h = bf(S, Cl_), bf(S, Cl_)
+            self.attn_sh = bf(P_, Sl, Cl_)
         self.x_a, self.x_b, self.x1, self.x2 = bf(Sl, c), bf(Sl, c), bf(Sl, c), bf(Sl, c)
         self.hidden = bf(Sl, cfg.ffn_dim)
         self.cq_buf, self.cq_n = bf(Sl, c), bf(Sl, c)
@@ -243,7 +249,7 @@ class CausalDiT:
         if not amax_given:
             if self.sync_amax:
                 if not have_local_amax:
-                    ops.amax_bf16(x, act.amax)
+                    ops.amax_bf16(x if x.dim() == 2 else x.view(-1, x.shape[-1]), act.amax)
                 sp.allreduce_max_(act.amax, self.group)
                 amax_given = True
             elif have_local_amax:
@@ -306,25 +312,32 @@ class CausalDiT:
         n_past = len(cache.past_slots())
         T = cfg.chunk_tokens
         win_k, win_v = self.win_k[li], self.win_v[li]
-        if self.P == 1:
-            v_dst = win_v[n_past * T:(n_past + 1) * T]
-            ks_dst = win_k[n_past * T:(n_past + 1) * T]
-        else:
-            v_dst, ks_dst = self.v_buf, self.k_smooth
+        cur_k, cur_v = win_k[n_past * T:(n_past + 1) * T], win_v[n_past * T:(n_past + 1) * T]
         self.v_amax.zero_()
-        self._gemm(self.act_c, Sl, blk.v, v_dst, out_amax=self.v_amax)
-        ops.rmsnorm_rope(x=self.q_buf, weight=blk.norm_q, cos=cos, sin=sin, eps=cfg.eps, out=self.q_rot)
-        ops.rmsnorm_rope(x=self.k_buf, weight=blk.norm_k, cos=cos, sin=sin, eps=cfg.eps, out=self.k_rot, out_smooth=ks_dst,
-                         amax_out=self.k_amax)
-        if self.P > 1:
-            if self.sync_amax:
-                sp.allreduce_max_(self.kv_amax, self.group)
-            q_h, ks_h, kr_h, v_h = sp.seq_to_head_many([self.q_rot, self.k_smooth, self.k_rot, self.v_buf], self.group)
-            win_k[n_past * T:(n_past + 1) * T].copy_(ks_h)
-            win_v[n_past * T:(n_past + 1) * T].copy_(v_h)
-            k_for_cache, v_for_cache = kr_h, v_h
+        if self.P == 1:
+            self._gemm(self.act_c, Sl, blk.v, cur_v, out_amax=self.v_amax)
+            ops.rmsnorm_rope(x=self.q_buf, weight=blk.norm_q, cos=cos, sin=sin, eps=cfg.eps, out=self.q_rot)
+            ops.rmsnorm_rope(x=self.k_buf, weight=blk.norm_k, cos=cos, sin=sin, eps=cfg.eps, out=self.k_rot, out_smooth=cur_k,
+                             amax_out=self.k_amax)
+            q_h, k_for_cache, v_for_cache = self.q_rot, self.k_rot, cur_v
         else:
-            q_h, k_for_cache, v_for_cache = self.q_rot, self.k_rot, v_dst
+            P_, grp = self.P, self.group
+            # tokens -> heads: every producer writes the send layout, every part lands where its
+            # consumer reads it (q, rotated keys for the cache, smoothed keys and values in the window)
+            ops.rmsnorm_rope(x=self.q_buf, weight=blk.norm_q, cos=cos, sin=sin, eps=cfg.eps, out=self.q_sh, shards=P_)
+            w_q = sp.exchange(self.q_sh, self.q_h, grp, async_op=True)
+            ops.rmsnorm_rope(x=self.k_buf, weight=blk.norm_k, cos=cos, sin=sin, eps=cfg.eps, out=self.kr_sh, out_smooth=self.ks_sh,
+                             amax_out=self.k_amax, shards=P_)
+            w_ks = sp.exchange(self.ks_sh, cur_k, grp, async_op=True)
+            w_kr = sp.exchange(self.kr_sh, self.kr_h, grp, async_op=True)
+            self._gemm(self.act_c, Sl, blk.v, self.v_buf, out_amax=self.v_amax)
+            self.v_sh.copy_(self.v_buf.view(Sl, P_, self.Cl).permute(1, 0, 2))
+            w_v = sp.exchange(self.v_sh, cur_v, grp, async_op=True)
+            if self.sync_amax:
+                sp.allreduce_max_(self.kv_amax, grp)
+            for w in (w_q, w_ks, w_kr, w_v):
+                w.wait()
+            q_h, k_for_cache, v_for_cache = self.q_h, self.kr_h, cur_v
         if n_past and self._window_version != cache.version:
             slots = cache.past_slots()
             ops.kv_dequant([cache.k[li][s].values for s in slots], [cache.k[li][s].scale_factors for s in slots],
@@ -346,7 +359,12 @@ class CausalDiT:
         cv.amax.copy_(self.v_amax)
         ops.quantize_nvfp4(k_for_cache.reshape(S * self.Hl, 128), MSE, ck.amax, ck.values, ck.scale_factors, amax_given=True)
         ops.quantize_nvfp4(v_for_cache.reshape(S * self.Hl, 128), MSE, cv.amax, cv.values, cv.scale_factors, amax_given=True)
-        attn = sp.head_to_seq(self.attn_out, self.group, out=self.attn_seq) if self.P > 1 else self.attn_out
+        if self.P > 1:
+            # heads -> tokens; the quantizer reads the received [source heads][my tokens] layout directly
+            sp.exchange(self.attn_out, self.attn_sh, self.group)
+            attn = self.attn_sh
+        else:
+            attn = self.attn_out
         self._quantize(attn, self.act_c, have_local_amax=fused_amax)
         x1, x2 = self.x1, self.x2
         self._gemm(self.act_c, Sl, blk.o, x1, residual=x, gate=e[:, 2], frame_rows=ft, row_offset=roff)

@@ -45,16 +45,25 @@ def quantize_nvfp4(x: torch.Tensor, rule_id: int, amax: torch.Tensor | None = No
                    amax_given: bool | None = None):
     """bf16 [M, K] (K % 64 == 0, unit column stride) -> (codes [Mp, K/2] u8, sf [Mp*K/16] e4m3, amax [1] f32).
 
+    A contiguous 3-D ``x`` [shards, M, K / shards] is read as the column-sharded form of the [M, K]
+    matrix (``llnv_quantize_nvfp4_ex``).
+
     ``amax`` is the fp32 tensor-scale buffer.  With ``amax_given`` (default: true when a buffer is
     passed) it is read as the scale; otherwise it is computed on the device into that buffer (or a
     new one).  ``codes`` / ``sf`` may be preallocated slot buffers (KV cache) written in place.
     """
     _require_cuda(x, "x")
-    if x.dim() != 2 or x.dtype != torch.bfloat16:
-        raise RuntimeError("quantize_nvfp4 expects a 2-D bfloat16 tensor")
-    if x.stride(1) != 1:
-        x = x.contiguous()
-    m, k = x.shape
+    shards = 1
+    if x.dim() == 3 and x.dtype == torch.bfloat16 and x.is_contiguous():
+        shards, m, ks = x.shape
+        k, ldx = shards * ks, ks
+    elif x.dim() != 2 or x.dtype != torch.bfloat16:
+        raise RuntimeError("quantize_nvfp4 expects a 2-D bfloat16 tensor (or a contiguous [shards, M, K/shards] one)")
+    else:
+        if x.stride(1) != 1:
+            x = x.contiguous()
+        m, k = x.shape
+        ldx = x.stride(0)
     mp = padded_rows(m)
     if codes is None:
         codes = torch.empty((mp, k // 2), dtype=torch.uint8, device=x.device)
@@ -66,8 +75,8 @@ def quantize_nvfp4(x: torch.Tensor, rule_id: int, amax: torch.Tensor | None = No
             raise ValueError("amax_given needs an amax tensor")
         amax = torch.empty(1, dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
-        _check(_lib.lib().llnv_quantize_nvfp4(x.data_ptr(), m, k, x.stride(0), rule_id, codes.data_ptr(), sf.data_ptr(),
-                                              amax.data_ptr(), 1 if given else 0, _stream(x)))
+        _check(_lib.lib().llnv_quantize_nvfp4_ex(x.data_ptr(), m, k, ldx, rule_id, codes.data_ptr(), sf.data_ptr(),
+                                                 amax.data_ptr(), 1 if given else 0, shards, _stream(x)))
     return codes, sf, amax
 
 
@@ -125,28 +134,34 @@ def layernorm_quantize_nvfp4(x, weight, bias, rule_id, eps=1e-6, *, want_y=False
 
 
 def rmsnorm_rope(x, weight=None, cos=None, sin=None, eps=1e-6, *, out=None, out_smooth=None, want_smooth=False,
-                 amax_out=None, want_amax=False):
+                 amax_out=None, want_amax=False, shards=1):
     """RMSNorm (if ``weight``) -> per-head RoPE (if ``cos``/``sin``, fp32 [S, 64]) on bf16 [S, C];
-    optionally the k_smooth copy and max|out|.  Returns (out, out_smooth or None, amax or None)."""
+    optionally the k_smooth copy and max|out|.  Returns (out, out_smooth or None, amax or None).
+    With ``shards`` > 1 the outputs are contiguous [shards, S, C / shards] tensors (head-sharded)."""
     _require_cuda(x, "x")
     if x.dim() != 2 or x.dtype != torch.bfloat16 or x.stride(1) != 1:
         raise RuntimeError("rmsnorm_rope expects a 2-D bfloat16 tensor with unit column stride")
     s, c = x.shape
+    oshape = (s, c) if shards == 1 else (shards, s, c // shards)
     if out is None:
-        out = torch.empty((s, c), dtype=torch.bfloat16, device=x.device)
+        out = torch.empty(oshape, dtype=torch.bfloat16, device=x.device)
     if out_smooth is None and want_smooth:
-        out_smooth = torch.empty((s, c), dtype=torch.bfloat16, device=x.device)
+        out_smooth = torch.empty(oshape, dtype=torch.bfloat16, device=x.device)
+    if shards > 1:
+        for t in (out, out_smooth):
+            if t is not None and (tuple(t.shape) != oshape or not t.is_contiguous()):
+                raise RuntimeError("sharded outputs must be contiguous [shards, S, C / shards]")
     if amax_out is None and want_amax:
         amax_out = torch.empty(1, dtype=torch.float32, device=x.device)
     if cos is not None and (cos.dtype != torch.float32 or cos.shape != (s, 64) or not cos.is_contiguous() or not sin.is_contiguous()):
         raise RuntimeError("cos/sin must be contiguous float32 [S, 64]")
     with torch.cuda.device(x.device):
-        _check(_lib.lib().llnv_rmsnorm_rope(
+        _check(_lib.lib().llnv_rmsnorm_rope_ex(
             x.data_ptr(), s, c, x.stride(0), weight.data_ptr() if weight is not None else None, float(eps),
             cos.data_ptr() if cos is not None else None, sin.data_ptr() if sin is not None else None,
-            out.data_ptr(), out.stride(0), out_smooth.data_ptr() if out_smooth is not None else None,
-            out_smooth.stride(0) if out_smooth is not None else 0,
-            amax_out.data_ptr() if amax_out is not None else None, _stream(x)))
+            out.data_ptr(), out.stride(-2), out_smooth.data_ptr() if out_smooth is not None else None,
+            out_smooth.stride(-2) if out_smooth is not None else 0,
+            amax_out.data_ptr() if amax_out is not None else None, shards, _stream(x)))
     return out, out_smooth, amax_out
 
 

@@ -64,6 +64,17 @@ def seq_to_head_many(tensors, group):
     return [recv[i] for i in range(n)]
 
 
+def exchange(send: torch.Tensor, recv: torch.Tensor, group, async_op: bool = False):
+    """One all-to-all of equal contiguous parts: part r of ``send`` goes to rank r, part s of ``recv``
+    comes from rank s.  With ``send`` = [P][S/P][C/P] (my tokens, destination's heads) ``recv`` is
+    [S][C/P] in global token order (tokens -> heads); with ``send`` = [S][C/P] viewed as P token
+    ranges ``recv`` is [P][S/P][C/P] (source's heads, my tokens).  Neither side needs a pack or
+    unpack copy: the producers write and the consumers read these layouts directly."""
+    rank, p = world(group)
+    assert send.is_contiguous() and recv.is_contiguous() and send.numel() == recv.numel()
+    return dist.all_to_all_single(recv.view(p, -1), send.view(p, -1), group=group, async_op=async_op)
+
+
 def allreduce_max_(t: torch.Tensor, group) -> torch.Tensor:
     """In-place MAX all-reduce of a small fp32 tensor (per-tensor amax values)."""
     rank, p = world(group)

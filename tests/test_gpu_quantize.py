@@ -176,3 +176,17 @@ def test_exact_division():
             assert rc == 0
             torch.cuda.synchronize()
             assert int(counter.item()) == 0, (divisor, sign, int(counter.item()))
+
+
+@pytest.mark.parametrize("shards", [2, 4])
+def test_quantize_column_sharded_input(shards):
+    """A [shards, M, K/shards] activation (the layout the head -> token exchange delivers) gives the
+    codes, scales and amax of the [M, K] matrix it represents."""
+    m, k = 200, 512
+    g = torch.Generator().manual_seed(31)
+    x = (torch.randn(m, k, generator=g) * 2).bfloat16().cuda()
+    xs = x.view(m, shards, k // shards).permute(1, 0, 2).contiguous()
+    ref = ops.quantize_nvfp4(x, 3)
+    got = ops.quantize_nvfp4(xs, 3)
+    for a, b in zip(ref, got):
+        assert torch.equal(a.view(torch.uint8) if a.dtype != torch.float32 else a, b.view(torch.uint8) if b.dtype != torch.float32 else b)

@@ -65,3 +65,22 @@ def test_prologue_writes_into_strided_window_buffer():
     ref, _, _ = ops.rmsnorm_rope(x)
     ops.rmsnorm_rope(x, out=window[2 * s:])
     assert torch.equal(window[2 * s:], ref) and torch.equal(ref, x) and int(window[: 2 * s].abs().max().item()) == 0
+
+
+@pytest.mark.parametrize("shards", [2, 4])
+def test_prologue_head_sharded_outputs(shards):
+    """shards > 1 writes [shards, S, C/shards] (the send layout of the token -> head exchange) with the
+    same values as the plain [S, C] call."""
+    s_, heads = 70, 4
+    c = heads * 128
+    g = torch.Generator().manual_seed(41)
+    x = torch.randn(s_, c, generator=g).bfloat16().cuda()
+    w = (1 + 0.1 * torch.randn(c, generator=g)).bfloat16().cuda()
+    ang = torch.rand(s_, 64, generator=g) * 6.28
+    cos, sin = ang.cos().float().cuda().contiguous(), ang.sin().float().cuda().contiguous()
+    out, sm, am = ops.rmsnorm_rope(x, w, cos, sin, want_smooth=True, want_amax=True)
+    out2, sm2, am2 = ops.rmsnorm_rope(x, w, cos, sin, want_smooth=True, want_amax=True, shards=shards)
+    assert out2.shape == (shards, s_, c // shards)
+    assert torch.equal(out2.permute(1, 0, 2).reshape(s_, c), out)
+    assert torch.equal(sm2.permute(1, 0, 2).reshape(s_, c), sm)
+    assert torch.equal(am, am2)

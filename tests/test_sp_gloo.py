@@ -37,6 +37,14 @@ def _worker(rank, world, port, q):
         assert torch.equal(back, mine)
         a, b = sp.seq_to_head_many([mine, mine * 2], g)
         assert torch.equal(a, heads) and torch.equal(b, heads * 2)
+        # copy-free form: the send buffer is already [destination][my tokens][its heads]
+        send = mine.view(sl, world, cl).permute(1, 0, 2).contiguous()
+        recv = torch.empty(S, cl)
+        sp.exchange(send, recv, g)
+        assert torch.equal(recv, heads)
+        back_sh = torch.empty(world, sl, cl)                  # [source heads][my tokens]
+        sp.exchange(heads, back_sh, g)
+        assert torch.equal(back_sh.permute(1, 0, 2).reshape(sl, C), mine)
         am = torch.tensor([float(rank + 1)])
         sp.allreduce_max_(am, g)
         assert float(am) == float(world)
