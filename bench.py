@@ -418,6 +418,7 @@ def bench_dit_chunk(dev, rank, world, group, steps: int, sync_amax: bool = True,
         times.append(s.elapsed_time(e))
         chunk += 1
     assert _lib.lib().llnv_check_status(None) == 0, _lib.lib().llnv_last_error()
+    exchange = "producer kernels store into peer memory (NVLink), own barrier" if model.arena is not None else "NCCL all-to-all"
     model.close()
     ms = statistics.median(times)
     if world > 1:
@@ -429,6 +430,7 @@ def bench_dit_chunk(dev, rank, world, group, steps: int, sync_amax: bool = True,
             "window_tokens": cfg.window_frames * cfg.frame_tokens, "chunk_tokens": cfg.chunk_tokens,
             "parallelism": f"sequence-parallel over {world} GPU(s)" if world > 1 else "single GPU",
             "amax_sync": bool(world > 1 and sync_amax), "cuda_graphs": bool(use_graphs), "scaling": "strong",
+            "exchange": ("none" if world == 1 else exchange),
             "kv_cache_bytes_per_rank": model.cache.bytes(),
             "data": "synthetic, random-init weights"}
 

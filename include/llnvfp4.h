@@ -154,6 +154,32 @@ int llnv_rmsnorm_rope_ex(const void* x, int64_t S, int64_t C, int64_t ldx, const
                          const float* cos, const float* sin, void* out, int64_t ldo, void* out_smooth, int64_t lds,
                          float* amax_out, int shards, llnv_stream_t stream);
 
+/* The same prologue with one base pointer per head shard (shard r of out / out_smooth is a
+ * [S, C / shards] matrix at out_ptrs[r] / smooth_ptrs[r] with row stride ldo / lds).  The pointers
+ * may address other GPUs of the node (peer-mapped symmetric memory): the kernel stores every shard
+ * at its final place on the rank that owns those heads, which is the token -> head all-to-all of
+ * sequence parallelism (ulysses_seq_to_head, sp_ulysses_inference.py:122-137) fused into the
+ * producer.  Follow it with llnv_peer_barrier before the consumers run.  smooth_ptrs may be NULL. */
+int llnv_rmsnorm_rope_scatter(const void* x, int64_t S, int64_t C, int64_t ldx, const void* weight, float eps,
+                              const float* cos, const float* sin, void* const* out_ptrs, int64_t ldo,
+                              void* const* smooth_ptrs, int64_t lds, float* amax_out, int shards, llnv_stream_t stream);
+
+/* Pushes a matrix to `shards` destinations with plain 16-byte stores (the destinations may be peer
+ * memory): destination r receives `rows` rows of `row_bytes` bytes read from
+ * src + r * src_shard_bytes with row pitch src_pitch, written with row pitch dst_pitch.
+ * Column blocks (src_shard_bytes = row_bytes) give the token -> head exchange of a [tokens, C]
+ * matrix, row blocks (src_shard_bytes = rows * src_pitch) the head -> token exchange
+ * (ulysses_head_to_seq, sp_ulysses_inference.py:139-154). */
+int llnv_scatter_2d(const void* src, int64_t src_shard_bytes, int64_t src_pitch, void* const* dst_ptrs, int64_t dst_pitch,
+                    int64_t rows, int64_t row_bytes, int shards, llnv_stream_t stream);
+
+/* Barrier over the `world` GPUs of a sequence-parallel group, on the stream: signal_ptrs[r] is rank
+ * r's signal area (>= 4 * world bytes of zero-initialised symmetric memory, peer-mapped), epoch a
+ * zero-initialised device uint32 of this rank.  Everything enqueued before the barrier on every
+ * rank (peer stores included) is visible to everything enqueued after it on every rank.  The wait
+ * is bounded; a rank that gives up records LLNV_E_TIMEOUT for llnv_check_status and returns. */
+int llnv_peer_barrier(void* const* signal_ptrs, int rank, int world, void* epoch, llnv_stream_t stream);
+
 /* Dequantize `num_blocks` KV-cache blocks, each an NVFP4 matrix [rows_padded, 128] holding
  * block_token_size*num_heads logical rows (token-major, head-minor), into one contiguous
  * tensor [1, num_blocks*block_token_size, num_heads, 128] of dtype_code.

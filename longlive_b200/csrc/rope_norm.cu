@@ -16,14 +16,20 @@ namespace llnv {
 namespace {
 
 constexpr int kMaxVec = 16;      // C <= 4096
+constexpr int kMaxShards = 8;
+
+// Base address of every head shard of the two outputs (one entry when the output is a plain
+// [S, C] matrix).  The entries may point into other GPUs' memory: they are only stored to.
+struct ShardOut {
+  uint16_t* out[kMaxShards];
+  uint16_t* smooth[kMaxShards];
+};
 
 __global__ void __launch_bounds__(256) rmsnorm_rope_kernel(const uint16_t* __restrict__ x, int64_t S, int64_t C, int64_t ldx,
                                                            const uint16_t* __restrict__ weight, float eps,
                                                            const float* __restrict__ cosv, const float* __restrict__ sinv,
-                                                           uint16_t* __restrict__ out, int64_t ldo,
-                                                           uint16_t* __restrict__ out_smooth, int64_t lds,
-                                                           float* __restrict__ amax_out, int shard_vecs, int64_t shard_stride_o,
-                                                           int64_t shard_stride_s) {
+                                                           const ShardOut dst, int64_t ldo, int64_t lds, bool want_smooth,
+                                                           float* __restrict__ amax_out, int shard_vecs) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * 8 + warp;
   // the norm weight is shared by all rows: one cooperative load per CTA instead of a dependent
@@ -112,8 +118,8 @@ __global__ void __launch_bounds__(256) rmsnorm_rope_kernel(const uint16_t* __res
       // head-sharded outputs: 16-byte vector idx lives in shard idx / shard_vecs (a whole number of heads)
       const int sh = shard_vecs ? idx / shard_vecs : 0;
       const int vi = shard_vecs ? idx - sh * shard_vecs : idx;
-      reinterpret_cast<uint4*>(out + sh * shard_stride_o + row * ldo)[vi] = o;
-      if (out_smooth) {
+      reinterpret_cast<uint4*>(dst.out[sh] + row * ldo)[vi] = o;
+      if (want_smooth) {
 #pragma unroll
         for (int sft = 8; sft > 0; sft >>= 1) hsum += __shfl_xor_sync(0xFFFFFFFFu, hsum, sft, 16);
         const float mean = round_bf16(hsum * (1.f / 128.f));
@@ -122,7 +128,7 @@ __global__ void __launch_bounds__(256) rmsnorm_rope_kernel(const uint16_t* __res
         s.y = pack_bf16x2(__fsub_rn(y[2], mean), __fsub_rn(y[3], mean));
         s.z = pack_bf16x2(__fsub_rn(y[4], mean), __fsub_rn(y[5], mean));
         s.w = pack_bf16x2(__fsub_rn(y[6], mean), __fsub_rn(y[7], mean));
-        reinterpret_cast<uint4*>(out_smooth + sh * shard_stride_s + row * lds)[vi] = s;
+        reinterpret_cast<uint4*>(dst.smooth[sh] + row * lds)[vi] = s;
       }
     }
   }
@@ -151,25 +157,55 @@ extern "C" int llnv_rmsnorm_rope(const void* x, int64_t S, int64_t C, int64_t ld
   return llnv_rmsnorm_rope_ex(x, S, C, ldx, weight, eps, cos, sin, out, ldo, out_smooth, lds, amax_out, 1, stream);
 }
 
-extern "C" int llnv_rmsnorm_rope_ex(const void* x, int64_t S, int64_t C, int64_t ldx, const void* weight, float eps,
-                                    const float* cos, const float* sin, void* out, int64_t ldo, void* out_smooth, int64_t lds,
-                                    float* amax_out, int shards, llnv_stream_t stream_) {
-  cudaStream_t stream = (cudaStream_t)stream_;
-  LLNV_REQUIRE(shards >= 1 && C % shards == 0 && (C / shards) % 128 == 0,
-               "llnv_rmsnorm_rope: shards must divide the channels into whole heads (C=%lld shards=%d)", (long long)C, shards);
-  const int64_t Cs = C / shards;
-  LLNV_REQUIRE(x && out, "llnv_rmsnorm_rope: null pointer");
+namespace {
+
+int rope_launch(const void* x, int64_t S, int64_t C, int64_t ldx, const void* weight, float eps, const float* cos, const float* sin,
+                const ShardOut& dst, int64_t ldo, int64_t lds, bool want_smooth, float* amax_out, int shards, cudaStream_t stream) {
+  LLNV_REQUIRE(x != nullptr, "llnv_rmsnorm_rope: null pointer");
   LLNV_REQUIRE((cos == nullptr) == (sin == nullptr), "llnv_rmsnorm_rope: cos and sin must be given together");
   LLNV_REQUIRE(S >= 0 && C > 0 && C % 128 == 0 && C <= 4096, "llnv_rmsnorm_rope: C must be a multiple of 128 (head_dim 128) and at most 4096 (got %lld)", (long long)C);
+  LLNV_REQUIRE(shards >= 1 && shards <= kMaxShards && C % shards == 0 && (C / shards) % 128 == 0,
+               "llnv_rmsnorm_rope: shards must divide the channels into whole heads, at most 8 (C=%lld shards=%d)", (long long)C, shards);
+  const int64_t Cs = C / shards;
   LLNV_REQUIRE(ldx >= C && ldx % 8 == 0 && ldo >= Cs && ldo % 8 == 0, "llnv_rmsnorm_rope: row strides must be >= the row width and multiples of 8");
-  LLNV_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)weight & 15) == 0 && ((uintptr_t)cos & 15) == 0 &&
-                   ((uintptr_t)sin & 15) == 0,
+  LLNV_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)weight & 15) == 0 && ((uintptr_t)cos & 15) == 0 && ((uintptr_t)sin & 15) == 0,
                "llnv_rmsnorm_rope: pointers must be 16-byte aligned");
-  if (out_smooth) LLNV_REQUIRE(lds >= Cs && lds % 8 == 0 && ((uintptr_t)out_smooth & 15) == 0, "llnv_rmsnorm_rope: out_smooth must be 16-byte aligned with a row stride that is a multiple of 8");
+  if (want_smooth) LLNV_REQUIRE(lds >= Cs && lds % 8 == 0, "llnv_rmsnorm_rope: out_smooth row stride must be >= the row width and a multiple of 8");
+  for (int r = 0; r < shards; ++r) {
+    LLNV_REQUIRE(dst.out[r] != nullptr && ((uintptr_t)dst.out[r] & 15) == 0, "llnv_rmsnorm_rope: output %d must be a 16-byte aligned pointer", r);
+    if (want_smooth) LLNV_REQUIRE(dst.smooth[r] != nullptr && ((uintptr_t)dst.smooth[r] & 15) == 0, "llnv_rmsnorm_rope: out_smooth %d must be a 16-byte aligned pointer", r);
+  }
   if (amax_out) LLNV_CUDA(cudaMemsetAsync(amax_out, 0, sizeof(float), stream));
   if (S == 0) return LLNV_OK;
   rmsnorm_rope_kernel<<<(unsigned)((S + 7) / 8), 256, 0, stream>>>((const uint16_t*)x, S, C, ldx, (const uint16_t*)weight, eps, cos, sin,
-                                                                  (uint16_t*)out, ldo, (uint16_t*)out_smooth, lds, amax_out,
-                                                                  shards > 1 ? (int)(Cs / 8) : 0, S * ldo, S * lds);
+                                                                  dst, ldo, lds, want_smooth, amax_out, shards > 1 ? (int)(Cs / 8) : 0);
   return launch_status("rmsnorm_rope_kernel");
+}
+
+}  // namespace
+
+extern "C" int llnv_rmsnorm_rope_ex(const void* x, int64_t S, int64_t C, int64_t ldx, const void* weight, float eps,
+                                    const float* cos, const float* sin, void* out, int64_t ldo, void* out_smooth, int64_t lds,
+                                    float* amax_out, int shards, llnv_stream_t stream) {
+  LLNV_REQUIRE(out != nullptr, "llnv_rmsnorm_rope: null pointer");
+  LLNV_REQUIRE(shards >= 1 && shards <= kMaxShards, "llnv_rmsnorm_rope: at most 8 shards");
+  ShardOut dst = {};
+  for (int r = 0; r < shards; ++r) {
+    dst.out[r] = (uint16_t*)out + (int64_t)r * S * ldo;
+    dst.smooth[r] = out_smooth ? (uint16_t*)out_smooth + (int64_t)r * S * lds : nullptr;
+  }
+  return rope_launch(x, S, C, ldx, weight, eps, cos, sin, dst, ldo, lds, out_smooth != nullptr, amax_out, shards, (cudaStream_t)stream);
+}
+
+extern "C" int llnv_rmsnorm_rope_scatter(const void* x, int64_t S, int64_t C, int64_t ldx, const void* weight, float eps,
+                                         const float* cos, const float* sin, void* const* out_ptrs, int64_t ldo,
+                                         void* const* smooth_ptrs, int64_t lds, float* amax_out, int shards, llnv_stream_t stream) {
+  LLNV_REQUIRE(out_ptrs != nullptr, "llnv_rmsnorm_rope_scatter: null pointer table");
+  LLNV_REQUIRE(shards >= 1 && shards <= kMaxShards, "llnv_rmsnorm_rope: at most 8 shards");
+  ShardOut dst = {};
+  for (int r = 0; r < shards; ++r) {
+    dst.out[r] = (uint16_t*)out_ptrs[r];
+    dst.smooth[r] = smooth_ptrs ? (uint16_t*)smooth_ptrs[r] : nullptr;
+  }
+  return rope_launch(x, S, C, ldx, weight, eps, cos, sin, dst, ldo, lds, smooth_ptrs != nullptr, amax_out, shards, (cudaStream_t)stream);
 }

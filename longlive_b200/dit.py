@@ -166,7 +166,7 @@ class KVCache:
 
 class CausalDiT:
     def __init__(self, cfg: DiTConfig | None = None, device="cuda", seed: int = 0, sp_group=None, sync_amax: bool = True,
-                 cache_text_kv: bool = True, use_graphs: bool = False):
+                 cache_text_kv: bool = True, use_graphs: bool = False, peer_exchange: bool = True):
         self.cfg = cfg = cfg or DiTConfig()
         self.use_graphs = use_graphs
         self.device = torch.device(device)
@@ -201,13 +201,26 @@ class CausalDiT:
         self.q_buf, self.k_buf, self.v_buf = bf(Sl, c), bf(Sl, c), bf(Sl, c)
         self.q_rot, self.k_rot, self.k_smooth = bf(Sl, c), bf(Sl, c), bf(Sl, c)
         self.attn_out = bf(S, self.Cl)
+        Lk = cfg.window_frames * cfg.frame_tokens
+        self.arena = None
         if self.P > 1:
-            # send / receive layouts of the two exchanges: [rank][my tokens][that rank's heads] and
-            # [all tokens][my heads]; written and read in place by the kernels on either side
             P_, Cl_ = self.P, self.Cl
-            self.q_sh, self.kr_sh, self.ks_sh, self.v_sh = bf(P_, Sl, Cl_), bf(P_, Sl, Cl_), bf(P_, Sl, Cl_), bf(P_, Sl, Cl_)
-            self.q_h, self.kr_h = bf(S, Cl_), bf(S, Cl_)
-            self.attn_sh = bf(P_, Sl, Cl_)
+            if peer_exchange:
+                # exchange targets in symmetric memory: peers store into them directly (longlive_b200/csrc/peer.cu)
+                layout = {"q_h": S * Cl_ * 2, "kr_h": S * Cl_ * 2, "attn_sh": S * Cl_ * 2}
+                for li in range(cfg.layers):
+                    layout[f"win_k{li}"] = Lk * Cl_ * 2
+                    layout[f"win_v{li}"] = Lk * Cl_ * 2
+                self.arena = sp.PeerArena.create(sp_group, dev, layout)
+            if self.arena is not None:
+                self.q_h, self.kr_h = self.arena.tensor("q_h", (S, Cl_)), self.arena.tensor("kr_h", (S, Cl_))
+                self.attn_sh = self.arena.tensor("attn_sh", (P_, Sl, Cl_))
+            else:
+                # NCCL exchange: send / receive layouts [rank][my tokens][that rank's heads] and
+                # [all tokens][my heads], written and read in place by the kernels on either side
+                self.q_sh, self.kr_sh, self.ks_sh, self.v_sh = bf(P_, Sl, Cl_), bf(P_, Sl, Cl_), bf(P_, Sl, Cl_), bf(P_, Sl, Cl_)
+                self.q_h, self.kr_h = bf(S, Cl_), bf(S, Cl_)
+                self.attn_sh = bf(P_, Sl, Cl_)
         self.x_a, self.x_b, self.x1, self.x2 = bf(Sl, c), bf(Sl, c), bf(Sl, c), bf(Sl, c)
         self.hidden = bf(Sl, cfg.ffn_dim)
         self.cq_buf, self.cq_n = bf(Sl, c), bf(Sl, c)
@@ -217,9 +230,12 @@ class CausalDiT:
         # the forwards of a chunk, so they are dequantized from the NVFP4 cache once per chunk (by the
         # first forward after the block table moved) instead of once per forward as the reference does
         # (causal_model.py:591-600); 2 x 81 MB per layer at full size.
-        Lk = cfg.window_frames * cfg.frame_tokens
-        self.win_k = [bf(Lk, self.Cl) for _ in range(cfg.layers)]
-        self.win_v = [bf(Lk, self.Cl) for _ in range(cfg.layers)]
+        if self.arena is not None:
+            self.win_k = [self.arena.tensor(f"win_k{li}", (Lk, self.Cl)) for li in range(cfg.layers)]
+            self.win_v = [self.arena.tensor(f"win_v{li}", (Lk, self.Cl)) for li in range(cfg.layers)]
+        else:
+            self.win_k = [bf(Lk, self.Cl) for _ in range(cfg.layers)]
+            self.win_v = [bf(Lk, self.Cl) for _ in range(cfg.layers)]
         self._window_version = -1             # cache.version whose past blocks the windows hold
         self.kv_amax = torch.zeros(2, dtype=torch.float32, device=dev)      # [k, v]: reduced with one collective
         self.k_amax, self.v_amax = self.kv_amax[0:1], self.kv_amax[1:2]
@@ -320,10 +336,26 @@ class CausalDiT:
             ops.rmsnorm_rope(x=self.k_buf, weight=blk.norm_k, cos=cos, sin=sin, eps=cfg.eps, out=self.k_rot, out_smooth=cur_k,
                              amax_out=self.k_amax)
             q_h, k_for_cache, v_for_cache = self.q_rot, self.k_rot, cur_v
+        elif self.arena is not None:
+            # tokens -> heads over peer memory: every producer stores each head shard at its final
+            # address on the rank that owns those heads (q, rotated keys for the cache, smoothed keys
+            # and values in that rank's window); one barrier makes all of it visible
+            ar, Cl = self.arena, self.Cl
+            row_off = self.rank * Sl * Cl * 2                   # my token block inside an [S, Cl] buffer
+            cur_off = n_past * T * Cl * 2 + row_off            # ... inside the current-chunk part of a window
+            ops.rmsnorm_rope_scatter(self.q_buf, blk.norm_q, cos, sin, cfg.eps, ar.ptrs("q_h", row_off), Cl)
+            ops.rmsnorm_rope_scatter(self.k_buf, blk.norm_k, cos, sin, cfg.eps, ar.ptrs("kr_h", row_off), Cl,
+                                     smooth_ptrs=ar.ptrs(f"win_k{li}", cur_off), lds=Cl, amax_out=self.k_amax)
+            self._gemm(self.act_c, Sl, blk.v, self.v_buf, out_amax=self.v_amax)
+            ops.scatter_2d(self.v_buf, Cl * 2, ar.ptrs(f"win_v{li}", cur_off), Cl * 2, Sl, Cl * 2)
+            if self.sync_amax:
+                sp.allreduce_max_(self.kv_amax, self.group)
+            ar.barrier()
+            q_h, k_for_cache, v_for_cache = self.q_h, self.kr_h, cur_v
         else:
             P_, grp = self.P, self.group
-            # tokens -> heads: every producer writes the send layout, every part lands where its
-            # consumer reads it (q, rotated keys for the cache, smoothed keys and values in the window)
+            # tokens -> heads with NCCL: every producer writes the send layout, every part lands where
+            # its consumer reads it
             ops.rmsnorm_rope(x=self.q_buf, weight=blk.norm_q, cos=cos, sin=sin, eps=cfg.eps, out=self.q_sh, shards=P_)
             w_q = sp.exchange(self.q_sh, self.q_h, grp, async_op=True)
             ops.rmsnorm_rope(x=self.k_buf, weight=blk.norm_k, cos=cos, sin=sin, eps=cfg.eps, out=self.kr_sh, out_smooth=self.ks_sh,
@@ -359,8 +391,14 @@ class CausalDiT:
         cv.amax.copy_(self.v_amax)
         ops.quantize_nvfp4(k_for_cache.reshape(S * self.Hl, 128), MSE, ck.amax, ck.values, ck.scale_factors, amax_given=True)
         ops.quantize_nvfp4(v_for_cache.reshape(S * self.Hl, 128), MSE, cv.amax, cv.values, cv.scale_factors, amax_given=True)
-        if self.P > 1:
-            # heads -> tokens; the quantizer reads the received [source heads][my tokens] layout directly
+        if self.arena is not None:
+            # heads -> tokens over peer memory: rank r receives my heads of its tokens in attn_sh[my rank];
+            # the quantizer reads that [source heads][my tokens] layout directly
+            blk_bytes = Sl * self.Cl * 2
+            ops.scatter_2d(self.attn_out, blk_bytes, self.arena.ptrs("attn_sh", self.rank * blk_bytes), self.Cl * 2, Sl, self.Cl * 2)
+            self.arena.barrier()
+            attn = self.attn_sh
+        elif self.P > 1:
             sp.exchange(self.attn_out, self.attn_sh, self.group)
             attn = self.attn_sh
         else:

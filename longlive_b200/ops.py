@@ -165,6 +165,40 @@ def rmsnorm_rope(x, weight=None, cos=None, sin=None, eps=1e-6, *, out=None, out_
     return out, out_smooth, amax_out
 
 
+def _ptr_table(ptrs):
+    arr = (C.c_void_p * len(ptrs))(*[int(p) for p in ptrs])
+    return arr
+
+
+def rmsnorm_rope_scatter(x, weight, cos, sin, eps, out_ptrs, ldo, smooth_ptrs=None, lds=0, amax_out=None):
+    """``rmsnorm_rope`` whose head shard r is stored at ``out_ptrs[r]`` (and ``smooth_ptrs[r]``): raw
+    device addresses, possibly on other GPUs of the node.  See ``llnv_rmsnorm_rope_scatter``."""
+    _require_cuda(x, "x")
+    s, c = x.shape
+    shards = len(out_ptrs)
+    with torch.cuda.device(x.device):
+        _check(_lib.lib().llnv_rmsnorm_rope_scatter(
+            x.data_ptr(), s, c, x.stride(0), weight.data_ptr() if weight is not None else None, float(eps),
+            cos.data_ptr() if cos is not None else None, sin.data_ptr() if sin is not None else None,
+            _ptr_table(out_ptrs), ldo, _ptr_table(smooth_ptrs) if smooth_ptrs is not None else None, lds,
+            amax_out.data_ptr() if amax_out is not None else None, shards, _stream(x)))
+
+
+def scatter_2d(src, src_shard_bytes, dst_ptrs, dst_pitch, rows, row_bytes):
+    """Push ``rows`` x ``row_bytes`` blocks of the 2-D tensor ``src`` (block r starts r * src_shard_bytes
+    bytes in) to the raw device addresses ``dst_ptrs`` (possibly peer memory).  See ``llnv_scatter_2d``."""
+    _require_cuda(src, "src")
+    with torch.cuda.device(src.device):
+        _check(_lib.lib().llnv_scatter_2d(src.data_ptr(), src_shard_bytes, src.stride(0) * src.element_size(), _ptr_table(dst_ptrs),
+                                          dst_pitch, rows, row_bytes, len(dst_ptrs), _stream(src)))
+
+
+def peer_barrier(signal_ptrs, rank, epoch):
+    """Stream-ordered barrier over the GPUs whose signal areas are ``signal_ptrs`` (``llnv_peer_barrier``)."""
+    with torch.cuda.device(epoch.device):
+        _check(_lib.lib().llnv_peer_barrier(_ptr_table(signal_ptrs), rank, len(signal_ptrs), epoch.data_ptr(), _stream(epoch)))
+
+
 def attention_bf16(q, k, v, heads, scale=None, out=None, key_splits=None, out_amax=None):
     """softmax(q k^T * scale) v per head, non-causal.  q: bf16 [Lq, heads*128]; k, v: bf16 [Lk, heads*128]
     (row strides free, unit column stride).  Returns bf16 [Lq, heads*128].  ``key_splits`` > 1 splits

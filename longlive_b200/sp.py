@@ -11,6 +11,8 @@ of one rank every function is the identity.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -91,3 +93,58 @@ def all_gather_tokens(x: torch.Tensor, group) -> torch.Tensor:
     out = torch.empty((p * x.shape[0], x.shape[1]), dtype=x.dtype, device=x.device)
     dist.all_gather_into_tensor(out, x.contiguous(), group=group)
     return out
+
+
+class PeerArena:
+    """One symmetric-memory allocation per rank, mapped on every GPU of the group, from which the
+    exchange buffers are carved.  ``tensor(name)`` is this rank's buffer, ``ptr(rank, name, offset)``
+    the address of the same buffer on another rank, as seen from this GPU (NVLink peer mapping).
+    The first 256 bytes hold the barrier flags (``llnv_peer_barrier``).
+
+    Built on ``torch.distributed._symmetric_memory`` (plain peer mappings; NVLink multicast binding
+    is switched off, nothing here uses it).  ``PeerArena.create`` returns None when symmetric
+    memory cannot be set up for the group, and callers fall back to the NCCL exchange."""
+
+    SIGNAL_BYTES = 256
+
+    def __init__(self, group, device, layout: dict[str, int]):
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.offsets, off = {}, self.SIGNAL_BYTES
+        for name, nbytes in layout.items():
+            self.offsets[name] = (off, nbytes)
+            off += (nbytes + 255) // 256 * 256
+        self.nbytes = off
+        self.buf = symm_mem.empty(off, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, group.group_name)
+        self.base = [int(p) for p in self.handle.buffer_ptrs]
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)                     # every rank's flags are zero before anyone signals
+
+    @classmethod
+    def create(cls, group, device, layout):
+        try:
+            return cls(group, device, layout)
+        except Exception as exc:  # symmetric memory unavailable (no peer access, old driver, ...)
+            import warnings
+            warnings.warn(f"peer-memory exchange unavailable, using NCCL all-to-all: {exc!r}")
+            return None
+
+    def tensor(self, name: str, shape, dtype=torch.bfloat16) -> torch.Tensor:
+        off, nbytes = self.offsets[name]
+        t = self.buf[off:off + nbytes].view(dtype)
+        return t.view(*shape)
+
+    def ptr(self, rank: int, name: str, byte_offset: int = 0) -> int:
+        return self.base[rank] + self.offsets[name][0] + byte_offset
+
+    def ptrs(self, name: str, byte_offset: int = 0) -> list[int]:
+        return [self.ptr(r, name, byte_offset) for r in range(self.world)]
+
+    def barrier(self) -> None:
+        from . import ops
+        ops.peer_barrier(self.base, self.rank, self.epoch)

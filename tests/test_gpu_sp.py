@@ -21,7 +21,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, q, use_graphs=False):
+def _worker(rank, world, port, q, use_graphs=False, peer=False):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
@@ -31,7 +31,8 @@ def _worker(rank, world, port, q, use_graphs=False):
     try:
         from longlive_b200 import dit
         cfg = dit.DiTConfig(**CFG)
-        par = dit.CausalDiT(cfg, device=dev, seed=4, sp_group=dist.group.WORLD, sync_amax=True, use_graphs=use_graphs)
+        par = dit.CausalDiT(cfg, device=dev, seed=4, sp_group=dist.group.WORLD, sync_amax=True, use_graphs=use_graphs, peer_exchange=peer)
+        assert (par.arena is not None) == peer
         ref = dit.CausalDiT(cfg, device=dev, seed=4)
         g = torch.Generator(device=dev).manual_seed(9)
         ctx_raw = torch.randn(cfg.text_len, cfg.text_dim, generator=g, device=dev).bfloat16()
@@ -65,13 +66,15 @@ def _worker(rank, world, port, q, use_graphs=False):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("use_graphs", [False, True])
-def test_sequence_parallel_matches_single_gpu(use_graphs):
+@pytest.mark.parametrize("use_graphs,peer", [(False, False), (True, False), (False, True), (True, True)])
+def test_sequence_parallel_matches_single_gpu(use_graphs, peer):
+    """peer=False exchanges with NCCL all-to-alls, peer=True with stores into the other GPU's
+    symmetric memory and the library's own barrier."""
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, use_graphs)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, use_graphs, peer)) for r in range(2)]
     for p in procs:
         p.start()
     results = sorted(q.get(timeout=600) for _ in procs)
