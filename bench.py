@@ -236,9 +236,17 @@ def run_gpu_arm(args):
             dist.barrier()
             torch.cuda.synchronize(dev)
 
+    # The 30 launches of a step are captured once in a CUDA graph and replayed: a step is short
+    # enough (about a millisecond) that launching from Python would otherwise bound it, more so
+    # with several ranks sharing the host.
+    gemm_step()
+    torch.cuda.synchronize(dev)
+    step_graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(step_graph, capture_error_mode="thread_local"):
+        gemm_step()
     for _ in range(max(args.warmup, 3)):
         flush.fill_(1)
-        gemm_step()
+        step_graph.replay()
     sync_all()
     assert lib.llnv_check_status(None) == 0, lib.llnv_last_error()
 
@@ -252,7 +260,7 @@ def run_gpu_arm(args):
     for i in range(args.steps):
         flush.fill_(i & 0xFF)          # evict the 126 MB L2 (not timed)
         starts[i].record()
-        gemm_step()
+        step_graph.replay()
         ends[i].record()
     sync_all()
     wall = time.perf_counter() - wall0
@@ -350,6 +358,7 @@ def run_gpu_arm(args):
             "config": {"workload": "DiT-block W4A4 GEMM sweep: q/k/v/o + cross q/o 3072x3072, cross k/v M=512, FFN 3072<->14336; "
                                    "M in {880,2640,10560}; 30 GEMMs per step",
                        "flops_per_step": fl_step, "l2": "flushed between timed steps (256 MiB write)",
+                       "launches": "the 30 GEMM launches of a step replayed as one CUDA graph",
                        "parallelism": f"tokens sharded over {world} rank(s), no collective"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
