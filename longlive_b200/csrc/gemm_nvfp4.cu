@@ -14,9 +14,11 @@
 //               epilogue.  Warp 1 also owns the TMEM allocation.
 //   warps 2-5   epilogue: tcgen05.ld of the fp32 accumulator (32 lanes x 32 columns per load),
 //               alpha / bias / GELU / gate*y + residual / amax, bf16 stores.
-// BN = 128 keeps two accumulators in tensor memory so the epilogue of a tile overlaps the main
-// loop of the next one; BN = 256 has one accumulator (2 x 256 columns + scales exceed the 512
-// columns) but halves the shared-memory traffic per flop.
+// BN = 128 and BN = 192 keep two accumulators in tensor memory so the epilogue of a tile overlaps
+// the main loop of the next one; BN = 256 has one accumulator (2 x 256 columns + scales exceed the
+// 512 columns) but the least shared-memory traffic per flop.  A 192-row B tile starts 0 or 64 rows
+// into a 128-row scale atom: both atoms it touches are copied to tensor memory and the MMA's scale
+// address starts 0 or 2 columns (32 rows per column) into them.
 //
 // Every mbarrier wait is bounded (see sm100.cuh); no CTA waits on another CTA.
 #include <cuda.h>
@@ -36,12 +38,14 @@ constexpr uint32_t kTmemCols = 512;
 
 template <int BN>
 struct Cfg {
-  static constexpr int kAcc = BN == 128 ? 2 : 1;
-  static constexpr int kStages = BN == 128 ? 5 : 3;
+  static constexpr int kAcc = BN == 256 ? 1 : 2;
+  static constexpr int kStages = BN == 128 ? 5 : (BN == 192 ? 4 : 3);
+  static constexpr int kSfbAtoms = (BN + 127) / 128;     // 128-row scale atoms a B tile touches (192 rows: always two)
   static constexpr uint32_t kABytes = BM * BK_BYTES;
   static constexpr uint32_t kBBytes = BN * BK_BYTES;
   static constexpr uint32_t kSfaBytes = 2048;
-  static constexpr uint32_t kSfbBytes = BN * 16;
+  static constexpr uint32_t kSfbBytes = kSfbAtoms * 2048;
+  static constexpr uint32_t kSfbColsPerK = 4 * kSfbAtoms;  // TMEM columns of B scales per K=64 MMA
   static constexpr uint32_t kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
   // epilogue staging: per epilogue warp two buffers of 32 rows x 64 bf16 columns (128-byte rows,
   // 128-byte swizzle) that TMA stores drain; the same buffers receive the residual tile first
@@ -52,7 +56,8 @@ struct Cfg {
   static constexpr uint32_t kSfaCol = kAcc * BN;          // first TMEM column of the A scales
   static constexpr uint32_t kSfbCol = kSfaCol + 16;       // 4 MMAs x 4 columns
   static_assert(kStageBytes % 1024 == 0, "stage must keep 1024-byte alignment");
-  static_assert(kSfbCol + 4 * (BN / 32) <= kTmemCols, "tensor memory overflow");
+  static_assert(BN == 128 || BN == 192 || BN == 256, "unsupported tile width");
+  static_assert(kSfbCol + 4 * kSfbColsPerK <= kTmemCols, "tensor memory overflow");
 };
 
 // GELU, tanh form: 0.5 x (1 + tanh(u)) = x / (1 + exp(-2u)), u = sqrt(2/pi) (x + 0.044715 x^3)
@@ -123,10 +128,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           tma_load_2d(st, &tmA, kb * BK_BYTES, mt * BM, &full_bar[stage]);
           tma_load_2d(st + C::kABytes, &tmB, kb * BK_BYTES, nt * BN, &full_bar[stage]);
           bulk_load(st + C::kABytes + C::kBBytes, p.sfa + ((int64_t)mt * k_atoms + kb * 4) * 512, 2048, &full_bar[stage]);
+          const int64_t atom0 = ((int64_t)nt * BN) / 128;      // first scale atom row of the B tile
 #pragma unroll
-          for (int h = 0; h < BN / 128; ++h)
+          for (int h = 0; h < C::kSfbAtoms; ++h)
             bulk_load(st + C::kABytes + C::kBBytes + C::kSfaBytes + h * 2048,
-                      p.sfb + (((int64_t)nt * (BN / 128) + h) * k_atoms + kb * 4) * 512, 2048, &full_bar[stage]);
+                      p.sfb + ((atom0 + h) * k_atoms + kb * 4) * 512, 2048, &full_bar[stage]);
           if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -141,6 +147,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_flag, p.status, 200u);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
+        const int nt = tile / num_m;
+        const uint32_t sfb_col0 = (uint32_t)((((int64_t)nt * BN) % 128) / 32);     // tile start inside its first scale atom
         for (int kb = 0; kb < num_kb; ++kb) {
           mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 201u);
           tc_fence_after();
@@ -153,8 +161,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             for (int g = 0; g < 4; ++g) {
               tmem_cp_sf(tmem_base + C::kSfaCol + 4 * g, make_sf_desc(sfa_addr + g * 512));
 #pragma unroll
-              for (int h = 0; h < BN / 128; ++h)
-                tmem_cp_sf(tmem_base + C::kSfbCol + (BN / 32) * g + 4 * h, make_sf_desc(sfb_addr + h * 2048 + g * 512));
+              for (int h = 0; h < C::kSfbAtoms; ++h)
+                tmem_cp_sf(tmem_base + C::kSfbCol + C::kSfbColsPerK * g + 4 * h, make_sf_desc(sfb_addr + h * 2048 + g * 512));
             }
           }
           const uint64_t a_desc = make_kmajor_sw128_desc(a_addr);
@@ -163,7 +171,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           for (int k = 0; k < ((p.debug & 2) ? 1 : 4); ++k) {
             // 64 E2M1 elements = 32 bytes further along K inside the 128-byte swizzled row
             mma_nvf4(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_base + C::kSfaCol + 4 * k,
-                     tmem_base + C::kSfbCol + (BN / 32) * k, (kb | k) != 0 ? 1u : 0u);
+                     tmem_base + C::kSfbCol + C::kSfbColsPerK * k + sfb_col0, (kb | k) != 0 ? 1u : 0u);
           }
           tc_commit(&empty_bar[stage]);
           if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
@@ -308,7 +316,7 @@ using namespace llnv;
 // Test/benchmark hook: force the kernel: 128 / 256 = one CTA per tile with that N tile, 2 = CTA pairs
 // (256 x 256 tile per pair); 0 restores the automatic choice.
 extern "C" int llnv_gemm_nvfp4_force_tile_n(int bn) {
-  LLNV_REQUIRE(bn == 0 || bn == 2 || bn == 128 || bn == 256, "llnv_gemm_nvfp4_force_tile_n: tile must be 0, 2, 128 or 256");
+  LLNV_REQUIRE(bn == 0 || bn == 2 || bn == 128 || bn == 192 || bn == 256, "llnv_gemm_nvfp4_force_tile_n: tile must be 0, 2, 128, 192 or 256");
   g_forced_bn = bn;
   return LLNV_OK;
 }
@@ -344,7 +352,11 @@ extern "C" int llnv_gemm_nvfp4(const void* a_codes, const void* a_sf, const floa
   int bn = (N % 256 == 0) ? 256 : 128;
   // few tokens (a sequence-parallel shard): 256-wide tiles would leave SMs idle, 128-wide tiles double the grid
   if (bn == 256 && ((M + 127) / 128) * (N / 256) * 2 <= (int64_t)sm_count() + 8) bn = 128;
+  // less than one wave of 256-wide tiles: 192-wide ones fill more SMs (and overlap their epilogue
+  // with the next main loop); with more tiles the lower operand traffic of the 256-wide tile wins
+  else if (bn == 256 && N % 192 == 0 && ((M + 127) / 128) * (N / 256) <= (int64_t)sm_count()) bn = 192;
   if (g_forced_bn == 128) bn = 128;
+  if (g_forced_bn == 192 && N % 192 == 0) bn = 192;
   if (g_forced_bn == 256 && N % 256 == 0) bn = 256;
 
   const uint64_t mp = (uint64_t)((M + 127) / 128 * 128);
@@ -384,7 +396,9 @@ extern "C" int llnv_gemm_nvfp4(const void* a_codes, const void* a_sf, const floa
   if (pair_ok && (g_forced_bn == 2 || pair_auto)) return gemm_nvfp4_pair(a_codes, a_sf, b_codes, b_sf, p, tmD, tmR, variant, stream);
 #define LLNV_GEMM_CASE(V)                                                                   \
   case V:                                                                                   \
-    return bn == 256 ? launch<256, V>(tmA, tmB, tmD, tmR, p, stream) : launch<128, V>(tmA, tmB, tmD, tmR, p, stream);
+    return bn == 256   ? launch<256, V>(tmA, tmB, tmD, tmR, p, stream)                            \
+           : bn == 192 ? launch<192, V>(tmA, tmB, tmD, tmR, p, stream)                            \
+                       : launch<128, V>(tmA, tmB, tmD, tmR, p, stream);
   switch (variant) {
     LLNV_GEMM_CASE(0)
     LLNV_GEMM_CASE(1)

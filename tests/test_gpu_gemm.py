@@ -170,3 +170,29 @@ def test_gemm_rejects_bad_shapes():
         L.fp4_matmul(x, w)
     with pytest.raises(ValueError):
         L.fp4_matmul(x, x, backend="pytorch")
+
+
+@pytest.mark.parametrize("m,n,k", [(200, 384, 512), (300, 768, 1024), (512, 3072, 3072), (2640, 3072, 3072)])
+def test_gemm_192_wide_tiles(m, n, k):
+    """192-wide B tiles start 0 or 64 rows into a 128-row scale atom; results equal the oracle and,
+    bit for bit, the 128-wide tiling (same products, same accumulation order along K)."""
+    lib = _lib.lib()
+    x = util.config_activation(m, k, seed=m + k)
+    w = util.config_weight(n, k, seed=n)
+    xq, wq = L.quantize_to_fp4(x.cuda()), L.quantize_to_fp4(w.cuda())
+    g = torch.Generator().manual_seed(8)
+    bias = torch.randn(n, generator=g).bfloat16().cuda()
+    resid = torch.randn(m, n, generator=g).bfloat16().cuda()
+    args = (xq.values, xq.scale_factors, xq.amax, 3, wq.values, wq.scale_factors, wq.amax, 3, m, n, k)
+    outs = {}
+    for tile in (192, 128):
+        lib.llnv_gemm_nvfp4_force_tile_n(tile)
+        try:
+            outs[tile] = (ops.gemm_nvfp4(*args), ops.gemm_nvfp4(*args, bias=bias, act=1), ops.gemm_nvfp4(*args, bias=bias, residual=resid))
+        finally:
+            lib.llnv_gemm_nvfp4_force_tile_n(0)
+    torch.cuda.synchronize()
+    assert lib.llnv_check_status(None) == 0, lib.llnv_last_error()
+    check_close(outs[192][0], O.bf16_round(oracle_matmul(xq, wq, m, n, k)), k)
+    for a, b in zip(outs[192], outs[128]):
+        assert torch.equal(a, b)
