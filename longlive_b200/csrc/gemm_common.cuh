@@ -39,27 +39,44 @@ __device__ __forceinline__ float gelu_tanh(float x) {
 // element and the whole epilogue fits the instruction cache)
 constexpr int kEpiBias = 1, kEpiGelu = 2, kEpiRes = 4;
 
-// Epilogue of one 64-column chunk of one accumulator row per thread: r holds the fp32 accumulators
-// (columns col .. col+63 of this thread's row), the result is written as bf16 into the warp's
+// First step of every epilogue: alpha * accumulator, rounded to bf16 (the reference's GEMM returns
+// bf16 before bias / activation / residual are applied), packed two columns per word.  After this
+// step the accumulator columns are no longer needed.
+__device__ __forceinline__ void drain_chunk(const uint32_t (&r)[2][32], float alpha, uint32_t (&pk)[32]) {
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int c0 = 2 * i, c1 = 2 * i + 1;
+    pk[i] = pack2(__fmul_rn(alpha, __uint_as_float(r[c0 >> 5][c0 & 31])), __fmul_rn(alpha, __uint_as_float(r[c1 >> 5][c1 & 31])));
+  }
+}
+
+// Rest of the epilogue of one 64-column chunk of one row per thread: pk holds bf16(alpha * acc) of
+// columns col .. col+63 of this thread's row, the result is written as bf16 into the warp's
 // swizzled staging buffer `buf` (32 rows x 128 bytes; with a residual the buffer holds the residual
 // tile on entry).  grow: this row's gate vector or nullptr.
 template <int EPI>
-__device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[2][32], float alpha, const uint16_t* __restrict__ bias,
-                                               const uint16_t* __restrict__ grow, int64_t col, uint8_t* buf, int lane,
-                                               bool want_amax, bool row_ok, float& local_amax) {
+__device__ __forceinline__ void epilogue_packed(const uint32_t (&pk)[32], const uint16_t* __restrict__ bias,
+                                                const uint16_t* __restrict__ grow, int64_t col, uint8_t* buf, int lane,
+                                                bool want_amax, bool row_ok, float& local_amax) {
   constexpr bool has_res = (EPI & kEpiRes) != 0;
 #pragma unroll
   for (int v8 = 0; v8 < 8; ++v8) {    // 8 columns (16 bytes) at a time
     uint4* slot = reinterpret_cast<uint4*>(buf + lane * 128 + ((v8 ^ (lane & 7)) << 4));
+    if (EPI == 0) {
+      if (want_amax && row_ok) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          local_amax = fmaxf(local_amax, fmaxf(fabsf(bf16_lo(pk[v8 * 4 + e])), fabsf(bf16_hi(pk[v8 * 4 + e]))));
+        }
+      }
+      *slot = make_uint4(pk[v8 * 4], pk[v8 * 4 + 1], pk[v8 * 4 + 2], pk[v8 * 4 + 3]);
+      continue;
+    }
     float y[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const int cc = v8 * 8 + e;      // column inside the 64-column chunk
-      y[e] = __fmul_rn(alpha, __uint_as_float(r[cc >> 5][cc & 31]));
-    }
-    if (EPI != 0 || want_amax) {
-#pragma unroll
-      for (int e = 0; e < 8; e += 2) round_bf16x2(y[e], y[e + 1]);
+    for (int e = 0; e < 4; ++e) {
+      y[2 * e] = bf16_lo(pk[v8 * 4 + e]);
+      y[2 * e + 1] = bf16_hi(pk[v8 * 4 + e]);
     }
     if (EPI & kEpiBias) {
       const uint4 bv = __ldg(reinterpret_cast<const uint4*>(bias + col + v8 * 8));
@@ -110,6 +127,16 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[2][32], float
     ov.w = pack2(y[6], y[7]);
     *slot = ov;
   }
+}
+
+// Both steps for one chunk (kernels whose accumulators rotate drain and finish chunk by chunk).
+template <int EPI>
+__device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[2][32], float alpha, const uint16_t* __restrict__ bias,
+                                               const uint16_t* __restrict__ grow, int64_t col, uint8_t* buf, int lane,
+                                               bool want_amax, bool row_ok, float& local_amax) {
+  uint32_t pk[32];
+  drain_chunk(r, alpha, pk);
+  epilogue_packed<EPI>(pk, bias, grow, col, buf, lane, want_amax, row_ok, local_amax);
 }
 
 }  // namespace gemm

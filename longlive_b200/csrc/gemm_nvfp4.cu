@@ -214,20 +214,10 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       }
       mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, 300u);
       tc_fence_after();
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 64, ++chunk) {
+      // everything after the accumulator has been drained: residual wait, epilogue math, staging, store
+      auto finish_chunk = [&](int c0, const uint32_t (&pkc)[32]) {
         const uint32_t b = chunk & 1u;
         uint8_t* buf = my_stage + b * 4096;
-        uint32_t r[2][32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c0, r[0]);
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c0 + 32, r[1]);
-        tmem_ld_wait();
-        if (c0 + 64 == BN) {
-          // accumulator fully read: hand it back to the MMA warp before the math and the stores
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&tempty_bar[acc]);
-        }
         if (row0 < p.M && !(p.debug & 4)) {
           if (has_res) {
             // prefetch the residual of the next chunk of this tile into the other buffer
@@ -243,13 +233,58 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             __syncwarp();
           }
           const int64_t col = (int64_t)nt * BN + c0;
-          epilogue_chunk<EPI>(r, alpha, bias, grow, col, buf, lane, p.epi.out_amax != nullptr, row_ok, local_amax);
+          epilogue_packed<EPI>(pkc, bias, grow, col, buf, lane, p.epi.out_amax != nullptr, row_ok, local_amax);
           fence_proxy_async();
           __syncwarp();
           if (lane == 0 && !(p.debug & 8)) {
             tma_store_2d(&tmD, buf, (int)col, row0);  // rows beyond M are clipped by the tensor map
             bulk_commit();
           }
+        }
+      };
+      const uint32_t acc_tmem = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+      if constexpr (C::kAcc == 1) {
+        // Single accumulator: drain all of it first (alpha, round to bf16, pack: 32 registers per 64
+        // columns) and hand it back to the MMA warp, so that the next tile's main loop runs while
+        // this tile's epilogue math, residual waits and stores are still in progress.
+        constexpr int kChunks = BN / 64;
+        uint32_t pk[kChunks][32];
+#pragma unroll
+        for (int ci = 0; ci < kChunks; ++ci) {
+          uint32_t r[2][32];
+          tmem_ld32(acc_tmem + ci * 64, r[0]);
+          tmem_ld32(acc_tmem + ci * 64 + 32, r[1]);
+          tmem_ld_wait();
+          drain_chunk(r, alpha, pk[ci]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 64, ++chunk) {
+          finish_chunk(c0, pk[0]);
+          // rotate the packed chunks so that the rolled loop always reads pk[0] (static register indices)
+#pragma unroll
+          for (int ci = 0; ci + 1 < kChunks; ++ci)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) pk[ci][i] = pk[ci + 1][i];
+        }
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 64, ++chunk) {
+          uint32_t r[2][32];
+          tmem_ld32(acc_tmem + c0, r[0]);
+          tmem_ld32(acc_tmem + c0 + 32, r[1]);
+          tmem_ld_wait();
+          if (c0 + 64 == BN) {
+            // accumulator fully read: hand it back to the MMA warp before the math and the stores
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+          }
+          uint32_t pkc[32];
+          drain_chunk(r, alpha, pkc);
+          finish_chunk(c0, pkc);
         }
       }
       if (++acc == C::kAcc) { acc = 0; acc_phase ^= 1u; }
