@@ -555,7 +555,7 @@ int ln_quantize_impl(int mode, const void* x, int64_t M, int64_t C, int64_t ldx,
   LLNV_REQUIRE(phase >= 0 && phase <= 2 && row_offset >= 0, "%s: phase must be 0, 1 or 2 and row_offset non-negative", who);
   if (phase != 2) LLNV_CUDA(cudaMemsetAsync(amax, 0, sizeof(float), stream));
   if (M == 0) return LLNV_OK;
-  Prologue pr;
+  Prologue pr = {};                 // every field the mode does not use stays zero (shard_cols = 0: plain input)
   pr.row_stats = row_stats;
   pr.p0 = (const uint16_t*)p0;
   pr.p1 = (const uint16_t*)p1;

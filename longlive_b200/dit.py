@@ -240,6 +240,7 @@ class CausalDiT:
         self.kv_amax = torch.zeros(2, dtype=torch.float32, device=dev)      # [k, v]: reduced with one collective
         self.k_amax, self.v_amax = self.kv_amax[0:1], self.kv_amax[1:2]
         self.h_amax = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.modulation_all = torch.stack([b.modulation for b in self.blocks], 0)       # [layers, 1, 6, dim]
         self.text_kv: list | None = None
         self.cache = KVCache(cfg, Hl, dev)
         # static inputs of a forward (a captured graph reads these addresses on every replay)
@@ -329,14 +330,17 @@ class CausalDiT:
         T = cfg.chunk_tokens
         win_k, win_v = self.win_k[li], self.win_v[li]
         cur_k, cur_v = win_k[n_past * T:(n_past + 1) * T], win_v[n_past * T:(n_past + 1) * T]
-        self.v_amax.zero_()
+        ck, cv = cache.k[li][cache.current_slot()], cache.v[li][cache.current_slot()]
         if self.P == 1:
-            self._gemm(self.act_c, Sl, blk.v, cur_v, out_amax=self.v_amax)
+            # the tensor scales of the cache block are produced in place by the V GEMM epilogue and the RoPE kernel
+            cv.amax.zero_()
+            self._gemm(self.act_c, Sl, blk.v, cur_v, out_amax=cv.amax)
             ops.rmsnorm_rope(x=self.q_buf, weight=blk.norm_q, cos=cos, sin=sin, eps=cfg.eps, out=self.q_rot)
             ops.rmsnorm_rope(x=self.k_buf, weight=blk.norm_k, cos=cos, sin=sin, eps=cfg.eps, out=self.k_rot, out_smooth=cur_k,
-                             amax_out=self.k_amax)
+                             amax_out=ck.amax)
             q_h, k_for_cache, v_for_cache = self.q_rot, self.k_rot, cur_v
         elif self.arena is not None:
+            self.v_amax.zero_()
             # tokens -> heads over peer memory: every producer stores each head shard at its final
             # address on the rank that owns those heads (q, rotated keys for the cache, smoothed keys
             # and values in that rank's window); one barrier makes all of it visible
@@ -353,6 +357,7 @@ class CausalDiT:
             ar.barrier()
             q_h, k_for_cache, v_for_cache = self.q_h, self.kr_h, cur_v
         else:
+            self.v_amax.zero_()
             P_, grp = self.P, self.group
             # tokens -> heads with NCCL: every producer writes the send layout, every part lands where
             # its consumer reads it
@@ -385,12 +390,19 @@ class CausalDiT:
         fused_amax = self.P == 1 or self.sync_amax
         ops.attention_bf16(q_h, win_k[:lk], win_v[:lk], self.Hl, out=self.attn_out, out_amax=self.act_c.amax if fused_amax else None)
         # cache write: rotated (un-smoothed) keys and values of the chunk, straight into the slot
-        cur = cache.current_slot()
-        ck, cv = cache.k[li][cur], cache.v[li][cur]
-        ck.amax.copy_(self.k_amax)
-        cv.amax.copy_(self.v_amax)
-        ops.quantize_nvfp4(k_for_cache.reshape(S * self.Hl, 128), MSE, ck.amax, ck.values, ck.scale_factors, amax_given=True)
-        ops.quantize_nvfp4(v_for_cache.reshape(S * self.Hl, 128), MSE, cv.amax, cv.values, cv.scale_factors, amax_given=True)
+        if self.P == 1:
+            kv_given = True
+        elif self.sync_amax:
+            # k_amax / v_amax (RoPE kernel, V GEMM epilogue), MAX-reduced over the group, are the amax of the cached tensors
+            ck.amax.copy_(self.k_amax)
+            cv.amax.copy_(self.v_amax)
+            kv_given = True
+        else:
+            # per-rank scales: the producers saw (my tokens, all heads), the cache block holds (all tokens,
+            # my heads); its own amax is taken so that no value can exceed the scale's range
+            kv_given = False
+        ops.quantize_nvfp4(k_for_cache.reshape(S * self.Hl, 128), MSE, ck.amax, ck.values, ck.scale_factors, amax_given=kv_given)
+        ops.quantize_nvfp4(v_for_cache.reshape(S * self.Hl, 128), MSE, cv.amax, cv.values, cv.scale_factors, amax_given=kv_given)
         if self.arena is not None:
             # heads -> tokens over peer memory: rank r receives my heads of its tokens in attn_sh[my rank];
             # the quantizer reads that [source heads][my tokens] layout directly
@@ -416,11 +428,10 @@ class CausalDiT:
         self._gemm(self.act_c, Sl, blk.co, x2, residual=x1)
         # -- FFN
         self._adaln_quantize(x2, e[:, 4], e[:, 3], self.act_c)
-        self.h_amax.zero_()
-        self._gemm(self.act_c, Sl, blk.ffn0, self.hidden, act=1, out_amax=self.h_amax)
+        self.act_f.amax.zero_()
+        self._gemm(self.act_c, Sl, blk.ffn0, self.hidden, act=1, out_amax=self.act_f.amax)
         if self.sync_amax:
-            sp.allreduce_max_(self.h_amax, self.group)
-        self.act_f.amax.copy_(self.h_amax)
+            sp.allreduce_max_(self.act_f.amax, self.group)
         ops.quantize_nvfp4(self.hidden, MSE, self.act_f.amax, self.act_f.codes, self.act_f.sf, amax_given=True)
         self._gemm(self.act_f, Sl, blk.ffn2, x_out, residual=x2, gate=e[:, 5], frame_rows=ft, row_offset=roff)
         return x_out
@@ -496,9 +507,9 @@ class CausalDiT:
         cos, sin = self.cos_buf, self.sin_buf
         self._ran_eager = True
         cur, nxt = self.x_a, self.x_b
+        em_all = self.modulation_all + e0.unsqueeze(0)                  # [layers, F, 6, dim], causal_model.py:863 for every block at once
         for li, blk in enumerate(self.blocks):
-            em = (blk.modulation + e0).contiguous()                    # [F, 6, dim], causal_model.py:863
-            self.block_forward(li, cur, nxt, em, ctx, cos, sin)
+            self.block_forward(li, cur, nxt, em_all[li], ctx, cos, sin)
             cur, nxt = nxt, cur
         # head: LayerNorm, modulate with (head.modulation + e), project (causal_model.py:1648)
         hm = (self.head_mod + e.unsqueeze(1)).float()                   # [F, 2, dim]
