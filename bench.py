@@ -379,10 +379,10 @@ def run_gpu_arm(args):
             line["dit_chunk"] = dit_chunk
         if world == 1 and not args.no_cpu_baseline:
             sample = [s for s in sweep_shapes((880,)) if s[0] in ("self_attn.q", "cross_attn.k", "ffn.0")]
-            v, dt, desc = cpu_port_tflops(sample)
+            v, dt, desc = cpu_port_tflops(sample, repeats=8)
             line["cpu_baseline"] = {"value": v, "unit": "TFLOP/s", "cores": os.cpu_count() or 1, "kind": "port",
                                     "sample": f"numpy restatement of the reference's dequantize-then-fp32-matmul backend, "
-                                              f"{dt:.1f} s on: {desc}"}
+                                              f"{dt:.1f} s for 8 passes over: {desc}"}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

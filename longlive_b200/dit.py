@@ -256,7 +256,7 @@ class CausalDiT:
     # ---- helpers ----------------------------------------------------------------------------
     def _gemm(self, a: _Act, rows: int, lin: _Linear, out, **epi):
         act = a
-        return ops.gemm_nvfp4(act.codes, act.sf, act.amax, MSE, lin.q.values, lin.q.scale_factors, lin.q.amax, MSE,
+        return ops.gemm_nvfp4(act.codes, act.sf, act.amax, MSE, lin.q.values, lin.q.scale_factors, lin.q.amax, lin.q.scale_rule.cuda_id(),
                               rows, lin.out_f, lin.in_f, out=out, bias=lin.bias, **epi)
 
     def _quantize(self, x, act: _Act, amax_given: bool = False, have_local_amax: bool = False):

@@ -8,6 +8,7 @@ import numpy as np
 import pytest
 import torch
 
+import longlive_b200 as L
 from longlive_b200 import dit, ops
 from oracle import dit_oracle as DO
 from oracle import nvfp4_oracle as O
@@ -115,3 +116,33 @@ def test_graph_replay_equals_eager():
                 te, tg = getattr(eager.cache, side)[layer][slot], getattr(graphed.cache, side)[layer][slot]
                 assert torch.equal(te.values, tg.values) and torch.equal(te.amax, tg.amax)
                 assert torch.equal(te.scale_factors.view(torch.uint8), tg.scale_factors.view(torch.uint8))
+
+
+def test_checkpoint_round_trip(tmp_path):
+    """A model saved in the reference's NVFP4 generator format and loaded into a model with other
+    weights reproduces the first model's forward bit for bit; bf16 master weights are quantized on load."""
+    from longlive_b200 import checkpoint as ck
+    cfg = dit.DiTConfig(**{**CFG, "layers": 2})
+    a, b = dit.CausalDiT(cfg, seed=5), dit.CausalDiT(cfg, seed=6)
+    path = str(tmp_path / "gen_nvfp4.pt")
+    ck.save_checkpoint(a, path)
+    saved = torch.load(path, map_location="cpu", weights_only=False)
+    assert saved["checkpoint_format"] == "longlive_generator_nvfp4" and saved["checkpoint_version"] == 1
+    assert sorted(saved["generator"]) == sorted(ck.expected_keys(cfg)) and ck.is_nvfp4_state_dict(saved["generator"])
+    assert ck.load_checkpoint(b, path) == []
+    g = torch.Generator().manual_seed(2)
+    raw = torch.randn(cfg.text_len, cfg.text_dim, generator=g).bfloat16().cuda()
+    lat = torch.randn(cfg.chunk_tokens, cfg.patch_dim, generator=g).bfloat16().cuda()
+    outs = [m.run_chunk(lat, m.encode_text(raw), 0) for m in (a, b)]
+    assert torch.equal(outs[0], outs[1])
+    # a bf16 checkpoint of one Linear: quantized on load with the stated rule
+    sd = dict(saved["generator"])
+    w = (torch.randn(cfg.dim, cfg.dim, generator=g) * 0.02).bfloat16()
+    for s in ("values", "scale_factors", "amax", "metadata"):
+        del sd[f"model.blocks.0.self_attn.q.quantized_weight_{s}"]
+    sd["model.blocks.0.self_attn.q.weight"] = w
+    assert ck.load_state_dict_into(b, sd) == []
+    ref = L.quantize_to_fp4(w.cuda(), L.QuantizationConfig(scale_rule="mse"))
+    assert torch.equal(b.blocks[0].q.q.values, ref.values) and torch.equal(b.blocks[0].q.q.amax, ref.amax)
+    with pytest.raises(KeyError):
+        ck.load_state_dict_into(b, {k: v for k, v in sd.items() if not k.endswith("norm3.bias")})
