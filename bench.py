@@ -341,10 +341,10 @@ def run_gpu_arm(args):
         dit_chunk = bench_dit_chunk(dev, rank, world, grp, args.chunk_steps, sync_amax=False)
         if world > 1:
             torch.cuda.empty_cache()
-            synced = bench_dit_chunk(dev, rank, world, grp, args.chunk_steps, sync_amax=True)
+            synced = bench_dit_chunk(dev, rank, world, grp, min(3, args.chunk_steps), sync_amax=True)
             dit_chunk["bit_identical_to_1gpu_amax_allreduce"] = {"value": synced["value"], "ms_per_chunk": synced["ms_per_chunk"]}
         torch.cuda.empty_cache()
-        eager = bench_dit_chunk(dev, rank, world, grp, args.chunk_steps, sync_amax=False, use_graphs=False)
+        eager = bench_dit_chunk(dev, rank, world, grp, min(3, args.chunk_steps), sync_amax=False, use_graphs=False)
         dit_chunk["eager_launches"] = {"value": eager["value"], "ms_per_chunk": eager["ms_per_chunk"]}
 
     if rank == 0:
@@ -429,13 +429,19 @@ def bench_dit_chunk(dev, rank, world, group, steps: int, sync_amax: bool = True,
     assert _lib.lib().llnv_check_status(None) == 0, _lib.lib().llnv_last_error()
     exchange = "producer kernels store into peer memory (NVLink), own barrier" if model.arena is not None else "NCCL all-to-all"
     model.close()
-    ms = statistics.median(times)
+    ts = sorted(times)
+    stats = [statistics.median(times), ts[int(0.1 * (len(ts) - 1))], ts[int(round(0.9 * (len(ts) - 1)))]]
     if world > 1:
-        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        t = torch.tensor(stats, dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+        stats = [float(v) for v in t.tolist()]
+    ms = stats[0]
+    # bytes every rank stores into other ranks' memory per chunk: q, rotated k, smoothed k, v and the
+    # attention output, each [2640 / P tokens, 3072 channels] bf16 per block and forward, (P - 1) / P of it remote
+    nvlink = 0 if world == 1 else int(5 * (cfg.chunk_tokens // world) * cfg.dim * 2 * (world - 1) / world) * cfg.layers * 5
     return {"metric": "dit_chunk_video_fps", "value": 12.0 / (ms * 1e-3), "unit": "frames/s", "latent_fps": 3.0 / (ms * 1e-3),
-            "ms_per_chunk": ms, "chunks_timed": steps, "layers": cfg.layers, "forwards_per_chunk": 5,
+            "ms_per_chunk": ms, "ms_per_chunk_p10": stats[1], "ms_per_chunk_p90": stats[2], "chunks_timed": steps,
+            "nvlink_bytes_sent_per_rank_per_chunk": nvlink, "layers": cfg.layers, "forwards_per_chunk": 5,
             "window_tokens": cfg.window_frames * cfg.frame_tokens, "chunk_tokens": cfg.chunk_tokens,
             "parallelism": f"sequence-parallel over {world} GPU(s)" if world > 1 else "single GPU",
             "amax_sync": bool(world > 1 and sync_amax), "cuda_graphs": bool(use_graphs), "scaling": "strong",
@@ -535,7 +541,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-dit", action="store_true", help="skip the 30-layer DiT chunk measurement")
-    ap.add_argument("--chunk-steps", type=int, default=3)
+    ap.add_argument("--chunk-steps", type=int, default=8, help="AR chunks timed for the dit_chunk figure (two periods of the rolling block table)")
     args = ap.parse_args()
     if args.kernel_case:
         run_kernel_case(args.kernel_case, args.iters)
