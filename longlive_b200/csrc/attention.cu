@@ -72,6 +72,28 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// three-input maximum (one instruction on sm_100) and packed two-lane fp32 arithmetic: they halve
+// the instruction count of the row maximum, the score scaling and the row sum
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float b, float c) {
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmov.b64 rc, {%5, %5};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+__device__ __forceinline__ void add2(float& d0, float& d1, float a0, float a1) {
+  asm("{\n\t.reg .b64 ra, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rd, {%0, %1};\n\t"
+      "add.rn.f32x2 rd, rd, ra;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "+f"(d0), "+f"(d1)
+      : "f"(a0), "f"(a1));
+}
+
 // 10 warps put three warps on some schedulers, whose 16 K-register files then allow 168 registers per thread
 __global__ void __launch_bounds__(kThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -237,7 +259,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
       for (int g = 0; g < 4; ++g)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) mx[i & 7] = fmaxf(mx[i & 7], __uint_as_float(sr[g][i]));
+        for (int i = 0; i < 32; i += 2) mx[(i >> 1) & 7] = fmax3(mx[(i >> 1) & 7], __uint_as_float(sr[g][i]), __uint_as_float(sr[g][i + 1]));
       const float mt = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
       // lazy rescale: keep the old offset unless this tile's maximum exceeds it by more than 2^8
       const bool grow = (mt - m) * c > 8.f;           // also true for the first tile (m = -inf)
@@ -263,19 +285,23 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         m = mt;                                        // first tile: nothing accumulated yet
       }
       const float mc = m * c;
-      float rsum[4] = {0.f, 0.f, 0.f, 0.f};
+      const float nmc = -mc;
+      float rsum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};      // four packed accumulators (even / odd columns)
       uint32_t pk0[32], pk1[32];
 #pragma unroll
       for (int g = 0; g < 4; ++g)
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float p0 = ex2(__fmaf_rn(__uint_as_float(sr[g][i]), c, -mc));
-          const float p1 = ex2(__fmaf_rn(__uint_as_float(sr[g][i + 1]), c, -mc));
-          rsum[(i >> 1) & 3] += p0 + p1;
+          float x0, x1;
+          fma2(x0, x1, __uint_as_float(sr[g][i]), __uint_as_float(sr[g][i + 1]), c, nmc);
+          const float p0 = ex2(x0);
+          const float p1 = ex2(x1);
+          const int a = ((i >> 1) & 3) * 2;
+          add2(rsum[a], rsum[a + 1], p0, p1);
           const uint32_t packed = pack2(p0, p1);
           if (g < 2) pk0[(g * 32 + i) >> 1] = packed; else pk1[((g - 2) * 32 + i) >> 1] = packed;
         }
-      const float rs = (rsum[0] + rsum[1]) + (rsum[2] + rsum[3]);
+      const float rs = ((rsum[0] + rsum[1]) + (rsum[2] + rsum[3])) + ((rsum[4] + rsum[5]) + (rsum[6] + rsum[7]));
       l += rs;
       tmem_st32(s_tmem, pk0);
       tmem_st32(s_tmem + 32, pk1);
