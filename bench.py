@@ -366,7 +366,7 @@ def run_gpu_arm(args):
             "gpu_launches": len(shapes) * args.steps,
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": fp4_peak, "unit": "TFLOP/s",
                          "frac": per_gpu / fp4_peak,
-                         "traffic": 53.5e6, "traffic_case": "dram read+write of one captured launch, M=2640 N=14336 K=3072 "
+                         "traffic": 51.3e6, "traffic_case": "dram read+write of one captured launch, M=2640 N=14336 K=3072 "
                                                             "(profiles/gemm_nvfp4_kernel__2640x14336x3072.md); algorithmic "
                                                             "operand+output bytes of that launch: 105 MB, of which 52 MB of output "
                                                             "stay dirty in L2",
