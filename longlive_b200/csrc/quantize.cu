@@ -395,53 +395,74 @@ __global__ void __launch_bounds__(256) quantize_nvfp4_kernel(const uint16_t* __r
 // ---- row statistics + amax of the transformed activation ----------------------------------------
 // One warp per row: mean and rstd in fp32 (two-pass over registers), then the row's transformed
 // values are formed once to find max|y|; nothing but the 8-byte statistics is stored.
-template <int MODE>
+// WPR warps share one row (each takes C / WPR channels): with one warp per row a chunk of 2640
+// tokens is only 2640 warps and the kernel is bound by the latency of each warp's dependent steps.
+template <int MODE, int WPR>
 __global__ void __launch_bounds__(256) ln_stats_amax_kernel(const uint16_t* __restrict__ x, int64_t M, int64_t C, int64_t ldx,
                                                             float eps, Prologue pr, float* __restrict__ row_stats,
                                                             float* __restrict__ amax) {
-  constexpr int kMaxVec = 16;                 // up to 16 x 8 elements per lane -> C <= 4096
+  constexpr int kVec = 16 / WPR;              // 16-byte vectors per lane: C <= 4096
+  constexpr int kRows = 8 / WPR;              // rows per CTA
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * 8 + warp;
-  // The modulation / affine vectors are shared by the rows of a CTA (8 consecutive rows touch at
+  const int part = warp % WPR;
+  const int64_t row = (int64_t)blockIdx.x * kRows + warp / WPR;
+  // The modulation / affine vectors are shared by the rows of a CTA (consecutive rows touch at
   // most two frames): stage them in shared memory once instead of loading them, dependently, in
   // every step of the per-row loop.
   __shared__ uint4 pa_sh[2][4096 / 8];
   __shared__ uint4 pb_sh[2][4096 / 8];
+  __shared__ float red_sh[2][8];
   const int nvec_all = (int)(C >> 3);
-  const int64_t first_row = (int64_t)blockIdx.x * 8;
-  const int64_t last_row = min(first_row + 7, M - 1);
+  const int pvec = nvec_all / WPR;            // vectors of this warp's part
+  const int vbase = part * pvec;
+  const int64_t first_row = (int64_t)blockIdx.x * kRows;
+  const int64_t last_row = min(first_row + kRows - 1, M - 1);
   const int64_t f0 = MODE == kAdaLN ? (first_row + pr.row_offset) / pr.frame_rows : 0;
   const int64_t f1 = MODE == kAdaLN ? (last_row + pr.row_offset) / pr.frame_rows : 0;
-  for (int i = threadIdx.x; i < nvec_all; i += blockDim.x) {
-    pa_sh[0][i] = __ldg(reinterpret_cast<const uint4*>(pr.p0 + f0 * pr.stride) + i);
-    pb_sh[0][i] = __ldg(reinterpret_cast<const uint4*>(pr.p1 + f0 * pr.stride) + i);
-    if (f1 != f0) {
-      pa_sh[1][i] = __ldg(reinterpret_cast<const uint4*>(pr.p0 + f1 * pr.stride) + i);
-      pb_sh[1][i] = __ldg(reinterpret_cast<const uint4*>(pr.p1 + f1 * pr.stride) + i);
+  // (with several warps per row a CTA has too few rows to amortise the staging: each lane then
+  // fetches its few vectors of the two parameter rows itself, together with x)
+  if (WPR == 1) {
+    for (int i = threadIdx.x; i < nvec_all; i += blockDim.x) {
+      pa_sh[0][i] = __ldg(reinterpret_cast<const uint4*>(pr.p0 + f0 * pr.stride) + i);
+      pb_sh[0][i] = __ldg(reinterpret_cast<const uint4*>(pr.p1 + f0 * pr.stride) + i);
+      if (f1 != f0) {
+        pa_sh[1][i] = __ldg(reinterpret_cast<const uint4*>(pr.p0 + f1 * pr.stride) + i);
+        pb_sh[1][i] = __ldg(reinterpret_cast<const uint4*>(pr.p1 + f1 * pr.stride) + i);
+      }
     }
   }
-  __syncthreads();
-  float wmax = 0.f;
-  if (row < M) {
-    const int nvec = (int)(C >> 3);           // 16-byte vectors per row
-    uint4 v[kMaxVec];
-    float sum = 0.f;
+  const bool live = row < M;
+  uint4 v[kVec], pa[kVec], pb[kVec];
+  float sum = 0.f;
+  if (live) {
+    const int64_t prow = MODE == kAdaLN ? ((row + pr.row_offset) / pr.frame_rows) * pr.stride : 0;
 #pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
-      const int idx = lane + 32 * i;
-      if (idx < nvec) {
-        v[i] = __ldg(reinterpret_cast<const uint4*>(x + row * ldx) + idx);
+    for (int i = 0; i < kVec; ++i) {
+      const int li = lane + 32 * i;
+      if (li < pvec) {
+        v[i] = __ldg(reinterpret_cast<const uint4*>(x + row * ldx) + vbase + li);
+        if (WPR > 1) {
+          pa[i] = __ldg(reinterpret_cast<const uint4*>(pr.p0 + prow) + vbase + li);
+          pb[i] = __ldg(reinterpret_cast<const uint4*>(pr.p1 + prow) + vbase + li);
+        }
         sum += bf16_lo(v[i].x) + bf16_hi(v[i].x) + bf16_lo(v[i].y) + bf16_hi(v[i].y) + bf16_lo(v[i].z) + bf16_hi(v[i].z) +
                bf16_lo(v[i].w) + bf16_hi(v[i].w);
       }
     }
+  }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
-    const float mean = sum / (float)C;
-    float sq = 0.f;
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+  if (lane == 0) red_sh[0][warp] = sum;
+  __syncthreads();                            // vectors staged, partial sums published
+  float tot = red_sh[0][warp - part];
 #pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
-      if (lane + 32 * i < nvec) {
+  for (int k = 1; k < WPR; ++k) tot += red_sh[0][warp - part + k];
+  const float mean = tot / (float)C;
+  float sq = 0.f;
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) {
+      if (lane + 32 * i < pvec) {
         const uint32_t ws[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -450,20 +471,29 @@ __global__ void __launch_bounds__(256) ln_stats_amax_kernel(const uint16_t* __re
         }
       }
     }
+  }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xFFFFFFFFu, sq, o);
-    const float rstd = 1.0f / sqrtf(sq / (float)C + eps);
-    if (lane == 0) {
+  for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xFFFFFFFFu, sq, o);
+  if (lane == 0) red_sh[1][warp] = sq;
+  __syncthreads();
+  float sqt = red_sh[1][warp - part];
+#pragma unroll
+  for (int k = 1; k < WPR; ++k) sqt += red_sh[1][warp - part + k];
+  const float rstd = 1.0f / sqrtf(sqt / (float)C + eps);
+  float wmax = 0.f;
+  if (live) {
+    if (lane == 0 && part == 0) {
       row_stats[2 * row] = mean;
       row_stats[2 * row + 1] = rstd;
     }
     const int fsel = (MODE == kAdaLN && (row + pr.row_offset) / pr.frame_rows != f0) ? 1 : 0;
 #pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
-      const int idx = lane + 32 * i;
-      if (idx < nvec) {
-        const uint4 a4 = pa_sh[fsel][idx];
-        const uint4 b4 = pb_sh[fsel][idx];
+    for (int i = 0; i < kVec; ++i) {
+      const int li = lane + 32 * i;
+      if (li < pvec) {
+        const int idx = vbase + li;
+        const uint4 a4 = WPR > 1 ? pa[i] : pa_sh[fsel][idx];
+        const uint4 b4 = WPR > 1 ? pb[i] : pb_sh[fsel][idx];
         const uint32_t ws[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
         const uint32_t aw[4] = {a4.x, a4.y, a4.z, a4.w};
         const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w};
@@ -563,10 +593,14 @@ int ln_quantize_impl(int mode, const void* x, int64_t M, int64_t C, int64_t ldx,
   pr.frame_rows = frame_rows > 0 ? frame_rows : 1;
   pr.add_one = add_one;
   pr.row_offset = row_offset;
-  const unsigned sblocks = (unsigned)((M + 7) / 8);
   if (phase != 2) {
-    if (mode == kAdaLN) ln_stats_amax_kernel<kAdaLN><<<sblocks, 256, 0, stream>>>((const uint16_t*)x, M, C, ldx, eps, pr, row_stats, amax);
-    else ln_stats_amax_kernel<kAffineLN><<<sblocks, 256, 0, stream>>>((const uint16_t*)x, M, C, ldx, eps, pr, row_stats, amax);
+    // warps per row: four when that leaves every lane at least one 16-byte vector (C a multiple of 1024), else one
+    const bool split = C % 1024 == 0;
+    const unsigned sblocks = split ? (unsigned)((M + 1) / 2) : (unsigned)((M + 7) / 8);
+    if (mode == kAdaLN && split) ln_stats_amax_kernel<kAdaLN, 4><<<sblocks, 256, 0, stream>>>((const uint16_t*)x, M, C, ldx, eps, pr, row_stats, amax);
+    else if (mode == kAdaLN) ln_stats_amax_kernel<kAdaLN, 1><<<sblocks, 256, 0, stream>>>((const uint16_t*)x, M, C, ldx, eps, pr, row_stats, amax);
+    else if (split) ln_stats_amax_kernel<kAffineLN, 4><<<sblocks, 256, 0, stream>>>((const uint16_t*)x, M, C, ldx, eps, pr, row_stats, amax);
+    else ln_stats_amax_kernel<kAffineLN, 1><<<sblocks, 256, 0, stream>>>((const uint16_t*)x, M, C, ldx, eps, pr, row_stats, amax);
     int rc = launch_status("ln_stats_amax_kernel");
     if (rc != LLNV_OK) return rc;
   }

@@ -25,25 +25,36 @@ struct ShardOut {
   uint16_t* smooth[kMaxShards];
 };
 
+// WPR warps share one token row (each takes C / WPR channels, a whole number of heads): a row is
+// short (6 KB), so with one warp per row a chunk of 2640 tokens would put only 2640 warps on the
+// device and the kernel would be bound by the latency of each warp's single pass.
+template <int WPR>
 __global__ void __launch_bounds__(256) rmsnorm_rope_kernel(const uint16_t* __restrict__ x, int64_t S, int64_t C, int64_t ldx,
                                                            const uint16_t* __restrict__ weight, float eps,
                                                            const float* __restrict__ cosv, const float* __restrict__ sinv,
                                                            const ShardOut dst, int64_t ldo, int64_t lds, bool want_smooth,
                                                            float* __restrict__ amax_out, int shard_vecs) {
+  constexpr int kVec = kMaxVec / WPR;        // 16-byte vectors per lane
+  constexpr int kRows = 8 / WPR;             // rows per CTA
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * 8 + warp;
+  const int part = warp % WPR;
+  const int64_t row = (int64_t)blockIdx.x * kRows + warp / WPR;
   // the norm weight is shared by all rows: one cooperative load per CTA instead of a dependent
   // global load in every step of the per-row loop
   __shared__ uint4 w_sh[4096 / 8];
+  __shared__ float ss_sh[8];
   const int nvec = (int)(C >> 3);
+  const int pvec = nvec / WPR;               // vectors of this warp's part
+  const int vbase = part * pvec;
   if (weight) {
     for (int i = threadIdx.x; i < nvec; i += blockDim.x) w_sh[i] = __ldg(reinterpret_cast<const uint4*>(weight) + i);
   }
-  __syncthreads();
-  float wmax = 0.f;
+  // this lane needs the same 4 cos / 4 sin values in every step (pair index depends on lane only:
+  // a part starts on a head boundary)
+  float cc[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
+  uint4 v[kVec];
+  float ss = 0.f;
   if (row < S) {
-    // this lane needs the same 4 cos / 4 sin values in every step (pair index depends on lane only)
-    float cc[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
     if (cosv) {
       const int pair0 = (lane & 15) * 4;
       const float4 c4 = __ldg(reinterpret_cast<const float4*>(cosv + row * 64 + pair0));
@@ -51,13 +62,11 @@ __global__ void __launch_bounds__(256) rmsnorm_rope_kernel(const uint16_t* __res
       cc[0] = c4.x; cc[1] = c4.y; cc[2] = c4.z; cc[3] = c4.w;
       sn[0] = s4.x; sn[1] = s4.y; sn[2] = s4.z; sn[3] = s4.w;
     }
-    uint4 v[kMaxVec];
-    float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
-      const int idx = lane + 32 * i;
-      if (idx < nvec) {
-        v[i] = __ldg(reinterpret_cast<const uint4*>(x + row * ldx) + idx);
+    for (int i = 0; i < kVec; ++i) {
+      const int li = lane + 32 * i;
+      if (li < pvec) {
+        v[i] = __ldg(reinterpret_cast<const uint4*>(x + row * ldx) + vbase + li);
         const uint32_t w4[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -66,16 +75,27 @@ __global__ void __launch_bounds__(256) rmsnorm_rope_kernel(const uint16_t* __res
         }
       }
     }
+  }
+  if (weight) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+    if (lane == 0) ss_sh[warp] = ss;
+  }
+  __syncthreads();                           // weight staged, partial sums of squares published
+  float wmax = 0.f;
+  if (row < S) {
     float rinv = 1.f;
     if (weight) {
+      float tot = ss_sh[warp - part];
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
-      rinv = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)C), eps)));
+      for (int k = 1; k < WPR; ++k) tot += ss_sh[warp - part + k];
+      rinv = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)C), eps)));
     }
 #pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
-      const int idx = lane + 32 * i;
-      if (idx >= nvec) continue;          // uniform per (i, lane half): C is a multiple of 128 so 16-lane groups stay whole
+    for (int i = 0; i < kVec; ++i) {
+      const int li = lane + 32 * i;
+      if (li >= pvec) continue;           // uniform per (i, lane half): a part is a whole number of heads, so 16-lane groups stay whole
+      const int idx = vbase + li;
       uint32_t w4[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
       float y[8];
 #pragma unroll
@@ -177,8 +197,17 @@ int rope_launch(const void* x, int64_t S, int64_t C, int64_t ldx, const void* we
   }
   if (amax_out) LLNV_CUDA(cudaMemsetAsync(amax_out, 0, sizeof(float), stream));
   if (S == 0) return LLNV_OK;
-  rmsnorm_rope_kernel<<<(unsigned)((S + 7) / 8), 256, 0, stream>>>((const uint16_t*)x, S, C, ldx, (const uint16_t*)weight, eps, cos, sin,
-                                                                  dst, ldo, lds, want_smooth, amax_out, shards > 1 ? (int)(Cs / 8) : 0);
+  const int sv = shards > 1 ? (int)(Cs / 8) : 0;
+  // warps per row: as many as leave every warp a whole number of heads and every lane some work
+  if (C % 512 == 0 && C >= 2048)
+    rmsnorm_rope_kernel<4><<<(unsigned)((S + 1) / 2), 256, 0, stream>>>((const uint16_t*)x, S, C, ldx, (const uint16_t*)weight, eps, cos, sin,
+                                                                       dst, ldo, lds, want_smooth, amax_out, sv);
+  else if (C % 256 == 0 && C >= 1024)
+    rmsnorm_rope_kernel<2><<<(unsigned)((S + 3) / 4), 256, 0, stream>>>((const uint16_t*)x, S, C, ldx, (const uint16_t*)weight, eps, cos, sin,
+                                                                       dst, ldo, lds, want_smooth, amax_out, sv);
+  else
+    rmsnorm_rope_kernel<1><<<(unsigned)((S + 7) / 8), 256, 0, stream>>>((const uint16_t*)x, S, C, ldx, (const uint16_t*)weight, eps, cos, sin,
+                                                                       dst, ldo, lds, want_smooth, amax_out, sv);
   return launch_status("rmsnorm_rope_kernel");
 }
 
