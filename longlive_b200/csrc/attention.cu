@@ -94,6 +94,22 @@ __device__ __forceinline__ void add2(float& d0, float& d1, float a0, float a1) {
       : "f"(a0), "f"(a1));
 }
 
+// exp2 on the FMA pipe for a share of the scores: floor via a round-down add of 1.5 * 2^23, a cubic
+// for 2^frac (relative error 8.6e-5, far below the bf16 rounding of P), exponent added as an integer.
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -125.f);
+  float r;
+  asm("add.rm.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(x), "f"(12582912.f));
+  const float f = x - (r - 12582912.f);            // fraction in [0, 1)
+  float pl = __fmaf_rn(f, 0.07706618f, 0.22764593f);
+  pl = __fmaf_rn(pl, f, 0.69511658f);
+  pl = __fmaf_rn(pl, f, 1.f);
+  return __int_as_float(__float_as_int(pl) + (__float_as_int(r) << 23));
+}
+#ifndef LLNV_ATTN_POLY_MOD
+#define LLNV_ATTN_POLY_MOD 8        // every 8th score takes the FMA-pipe exp2 (measured best; 4 is already slower, 0 = none)
+#endif
+
 // 10 warps put three warps on some schedulers, whose 16 K-register files then allow 168 registers per thread
 __global__ void __launch_bounds__(kThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -294,8 +310,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int i = 0; i < 32; i += 2) {
           float x0, x1;
           fma2(x0, x1, __uint_as_float(sr[g][i]), __uint_as_float(sr[g][i + 1]), c, nmc);
+          constexpr int kMod = LLNV_ATTN_POLY_MOD;
           const float p0 = ex2(x0);
-          const float p1 = ex2(x1);
+          const float p1 = (kMod > 0 && (i + 1) % kMod == kMod - 1) ? ex2_poly(x1) : ex2(x1);
           const int a = ((i >> 1) & 3) * 2;
           add2(rsum[a], rsum[a + 1], p0, p1);
           const uint32_t packed = pack2(p0, p1);
