@@ -84,6 +84,49 @@ __device__ __forceinline__ void round_bf16x2(float& a, float& b) {
 // round an fp32 value to bf16 precision, keep it in fp32
 __device__ __forceinline__ float round_bf16(float f) { return __uint_as_float(f2bf(f) << 16); }
 
+// Packed two-lane fp32 arithmetic (sm_100): each lane is the correctly rounded IEEE operation, so a
+// packed instruction gives bit for bit what the two scalar ones give, at half the issue slots.
+struct F2 {
+  float x, y;
+};
+__device__ __forceinline__ F2 f2_fma(F2 a, F2 b, F2 c) {
+  F2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ F2 f2_mul(F2 a, F2 b) {
+  F2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "mul.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ F2 f2_add(F2 a, F2 b) {
+  F2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ F2 f2_sub(F2 a, F2 b) {
+  F2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "sub.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ F2 f2_splat(float v) { return F2{v, v}; }
+
 // e4m3 byte -> fp32 (exact)
 __device__ __forceinline__ float e4m3_to_float(uint32_t b) {
   __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)(b & 0xFF), __NV_E4M3);

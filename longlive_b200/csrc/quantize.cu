@@ -73,6 +73,15 @@ __device__ __forceinline__ float div_const(float x) {
   return __fmaf_rn(rem, r, q);
 }
 
+template <int D>
+__device__ __forceinline__ F2 div_const2(F2 x) {
+  constexpr float d = (float)D;
+  constexpr float r = 1.0f / d;
+  const F2 q = f2_mul(x, f2_splat(r));
+  const F2 rem = f2_fma(f2_splat(-d), q, x);
+  return f2_fma(rem, f2_splat(r), q);
+}
+
 // ---- hardware conversions ---------------------------------------------------------------------
 // two fp32 -> two E2M1 codes (lo in bits 0-3, hi in bits 4-7), round to nearest even, saturating
 __device__ __forceinline__ uint32_t cvt_e2m1x2(float lo, float hi) {
@@ -225,33 +234,49 @@ __device__ __forceinline__ void quant_block(const uint32_t (&w)[8], const QuantC
   // element i to element i+8 first, then the eight lane sums left to right
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    const float xa0 = bf16_lo(w[j]), xa1 = bf16_hi(w[j]);            // elements 2j, 2j+1
-    const float xb0 = bf16_lo(w[j + 4]), xb1 = bf16_hi(w[j + 4]);    // elements 2j+8, 2j+9
+    const F2 xa = {bf16_lo(w[j]), bf16_hi(w[j])};                    // elements 2j, 2j+1
+    const F2 xb = {bf16_lo(w[j + 4]), bf16_hi(w[j + 4])};            // elements 2j+8, 2j+9
     // the +0 addend turns a -0 product (input -0.0) into +0, as the reference's sign(x)*|.| does
-    const uint32_t ca6 = cvt_e2m1x2(__fmaf_rn(xa0, inv6, 0.f), __fmaf_rn(xa1, inv6, 0.f));
-    const uint32_t cb6 = cvt_e2m1x2(__fmaf_rn(xb0, inv6, 0.f), __fmaf_rn(xb1, inv6, 0.f));
-    const uint32_t ca4 = cvt_e2m1x2(__fmaf_rn(xa0, inv4, 0.f), __fmaf_rn(xa1, inv4, 0.f));
-    const uint32_t cb4 = cvt_e2m1x2(__fmaf_rn(xb0, inv4, 0.f), __fmaf_rn(xb1, inv4, 0.f));
+    const F2 zero = f2_splat(0.f);
+    const F2 sa6v = f2_fma(xa, f2_splat(inv6), zero), sb6v = f2_fma(xb, f2_splat(inv6), zero);
+    const F2 sa4v = f2_fma(xa, f2_splat(inv4), zero), sb4v = f2_fma(xb, f2_splat(inv4), zero);
+    const uint32_t ca6 = cvt_e2m1x2(sa6v.x, sa6v.y);
+    const uint32_t cb6 = cvt_e2m1x2(sb6v.x, sb6v.y);
+    const uint32_t ca4 = cvt_e2m1x2(sa4v.x, sa4v.y);
+    const uint32_t cb4 = cvt_e2m1x2(sb4v.x, sb4v.y);
     lo6 |= ca6 << (8 * j); hi6 |= cb6 << (8 * j);
     lo4 |= ca4 << (8 * j); hi4 |= cb4 << (8 * j);
     const float2 qa6 = e2m1x2_to_float2(ca6), qb6 = e2m1x2_to_float2(cb6);
     const float2 qa4 = e2m1x2_to_float2(ca4), qb4 = e2m1x2_to_float2(cb4);
-    const float t6a0 = err_term<RULE>(__fsub_rn(div_const<1536>(__fmul_rn(qa6.x, sa6)), xa0));
-    const float t6b0 = err_term<RULE>(__fsub_rn(div_const<1536>(__fmul_rn(qb6.x, sa6)), xb0));
-    const float t6a1 = err_term<RULE>(__fsub_rn(div_const<1536>(__fmul_rn(qa6.y, sa6)), xa1));
-    const float t6b1 = err_term<RULE>(__fsub_rn(div_const<1536>(__fmul_rn(qb6.y, sa6)), xb1));
-    const float t4a0 = err_term<RULE>(__fsub_rn(div_const<1536>(__fmul_rn(qa4.x, sa4)), xa0));
-    const float t4b0 = err_term<RULE>(__fsub_rn(div_const<1536>(__fmul_rn(qb4.x, sa4)), xb0));
-    const float t4a1 = err_term<RULE>(__fsub_rn(div_const<1536>(__fmul_rn(qa4.y, sa4)), xa1));
-    const float t4b1 = err_term<RULE>(__fsub_rn(div_const<1536>(__fmul_rn(qb4.y, sa4)), xb1));
-    if (RULE == LLNV_RULE_ABS_MAX) {
-      e6 = fmaxf(fmaxf(e6, fmaxf(t6a0, t6b0)), fmaxf(t6a1, t6b1));
-      e4 = fmaxf(fmaxf(e4, fmaxf(t4a0, t4b0)), fmaxf(t4a1, t4b1));
+    // dequantized candidates minus x, two elements per packed instruction (every lane rounds as the scalar op does)
+    const F2 da6 = f2_sub(div_const2<1536>(f2_mul(F2{qa6.x, qa6.y}, f2_splat(sa6))), xa);
+    const F2 db6 = f2_sub(div_const2<1536>(f2_mul(F2{qb6.x, qb6.y}, f2_splat(sa6))), xb);
+    const F2 da4 = f2_sub(div_const2<1536>(f2_mul(F2{qa4.x, qa4.y}, f2_splat(sa4))), xa);
+    const F2 db4 = f2_sub(div_const2<1536>(f2_mul(F2{qb4.x, qb4.y}, f2_splat(sa4))), xb);
+    if (RULE == LLNV_RULE_MSE) {
+      // lanes 2j and 2j+1 of the 8-lane partial sums: element i plus element i+8
+      const F2 l6 = f2_add(f2_mul(da6, da6), f2_mul(db6, db6));
+      const F2 l4 = f2_add(f2_mul(da4, da4), f2_mul(db4, db4));
+      // running sums of both candidates side by side: (e6, e4) + lane 2j, then + lane 2j+1
+      if (j == 0) {
+        const F2 e = f2_add(F2{l6.x, l4.x}, F2{l6.y, l4.y});
+        e6 = e.x; e4 = e.y;
+      } else {
+        const F2 e = f2_add(f2_add(F2{e6, e4}, F2{l6.x, l4.x}), F2{l6.y, l4.y});
+        e6 = e.x; e4 = e.y;
+      }
     } else {
-      const float l6a = __fadd_rn(t6a0, t6b0), l6b = __fadd_rn(t6a1, t6b1);   // lanes 2j and 2j+1
-      const float l4a = __fadd_rn(t4a0, t4b0), l4b = __fadd_rn(t4a1, t4b1);
-      e6 = j == 0 ? __fadd_rn(l6a, l6b) : __fadd_rn(__fadd_rn(e6, l6a), l6b);
-      e4 = j == 0 ? __fadd_rn(l4a, l4b) : __fadd_rn(__fadd_rn(e4, l4a), l4b);
+      const float t6a0 = fabsf(da6.x), t6a1 = fabsf(da6.y), t6b0 = fabsf(db6.x), t6b1 = fabsf(db6.y);
+      const float t4a0 = fabsf(da4.x), t4a1 = fabsf(da4.y), t4b0 = fabsf(db4.x), t4b1 = fabsf(db4.y);
+      if (RULE == LLNV_RULE_ABS_MAX) {
+        e6 = fmaxf(fmaxf(e6, fmaxf(t6a0, t6b0)), fmaxf(t6a1, t6b1));
+        e4 = fmaxf(fmaxf(e4, fmaxf(t4a0, t4b0)), fmaxf(t4a1, t4b1));
+      } else {
+        const float l6a = __fadd_rn(t6a0, t6b0), l6b = __fadd_rn(t6a1, t6b1);   // lanes 2j and 2j+1
+        const float l4a = __fadd_rn(t4a0, t4b0), l4b = __fadd_rn(t4a1, t4b1);
+        e6 = j == 0 ? __fadd_rn(l6a, l6b) : __fadd_rn(__fadd_rn(e6, l6a), l6b);
+        e4 = j == 0 ? __fadd_rn(l4a, l4b) : __fadd_rn(__fadd_rn(e4, l4a), l4b);
+      }
     }
   }
   const bool sel4 = e4 < e6;
