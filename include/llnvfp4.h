@@ -180,6 +180,13 @@ int llnv_scatter_2d(const void* src, int64_t src_shard_bytes, int64_t src_pitch,
  * is bounded; a rank that gives up records LLNV_E_TIMEOUT for llnv_check_status and returns. */
 int llnv_peer_barrier(void* const* signal_ptrs, int rank, int world, void* epoch, llnv_stream_t stream);
 
+/* MAX all-reduce of n <= 32 device floats over the group, in place, fused with that barrier (same
+ * signal areas and epoch; counts as one barrier).  slot_ptrs[r] is rank r's slot area: 2 * 8 * 32
+ * floats of symmetric memory.  Used for the per-tensor amax values of the quantizers, so that a
+ * sequence-parallel group produces the codes and scales of the single-GPU run. */
+int llnv_peer_allreduce_max(float* vals, int n, void* const* slot_ptrs, void* const* signal_ptrs, int rank, int world,
+                            void* epoch, llnv_stream_t stream);
+
 /* Dequantize `num_blocks` KV-cache blocks, each an NVFP4 matrix [rows_padded, 128] holding
  * block_token_size*num_heads logical rows (token-major, head-minor), into one contiguous
  * tensor [1, num_blocks*block_token_size, num_heads, 128] of dtype_code.

@@ -64,6 +64,56 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(PeerPtrs signals, int 
   if (threadIdx.x == 0) *epoch = e;
 }
 
+// MAX all-reduce of up to 32 floats over the group, fused with the barrier: thread r stores this
+// rank's values into rank r's slot array (slots[epoch parity][my rank][i]), signals and waits as
+// peer_barrier_kernel does, then thread i takes the maximum of slot i over all ranks.  Two slot
+// arrays alternate with the epoch, so a rank that is already in the next reduction cannot overwrite
+// values a slower rank has not read yet (it cannot be two reductions ahead: each one is a barrier).
+__global__ void __launch_bounds__(32) peer_allreduce_max_kernel(float* __restrict__ vals, int n, PeerPtrs slots, PeerPtrs signals,
+                                                                int rank, int world, unsigned int* epoch, unsigned int* status) {
+  __shared__ unsigned int e_sh;
+  if (threadIdx.x == 0) e_sh = *epoch + 1u;
+  __syncwarp();
+  const unsigned int e = e_sh;
+  const int r = threadIdx.x;
+  const int par = (int)(e & 1u);
+  bool ok = true;
+  if (r < world) {
+    float* theirs = reinterpret_cast<float*>(slots.p[r]) + ((int64_t)par * kMaxPeers + rank) * 32;
+    for (int i = 0; i < n; ++i) theirs[i] = vals[i];
+    unsigned int* flag = reinterpret_cast<unsigned int*>(signals.p[r]) + rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(e) : "memory");
+    const unsigned int* mine = reinterpret_cast<const unsigned int*>(signals.p[rank]) + r;
+    ok = false;
+    for (uint32_t i = 0; i < kPeerPolls; ++i) {
+      unsigned int v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+      if ((int)(v - e) >= 0) {
+        ok = true;
+        break;
+      }
+    }
+  }
+  if (!ok && status && atomicCAS(status, 0u, 3u) == 0u) {
+    status[1] = 701u;
+    status[2] = (unsigned int)r;
+    status[3] = e;
+  }
+  __syncwarp();
+  if (threadIdx.x < n) {
+    const float* mine = reinterpret_cast<const float*>(slots.p[rank]) + (int64_t)par * kMaxPeers * 32 + threadIdx.x;
+    float m = -INFINITY;
+    for (int q = 0; q < world; ++q) {
+      float v;
+      asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(mine + q * 32) : "memory");
+      m = fmaxf(m, v);
+    }
+    vals[threadIdx.x] = m;
+  }
+  __syncwarp();
+  if (threadIdx.x == 0) *epoch = e;
+}
+
 // dst[r][i][0:row_bytes] = src[r * src_shard_bytes + i * src_pitch : ... + row_bytes], 16-byte vectors.
 __global__ void __launch_bounds__(256) scatter_2d_kernel(const uint8_t* __restrict__ src, int64_t src_shard_bytes, int64_t src_pitch,
                                                          PeerPtrs dst, int64_t dst_pitch, int64_t rows, int vec_per_row) {
@@ -95,6 +145,23 @@ extern "C" int llnv_peer_barrier(void* const* signal_ptrs, int rank, int world, 
   }
   peer_barrier_kernel<<<1, 32, 0, stream>>>(sp, rank, world, (unsigned int*)epoch, device_status_word());
   return launch_status("peer_barrier_kernel");
+}
+
+extern "C" int llnv_peer_allreduce_max(float* vals, int n, void* const* slot_ptrs, void* const* signal_ptrs, int rank, int world,
+                                       void* epoch, llnv_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  LLNV_REQUIRE(vals && slot_ptrs && signal_ptrs && epoch, "llnv_peer_allreduce_max: null pointer");
+  LLNV_REQUIRE(n >= 1 && n <= 32, "llnv_peer_allreduce_max: 1 to 32 values (got %d)", n);
+  LLNV_REQUIRE(world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world, "llnv_peer_allreduce_max: need 1 <= world <= 8 and 0 <= rank < world");
+  PeerPtrs sl = {}, sg = {};
+  for (int r = 0; r < world; ++r) {
+    LLNV_REQUIRE(slot_ptrs[r] != nullptr && signal_ptrs[r] != nullptr && ((uintptr_t)slot_ptrs[r] & 3) == 0 && ((uintptr_t)signal_ptrs[r] & 3) == 0,
+                 "llnv_peer_allreduce_max: bad pointer of rank %d", r);
+    sl.p[r] = slot_ptrs[r];
+    sg.p[r] = signal_ptrs[r];
+  }
+  peer_allreduce_max_kernel<<<1, 32, 0, stream>>>(vals, n, sl, sg, rank, world, (unsigned int*)epoch, device_status_word());
+  return launch_status("peer_allreduce_max_kernel");
 }
 
 extern "C" int llnv_scatter_2d(const void* src, int64_t src_shard_bytes, int64_t src_pitch, void* const* dst_ptrs, int64_t dst_pitch,

@@ -254,6 +254,14 @@ class CausalDiT:
         self._ran_eager = False
 
     # ---- helpers ----------------------------------------------------------------------------
+    def _allreduce_max(self, t: torch.Tensor) -> None:
+        """MAX over the group of a small fp32 tensor (per-tensor amax): through peer memory when the
+        arena exists (one small kernel, no NCCL launch), else an NCCL all-reduce."""
+        if self.arena is not None:
+            self.arena.allreduce_max_(t)
+        else:
+            sp.allreduce_max_(t, self.group)
+
     def _gemm(self, a: _Act, rows: int, lin: _Linear, out, **epi):
         act = a
         return ops.gemm_nvfp4(act.codes, act.sf, act.amax, MSE, lin.q.values, lin.q.scale_factors, lin.q.amax, lin.q.scale_rule.cuda_id(),
@@ -267,7 +275,7 @@ class CausalDiT:
             if self.sync_amax:
                 if not have_local_amax:
                     ops.amax_bf16(x if x.dim() == 2 else x.view(-1, x.shape[-1]), act.amax)
-                sp.allreduce_max_(act.amax, self.group)
+                self._allreduce_max(act.amax)
                 amax_given = True
             elif have_local_amax:
                 amax_given = True
@@ -278,7 +286,7 @@ class CausalDiT:
         kw = dict(codes=act.codes, sf=act.sf, amax=act.amax, row_stats=self.row_stats, row_offset=self.rank * self.Sl)
         if self.sync_amax:
             ops.adaln_quantize_nvfp4(x, scale, shift, cfg.frame_tokens, MSE, cfg.eps, phase=1, **kw)
-            sp.allreduce_max_(act.amax, self.group)
+            self._allreduce_max(act.amax)
             ops.adaln_quantize_nvfp4(x, scale, shift, cfg.frame_tokens, MSE, cfg.eps, phase=2, **kw)
         else:
             ops.adaln_quantize_nvfp4(x, scale, shift, cfg.frame_tokens, MSE, cfg.eps, **kw)
@@ -287,7 +295,7 @@ class CausalDiT:
         kw = dict(codes=act.codes, sf=act.sf, amax=act.amax, row_stats=self.row_stats)
         if self.sync_amax:
             ops.layernorm_quantize_nvfp4(x, w, b, MSE, self.cfg.eps, phase=1, **kw)
-            sp.allreduce_max_(act.amax, self.group)
+            self._allreduce_max(act.amax)
             ops.layernorm_quantize_nvfp4(x, w, b, MSE, self.cfg.eps, phase=2, **kw)
         else:
             ops.layernorm_quantize_nvfp4(x, w, b, MSE, self.cfg.eps, **kw)
@@ -353,8 +361,9 @@ class CausalDiT:
             self._gemm(self.act_c, Sl, blk.v, self.v_buf, out_amax=self.v_amax)
             ops.scatter_2d(self.v_buf, Cl * 2, ar.ptrs(f"win_v{li}", cur_off), Cl * 2, Sl, Cl * 2)
             if self.sync_amax:
-                sp.allreduce_max_(self.kv_amax, self.group)
-            ar.barrier()
+                ar.allreduce_max_(self.kv_amax)         # also the barrier that publishes the stores above
+            else:
+                ar.barrier()
             q_h, k_for_cache, v_for_cache = self.q_h, self.kr_h, cur_v
         else:
             self.v_amax.zero_()
@@ -431,7 +440,7 @@ class CausalDiT:
         self.act_f.amax.zero_()
         self._gemm(self.act_c, Sl, blk.ffn0, self.hidden, act=1, out_amax=self.act_f.amax)
         if self.sync_amax:
-            sp.allreduce_max_(self.act_f.amax, self.group)
+            self._allreduce_max(self.act_f.amax)
         ops.quantize_nvfp4(self.hidden, MSE, self.act_f.amax, self.act_f.codes, self.act_f.sf, amax_given=True)
         self._gemm(self.act_f, Sl, blk.ffn2, x_out, residual=x2, gate=e[:, 5], frame_rows=ft, row_offset=roff)
         return x_out

@@ -199,6 +199,13 @@ def peer_barrier(signal_ptrs, rank, epoch):
         _check(_lib.lib().llnv_peer_barrier(_ptr_table(signal_ptrs), rank, len(signal_ptrs), epoch.data_ptr(), _stream(epoch)))
 
 
+def peer_allreduce_max(vals, slot_ptrs, signal_ptrs, rank, epoch):
+    """In-place MAX all-reduce of a small fp32 tensor over the GPUs of a peer arena (``llnv_peer_allreduce_max``)."""
+    with torch.cuda.device(vals.device):
+        _check(_lib.lib().llnv_peer_allreduce_max(vals.data_ptr(), vals.numel(), _ptr_table(slot_ptrs), _ptr_table(signal_ptrs), rank,
+                                                  len(signal_ptrs), epoch.data_ptr(), _stream(vals)))
+
+
 def attention_bf16(q, k, v, heads, scale=None, out=None, key_splits=None, out_amax=None):
     """softmax(q k^T * scale) v per head, non-causal.  q: bf16 [Lq, heads*128]; k, v: bf16 [Lk, heads*128]
     (row strides free, unit column stride).  Returns bf16 [Lq, heads*128].  ``key_splits`` > 1 splits

@@ -99,20 +99,22 @@ class PeerArena:
     """One symmetric-memory allocation per rank, mapped on every GPU of the group, from which the
     exchange buffers are carved.  ``tensor(name)`` is this rank's buffer, ``ptr(rank, name, offset)``
     the address of the same buffer on another rank, as seen from this GPU (NVLink peer mapping).
-    The first 256 bytes hold the barrier flags (``llnv_peer_barrier``).
+    The first 256 bytes hold the barrier flags (``llnv_peer_barrier``), the next 2 KiB the value
+    slots of ``llnv_peer_allreduce_max``.
 
     Built on ``torch.distributed._symmetric_memory`` (plain peer mappings; NVLink multicast binding
     is switched off, nothing here uses it).  ``PeerArena.create`` returns None when symmetric
     memory cannot be set up for the group, and callers fall back to the NCCL exchange."""
 
     SIGNAL_BYTES = 256
+    SLOT_BYTES = 2 * 8 * 32 * 4
 
     def __init__(self, group, device, layout: dict[str, int]):
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
         self.group = group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
-        self.offsets, off = {}, self.SIGNAL_BYTES
+        self.offsets, off = {}, self.SIGNAL_BYTES + self.SLOT_BYTES
         for name, nbytes in layout.items():
             self.offsets[name] = (off, nbytes)
             off += (nbytes + 255) // 256 * 256
@@ -148,3 +150,9 @@ class PeerArena:
     def barrier(self) -> None:
         from . import ops
         ops.peer_barrier(self.base, self.rank, self.epoch)
+
+    def allreduce_max_(self, vals: torch.Tensor) -> torch.Tensor:
+        """In-place MAX all-reduce of up to 32 fp32 values; also a barrier."""
+        from . import ops
+        ops.peer_allreduce_max(vals, [b + self.SIGNAL_BYTES for b in self.base], self.base, self.rank, self.epoch)
+        return vals
