@@ -360,10 +360,9 @@ class CausalDiT:
                                      smooth_ptrs=ar.ptrs(f"win_k{li}", cur_off), lds=Cl, amax_out=self.k_amax)
             self._gemm(self.act_c, Sl, blk.v, self.v_buf, out_amax=self.v_amax)
             ops.scatter_2d(self.v_buf, Cl * 2, ar.ptrs(f"win_v{li}", cur_off), Cl * 2, Sl, Cl * 2)
-            if self.sync_amax:
-                ar.allreduce_max_(self.kv_amax)         # also the barrier that publishes the stores above
-            else:
-                ar.barrier()
+            # the barrier that publishes the stores above also carries the K / V amax: its group maximum
+            # is the tensor scale of every rank's cache block (and the one a single GPU would use)
+            ar.allreduce_max_(self.kv_amax)
             q_h, k_for_cache, v_for_cache = self.q_h, self.kr_h, cur_v
         else:
             self.v_amax.zero_()
@@ -395,13 +394,14 @@ class CausalDiT:
         lk = (n_past + 1) * T
         # The attention epilogue also produces max |out|.  Across a sequence-parallel group that is
         # the amax of (all tokens, my heads), which bounds the (my tokens, all heads) tensor quantized
-        # after the exchange only once it is MAX-reduced, so it is used on one GPU or with sync_amax.
-        fused_amax = self.P == 1 or self.sync_amax
+        # after the exchange only once it is MAX-reduced: the peer-memory barrier after the exchange
+        # does that for free; with the NCCL exchange it is used only under sync_amax.
+        fused_amax = self.P == 1 or self.sync_amax or self.arena is not None
         ops.attention_bf16(q_h, win_k[:lk], win_v[:lk], self.Hl, out=self.attn_out, out_amax=self.act_c.amax if fused_amax else None)
         # cache write: rotated (un-smoothed) keys and values of the chunk, straight into the slot
         if self.P == 1:
             kv_given = True
-        elif self.sync_amax:
+        elif self.sync_amax or self.arena is not None:
             # k_amax / v_amax (RoPE kernel, V GEMM epilogue), MAX-reduced over the group, are the amax of the cached tensors
             ck.amax.copy_(self.k_amax)
             cv.amax.copy_(self.v_amax)
@@ -417,14 +417,14 @@ class CausalDiT:
             # the quantizer reads that [source heads][my tokens] layout directly
             blk_bytes = Sl * self.Cl * 2
             ops.scatter_2d(self.attn_out, blk_bytes, self.arena.ptrs("attn_sh", self.rank * blk_bytes), self.Cl * 2, Sl, self.Cl * 2)
-            self.arena.barrier()
+            self.arena.allreduce_max_(self.act_c.amax)          # barrier + group maximum of the attention output's amax
             attn = self.attn_sh
         elif self.P > 1:
             sp.exchange(self.attn_out, self.attn_sh, self.group)
             attn = self.attn_sh
         else:
             attn = self.attn_out
-        self._quantize(attn, self.act_c, have_local_amax=fused_amax)
+        self._quantize(attn, self.act_c, amax_given=self.arena is not None, have_local_amax=fused_amax)
         x1, x2 = self.x1, self.x2
         self._gemm(self.act_c, Sl, blk.o, x1, residual=x, gate=e[:, 2], frame_rows=ft, row_offset=roff)
         # -- cross attention
