@@ -83,6 +83,13 @@ int llnv_quantize_nvfp4(const void* x, int64_t M, int64_t K, int64_t ldx, int ru
 int llnv_quantize_nvfp4_ex(const void* x, int64_t M, int64_t K, int64_t ldx, int rule,
                            void* codes, void* sf, float* amax, int amax_given, int shards, llnv_stream_t stream);
 
+/* Two tensors of the same shape and row stride in one launch, each with its own outputs and tensor
+ * scale: the K and the V block of a KV-cache write (wan_5b/modules/causal_model.py:1420-1470 quantizes
+ * them one after the other). */
+int llnv_quantize_nvfp4_pair(const void* x0, const void* x1, int64_t M, int64_t K, int64_t ldx, int rule, void* codes0,
+                             void* sf0, float* amax0, void* codes1, void* sf1, float* amax1, int amax_given,
+                             llnv_stream_t stream);
+
 /* adaLN modulation fused into the quantizer: y = LayerNorm(x) (no affine, eps) -> bf16 ->
  * * bf16(1 + scale[f]) -> bf16 -> + shift[f] -> bf16, f = row / frame_rows, then y is quantized as by
  * llnv_quantize_nvfp4 (amax computed here).  Stands in for adaln_modulate_triton
@@ -163,6 +170,15 @@ int llnv_rmsnorm_rope_ex(const void* x, int64_t S, int64_t C, int64_t ldx, const
 int llnv_rmsnorm_rope_scatter(const void* x, int64_t S, int64_t C, int64_t ldx, const void* weight, float eps,
                               const float* cos, const float* sin, void* const* out_ptrs, int64_t ldo,
                               void* const* smooth_ptrs, int64_t lds, float* amax_out, int shards, llnv_stream_t stream);
+
+/* The q and the k prologue of one block in a single launch (they share tokens, channels and rotary
+ * tables; causal_model.py:363-365, 479-486, 568): q gets RMSNorm(wq) + RoPE, k gets RMSNorm(wk) +
+ * RoPE plus, optionally, the smoothed copy and its amax.  Outputs are pointer tables as in
+ * llnv_rmsnorm_rope_scatter (one entry per head shard; shards = 1 for plain [S, C] outputs). */
+int llnv_rmsnorm_rope_qk(const void* xq, int64_t ldxq, const void* wq, void* const* q_ptrs, int64_t ldq, const void* xk,
+                         int64_t ldxk, const void* wk, void* const* k_ptrs, int64_t ldk, void* const* k_smooth_ptrs,
+                         int64_t lds, float* k_amax, int64_t S, int64_t C, float eps, const float* cos, const float* sin,
+                         int shards, llnv_stream_t stream);
 
 /* Pushes a matrix to `shards` destinations with plain 16-byte stores (the destinations may be peer
  * memory): destination r receives `rows` rows of `row_bytes` bytes read from

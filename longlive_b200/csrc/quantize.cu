@@ -302,6 +302,12 @@ struct Prologue {
   // shard and shard_stride elements between shards (the receive layout of the head -> token
   // exchange of sequence parallelism); 0 = one plain [M][K] matrix
   int64_t shard_cols, shard_stride;
+  // second tensor of the same shape handled by the same launch (blockIdx.z == 1), e.g. the K and
+  // the V block of a KV-cache write; nullptr = none
+  const uint16_t* x2;
+  const float* amax2;
+  uint8_t* codes2;
+  uint8_t* sf2;
 };
 
 template <int MODE>
@@ -342,10 +348,16 @@ __device__ __forceinline__ void transform_block(uint32_t (&w)[8], const Prologue
 }
 
 template <int RULE, int MODE>
-__global__ void __launch_bounds__(256) quantize_nvfp4_kernel(const uint16_t* __restrict__ x, int64_t M, int64_t K,
-                                                             int64_t ldx, const float* __restrict__ amax_ptr,
-                                                             uint8_t* __restrict__ codes, uint8_t* __restrict__ sf,
+__global__ void __launch_bounds__(256) quantize_nvfp4_kernel(const uint16_t* x, int64_t M, int64_t K,
+                                                             int64_t ldx, const float* amax_ptr,
+                                                             uint8_t* codes, uint8_t* sf,
                                                              const Prologue pr, uint16_t* __restrict__ y_out, int64_t ldy) {
+  if (blockIdx.z == 1) {          // second tensor of a two-tensor launch
+    x = pr.x2;
+    amax_ptr = pr.amax2;
+    codes = pr.codes2;
+    sf = pr.sf2;
+  }
   constexpr float kE2 = RULE == LLNV_RULE_STATIC_4 ? 4.f : 6.f;
   constexpr float kE4 = (RULE == LLNV_RULE_STATIC_6 || RULE == LLNV_RULE_STATIC_4) ? 448.f : 256.f;
   QuantConsts qc;
@@ -692,6 +704,34 @@ extern "C" int llnv_quantize_nvfp4_ex(const void* x, int64_t M, int64_t K, int64
     pr.shard_stride = M * ldx;
   }
   return launch_quantize<kPlain>(rule, grid, stream, (const uint16_t*)x, M, K, ldx, amax, (uint8_t*)codes, (uint8_t*)sf, pr, nullptr, 0);
+}
+
+extern "C" int llnv_quantize_nvfp4_pair(const void* x0, const void* x1, int64_t M, int64_t K, int64_t ldx, int rule, void* codes0,
+                                        void* sf0, float* amax0, void* codes1, void* sf1, float* amax1, int amax_given,
+                                        llnv_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  LLNV_REQUIRE(x0 && x1 && codes0 && codes1 && sf0 && sf1 && amax0 && amax1, "llnv_quantize_nvfp4_pair: null pointer");
+  LLNV_REQUIRE(M >= 0 && K > 0 && K % 64 == 0, "llnv_quantize_nvfp4_pair: K must be a positive multiple of 64 (got %lld)", (long long)K);
+  LLNV_REQUIRE(ldx >= K && ldx % 8 == 0, "llnv_quantize_nvfp4_pair: ldx must be >= K and a multiple of 8 (got %lld)", (long long)ldx);
+  LLNV_REQUIRE(rule >= 0 && rule <= 4, "llnv_quantize_nvfp4_pair: unknown scale rule %d", rule);
+  LLNV_REQUIRE(((uintptr_t)x0 & 15) == 0 && ((uintptr_t)x1 & 15) == 0 && ((uintptr_t)codes0 & 7) == 0 && ((uintptr_t)codes1 & 7) == 0 &&
+                   ((uintptr_t)sf0 & 3) == 0 && ((uintptr_t)sf1 & 3) == 0,
+               "llnv_quantize_nvfp4_pair: x must be 16-byte, codes 8-byte, sf 4-byte aligned");
+  if (!amax_given) {
+    int rc = llnv_amax_bf16(x0, M, K, ldx, amax0, stream_);
+    if (rc == LLNV_OK) rc = llnv_amax_bf16(x1, M, K, ldx, amax1, stream_);
+    if (rc != LLNV_OK) return rc;
+  }
+  if (M == 0) return LLNV_OK;
+  const int64_t mp = (M + 127) / 128 * 128;
+  LLNV_REQUIRE(mp / 128 <= 65535, "llnv_quantize_nvfp4_pair: too many rows (%lld)", (long long)M);
+  dim3 grid((unsigned)((K + 127) / 128), (unsigned)(mp / 128), 2);
+  Prologue pr = {};
+  pr.x2 = (const uint16_t*)x1;
+  pr.amax2 = amax1;
+  pr.codes2 = (uint8_t*)codes1;
+  pr.sf2 = (uint8_t*)sf1;
+  return launch_quantize<kPlain>(rule, grid, stream, (const uint16_t*)x0, M, K, ldx, amax0, (uint8_t*)codes0, (uint8_t*)sf0, pr, nullptr, 0);
 }
 
 extern "C" int llnv_adaln_quantize_nvfp4(const void* x, int64_t M, int64_t C, int64_t ldx, const void* scale, const void* shift,

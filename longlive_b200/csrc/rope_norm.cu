@@ -25,15 +25,34 @@ struct ShardOut {
   uint16_t* smooth[kMaxShards];
 };
 
+// One tensor to process; a launch takes up to two (blockIdx.y), e.g. the q and the k projection of
+// a block, which share the token count, the channel count and the rotary tables.
+struct RopeJob {
+  const uint16_t* x;
+  const uint16_t* weight;
+  ShardOut dst;
+  int64_t ldx, ldo, lds;
+  float* amax_out;
+  int want_smooth;
+};
+struct RopeJobs {
+  RopeJob job[2];
+};
+
 // WPR warps share one token row (each takes C / WPR channels, a whole number of heads): a row is
 // short (6 KB), so with one warp per row a chunk of 2640 tokens would put only 2640 warps on the
 // device and the kernel would be bound by the latency of each warp's single pass.
 template <int WPR>
-__global__ void __launch_bounds__(256) rmsnorm_rope_kernel(const uint16_t* __restrict__ x, int64_t S, int64_t C, int64_t ldx,
-                                                           const uint16_t* __restrict__ weight, float eps,
+__global__ void __launch_bounds__(256) rmsnorm_rope_kernel(const __grid_constant__ RopeJobs jobs, int64_t S, int64_t C, float eps,
                                                            const float* __restrict__ cosv, const float* __restrict__ sinv,
-                                                           const ShardOut dst, int64_t ldo, int64_t lds, bool want_smooth,
-                                                           float* __restrict__ amax_out, int shard_vecs) {
+                                                           int shard_vecs) {
+  const RopeJob& jb = jobs.job[blockIdx.y];
+  const uint16_t* __restrict__ x = jb.x;
+  const uint16_t* __restrict__ weight = jb.weight;
+  const ShardOut& dst = jb.dst;
+  const int64_t ldx = jb.ldx, ldo = jb.ldo, lds = jb.lds;
+  const bool want_smooth = jb.want_smooth != 0;
+  float* __restrict__ amax_out = jb.amax_out;
   constexpr int kVec = kMaxVec / WPR;        // 16-byte vectors per lane
   constexpr int kRows = 8 / WPR;             // rows per CTA
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -179,36 +198,48 @@ extern "C" int llnv_rmsnorm_rope(const void* x, int64_t S, int64_t C, int64_t ld
 
 namespace {
 
-int rope_launch(const void* x, int64_t S, int64_t C, int64_t ldx, const void* weight, float eps, const float* cos, const float* sin,
-                const ShardOut& dst, int64_t ldo, int64_t lds, bool want_smooth, float* amax_out, int shards, cudaStream_t stream) {
-  LLNV_REQUIRE(x != nullptr, "llnv_rmsnorm_rope: null pointer");
+int check_job(const RopeJob& jb, int64_t C, int shards) {
+  const int64_t Cs = C / shards;
+  LLNV_REQUIRE(jb.x != nullptr, "llnv_rmsnorm_rope: null pointer");
+  LLNV_REQUIRE(jb.ldx >= C && jb.ldx % 8 == 0 && jb.ldo >= Cs && jb.ldo % 8 == 0, "llnv_rmsnorm_rope: row strides must be >= the row width and multiples of 8");
+  LLNV_REQUIRE(((uintptr_t)jb.x & 15) == 0 && ((uintptr_t)jb.weight & 15) == 0, "llnv_rmsnorm_rope: pointers must be 16-byte aligned");
+  if (jb.want_smooth) LLNV_REQUIRE(jb.lds >= Cs && jb.lds % 8 == 0, "llnv_rmsnorm_rope: out_smooth row stride must be >= the row width and a multiple of 8");
+  for (int r = 0; r < shards; ++r) {
+    LLNV_REQUIRE(jb.dst.out[r] != nullptr && ((uintptr_t)jb.dst.out[r] & 15) == 0, "llnv_rmsnorm_rope: output %d must be a 16-byte aligned pointer", r);
+    if (jb.want_smooth) LLNV_REQUIRE(jb.dst.smooth[r] != nullptr && ((uintptr_t)jb.dst.smooth[r] & 15) == 0, "llnv_rmsnorm_rope: out_smooth %d must be a 16-byte aligned pointer", r);
+  }
+  return LLNV_OK;
+}
+
+int rope_launch_jobs(const RopeJobs& jobs, int njobs, int64_t S, int64_t C, float eps, const float* cos, const float* sin, int shards,
+                     cudaStream_t stream) {
   LLNV_REQUIRE((cos == nullptr) == (sin == nullptr), "llnv_rmsnorm_rope: cos and sin must be given together");
   LLNV_REQUIRE(S >= 0 && C > 0 && C % 128 == 0 && C <= 4096, "llnv_rmsnorm_rope: C must be a multiple of 128 (head_dim 128) and at most 4096 (got %lld)", (long long)C);
   LLNV_REQUIRE(shards >= 1 && shards <= kMaxShards && C % shards == 0 && (C / shards) % 128 == 0,
                "llnv_rmsnorm_rope: shards must divide the channels into whole heads, at most 8 (C=%lld shards=%d)", (long long)C, shards);
-  const int64_t Cs = C / shards;
-  LLNV_REQUIRE(ldx >= C && ldx % 8 == 0 && ldo >= Cs && ldo % 8 == 0, "llnv_rmsnorm_rope: row strides must be >= the row width and multiples of 8");
-  LLNV_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)weight & 15) == 0 && ((uintptr_t)cos & 15) == 0 && ((uintptr_t)sin & 15) == 0,
-               "llnv_rmsnorm_rope: pointers must be 16-byte aligned");
-  if (want_smooth) LLNV_REQUIRE(lds >= Cs && lds % 8 == 0, "llnv_rmsnorm_rope: out_smooth row stride must be >= the row width and a multiple of 8");
-  for (int r = 0; r < shards; ++r) {
-    LLNV_REQUIRE(dst.out[r] != nullptr && ((uintptr_t)dst.out[r] & 15) == 0, "llnv_rmsnorm_rope: output %d must be a 16-byte aligned pointer", r);
-    if (want_smooth) LLNV_REQUIRE(dst.smooth[r] != nullptr && ((uintptr_t)dst.smooth[r] & 15) == 0, "llnv_rmsnorm_rope: out_smooth %d must be a 16-byte aligned pointer", r);
+  LLNV_REQUIRE(((uintptr_t)cos & 15) == 0 && ((uintptr_t)sin & 15) == 0, "llnv_rmsnorm_rope: pointers must be 16-byte aligned");
+  for (int j = 0; j < njobs; ++j) {
+    int rc = check_job(jobs.job[j], C, shards);
+    if (rc != LLNV_OK) return rc;
+    if (jobs.job[j].amax_out) LLNV_CUDA(cudaMemsetAsync(jobs.job[j].amax_out, 0, sizeof(float), stream));
   }
-  if (amax_out) LLNV_CUDA(cudaMemsetAsync(amax_out, 0, sizeof(float), stream));
   if (S == 0) return LLNV_OK;
-  const int sv = shards > 1 ? (int)(Cs / 8) : 0;
+  const int sv = shards > 1 ? (int)(C / shards / 8) : 0;
   // warps per row: as many as leave every warp a whole number of heads and every lane some work
   if (C % 512 == 0 && C >= 2048)
-    rmsnorm_rope_kernel<4><<<(unsigned)((S + 1) / 2), 256, 0, stream>>>((const uint16_t*)x, S, C, ldx, (const uint16_t*)weight, eps, cos, sin,
-                                                                       dst, ldo, lds, want_smooth, amax_out, sv);
+    rmsnorm_rope_kernel<4><<<dim3((unsigned)((S + 1) / 2), (unsigned)njobs), 256, 0, stream>>>(jobs, S, C, eps, cos, sin, sv);
   else if (C % 256 == 0 && C >= 1024)
-    rmsnorm_rope_kernel<2><<<(unsigned)((S + 3) / 4), 256, 0, stream>>>((const uint16_t*)x, S, C, ldx, (const uint16_t*)weight, eps, cos, sin,
-                                                                       dst, ldo, lds, want_smooth, amax_out, sv);
+    rmsnorm_rope_kernel<2><<<dim3((unsigned)((S + 3) / 4), (unsigned)njobs), 256, 0, stream>>>(jobs, S, C, eps, cos, sin, sv);
   else
-    rmsnorm_rope_kernel<1><<<(unsigned)((S + 7) / 8), 256, 0, stream>>>((const uint16_t*)x, S, C, ldx, (const uint16_t*)weight, eps, cos, sin,
-                                                                       dst, ldo, lds, want_smooth, amax_out, sv);
+    rmsnorm_rope_kernel<1><<<dim3((unsigned)((S + 7) / 8), (unsigned)njobs), 256, 0, stream>>>(jobs, S, C, eps, cos, sin, sv);
   return launch_status("rmsnorm_rope_kernel");
+}
+
+int rope_launch(const void* x, int64_t S, int64_t C, int64_t ldx, const void* weight, float eps, const float* cos, const float* sin,
+                const ShardOut& dst, int64_t ldo, int64_t lds, bool want_smooth, float* amax_out, int shards, cudaStream_t stream) {
+  RopeJobs jobs = {};
+  jobs.job[0] = RopeJob{(const uint16_t*)x, (const uint16_t*)weight, dst, ldx, ldo, lds, amax_out, want_smooth ? 1 : 0};
+  return rope_launch_jobs(jobs, 1, S, C, eps, cos, sin, shards, stream);
 }
 
 }  // namespace
@@ -237,4 +268,22 @@ extern "C" int llnv_rmsnorm_rope_scatter(const void* x, int64_t S, int64_t C, in
     dst.smooth[r] = smooth_ptrs ? (uint16_t*)smooth_ptrs[r] : nullptr;
   }
   return rope_launch(x, S, C, ldx, weight, eps, cos, sin, dst, ldo, lds, smooth_ptrs != nullptr, amax_out, shards, (cudaStream_t)stream);
+}
+
+extern "C" int llnv_rmsnorm_rope_qk(const void* xq, int64_t ldxq, const void* wq, void* const* q_ptrs, int64_t ldq, const void* xk,
+                                    int64_t ldxk, const void* wk, void* const* k_ptrs, int64_t ldk, void* const* k_smooth_ptrs,
+                                    int64_t lds, float* k_amax, int64_t S, int64_t C, float eps, const float* cos, const float* sin,
+                                    int shards, llnv_stream_t stream) {
+  LLNV_REQUIRE(q_ptrs != nullptr && k_ptrs != nullptr, "llnv_rmsnorm_rope_qk: null pointer table");
+  LLNV_REQUIRE(shards >= 1 && shards <= kMaxShards, "llnv_rmsnorm_rope: at most 8 shards");
+  RopeJobs jobs = {};
+  ShardOut dq = {}, dk = {};
+  for (int r = 0; r < shards; ++r) {
+    dq.out[r] = (uint16_t*)q_ptrs[r];
+    dk.out[r] = (uint16_t*)k_ptrs[r];
+    dk.smooth[r] = k_smooth_ptrs ? (uint16_t*)k_smooth_ptrs[r] : nullptr;
+  }
+  jobs.job[0] = RopeJob{(const uint16_t*)xq, (const uint16_t*)wq, dq, ldxq, ldq, 0, nullptr, 0};
+  jobs.job[1] = RopeJob{(const uint16_t*)xk, (const uint16_t*)wk, dk, ldxk, ldk, lds, k_amax, k_smooth_ptrs ? 1 : 0};
+  return rope_launch_jobs(jobs, 2, S, C, eps, cos, sin, shards, (cudaStream_t)stream);
 }

@@ -343,9 +343,8 @@ class CausalDiT:
             # the tensor scales of the cache block are produced in place by the V GEMM epilogue and the RoPE kernel
             cv.amax.zero_()
             self._gemm(self.act_c, Sl, blk.v, cur_v, out_amax=cv.amax)
-            ops.rmsnorm_rope(x=self.q_buf, weight=blk.norm_q, cos=cos, sin=sin, eps=cfg.eps, out=self.q_rot)
-            ops.rmsnorm_rope(x=self.k_buf, weight=blk.norm_k, cos=cos, sin=sin, eps=cfg.eps, out=self.k_rot, out_smooth=cur_k,
-                             amax_out=ck.amax)
+            ops.rmsnorm_rope_qk(self.q_buf, blk.norm_q, [self.q_rot.data_ptr()], cfg.dim, self.k_buf, blk.norm_k, [self.k_rot.data_ptr()],
+                                cfg.dim, [cur_k.data_ptr()], cfg.dim, ck.amax, cos, sin, cfg.eps)
             q_h, k_for_cache, v_for_cache = self.q_rot, self.k_rot, cur_v
         elif self.arena is not None:
             self.v_amax.zero_()
@@ -355,9 +354,8 @@ class CausalDiT:
             ar, Cl = self.arena, self.Cl
             row_off = self.rank * Sl * Cl * 2                   # my token block inside an [S, Cl] buffer
             cur_off = n_past * T * Cl * 2 + row_off            # ... inside the current-chunk part of a window
-            ops.rmsnorm_rope_scatter(self.q_buf, blk.norm_q, cos, sin, cfg.eps, ar.ptrs("q_h", row_off), Cl)
-            ops.rmsnorm_rope_scatter(self.k_buf, blk.norm_k, cos, sin, cfg.eps, ar.ptrs("kr_h", row_off), Cl,
-                                     smooth_ptrs=ar.ptrs(f"win_k{li}", cur_off), lds=Cl, amax_out=self.k_amax)
+            ops.rmsnorm_rope_qk(self.q_buf, blk.norm_q, ar.ptrs("q_h", row_off), Cl, self.k_buf, blk.norm_k, ar.ptrs("kr_h", row_off), Cl,
+                                ar.ptrs(f"win_k{li}", cur_off), Cl, self.k_amax, cos, sin, cfg.eps)
             self._gemm(self.act_c, Sl, blk.v, self.v_buf, out_amax=self.v_amax)
             ops.scatter_2d(self.v_buf, Cl * 2, ar.ptrs(f"win_v{li}", cur_off), Cl * 2, Sl, Cl * 2)
             # the barrier that publishes the stores above also carries the K / V amax: its group maximum
@@ -410,8 +408,7 @@ class CausalDiT:
             # per-rank scales: the producers saw (my tokens, all heads), the cache block holds (all tokens,
             # my heads); its own amax is taken so that no value can exceed the scale's range
             kv_given = False
-        ops.quantize_nvfp4(k_for_cache.reshape(S * self.Hl, 128), MSE, ck.amax, ck.values, ck.scale_factors, amax_given=kv_given)
-        ops.quantize_nvfp4(v_for_cache.reshape(S * self.Hl, 128), MSE, cv.amax, cv.values, cv.scale_factors, amax_given=kv_given)
+        ops.quantize_nvfp4_pair(k_for_cache.reshape(S * self.Hl, 128), v_for_cache.reshape(S * self.Hl, 128), MSE, ck, cv, amax_given=kv_given)
         if self.arena is not None:
             # heads -> tokens over peer memory: rank r receives my heads of its tokens in attn_sh[my rank];
             # the quantizer reads that [source heads][my tokens] layout directly

@@ -165,6 +165,19 @@ def rmsnorm_rope(x, weight=None, cos=None, sin=None, eps=1e-6, *, out=None, out_
     return out, out_smooth, amax_out
 
 
+def quantize_nvfp4_pair(x0, x1, rule_id, q0, q1, amax_given=True):
+    """Quantize two bf16 [M, K] tensors of the same shape in one launch into the preallocated
+    QuantizedTensor-like targets q0 / q1 (``values``, ``scale_factors``, ``amax``)."""
+    _require_cuda(x0, "x0")
+    if x0.shape != x1.shape or x0.stride(0) != x1.stride(0) or x0.stride(1) != 1 or x1.stride(1) != 1 or x0.dtype != torch.bfloat16:
+        raise RuntimeError("quantize_nvfp4_pair expects two bfloat16 [M, K] tensors of the same shape and row stride")
+    m, k = x0.shape
+    with torch.cuda.device(x0.device):
+        _check(_lib.lib().llnv_quantize_nvfp4_pair(x0.data_ptr(), x1.data_ptr(), m, k, x0.stride(0), rule_id, q0.values.data_ptr(),
+                                                   q0.scale_factors.data_ptr(), q0.amax.data_ptr(), q1.values.data_ptr(),
+                                                   q1.scale_factors.data_ptr(), q1.amax.data_ptr(), 1 if amax_given else 0, _stream(x0)))
+
+
 def _ptr_table(ptrs):
     arr = (C.c_void_p * len(ptrs))(*[int(p) for p in ptrs])
     return arr
@@ -182,6 +195,18 @@ def rmsnorm_rope_scatter(x, weight, cos, sin, eps, out_ptrs, ldo, smooth_ptrs=No
             cos.data_ptr() if cos is not None else None, sin.data_ptr() if sin is not None else None,
             _ptr_table(out_ptrs), ldo, _ptr_table(smooth_ptrs) if smooth_ptrs is not None else None, lds,
             amax_out.data_ptr() if amax_out is not None else None, shards, _stream(x)))
+
+
+def rmsnorm_rope_qk(xq, wq, q_ptrs, ldq, xk, wk, k_ptrs, ldk, k_smooth_ptrs, lds, k_amax, cos, sin, eps):
+    """The q and the k prologue of a block in one launch (``llnv_rmsnorm_rope_qk``); outputs are raw
+    device addresses, one per head shard."""
+    _require_cuda(xq, "xq")
+    s, c = xq.shape
+    with torch.cuda.device(xq.device):
+        _check(_lib.lib().llnv_rmsnorm_rope_qk(
+            xq.data_ptr(), xq.stride(0), wq.data_ptr(), _ptr_table(q_ptrs), ldq, xk.data_ptr(), xk.stride(0), wk.data_ptr(),
+            _ptr_table(k_ptrs), ldk, _ptr_table(k_smooth_ptrs) if k_smooth_ptrs is not None else None, lds,
+            k_amax.data_ptr() if k_amax is not None else None, s, c, float(eps), cos.data_ptr(), sin.data_ptr(), len(q_ptrs), _stream(xq)))
 
 
 def scatter_2d(src, src_shard_bytes, dst_ptrs, dst_pitch, rows, row_bytes):

@@ -190,3 +190,19 @@ def test_quantize_column_sharded_input(shards):
     got = ops.quantize_nvfp4(xs, 3)
     for a, b in zip(ref, got):
         assert torch.equal(a.view(torch.uint8) if a.dtype != torch.float32 else a, b.view(torch.uint8) if b.dtype != torch.float32 else b)
+
+
+def test_quantize_two_tensors_in_one_launch():
+    g = torch.Generator().manual_seed(37)
+    a = torch.randn(300, 128, generator=g).bfloat16().cuda()
+    b = (torch.randn(300, 128, generator=g) * 5).bfloat16().cuda()
+    ra, rb = L.quantize_to_fp4(a), L.quantize_to_fp4(b)
+    qa, qb = L.quantize_to_fp4(torch.zeros_like(a)), L.quantize_to_fp4(torch.zeros_like(b))
+    for given in (False, True):
+        if given:
+            qa.amax.copy_(ra.amax); qb.amax.copy_(rb.amax)
+            qa.values.zero_(); qb.values.zero_()
+        ops.quantize_nvfp4_pair(a, b, 3, qa, qb, amax_given=given)
+        for r, q in ((ra, qa), (rb, qb)):
+            assert torch.equal(r.values, q.values) and torch.equal(r.amax, q.amax)
+            assert torch.equal(r.scale_factors.view(torch.uint8), q.scale_factors.view(torch.uint8))

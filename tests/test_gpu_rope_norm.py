@@ -84,3 +84,20 @@ def test_prologue_head_sharded_outputs(shards):
     assert torch.equal(out2.permute(1, 0, 2).reshape(s_, c), out)
     assert torch.equal(sm2.permute(1, 0, 2).reshape(s_, c), sm)
     assert torch.equal(am, am2)
+
+
+def test_qk_prologue_in_one_launch():
+    """llnv_rmsnorm_rope_qk gives exactly what the two separate calls give."""
+    s_, heads = 90, 4
+    c = heads * 128
+    g = torch.Generator().manual_seed(43)
+    xq, xk = torch.randn(s_, c, generator=g).bfloat16().cuda(), (torch.randn(s_, c, generator=g) * 2).bfloat16().cuda()
+    wq, wk = (1 + 0.1 * torch.randn(c, generator=g)).bfloat16().cuda(), (1 + 0.1 * torch.randn(c, generator=g)).bfloat16().cuda()
+    ang = torch.rand(s_, 64, generator=g) * 6.28
+    cos, sin = ang.cos().float().cuda().contiguous(), ang.sin().float().cuda().contiguous()
+    q_ref, _, _ = ops.rmsnorm_rope(xq, wq, cos, sin)
+    k_ref, ks_ref, am_ref = ops.rmsnorm_rope(xk, wk, cos, sin, want_smooth=True, want_amax=True)
+    q, k, ks = torch.empty_like(q_ref), torch.empty_like(k_ref), torch.empty_like(ks_ref)
+    am = torch.zeros(1, dtype=torch.float32, device="cuda")
+    ops.rmsnorm_rope_qk(xq, wq, [q.data_ptr()], c, xk, wk, [k.data_ptr()], c, [ks.data_ptr()], c, am, cos, sin, 1e-6)
+    assert torch.equal(q, q_ref) and torch.equal(k, k_ref) and torch.equal(ks, ks_ref) and torch.equal(am, am_ref)
