@@ -116,24 +116,33 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
+    // Both pipeline threads walk the K blocks in groups of kStages with the stage index a
+    // compile-time constant (and one phase bit per stage), so that every shared-memory address,
+    // barrier address and descriptor below is loop-invariant: the single issuing thread of each
+    // role is on the critical path of every K block.
     if (elect_one()) {
-      int stage = 0;
-      uint32_t phase = 0;
+      uint32_t phases = 0;                   // bit s: parity the stage's empty barrier completed last
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
         const int mt = tile % num_m, nt = tile / num_m;
-        for (int kb = 0; kb < num_kb; ++kb) {
-          mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 100u);
-          uint8_t* st = smem + stage * C::kStageBytes;
-          mbar_arrive_expect_tx(&full_bar[stage], C::kStageBytes);
-          tma_load_2d(st, &tmA, kb * BK_BYTES, mt * BM, &full_bar[stage]);
-          tma_load_2d(st + C::kABytes, &tmB, kb * BK_BYTES, nt * BN, &full_bar[stage]);
-          bulk_load(st + C::kABytes + C::kBBytes, p.sfa + ((int64_t)mt * k_atoms + kb * 4) * 512, 2048, &full_bar[stage]);
-          const int64_t atom0 = ((int64_t)nt * BN) / 128;      // first scale atom row of the B tile
+        const uint8_t* sfa_src = p.sfa + (int64_t)mt * k_atoms * 512;
+        const uint8_t* sfb_src = p.sfb + (((int64_t)nt * BN) / 128) * k_atoms * 512;      // first scale atom row of the B tile
+        for (int kb0 = 0; kb0 < num_kb; kb0 += C::kStages) {
 #pragma unroll
-          for (int h = 0; h < C::kSfbAtoms; ++h)
-            bulk_load(st + C::kABytes + C::kBBytes + C::kSfaBytes + h * 2048,
-                      p.sfb + ((atom0 + h) * k_atoms + kb * 4) * 512, 2048, &full_bar[stage]);
-          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+          for (int s = 0; s < C::kStages; ++s) {
+            const int kb = kb0 + s;
+            if (kb >= num_kb) break;
+            mbar_wait(&empty_bar[s], ((phases >> s) & 1u) ^ 1u, abort_flag, p.status, 100u);
+            phases ^= 1u << s;
+            uint8_t* st = smem + s * C::kStageBytes;
+            mbar_arrive_expect_tx(&full_bar[s], C::kStageBytes);
+            tma_load_2d(st, &tmA, kb * BK_BYTES, mt * BM, &full_bar[s]);
+            tma_load_2d(st + C::kABytes, &tmB, kb * BK_BYTES, nt * BN, &full_bar[s]);
+            bulk_load(st + C::kABytes + C::kBBytes, sfa_src + (int64_t)kb * 2048, 2048, &full_bar[s]);
+#pragma unroll
+            for (int h = 0; h < C::kSfbAtoms; ++h)
+              bulk_load(st + C::kABytes + C::kBBytes + C::kSfaBytes + h * 2048, sfb_src + ((int64_t)h * k_atoms + kb * 4) * 512, 2048,
+                        &full_bar[s]);
+          }
         }
       }
     }
@@ -141,40 +150,48 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     // ------------------------------------------------------------------ MMA issuer
     if (elect_one()) {
       constexpr uint32_t idesc = make_idesc_nvf4(BM, BN);
-      int stage = 0, acc = 0;
-      uint32_t phase = 0, acc_phase = 0;
+      // upper words of the shared-memory descriptors (stride between 8-row groups, version, layout) are constants;
+      // the lower word is (address >> 4) | (leading-dimension field << 16)
+      constexpr uint32_t kOpHi = (uint32_t)(make_smem_desc(0, 16, 1024, 2) >> 32);
+      constexpr uint32_t kSfHi = (uint32_t)(make_smem_desc(0, 0, 128, 0) >> 32);
+      const uint32_t smem_base = smem_u32(smem);
+      int acc = 0;
+      uint32_t phases = 0, acc_phase = 0;
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
         mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_flag, p.status, 200u);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         const int nt = tile / num_m;
         const uint32_t sfb_col0 = (uint32_t)((((int64_t)nt * BN) % 128) / 32);     // tile start inside its first scale atom
-        for (int kb = 0; kb < num_kb; ++kb) {
-          mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 201u);
-          tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + stage * C::kStageBytes);
-          const uint32_t b_addr = a_addr + C::kABytes;
-          const uint32_t sfa_addr = b_addr + C::kBBytes;
-          const uint32_t sfb_addr = sfa_addr + C::kSfaBytes;
-          if (!(p.debug & 1) || kb == 0) {
+        for (int kb0 = 0; kb0 < num_kb; kb0 += C::kStages) {
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              tmem_cp_sf(tmem_base + C::kSfaCol + 4 * g, make_sf_desc(sfa_addr + g * 512));
+          for (int s = 0; s < C::kStages; ++s) {
+            const int kb = kb0 + s;
+            if (kb >= num_kb) break;
+            mbar_wait(&full_bar[s], (phases >> s) & 1u, abort_flag, p.status, 201u);
+            phases ^= 1u << s;
+            tc_fence_after();
+            const uint32_t a_lo = ((smem_base + s * C::kStageBytes) >> 4) | (1u << 16);
+            const uint32_t b_lo = a_lo + (C::kABytes >> 4);
+            const uint32_t sfa_lo = (smem_base + s * C::kStageBytes + C::kABytes + C::kBBytes) >> 4;
+            const uint32_t sfb_lo = sfa_lo + (C::kSfaBytes >> 4);
+            if (!(p.debug & 1) || kb == 0) {
 #pragma unroll
-              for (int h = 0; h < C::kSfbAtoms; ++h)
-                tmem_cp_sf(tmem_base + C::kSfbCol + C::kSfbColsPerK * g + 4 * h, make_sf_desc(sfb_addr + h * 2048 + g * 512));
+              for (int g = 0; g < 4; ++g) {
+                tmem_cp_sf(tmem_base + C::kSfaCol + 4 * g, ((uint64_t)kSfHi << 32) | (sfa_lo + 32 * g));
+#pragma unroll
+                for (int h = 0; h < C::kSfbAtoms; ++h)
+                  tmem_cp_sf(tmem_base + C::kSfbCol + C::kSfbColsPerK * g + 4 * h, ((uint64_t)kSfHi << 32) | (sfb_lo + 128 * h + 32 * g));
+              }
             }
-          }
-          const uint64_t a_desc = make_kmajor_sw128_desc(a_addr);
-          const uint64_t b_desc = make_kmajor_sw128_desc(b_addr);
 #pragma unroll
-          for (int k = 0; k < ((p.debug & 2) ? 1 : 4); ++k) {
-            // 64 E2M1 elements = 32 bytes further along K inside the 128-byte swizzled row
-            mma_nvf4(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, tmem_base + C::kSfaCol + 4 * k,
-                     tmem_base + C::kSfbCol + C::kSfbColsPerK * k + sfb_col0, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < ((p.debug & 2) ? 1 : 4); ++k) {
+              // 64 E2M1 elements = 32 bytes further along K inside the 128-byte swizzled row
+              mma_nvf4(d_tmem, ((uint64_t)kOpHi << 32) | (a_lo + 2 * k), ((uint64_t)kOpHi << 32) | (b_lo + 2 * k), idesc,
+                       tmem_base + C::kSfaCol + 4 * k, tmem_base + C::kSfbCol + C::kSfbColsPerK * k + sfb_col0, (kb | k) != 0 ? 1u : 0u);
+            }
+            tc_commit(&empty_bar[s]);
           }
-          tc_commit(&empty_bar[stage]);
-          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
         }
         tc_commit(&tfull_bar[acc]);
         if (++acc == C::kAcc) { acc = 0; acc_phase ^= 1u; }

@@ -201,7 +201,7 @@ __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.
 //   bits  0-13 start address >> 4      bits 16-29 leading byte offset >> 4
 //   bits 32-45 stride byte offset >> 4 bits 46-47 version (1)
 //   bits 49-51 base offset             bits 61-63 layout (0 none, 2 = 128B swizzle, 4 = 64B, 6 = 32B)
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
+__host__ __device__ constexpr uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
   uint64_t d = 0;
   d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
   d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
