@@ -286,6 +286,18 @@ int llnv_gemm_nvfp4(const void* a_codes, const void* a_sf, const float* a_amax, 
                     int64_t M, int64_t N, int64_t K, const llnv_epilogue_t* epilogue,
                     void* d, int64_t ldd, llnv_stream_t stream);
 
+/* Two or three Linears that share their input in one launch: B is the concatenation along N of
+ * `groups` weight matrices of N_each rows (codes and swizzled scales concatenated, b_amax one fp32
+ * per matrix), matrix g is written to d[g] (row stride ldd[g]) and, if out_amax[g] is not NULL, its
+ * output amax to out_amax[g] (overwritten).  The q, k and v projections of a block
+ * (wan_5b/modules/causal_model.py:363-366) are such a group: one grid of 3x the tiles fills the SMs
+ * better than three grids, and two launches are saved.  The epilogue may carry bias (N_each * groups
+ * values, concatenated) and act; residual / gate / alpha / out_amax belong to llnv_gemm_nvfp4. */
+int llnv_gemm_nvfp4_grouped(const void* a_codes, const void* a_sf, const float* a_amax, int a_rule, const void* b_codes,
+                            const void* b_sf, const float* b_amax, int b_rule, int64_t M, int64_t N_each, int64_t K, int groups,
+                            const llnv_epilogue_t* epilogue, void* const* d, const int64_t* ldd, float* const* out_amax,
+                            llnv_stream_t stream);
+
 /* Test / benchmark hooks (no counterpart in the reference). */
 int llnv_gemm_nvfp4_force_tile_n(int bn);       /* 0 = automatic, 128 or 256 */
 int llnv_gemm_nvfp4_debug(int flags);           /* timing experiments; results become wrong when non-zero */

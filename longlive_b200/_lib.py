@@ -10,7 +10,7 @@ LIB_PATH = os.path.join(_PKG, "libllnvfp4.so")
 # names declared in include/llnvfp4.h
 EXPORTS = [
     "llnv_version", "llnv_last_error", "llnv_check_status", "llnv_amax_bf16", "llnv_quantize_nvfp4",
-    "llnv_kv_dequant", "llnv_dequantize_nvfp4", "llnv_gemm_nvfp4", "llnv_adaln_quantize_nvfp4",
+    "llnv_kv_dequant", "llnv_dequantize_nvfp4", "llnv_gemm_nvfp4", "llnv_gemm_nvfp4_grouped", "llnv_adaln_quantize_nvfp4",
     "llnv_layernorm_quantize_nvfp4", "llnv_gemm_nvfp4_force_tile_n", "llnv_gemm_nvfp4_debug", "llnv_selftest_div_const",
     "llnv_adaln_quantize_nvfp4_static", "llnv_static_max_rows", "llnv_rmsnorm_rope", "llnv_attention_bf16", "llnv_attention_bf16_ex", "llnv_quantize_nvfp4_ex", "llnv_quantize_nvfp4_pair", "llnv_rmsnorm_rope_ex", "llnv_rmsnorm_rope_scatter", "llnv_rmsnorm_rope_qk", "llnv_scatter_2d", "llnv_peer_barrier", "llnv_peer_allreduce_max", "llnv_attention_key_splits", "llnv_attention_workspace_bytes", "llnv_adaln_quantize_nvfp4_ex", "llnv_layernorm_quantize_nvfp4_ex",
 ]
@@ -67,6 +67,7 @@ def lib() -> C.CDLL:
         l.llnv_quantize_nvfp4_ex.argtypes = [p, i64, i64, i64, i32, p, p, p, i32, i32, p]
         l.llnv_rmsnorm_rope_scatter.argtypes = [p, i64, i64, i64, p, f32, p, p, p, i64, p, i64, p, i32, p]
         l.llnv_quantize_nvfp4_pair.argtypes = [p, p, i64, i64, i64, i32, p, p, p, p, p, p, i32, p]
+        l.llnv_gemm_nvfp4_grouped.argtypes = [p, p, p, i32, p, p, p, i32, i64, i64, i64, i32, p, p, p, p, p]
         l.llnv_rmsnorm_rope_qk.argtypes = [p, i64, p, p, i64, p, i64, p, p, i64, p, i64, p, i64, i64, f32, p, p, i32, p]
         l.llnv_scatter_2d.argtypes = [p, i64, i64, p, i64, i64, i64, i32, p]
         l.llnv_peer_barrier.argtypes = [p, i32, i32, p, p]

@@ -168,6 +168,8 @@ def load_state_dict_into(model, state_dict: Mapping, prefix: str = "model.", wei
             t = take(key)
             if t is not None:
                 _copy(getattr(model, attr), t, key)
+    for blk in model.blocks:
+        blk.fuse_qkv()
     model.modulation_all = torch.stack([blk.modulation for blk in model.blocks], 0)
     model.text_kv = None                       # cached text K/V belong to the old weights
     model._graphs.clear()                      # captured graphs hold the old weight addresses

@@ -21,6 +21,15 @@ struct GemmParams {
   int64_t ldd;
   unsigned int* status;
   int debug;               // timing experiments only: bit0 skip scale copies, bit1 one MMA per stage, bit2 skip stores
+  // Grouped launch (1-CTA kernel): B is the concatenation along N of up to three weight matrices
+  // of group_cols rows each, every one with its own tensor amax (b_amax[g]), output matrix and
+  // optional output amax; 0 = one ordinary GEMM.
+  int64_t group_cols;
+  float* group_amax[3];
+};
+
+struct GroupMaps {
+  CUtensorMap m[2];        // output maps of groups 1 and 2 (group 0 uses the kernel's main output map)
 };
 
 // two fp32 -> packed bf16x2 (one conversion instruction, round to nearest even)

@@ -64,7 +64,8 @@ struct Cfg {
 template <int BN, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                  const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmR, const GemmParams p) {
+                  const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmR,
+                  const __grid_constant__ GroupMaps gmaps, const GemmParams p) {
   using C = Cfg<BN>;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::kBarOff);
@@ -200,16 +201,20 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;                           // TMEM lane quarter this warp may access
-    float alpha;
-    if (p.epi.alpha) alpha = __ldg(p.epi.alpha);
-    else alpha = __fdiv_rn(__fmul_rn(__ldg(p.a_amax), __ldg(p.b_amax)), p.alpha_denom);
+    float alpha0, alpha1 = 0.f, alpha2 = 0.f;           // per weight group (one group unless p.group_cols)
+    if (p.epi.alpha) alpha0 = __ldg(p.epi.alpha);
+    else alpha0 = __fdiv_rn(__fmul_rn(__ldg(p.a_amax), __ldg(p.b_amax)), p.alpha_denom);
+    if (p.group_cols) {
+      alpha1 = __fdiv_rn(__fmul_rn(__ldg(p.a_amax), __ldg(p.b_amax + 1)), p.alpha_denom);
+      if (p.N >= 3 * p.group_cols) alpha2 = __fdiv_rn(__fmul_rn(__ldg(p.a_amax), __ldg(p.b_amax + 2)), p.alpha_denom);
+    }
+    float amax0 = 0.f, amax1 = 0.f, amax2 = 0.f;
     const uint16_t* bias = reinterpret_cast<const uint16_t*>(p.epi.bias);
     constexpr bool has_res = (EPI & kEpiRes) != 0;
     const uint16_t* gate = reinterpret_cast<const uint16_t*>(p.epi.gate);
     uint8_t* my_stage = smem + C::kStagingOff + q * 8192;
     uint64_t* my_res_bar = res_bar + q * 2;
     uint32_t res_phase = 0u;                          // bit b = parity to wait for on buffer b
-    float local_amax = 0.f;
     int acc = 0;
     uint32_t acc_phase = 0;
     uint32_t chunk = 0;                               // running chunk counter -> staging buffer
@@ -220,6 +225,14 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const bool row_ok = row < p.M;
       const uint16_t* grow = nullptr;
       if (gate && row_ok) grow = gate + ((row + p.epi.row_offset) / p.epi.frame_rows) * p.epi.gate_stride;
+      // weight group of this tile: its scale, its output matrix, its amax target
+      const int grp = p.group_cols ? (int)(((int64_t)nt * BN) / p.group_cols) : 0;
+      const int64_t gcol0 = (int64_t)grp * p.group_cols;
+      const float alpha = grp == 0 ? alpha0 : (grp == 1 ? alpha1 : alpha2);
+      const CUtensorMap* tm_out = grp == 0 ? &tmD : &gmaps.m[grp - 1];
+      const float* amax_dst = grp == 0 ? p.group_amax[0] : (grp == 1 ? p.group_amax[1] : p.group_amax[2]);
+      const bool want_amax = p.group_cols ? amax_dst != nullptr : p.epi.out_amax != nullptr;
+      float local_amax = 0.f;
       // residual tile of the first chunk can be fetched while the main loop is still running
       if (has_res && row0 < p.M) {
         const uint32_t b0 = chunk & 1u;
@@ -250,11 +263,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             __syncwarp();
           }
           const int64_t col = (int64_t)nt * BN + c0;
-          epilogue_packed<EPI>(pkc, bias, grow, col, buf, lane, p.epi.out_amax != nullptr, row_ok, local_amax);
+          epilogue_packed<EPI>(pkc, bias, grow, col, buf, lane, want_amax, row_ok, local_amax);
           fence_proxy_async();
           __syncwarp();
           if (lane == 0 && !(p.debug & 8)) {
-            tma_store_2d(&tmD, buf, (int)col, row0);  // rows beyond M are clipped by the tensor map
+            tma_store_2d(tm_out, buf, (int)(col - gcol0), row0);  // rows beyond M are clipped by the tensor map
             bulk_commit();
           }
         }
@@ -304,12 +317,20 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           finish_chunk(c0, pkc);
         }
       }
+      if (grp == 0) amax0 = fmaxf(amax0, local_amax);
+      else if (grp == 1) amax1 = fmaxf(amax1, local_amax);
+      else amax2 = fmaxf(amax2, local_amax);
       if (++acc == C::kAcc) { acc = 0; acc_phase ^= 1u; }
     }
     if (lane == 0) bulk_wait<0>();
-    if (p.epi.out_amax) {
-      local_amax = warp_max(local_amax);
-      if (lane == 0 && local_amax > 0.f) atomic_max_nonneg(p.epi.out_amax, local_amax);
+    if (p.group_cols) {
+      const float am[3] = {warp_max(amax0), warp_max(amax1), warp_max(amax2)};
+#pragma unroll
+      for (int g = 0; g < 3; ++g)
+        if (lane == 0 && p.group_amax[g] && am[g] > 0.f) atomic_max_nonneg(p.group_amax[g], am[g]);
+    } else if (p.epi.out_amax) {
+      amax0 = warp_max(amax0);
+      if (lane == 0 && amax0 > 0.f) atomic_max_nonneg(p.epi.out_amax, amax0);
     }
   }
 
@@ -343,7 +364,7 @@ int get_out_map(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols,
 
 template <int BN, int EPI>
 int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD, const CUtensorMap& tmR,
-           const GemmParams& p, cudaStream_t stream) {
+           const GemmParams& p, cudaStream_t stream, const GroupMaps& gmaps) {
   static bool attr_set[64] = {};
   int dev = 0;
   LLNV_CUDA(cudaGetDevice(&dev));
@@ -353,7 +374,7 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tm
   }
   const int64_t tiles = ((p.M + BM - 1) / BM) * (p.N / BN);
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  gemm_nvfp4_kernel<BN, EPI><<<grid, kThreads, Cfg<BN>::kSmemBytes, stream>>>(tmA, tmB, tmD, tmR, p);
+  gemm_nvfp4_kernel<BN, EPI><<<grid, kThreads, Cfg<BN>::kSmemBytes, stream>>>(tmA, tmB, tmD, tmR, gmaps, p);
   return launch_status("gemm_nvfp4_kernel");
 }
 
@@ -379,15 +400,19 @@ extern "C" int llnv_gemm_nvfp4_debug(int flags) {
   return LLNV_OK;
 }
 
-extern "C" int llnv_gemm_nvfp4(const void* a_codes, const void* a_sf, const float* a_amax, int a_rule, const void* b_codes,
-                               const void* b_sf, const float* b_amax, int b_rule, int64_t M, int64_t N, int64_t K,
-                               const llnv_epilogue_t* epilogue, void* d, int64_t ldd, llnv_stream_t stream_) {
-  cudaStream_t stream = (cudaStream_t)stream_;
+namespace {
+
+// groups == 1: one GEMM into d.  groups == 2 or 3: B holds that many weight matrices of N / groups rows
+// each, b_amax one tensor amax per matrix; matrix g is written to d_groups[g] (row stride ldd_groups[g])
+// and its output amax, if wanted, to amax_groups[g].
+int gemm_run(const void* a_codes, const void* a_sf, const float* a_amax, int a_rule, const void* b_codes, const void* b_sf,
+             const float* b_amax, int b_rule, int64_t M, int64_t N, int64_t K, const llnv_epilogue_t* epilogue, void* d, int64_t ldd,
+             cudaStream_t stream, int groups, void* const* d_groups, const int64_t* ldd_groups, float* const* amax_groups) {
   LLNV_REQUIRE(a_codes && a_sf && b_codes && b_sf && d, "llnv_gemm_nvfp4: null pointer");
   LLNV_REQUIRE(M >= 0 && N > 0 && K > 0, "llnv_gemm_nvfp4: bad shape M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
   LLNV_REQUIRE(N % 128 == 0, "llnv_gemm_nvfp4: N must be a multiple of 128 (got %lld)", (long long)N);
   LLNV_REQUIRE(K % 256 == 0, "llnv_gemm_nvfp4: K must be a multiple of 256 (got %lld)", (long long)K);
-  LLNV_REQUIRE(ldd >= N && ldd % 8 == 0 && ((uintptr_t)d & 15) == 0, "llnv_gemm_nvfp4: d must be 16-byte aligned with ldd a multiple of 8");
+  LLNV_REQUIRE(ldd >= N / groups && ldd % 8 == 0 && ((uintptr_t)d & 15) == 0, "llnv_gemm_nvfp4: d must be 16-byte aligned with ldd a multiple of 8");
   LLNV_REQUIRE(((uintptr_t)a_sf & 15) == 0 && ((uintptr_t)b_sf & 15) == 0, "llnv_gemm_nvfp4: scale arrays must be 16-byte aligned");
   LLNV_REQUIRE(a_rule >= 0 && a_rule <= 4 && b_rule >= 0 && b_rule <= 4, "llnv_gemm_nvfp4: unknown scale rule");
   llnv_epilogue_t epi;
@@ -401,15 +426,16 @@ extern "C" int llnv_gemm_nvfp4(const void* a_codes, const void* a_sf, const floa
   if (epi.gate) LLNV_REQUIRE(epi.residual && epi.frame_rows > 0 && epi.gate_stride >= N, "llnv_gemm_nvfp4: gate needs residual, frame_rows > 0 and gate_stride >= N");
   if (M == 0) return LLNV_OK;
 
-  int bn = (N % 256 == 0) ? 256 : 128;
+  const int64_t group_cols = groups > 1 ? N / groups : 0;
+  int bn = (N % 256 == 0 && (groups == 1 || group_cols % 256 == 0)) ? 256 : 128;
   // few tokens (a sequence-parallel shard): 256-wide tiles would leave SMs idle, 128-wide tiles double the grid
   if (bn == 256 && ((M + 127) / 128) * (N / 256) * 2 <= (int64_t)sm_count() + 8) bn = 128;
   // less than one wave of 256-wide tiles: 192-wide ones fill more SMs (and overlap their epilogue
   // with the next main loop); with more tiles the lower operand traffic of the 256-wide tile wins
-  else if (bn == 256 && N % 192 == 0 && ((M + 127) / 128) * (N / 256) <= (int64_t)sm_count()) bn = 192;
+  else if (bn == 256 && N % 192 == 0 && (groups == 1 || group_cols % 192 == 0) && ((M + 127) / 128) * (N / 256) <= (int64_t)sm_count()) bn = 192;
   if (g_forced_bn == 128) bn = 128;
-  if (g_forced_bn == 192 && N % 192 == 0) bn = 192;
-  if (g_forced_bn == 256 && N % 256 == 0) bn = 256;
+  if (g_forced_bn == 192 && N % 192 == 0 && (groups == 1 || group_cols % 192 == 0)) bn = 192;
+  if (g_forced_bn == 256 && N % 256 == 0 && (groups == 1 || group_cols % 256 == 0)) bn = 256;
 
   const uint64_t mp = (uint64_t)((M + 127) / 128 * 128);
   CUtensorMap tmA, tmB;
@@ -433,8 +459,18 @@ extern "C" int llnv_gemm_nvfp4(const void* a_codes, const void* a_sf, const floa
   p.status = device_status_word();
   p.debug = g_debug;
   CUtensorMap tmD, tmR;
-  rc = get_out_map(&tmD, d, (uint64_t)M, (uint64_t)N, (uint64_t)ldd);
+  GroupMaps gmaps;
+  memset(&gmaps, 0, sizeof(gmaps));
+  p.group_cols = group_cols;
+  for (int g = 0; g < 3; ++g) p.group_amax[g] = (groups > 1 && g < groups && amax_groups) ? amax_groups[g] : nullptr;
+  rc = get_out_map(&tmD, d, (uint64_t)M, (uint64_t)(groups > 1 ? group_cols : N), (uint64_t)ldd);
   if (rc != LLNV_OK) return rc;
+  gmaps.m[0] = tmD;
+  gmaps.m[1] = tmD;
+  for (int g = 1; g < groups; ++g) {
+    rc = get_out_map(&gmaps.m[g - 1], d_groups[g], (uint64_t)M, (uint64_t)group_cols, (uint64_t)ldd_groups[g]);
+    if (rc != LLNV_OK) return rc;
+  }
   tmR = tmD;
   if (epi.residual) {
     LLNV_REQUIRE(((uintptr_t)epi.residual & 15) == 0 && epi.ldr % 8 == 0, "llnv_gemm_nvfp4: residual must be 16-byte aligned with ldr a multiple of 8");
@@ -444,13 +480,13 @@ extern "C" int llnv_gemm_nvfp4(const void* a_codes, const void* a_sf, const floa
   const int variant = (epi.bias ? kEpiBias : 0) | (epi.act == 1 ? kEpiGelu : 0) | (epi.residual ? kEpiRes : 0);
   // CTA pairs pay off when the K loop dominates (measured: +13..17 % at K = 14336, no gain at K = 3072)
   const bool pair_ok = N % 256 == 0;
-  const bool pair_auto = g_forced_bn == 0 && K >= 8192 && M >= 1024;
-  if (pair_ok && (g_forced_bn == 2 || pair_auto)) return gemm_nvfp4_pair(a_codes, a_sf, b_codes, b_sf, p, tmD, tmR, variant, stream);
+  const bool pair_auto = g_forced_bn == 0 && K >= 8192 && M >= 1024 && groups == 1;
+  if (pair_ok && groups == 1 && (g_forced_bn == 2 || pair_auto)) return gemm_nvfp4_pair(a_codes, a_sf, b_codes, b_sf, p, tmD, tmR, variant, stream);
 #define LLNV_GEMM_CASE(V)                                                                   \
   case V:                                                                                   \
-    return bn == 256   ? launch<256, V>(tmA, tmB, tmD, tmR, p, stream)                            \
-           : bn == 192 ? launch<192, V>(tmA, tmB, tmD, tmR, p, stream)                            \
-                       : launch<128, V>(tmA, tmB, tmD, tmR, p, stream);
+    return bn == 256   ? launch<256, V>(tmA, tmB, tmD, tmR, p, stream, gmaps)                     \
+           : bn == 192 ? launch<192, V>(tmA, tmB, tmD, tmR, p, stream, gmaps)                     \
+                       : launch<128, V>(tmA, tmB, tmD, tmR, p, stream, gmaps);
   switch (variant) {
     LLNV_GEMM_CASE(0)
     LLNV_GEMM_CASE(1)
@@ -464,4 +500,33 @@ extern "C" int llnv_gemm_nvfp4(const void* a_codes, const void* a_sf, const floa
 #undef LLNV_GEMM_CASE
   set_error("llnv_gemm_nvfp4: internal dispatch error");
   return LLNV_E_INVALID;
+}
+
+}  // namespace
+
+extern "C" int llnv_gemm_nvfp4(const void* a_codes, const void* a_sf, const float* a_amax, int a_rule, const void* b_codes,
+                               const void* b_sf, const float* b_amax, int b_rule, int64_t M, int64_t N, int64_t K,
+                               const llnv_epilogue_t* epilogue, void* d, int64_t ldd, llnv_stream_t stream) {
+  return gemm_run(a_codes, a_sf, a_amax, a_rule, b_codes, b_sf, b_amax, b_rule, M, N, K, epilogue, d, ldd, (cudaStream_t)stream, 1, nullptr,
+                  nullptr, nullptr);
+}
+
+extern "C" int llnv_gemm_nvfp4_grouped(const void* a_codes, const void* a_sf, const float* a_amax, int a_rule, const void* b_codes,
+                                       const void* b_sf, const float* b_amax, int b_rule, int64_t M, int64_t N_each, int64_t K, int groups,
+                                       const llnv_epilogue_t* epilogue, void* const* d, const int64_t* ldd, float* const* out_amax,
+                                       llnv_stream_t stream) {
+  LLNV_REQUIRE(groups >= 2 && groups <= 3, "llnv_gemm_nvfp4_grouped: 2 or 3 weight groups (got %d)", groups);
+  LLNV_REQUIRE(d && ldd && a_amax && b_amax, "llnv_gemm_nvfp4_grouped: null pointer");
+  LLNV_REQUIRE(N_each > 0 && N_each % 128 == 0, "llnv_gemm_nvfp4_grouped: rows per weight matrix must be a multiple of 128");
+  for (int g = 0; g < groups; ++g)
+    LLNV_REQUIRE(d[g] != nullptr && ldd[g] >= N_each && ldd[g] % 8 == 0 && ((uintptr_t)d[g] & 15) == 0,
+                 "llnv_gemm_nvfp4_grouped: output %d must be 16-byte aligned with a row stride >= N_each that is a multiple of 8", g);
+  if (epilogue) LLNV_REQUIRE(!epilogue->residual && !epilogue->gate && !epilogue->alpha && !epilogue->out_amax,
+                             "llnv_gemm_nvfp4_grouped: residual, gate, alpha and out_amax belong to the single-matrix call");
+  if (out_amax) {
+    for (int g = 0; g < groups; ++g)
+      if (out_amax[g]) LLNV_CUDA(cudaMemsetAsync(out_amax[g], 0, sizeof(float), (cudaStream_t)stream));
+  }
+  return gemm_run(a_codes, a_sf, a_amax, a_rule, b_codes, b_sf, b_amax, b_rule, M, N_each * groups, K, epilogue, d[0], ldd[0],
+                  (cudaStream_t)stream, groups, d, ldd, out_amax);
 }

@@ -40,7 +40,7 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccBufs = 3;
 constexpr uint32_t kSfaCol = 384, kSfbCol = 400;
 static_assert(kStageBytes % 1024 == 0, "stage must keep 1024-byte alignment");
-static_assert(kSmemBytes <= 232448, "shared memory budget");
+static_assert(kSmemBytes <= 232448, "more shared memory than one CTA may use");
 
 template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)

@@ -122,6 +122,18 @@ class Block:
         self.norm_q, self.norm_k, self.cnorm_q, self.cnorm_k = ones(), ones(), ones(), ones()
         self.norm3_w, self.norm3_b = ones(), (0.02 * torch.randn(c, generator=gen, device=device)).bfloat16()
         self.modulation = (torch.randn(1, 6, c, generator=gen, device=device) / math.sqrt(c)).bfloat16()
+        self.fuse_qkv()
+
+    def fuse_qkv(self) -> None:
+        """Concatenate the q, k and v weights (codes, swizzled scales, bias; one amax each) for the
+        grouped GEMM launch.  Call again after the weights were replaced."""
+        qs = [self.q.q, self.k.q, self.v.q]
+        self.qkv_rule = qs[0].scale_rule
+        self.qkv_ok = all(t.scale_rule == self.qkv_rule and t.original_shape == qs[0].original_shape for t in qs)
+        self.qkv_codes = torch.cat([t.values for t in qs], 0)
+        self.qkv_sf = torch.cat([t.scale_factors.view(torch.uint8).reshape(-1) for t in qs], 0).view(torch.float8_e4m3fn)
+        self.qkv_amax = torch.cat([t.amax.reshape(1) for t in qs], 0)
+        self.qkv_bias = torch.cat([self.q.bias, self.k.bias, self.v.bias], 0)
 
 
 class KVCache:
@@ -332,22 +344,29 @@ class CausalDiT:
         roff = self.rank * Sl
         # -- self attention
         self._adaln_quantize(x, e[:, 1], e[:, 0], self.act_c)
-        self._gemm(self.act_c, Sl, blk.q, self.q_buf)
-        self._gemm(self.act_c, Sl, blk.k, self.k_buf)
         n_past = len(cache.past_slots())
         T = cfg.chunk_tokens
         win_k, win_v = self.win_k[li], self.win_v[li]
         cur_k, cur_v = win_k[n_past * T:(n_past + 1) * T], win_v[n_past * T:(n_past + 1) * T]
         ck, cv = cache.k[li][cache.current_slot()], cache.v[li][cache.current_slot()]
+        # q, k and v projections in one grouped launch; V lands in the window (one GPU) or in v_buf, with its amax
+        v_out = cur_v if self.P == 1 else self.v_buf
+        v_am = cv.amax if self.P == 1 else self.v_amax
+        if blk.qkv_ok:
+            a = self.act_c
+            ops.gemm_nvfp4_grouped(a.codes, a.sf, a.amax, MSE, blk.qkv_codes, blk.qkv_sf, blk.qkv_amax, blk.qkv_rule.cuda_id(), Sl, cfg.dim,
+                                   cfg.dim, [self.q_buf, self.k_buf, v_out], bias=blk.qkv_bias, out_amax=[None, None, v_am])
+        else:
+            self._gemm(self.act_c, Sl, blk.q, self.q_buf)
+            self._gemm(self.act_c, Sl, blk.k, self.k_buf)
+            v_am.zero_()
+            self._gemm(self.act_c, Sl, blk.v, v_out, out_amax=v_am)
         if self.P == 1:
             # the tensor scales of the cache block are produced in place by the V GEMM epilogue and the RoPE kernel
-            cv.amax.zero_()
-            self._gemm(self.act_c, Sl, blk.v, cur_v, out_amax=cv.amax)
             ops.rmsnorm_rope_qk(self.q_buf, blk.norm_q, [self.q_rot.data_ptr()], cfg.dim, self.k_buf, blk.norm_k, [self.k_rot.data_ptr()],
                                 cfg.dim, [cur_k.data_ptr()], cfg.dim, ck.amax, cos, sin, cfg.eps)
             q_h, k_for_cache, v_for_cache = self.q_rot, self.k_rot, cur_v
         elif self.arena is not None:
-            self.v_amax.zero_()
             # tokens -> heads over peer memory: every producer stores each head shard at its final
             # address on the rank that owns those heads (q, rotated keys for the cache, smoothed keys
             # and values in that rank's window); one barrier makes all of it visible
@@ -356,14 +375,12 @@ class CausalDiT:
             cur_off = n_past * T * Cl * 2 + row_off            # ... inside the current-chunk part of a window
             ops.rmsnorm_rope_qk(self.q_buf, blk.norm_q, ar.ptrs("q_h", row_off), Cl, self.k_buf, blk.norm_k, ar.ptrs("kr_h", row_off), Cl,
                                 ar.ptrs(f"win_k{li}", cur_off), Cl, self.k_amax, cos, sin, cfg.eps)
-            self._gemm(self.act_c, Sl, blk.v, self.v_buf, out_amax=self.v_amax)
             ops.scatter_2d(self.v_buf, Cl * 2, ar.ptrs(f"win_v{li}", cur_off), Cl * 2, Sl, Cl * 2)
             # the barrier that publishes the stores above also carries the K / V amax: its group maximum
             # is the tensor scale of every rank's cache block (and the one a single GPU would use)
             ar.allreduce_max_(self.kv_amax)
             q_h, k_for_cache, v_for_cache = self.q_h, self.kr_h, cur_v
         else:
-            self.v_amax.zero_()
             P_, grp = self.P, self.group
             # tokens -> heads with NCCL: every producer writes the send layout, every part lands where
             # its consumer reads it
@@ -373,7 +390,6 @@ class CausalDiT:
                              amax_out=self.k_amax, shards=P_)
             w_ks = sp.exchange(self.ks_sh, cur_k, grp, async_op=True)
             w_kr = sp.exchange(self.kr_sh, self.kr_h, grp, async_op=True)
-            self._gemm(self.act_c, Sl, blk.v, self.v_buf, out_amax=self.v_amax)
             self.v_sh.copy_(self.v_buf.view(Sl, P_, self.Cl).permute(1, 0, 2))
             w_v = sp.exchange(self.v_sh, cur_v, grp, async_op=True)
             if self.sync_amax:

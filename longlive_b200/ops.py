@@ -332,3 +332,24 @@ def gemm_nvfp4(a_codes, a_sf, a_amax, a_rule, b_codes, b_sf, b_amax, b_rule, m, 
                                           b_amax.data_ptr() if b_amax is not None else None, b_rule,
                                           m, n, k, C.byref(epi), out.data_ptr(), out.stride(0), _stream(a_codes)))
     return out
+
+
+def gemm_nvfp4_grouped(a_codes, a_sf, a_amax, a_rule, b_codes, b_sf, b_amax, b_rule, m, n_each, k, outs, *, bias=None, act=0,
+                       out_amax=None):
+    """Two or three Linears sharing their input in one launch (``llnv_gemm_nvfp4_grouped``): ``b_codes`` /
+    ``b_sf`` are the weights concatenated along N, ``b_amax`` an fp32 tensor with one amax per weight,
+    ``outs`` the output tensors (bf16 [m, n_each], any row stride), ``out_amax`` a list of fp32 [1]
+    tensors or None per output."""
+    _require_cuda(a_codes, "a_codes")
+    g = len(outs)
+    epi = _lib.Epilogue()
+    epi.bias = bias.data_ptr() if bias is not None else None
+    epi.act = int(act)
+    d = _ptr_table([o.data_ptr() for o in outs])
+    ldd = (C.c_int64 * g)(*[o.stride(0) for o in outs])
+    am = _ptr_table([(t.data_ptr() if t is not None else 0) for t in out_amax]) if out_amax is not None else None
+    with torch.cuda.device(a_codes.device):
+        _check(_lib.lib().llnv_gemm_nvfp4_grouped(a_codes.data_ptr(), a_sf.data_ptr(), a_amax.data_ptr(), a_rule, b_codes.data_ptr(),
+                                                  b_sf.data_ptr(), b_amax.data_ptr(), b_rule, m, n_each, k, g, C.byref(epi), d, ldd, am,
+                                                  _stream(a_codes)))
+    return outs

@@ -196,3 +196,31 @@ def test_gemm_192_wide_tiles(m, n, k):
     check_close(outs[192][0], O.bf16_round(oracle_matmul(xq, wq, m, n, k)), k)
     for a, b in zip(outs[192], outs[128]):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("m,n_each,k", [(200, 256, 512), (700, 768, 1024), (2640, 3072, 3072), (330, 3072, 3072)])
+def test_grouped_gemm_equals_separate_launches(m, n_each, k):
+    """Three Linears sharing their input in one launch: every output, and the output amax, equals the separate calls."""
+    x = util.config_activation(m, k, seed=m + k).cuda()
+    xq = L.quantize_to_fp4(x)
+    ws = [L.quantize_to_fp4(util.config_weight(n_each, k, seed=50 + i).cuda() * (1 + i)) for i in range(3)]
+    g = torch.Generator().manual_seed(9)
+    biases = [torch.randn(n_each, generator=g).bfloat16().cuda() for _ in range(3)]
+    ref, ref_am = [], []
+    for w, b in zip(ws, biases):
+        am = torch.zeros(1, dtype=torch.float32, device="cuda")
+        ref.append(ops.gemm_nvfp4(xq.values, xq.scale_factors, xq.amax, 3, w.values, w.scale_factors, w.amax, 3, m, n_each, k, bias=b, out_amax=am))
+        ref_am.append(am)
+    codes = torch.cat([w.values for w in ws], 0)
+    sf = torch.cat([w.scale_factors.view(torch.uint8).reshape(-1) for w in ws], 0).view(torch.float8_e4m3fn)
+    amax = torch.cat([w.amax.reshape(1) for w in ws], 0)
+    big = torch.zeros(m, 2 * n_each + 64, dtype=torch.bfloat16, device="cuda")        # outputs with different row strides
+    outs = [torch.empty(m, n_each, dtype=torch.bfloat16, device="cuda"), big[:, :n_each], big[:, n_each + 64:]]
+    ams = [torch.full((1,), 7.0, device="cuda"), None, torch.full((1,), 7.0, device="cuda")]
+    ops.gemm_nvfp4_grouped(xq.values, xq.scale_factors, xq.amax, 3, codes, sf, amax, 3, m, n_each, k, outs, bias=torch.cat(biases), out_amax=ams)
+    torch.cuda.synchronize()
+    assert _lib.lib().llnv_check_status(None) == 0, _lib.lib().llnv_last_error()
+    for o, r in zip(outs, ref):
+        assert torch.equal(o, r)
+    assert torch.equal(ams[0], ref_am[0]) and torch.equal(ams[2], ref_am[2])
+    assert float(big[:, n_each:n_each + 64].abs().max()) == 0.0
