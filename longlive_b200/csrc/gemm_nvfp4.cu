@@ -49,7 +49,10 @@ struct Cfg {
   static constexpr uint32_t kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
   // epilogue staging: per epilogue warp two buffers of 32 rows x 64 bf16 columns (128-byte rows,
   // 128-byte swizzle) that TMA stores drain; the same buffers receive the residual tile first
-  static constexpr uint32_t kStagingBytes = 4 * 2 * 4096;
+  // (the single-accumulator tile has one buffer per 64-column chunk, so that the residual of a whole
+  // tile can be fetched while its main loop still runs)
+  static constexpr int kBufs = kAcc == 1 ? BN / 64 : 2;
+  static constexpr uint32_t kStagingBytes = 4 * kBufs * 4096;
   static constexpr uint32_t kStagingOff = kStages * kStageBytes;
   static constexpr uint32_t kBarOff = kStagingOff + kStagingBytes;
   static constexpr uint32_t kSmemBytes = kBarOff + 1024;
@@ -73,7 +76,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   uint64_t* tfull_bar = empty_bar + C::kStages;
   uint64_t* tempty_bar = tfull_bar + C::kAcc;
   uint64_t* res_bar = tempty_bar + C::kAcc;                 // [4 warps][2 buffers]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_bar + 8);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_bar + 16);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -99,7 +102,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       mbar_init(&tfull_bar[i], 1);
       mbar_init(&tempty_bar[i], 4);
     }
-    for (int i = 0; i < 8; ++i) mbar_init(&res_bar[i], 1);
+    for (int i = 0; i < 16; ++i) mbar_init(&res_bar[i], 1);
     *abort_flag = 0u;
     fence_barrier_init();
     prefetch_tensormap(&tmA);
@@ -212,8 +215,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const uint16_t* bias = reinterpret_cast<const uint16_t*>(p.epi.bias);
     constexpr bool has_res = (EPI & kEpiRes) != 0;
     const uint16_t* gate = reinterpret_cast<const uint16_t*>(p.epi.gate);
-    uint8_t* my_stage = smem + C::kStagingOff + q * 8192;
-    uint64_t* my_res_bar = res_bar + q * 2;
+    uint8_t* my_stage = smem + C::kStagingOff + q * C::kBufs * 4096;
+    uint64_t* my_res_bar = res_bar + q * C::kBufs;
     uint32_t res_phase = 0u;                          // bit b = parity to wait for on buffer b
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -233,8 +236,22 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const float* amax_dst = grp == 0 ? p.group_amax[0] : (grp == 1 ? p.group_amax[1] : p.group_amax[2]);
       const bool want_amax = p.group_cols ? amax_dst != nullptr : p.epi.out_amax != nullptr;
       float local_amax = 0.f;
-      // residual tile of the first chunk can be fetched while the main loop is still running
-      if (has_res && row0 < p.M) {
+      if (C::kAcc == 1) {
+        // one buffer per chunk: once the previous tile's stores have read them, the residual of the
+        // whole tile is fetched while the main loop is still running
+        if (row0 < p.M && lane == 0) {
+          bulk_wait_read<0>();
+          if (has_res) {
+#pragma unroll
+            for (int ci = 0; ci < C::kBufs; ++ci) {
+              mbar_arrive_expect_tx(&my_res_bar[ci], 4096);
+              tma_load_2d(my_stage + ci * 4096, &tmR, nt * BN + ci * 64, row0, &my_res_bar[ci]);
+            }
+          }
+        }
+        __syncwarp();
+      } else if (has_res && row0 < p.M) {
+        // residual tile of the first chunk can be fetched while the main loop is still running
         const uint32_t b0 = chunk & 1u;
         if (lane == 0) {
           bulk_wait_read<1>();                        // the store that used this buffer two chunks ago has read it
@@ -246,10 +263,15 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       tc_fence_after();
       // everything after the accumulator has been drained: residual wait, epilogue math, staging, store
       auto finish_chunk = [&](int c0, const uint32_t (&pkc)[32]) {
-        const uint32_t b = chunk & 1u;
+        const uint32_t b = C::kAcc == 1 ? (uint32_t)(c0 >> 6) : (chunk & 1u);
         uint8_t* buf = my_stage + b * 4096;
         if (row0 < p.M && !(p.debug & 4)) {
-          if (has_res) {
+          if (C::kAcc == 1) {
+            if (has_res) {
+              mbar_wait(&my_res_bar[b], (res_phase >> b) & 1u, abort_flag, p.status, 301u);
+              res_phase ^= 1u << b;
+            }
+          } else if (has_res) {
             // prefetch the residual of the next chunk of this tile into the other buffer
             if (c0 + 64 < BN && lane == 0) {
               bulk_wait_read<0>();
