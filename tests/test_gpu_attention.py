@@ -131,3 +131,22 @@ def test_attention_output_amax(lq, splits):
     out = ops.attention_bf16(q, k, v, heads, key_splits=splits, out_amax=amax)
     torch.cuda.synchronize()
     assert float(amax.item()) == float(out.float().abs().max().item())
+
+
+def test_attention_full_window_properties():
+    """At the benchmark window (2640 queries, 13200 keys): with V = 1 every output is 1 (the softmax
+    weights of a row sum to one), and the key-split schedule agrees with the single pass."""
+    lq, lk, heads = 2640, 13200, 3
+    g = torch.Generator(device="cuda").manual_seed(5)
+    q = torch.randn(lq, heads * 128, generator=g, device="cuda").bfloat16()
+    k = torch.randn(lk, heads * 128, generator=g, device="cuda").bfloat16()
+    ones = torch.ones(lk, heads * 128, device="cuda").bfloat16()
+    for splits in (1, 4):
+        out = ops.attention_bf16(q, k, ones, heads, key_splits=splits)
+        assert float((out.float() - 1).abs().max()) <= 2.0 ** -7
+    v = torch.randn(lk, heads * 128, generator=g, device="cuda").bfloat16()
+    a = ops.attention_bf16(q, k, v, heads, key_splits=1).float()
+    b = ops.attention_bf16(q, k, v, heads, key_splits=4).float()
+    torch.cuda.synchronize()
+    assert _lib.lib().llnv_check_status(None) == 0, _lib.lib().llnv_last_error()
+    assert float((a - b).abs().max()) <= 2.0 ** -8 + 2.0 ** -6 * float(a.abs().max())

@@ -224,3 +224,26 @@ def test_grouped_gemm_equals_separate_launches(m, n_each, k):
         assert torch.equal(o, r)
     assert torch.equal(ams[0], ref_am[0]) and torch.equal(ams[2], ref_am[2])
     assert float(big[:, n_each:n_each + 64].abs().max()) == 0.0
+
+
+def test_gemm_full_size_tilings_agree():
+    """At the benchmark's FFN shape the 256-, 192-... tilings and the CTA-pair kernel give bit-identical
+    results (same products, same order along K), and a row of ones through identical weights repeats."""
+    m, n, k = 2640, 3072, 14336
+    x = util.config_activation(m, k, seed=3).cuda()
+    w = util.config_weight(n, k, seed=4).cuda()
+    xq, wq = L.quantize_to_fp4(x), L.quantize_to_fp4(w)
+    args = (xq.values, xq.scale_factors, xq.amax, 3, wq.values, wq.scale_factors, wq.amax, 3, m, n, k)
+    lib = _lib.lib()
+    outs = []
+    for tile in (256, 192, 128, 2):
+        lib.llnv_gemm_nvfp4_force_tile_n(tile)
+        try:
+            outs.append(ops.gemm_nvfp4(*args))
+        finally:
+            lib.llnv_gemm_nvfp4_force_tile_n(0)
+    torch.cuda.synchronize()
+    assert lib.llnv_check_status(None) == 0, lib.llnv_last_error()
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0])
+    assert torch.isfinite(outs[0].float()).all()
