@@ -366,10 +366,13 @@ __global__ void __launch_bounds__(256) quantize_nvfp4_kernel(const uint16_t* x, 
   qc.dec = __fdiv_rn(1.f, qc.enc);            // reference.py:159-166
   qc.fast = (__float_as_uint(qc.amax) & 0xFFFFu) == 0u && qc.amax > 1.0e-20f && qc.amax < 1.0e30f;
 
+  // 256 threads cover 128 x 128 elements, 128 threads 128 x 64 (one scale atom): the narrower CTA
+  // is launched for small tensors, whose few wide CTAs would spread unevenly over the SMs
   const int t = threadIdx.x;
-  const int cb = t & 7;
-  const int r0 = t >> 3;
-  const int64_t col = (int64_t)blockIdx.x * 128 + cb * 16;
+  const int cshift = blockDim.x == 256 ? 3 : 2;
+  const int cb = t & ((1 << cshift) - 1);
+  const int r0 = t >> cshift;
+  const int64_t col = (int64_t)blockIdx.x * (16 << cshift) + cb * 16;
   const int64_t row_base = (int64_t)blockIdx.y * 128;
   const bool col_ok = col < K;
   const int64_t xoff = pr.shard_cols ? (col / pr.shard_cols) * pr.shard_stride + col % pr.shard_cols : col;
@@ -592,12 +595,18 @@ __global__ void div_const_selftest_kernel(uint32_t first, uint64_t count, unsign
 template <int MODE>
 int launch_quantize(int rule, dim3 grid, cudaStream_t stream, const uint16_t* x, int64_t M, int64_t K, int64_t ldx,
                     const float* amax, uint8_t* codes, uint8_t* sf, const Prologue& pr, uint16_t* y_out, int64_t ldy) {
+  // few 128 x 128 CTAs: halve their width (grid.x doubles)
+  int threads = 256;
+  if ((int64_t)grid.x * grid.y * grid.z < 6 * (int64_t)sm_count()) {
+    threads = 128;
+    grid.x = (unsigned)((K + 63) / 64);
+  }
   switch (rule) {
-    case LLNV_RULE_STATIC_6: quantize_nvfp4_kernel<LLNV_RULE_STATIC_6, MODE><<<grid, 256, 0, stream>>>(x, M, K, ldx, amax, codes, sf, pr, y_out, ldy); break;
-    case LLNV_RULE_STATIC_4: quantize_nvfp4_kernel<LLNV_RULE_STATIC_4, MODE><<<grid, 256, 0, stream>>>(x, M, K, ldx, amax, codes, sf, pr, y_out, ldy); break;
-    case LLNV_RULE_MAE: quantize_nvfp4_kernel<LLNV_RULE_MAE, MODE><<<grid, 256, 0, stream>>>(x, M, K, ldx, amax, codes, sf, pr, y_out, ldy); break;
-    case LLNV_RULE_MSE: quantize_nvfp4_kernel<LLNV_RULE_MSE, MODE><<<grid, 256, 0, stream>>>(x, M, K, ldx, amax, codes, sf, pr, y_out, ldy); break;
-    default: quantize_nvfp4_kernel<LLNV_RULE_ABS_MAX, MODE><<<grid, 256, 0, stream>>>(x, M, K, ldx, amax, codes, sf, pr, y_out, ldy); break;
+    case LLNV_RULE_STATIC_6: quantize_nvfp4_kernel<LLNV_RULE_STATIC_6, MODE><<<grid, threads, 0, stream>>>(x, M, K, ldx, amax, codes, sf, pr, y_out, ldy); break;
+    case LLNV_RULE_STATIC_4: quantize_nvfp4_kernel<LLNV_RULE_STATIC_4, MODE><<<grid, threads, 0, stream>>>(x, M, K, ldx, amax, codes, sf, pr, y_out, ldy); break;
+    case LLNV_RULE_MAE: quantize_nvfp4_kernel<LLNV_RULE_MAE, MODE><<<grid, threads, 0, stream>>>(x, M, K, ldx, amax, codes, sf, pr, y_out, ldy); break;
+    case LLNV_RULE_MSE: quantize_nvfp4_kernel<LLNV_RULE_MSE, MODE><<<grid, threads, 0, stream>>>(x, M, K, ldx, amax, codes, sf, pr, y_out, ldy); break;
+    default: quantize_nvfp4_kernel<LLNV_RULE_ABS_MAX, MODE><<<grid, threads, 0, stream>>>(x, M, K, ldx, amax, codes, sf, pr, y_out, ldy); break;
   }
   return launch_status("quantize_nvfp4_kernel");
 }
