@@ -298,6 +298,41 @@ int llnv_gemm_nvfp4_grouped(const void* a_codes, const void* a_sf, const float* 
                             const llnv_epilogue_t* epilogue, void* const* d, const int64_t* ldd, float* const* out_amax,
                             llnv_stream_t stream);
 
+/* ---- flow-matching UniPC scheduler step ------------------------------------------------------ */
+
+/* Scalars of one scheduler step, computed on the host in fp32 exactly as the reference computes
+ * them as 0-dim tensors (wan_5b/utils/fm_solvers_unipc.py:407-455 for the predictor, :550-605 for
+ * the corrector): with sigma_t / sigma_s0 the sigmas the update goes to / starts from,
+ * lambda = log(1 - sigma) - log(sigma), h = lambda_t - lambda_s0,
+ *   c1 = sigma_t / sigma_s0, c2 = (1 - sigma_t) * expm1(-h), c3 = (1 - sigma_t) * B(h) with B(h) = expm1(-h),
+ *   inv_rk = 1 / r_1 (r_1 = (lambda_older - lambda_s0) / h, order 2 only),
+ *   rho: the UniC weights (0.5 for order 1, the 2 x 2 solve for order 2), already rounded to the
+ *   latents' dtype; the UniP weight of order 2 is the constant 0.5.
+ * p_zero is c3 * 0 of the predictor (the term an order-1 predictor subtracts; it is -0 or +0). */
+typedef struct {
+  float sigma;               /* sigma of this step: x0 = sample - sigma * model_output (:320-323) */
+  int use_corrector;         /* 0 on the first step (:689-693) */
+  int corrector_order;       /* 1 or 2: the order the previous step's predictor used */
+  float cc1, cc2, cc3, c_inv_rk, c_rho0, c_rho1;
+  int predictor_order;       /* 1 or 2 (:714-722) */
+  float pc1, pc2, pc3, p_inv_rk, p_zero;
+} llnv_unipc_coef;
+
+/* scheduler.step of FlowUniPCMultistepScheduler (wan_5b/utils/fm_solvers_unipc.py:657-741, called
+ * once per denoising step by the chunk loop, pipeline/causal_diffusion_inference.py:604-609) for
+ * solver order <= 2, `bh2`, x0 prediction from a flow prediction, as one elementwise pass over n
+ * values of dtype 0 (bf16) or 1 (fp32):
+ *   x0_out     = sample - sigma * model_output                    (convert_model_output, :320-323)
+ *   sample_out = UniC(last_sample, x0_prev, x0_older, x0_out)     (:599-627) or sample without corrector
+ *   next_out   = UniP(sample_out, x0_out, x0_prev)                (:457-485)
+ * with every intermediate rounded to the dtype as the reference's PyTorch calls round it on a GPU.
+ * x0_prev / x0_older are the x0_out of the previous two steps, last_sample the previous step's
+ * sample_out; pointers a step does not need may be NULL.  Outputs may alias inputs (x0_out =
+ * x0_older rotates the history in place).  All pointers are device memory. */
+int llnv_unipc_step(const void* model_output, const void* sample, const void* x0_prev, const void* x0_older,
+                    const void* last_sample, void* x0_out, void* sample_out, void* next_out, int64_t n, int dtype,
+                    const llnv_unipc_coef* coef, llnv_stream_t stream);
+
 /* Test / benchmark hooks (no counterpart in the reference). */
 int llnv_gemm_nvfp4_force_tile_n(int bn);       /* 0 = automatic, 128 or 256 */
 int llnv_gemm_nvfp4_debug(int flags);           /* timing experiments; results become wrong when non-zero */

@@ -12,7 +12,7 @@ EXPORTS = [
     "llnv_version", "llnv_last_error", "llnv_check_status", "llnv_amax_bf16", "llnv_quantize_nvfp4",
     "llnv_kv_dequant", "llnv_dequantize_nvfp4", "llnv_gemm_nvfp4", "llnv_gemm_nvfp4_grouped", "llnv_adaln_quantize_nvfp4",
     "llnv_layernorm_quantize_nvfp4", "llnv_gemm_nvfp4_force_tile_n", "llnv_gemm_nvfp4_debug", "llnv_selftest_div_const",
-    "llnv_adaln_quantize_nvfp4_static", "llnv_static_max_rows", "llnv_rmsnorm_rope", "llnv_attention_bf16", "llnv_attention_bf16_ex", "llnv_quantize_nvfp4_ex", "llnv_quantize_nvfp4_pair", "llnv_rmsnorm_rope_ex", "llnv_rmsnorm_rope_scatter", "llnv_rmsnorm_rope_qk", "llnv_scatter_2d", "llnv_peer_barrier", "llnv_peer_allreduce_max", "llnv_attention_key_splits", "llnv_attention_workspace_bytes", "llnv_adaln_quantize_nvfp4_ex", "llnv_layernorm_quantize_nvfp4_ex",
+    "llnv_adaln_quantize_nvfp4_static", "llnv_static_max_rows", "llnv_rmsnorm_rope", "llnv_attention_bf16", "llnv_attention_bf16_ex", "llnv_quantize_nvfp4_ex", "llnv_quantize_nvfp4_pair", "llnv_rmsnorm_rope_ex", "llnv_rmsnorm_rope_scatter", "llnv_rmsnorm_rope_qk", "llnv_scatter_2d", "llnv_peer_barrier", "llnv_peer_allreduce_max", "llnv_attention_key_splits", "llnv_attention_workspace_bytes", "llnv_adaln_quantize_nvfp4_ex", "llnv_layernorm_quantize_nvfp4_ex", "llnv_unipc_step",
 ]
 
 
@@ -22,6 +22,15 @@ class Epilogue(C.Structure):
         ("alpha", C.c_void_p), ("bias", C.c_void_p), ("act", C.c_int32), ("residual", C.c_void_p),
         ("ldr", C.c_int64), ("gate", C.c_void_p), ("gate_stride", C.c_int64), ("frame_rows", C.c_int32),
         ("out_amax", C.c_void_p), ("row_offset", C.c_int32),
+    ]
+
+
+class UniPCCoef(C.Structure):
+    """Mirror of ``llnv_unipc_coef``."""
+    _fields_ = [
+        ("sigma", C.c_float), ("use_corrector", C.c_int32), ("corrector_order", C.c_int32), ("cc1", C.c_float), ("cc2", C.c_float),
+        ("cc3", C.c_float), ("c_inv_rk", C.c_float), ("c_rho0", C.c_float), ("c_rho1", C.c_float), ("predictor_order", C.c_int32),
+        ("pc1", C.c_float), ("pc2", C.c_float), ("pc3", C.c_float), ("p_inv_rk", C.c_float), ("p_zero", C.c_float),
     ]
 
 
@@ -72,6 +81,7 @@ def lib() -> C.CDLL:
         l.llnv_scatter_2d.argtypes = [p, i64, i64, p, i64, i64, i64, i32, p]
         l.llnv_peer_barrier.argtypes = [p, i32, i32, p, p]
         l.llnv_peer_allreduce_max.argtypes = [p, i32, p, p, i32, i32, p, p]
+        l.llnv_unipc_step.argtypes = [p, p, p, p, p, p, p, p, i64, i32, p, p]
         for name in EXPORTS:
             getattr(l, name)
         _lib = l

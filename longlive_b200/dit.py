@@ -30,6 +30,7 @@ import torch
 from . import ops, sp
 from .enums import ScaleRule
 from .quantize import QuantizationConfig, QuantizedTensor, quantize_to_fp4
+from .scheduler import FlowUniPCMultistepScheduler
 
 MSE = ScaleRule.mse.cuda_id()
 
@@ -262,6 +263,7 @@ class CausalDiT:
         self.sin_buf = torch.empty((Sl, 64), dtype=torch.float32, device=dev)
         self._rope_frame: int | None = None
         self._graphs: dict = {}
+        self._scheduler = None
         self._graph_pool = None
         self._ran_eager = False
 
@@ -541,19 +543,22 @@ class CausalDiT:
         return torch.nn.functional.linear(y, self.head_w, self.head_b)
 
     def run_chunk(self, latent_tokens: torch.Tensor, ctx: torch.Tensor, chunk_index: int,
-                  timesteps=(999, 937, 833, 624)) -> torch.Tensor:
-        """One AR chunk: 4 denoising forwards + 1 clean re-cache forward
-        (pipeline/causal_diffusion_inference.py:567-647).  The scheduler update between steps is a
-        plain flow-matching Euler step (the UniPC solver is outside the hot path)."""
+                  sampling_steps: int = 4, timestep_shift: float = 5.0) -> torch.Tensor:
+        """One AR chunk: ``sampling_steps`` denoising forwards, each followed by a UniPC scheduler step,
+        then one clean re-cache forward at timestep 0 (pipeline/causal_diffusion_inference.py:566-647;
+        4 steps at shift 5 are the timesteps 999, 937, 833, 624 of configs/inference.yaml)."""
         cfg = self.cfg
         self.cache.begin_chunk()
         start_frame = chunk_index * cfg.frames_per_chunk
-        x_t = latent_tokens
         F = cfg.frames_per_chunk
-        sig = [t / 1000.0 for t in timesteps] + [0.0]
-        for i, t in enumerate(timesteps):
+        if self._scheduler is None:
+            self._scheduler = FlowUniPCMultistepScheduler(num_train_timesteps=1000, shift=1, use_dynamic_shifting=False)
+        sched = self._scheduler
+        sched.set_timesteps(sampling_steps, device="cpu", shift=timestep_shift)      # a new scheduler per chunk, :566, :892-899
+        x_t = latent_tokens
+        for t in sched.timesteps.tolist():
             tt = torch.full((F,), float(t), device=self.device)
             flow = self.forward(x_t, tt, ctx, start_frame)
-            x_t = (x_t.float() + (sig[i + 1] - sig[i]) * flow.float()).bfloat16()
+            x_t = sched.step(flow, t, x_t, return_dict=False)[0]
         self.forward(x_t, torch.zeros(F, device=self.device), ctx, start_frame)
         return x_t
