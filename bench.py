@@ -452,7 +452,8 @@ def bench_dit_chunk(dev, rank, world, group, steps: int, sync_amax: bool = True,
 
 def run_kernel_case(spec: str, iters: int):
     """Run one kernel on one shape a few times (used for ncu captures and quick timing):
-    gemm:MxNxK[:tile]   quantize:MxK[:rule]   kvdequant:BLOCKSxTOKENSxHEADS   attention:LQxLKxHEADS   ropenorm:TOKENSxHEADS"""
+    gemm:MxNxK[:tile]   quantize:MxK[:rule]   kvdequant:BLOCKSxTOKENSxHEADS   attention:LQxLKxHEADS   ropenorm:TOKENSxHEADS
+    unipc:ELEMENTS[:f32]  (the scheduler step with order-2 corrector and predictor: 5 tensors read, 3 written)"""
     import torch
 
     import longlive_b200 as L
@@ -511,6 +512,19 @@ def run_kernel_case(spec: str, iters: int):
         amax = torch.empty(1, dtype=torch.float32, device=dev)
         fn = lambda: ops.rmsnorm_rope(x, w, cos, sin, out=out, out_smooth=sm, amax_out=amax)
         work, unit = s_ * heads * 128 * 6 / 1e9, "GB/s"
+    elif kind == "unipc":
+        import ctypes
+        from longlive_b200.scheduler import FlowUniPCMultistepScheduler
+        n, = d
+        dt = torch.float32 if opt == "f32" else torch.bfloat16
+        sched = FlowUniPCMultistepScheduler(num_train_timesteps=1000, shift=1, use_dynamic_shifting=False)
+        sched.set_timesteps(4, device="cpu", shift=5.0)
+        coef = sched.coefficients(2, dt)
+        t8 = [torch.randn(n, generator=gen, device=dev).to(dt) for _ in range(8)]
+        stream = torch.cuda.current_stream().cuda_stream
+        fn = lambda: _lib.check(lib.llnv_unipc_step(*[t.data_ptr() for t in t8], n, 0 if dt == torch.bfloat16 else 1,
+                                                    ctypes.byref(coef), stream))
+        work, unit = 8.0 * n * t8[0].element_size() / 1e9, "GB/s"
     else:
         raise SystemExit(f"unknown kernel case {spec}")
     for _ in range(3):

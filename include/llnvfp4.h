@@ -334,6 +334,11 @@ int llnv_unipc_step(const void* model_output, const void* sample, const void* x0
                     const llnv_unipc_coef* coef, llnv_stream_t stream);
 
 /* Test / benchmark hooks (no counterpart in the reference). */
+/* Kernels are launched with programmatic stream serialization (the next kernel of a stream is
+ * scheduled while the previous one drains and waits for it on the device); 0 turns that off, e.g.
+ * to time its effect.  Returns the previous setting.  The environment variable LLNV_PDL=0 does the
+ * same at load time.  Results do not depend on it. */
+int llnv_set_pdl(int on);
 int llnv_gemm_nvfp4_force_tile_n(int bn);       /* 0 = automatic, 128 or 256 */
 int llnv_gemm_nvfp4_debug(int flags);           /* timing experiments; results become wrong when non-zero */
 int llnv_selftest_div_const(int divisor, uint32_t first_bits, uint64_t count, unsigned long long* mismatches,

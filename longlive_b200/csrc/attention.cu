@@ -114,6 +114,7 @@ __device__ __forceinline__ float ex2_poly(float x) {
 __global__ void __launch_bounds__(kThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const AttnParams p) {
+  pdl_wait();
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* q_full = reinterpret_cast<uint64_t*>(smem + kBarOff);
   uint64_t* k_full = q_full + 1;
@@ -408,6 +409,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 __global__ void __launch_bounds__(256) attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                                 int nsplit, int64_t Lq, int heads, float scale_log2,
                                                                 uint16_t* __restrict__ out, int64_t ldo, float* __restrict__ out_amax) {
+  pdl_wait();
   const int64_t unit = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);      // row * heads + head
   const int lane = threadIdx.x & 31;
   if (unit >= Lq * heads) return;
@@ -513,11 +515,11 @@ extern "C" int llnv_attention_bf16_ex(const void* q, int64_t Lq, int64_t ldq, co
   p.part_ml = key_splits > 1 ? (float*)workspace + (int64_t)key_splits * Lq * heads * kD : nullptr;
   p.out_amax = key_splits > 1 ? nullptr : out_amax;
   dim3 grid((unsigned)((Lq + kBQ - 1) / kBQ), (unsigned)heads, (unsigned)key_splits);
-  attention_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmQ, tmK, tmV, tmO, p);
+  launch_k(attention_kernel, grid, kThreads, kSmemBytes, stream, tmQ, tmK, tmV, tmO, p);
   int st = launch_status("attention_kernel");
   if (st != LLNV_OK || key_splits == 1) return st;
   const int64_t units = Lq * heads;
-  attention_combine_kernel<<<(unsigned)((units + 7) / 8), 256, 0, stream>>>(p.part_o, p.part_ml, key_splits, Lq, heads, p.scale_log2,
+  launch_k(attention_combine_kernel, (unsigned)((units + 7) / 8), 256, 0, stream, p.part_o, p.part_ml, key_splits, Lq, heads, p.scale_log2,
                                                                            (uint16_t*)out, ldo, out_amax);
   return launch_status("attention_combine_kernel");
 }

@@ -2,6 +2,8 @@
 #include <cstring>
 #include <mutex>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace llnv {
@@ -49,7 +51,25 @@ int sm_count() {
   return g_sms[dev];
 }
 
+namespace {
+int g_pdl = -1;                        // -1: not decided yet (environment LLNV_PDL, default on)
+}
+
+bool pdl_enabled() {
+  if (g_pdl < 0) {
+    const char* e = getenv("LLNV_PDL");
+    g_pdl = (e && e[0] == '0') ? 0 : 1;
+  }
+  return g_pdl != 0;
+}
+
 }  // namespace llnv
+
+extern "C" int llnv_set_pdl(int on) {
+  const int before = llnv::pdl_enabled() ? 1 : 0;
+  llnv::g_pdl = on ? 1 : 0;
+  return before;
+}
 
 extern "C" int llnv_version(void) { return 1; }
 

@@ -79,6 +79,7 @@ template <typename T, int ROUNDING>
 __global__ void __launch_bounds__(256) dequant_matrix_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ sf,
                                                              const float* __restrict__ amax_ptr, int64_t rows, int64_t cols,
                                                              int64_t cols_padded, float denom, T* __restrict__ out, int64_t ldo) {
+  pdl_wait();
   const int64_t groups_per_row = cols >> 4;
   const int64_t total = rows * groups_per_row;
   const float amax = *amax_ptr;
@@ -97,6 +98,7 @@ __global__ void __launch_bounds__(256) dequant_matrix_kernel(const uint8_t* __re
 template <typename T, int ROUNDING>
 __global__ void __launch_bounds__(256) dequant_kv_kernel(BlockTable tab, int num_blocks, int64_t rows, float denom,
                                                          T* __restrict__ out) {
+  pdl_wait();
   const int64_t per_block = rows * 8;
   const int64_t total = per_block * num_blocks;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -123,9 +125,9 @@ int launch_matrix(const uint8_t* codes, const uint8_t* sf, const float* amax, in
   if (blocks > cap) blocks = cap;
   T* o = (T*)out;
   switch (rounding) {
-    case LLNV_DEQ_FUSED: dequant_matrix_kernel<T, LLNV_DEQ_FUSED><<<(unsigned)blocks, 256, 0, stream>>>(codes, sf, amax, rows, cols, cols_padded, denom, o, ldo); break;
-    case LLNV_DEQ_PYTORCH: dequant_matrix_kernel<T, LLNV_DEQ_PYTORCH><<<(unsigned)blocks, 256, 0, stream>>>(codes, sf, amax, rows, cols, cols_padded, denom, o, ldo); break;
-    default: dequant_matrix_kernel<T, LLNV_DEQ_TRITON><<<(unsigned)blocks, 256, 0, stream>>>(codes, sf, amax, rows, cols, cols_padded, denom, o, ldo); break;
+    case LLNV_DEQ_FUSED: launch_k(dequant_matrix_kernel<T, LLNV_DEQ_FUSED>, (unsigned)blocks, 256, 0, stream, codes, sf, amax, rows, cols, cols_padded, denom, o, ldo); break;
+    case LLNV_DEQ_PYTORCH: launch_k(dequant_matrix_kernel<T, LLNV_DEQ_PYTORCH>, (unsigned)blocks, 256, 0, stream, codes, sf, amax, rows, cols, cols_padded, denom, o, ldo); break;
+    default: launch_k(dequant_matrix_kernel<T, LLNV_DEQ_TRITON>, (unsigned)blocks, 256, 0, stream, codes, sf, amax, rows, cols, cols_padded, denom, o, ldo); break;
   }
   return launch_status("dequant_matrix_kernel");
 }
@@ -138,9 +140,9 @@ int launch_kv(const BlockTable& tab, int n, int64_t rows, float denom, int round
   const int64_t cap = (int64_t)sm_count() * 16;
   if (blocks > cap) blocks = cap;
   switch (rounding) {
-    case LLNV_DEQ_FUSED: dequant_kv_kernel<T, LLNV_DEQ_FUSED><<<(unsigned)blocks, 256, 0, stream>>>(tab, n, rows, denom, out); break;
-    case LLNV_DEQ_PYTORCH: dequant_kv_kernel<T, LLNV_DEQ_PYTORCH><<<(unsigned)blocks, 256, 0, stream>>>(tab, n, rows, denom, out); break;
-    default: dequant_kv_kernel<T, LLNV_DEQ_TRITON><<<(unsigned)blocks, 256, 0, stream>>>(tab, n, rows, denom, out); break;
+    case LLNV_DEQ_FUSED: launch_k(dequant_kv_kernel<T, LLNV_DEQ_FUSED>, (unsigned)blocks, 256, 0, stream, tab, n, rows, denom, out); break;
+    case LLNV_DEQ_PYTORCH: launch_k(dequant_kv_kernel<T, LLNV_DEQ_PYTORCH>, (unsigned)blocks, 256, 0, stream, tab, n, rows, denom, out); break;
+    default: launch_k(dequant_kv_kernel<T, LLNV_DEQ_TRITON>, (unsigned)blocks, 256, 0, stream, tab, n, rows, denom, out); break;
   }
   return launch_status("dequant_kv_kernel");
 }

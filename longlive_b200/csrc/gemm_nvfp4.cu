@@ -69,6 +69,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmR,
                   const __grid_constant__ GroupMaps gmaps, const GemmParams p) {
+  pdl_wait();
   using C = Cfg<BN>;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::kBarOff);
@@ -396,7 +397,7 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tm
   }
   const int64_t tiles = ((p.M + BM - 1) / BM) * (p.N / BN);
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  gemm_nvfp4_kernel<BN, EPI><<<grid, kThreads, Cfg<BN>::kSmemBytes, stream>>>(tmA, tmB, tmD, tmR, gmaps, p);
+  launch_k(gemm_nvfp4_kernel<BN, EPI>, grid, kThreads, Cfg<BN>::kSmemBytes, stream, tmA, tmB, tmD, tmR, gmaps, p);
   return launch_status("gemm_nvfp4_kernel");
 }
 

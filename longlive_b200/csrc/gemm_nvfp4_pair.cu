@@ -47,6 +47,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                        const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
                        const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmR, const GemmParams p) {
+  pdl_wait();
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kBarOff);     // used in the leader only
   uint64_t* empty_bar = full_bar + kStages;
@@ -283,7 +284,7 @@ int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMa
   const int64_t tiles = ((p.M + 255) / 256) * (p.N / 256);
   int64_t pairs = sm_count() / 2;
   if (tiles < pairs) pairs = tiles;
-  gemm_nvfp4_pair_kernel<EPI><<<(unsigned)(2 * pairs), kThreads, kSmemBytes, stream>>>(tmA, tmB, tmSFA, tmSFB, tmD, tmR, p);
+  launch_k(gemm_nvfp4_pair_kernel<EPI>, (unsigned)(2 * pairs), kThreads, kSmemBytes, stream, tmA, tmB, tmSFA, tmSFB, tmD, tmR, p);
   return launch_status("gemm_nvfp4_pair_kernel");
 }
 

@@ -35,6 +35,7 @@ struct PeerPtrs {
 
 __global__ void __launch_bounds__(32) peer_barrier_kernel(PeerPtrs signals, int rank, int world, unsigned int* epoch,
                                                           unsigned int* status) {
+  pdl_wait();
   __shared__ unsigned int e_sh;
   if (threadIdx.x == 0) e_sh = *epoch + 1u;
   __syncwarp();
@@ -71,6 +72,7 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(PeerPtrs signals, int 
 // values a slower rank has not read yet (it cannot be two reductions ahead: each one is a barrier).
 __global__ void __launch_bounds__(32) peer_allreduce_max_kernel(float* __restrict__ vals, int n, PeerPtrs slots, PeerPtrs signals,
                                                                 int rank, int world, unsigned int* epoch, unsigned int* status) {
+  pdl_wait();
   __shared__ unsigned int e_sh;
   if (threadIdx.x == 0) e_sh = *epoch + 1u;
   __syncwarp();
@@ -117,6 +119,7 @@ __global__ void __launch_bounds__(32) peer_allreduce_max_kernel(float* __restric
 // dst[r][i][0:row_bytes] = src[r * src_shard_bytes + i * src_pitch : ... + row_bytes], 16-byte vectors.
 __global__ void __launch_bounds__(256) scatter_2d_kernel(const uint8_t* __restrict__ src, int64_t src_shard_bytes, int64_t src_pitch,
                                                          PeerPtrs dst, int64_t dst_pitch, int64_t rows, int vec_per_row) {
+  pdl_wait();
   const int r = blockIdx.y;
   const uint8_t* s = src + (int64_t)r * src_shard_bytes;
   uint8_t* d = reinterpret_cast<uint8_t*>(dst.p[r]);
@@ -143,7 +146,7 @@ extern "C" int llnv_peer_barrier(void* const* signal_ptrs, int rank, int world, 
     LLNV_REQUIRE(signal_ptrs[r] != nullptr && ((uintptr_t)signal_ptrs[r] & 3) == 0, "llnv_peer_barrier: bad signal pointer of rank %d", r);
     sp.p[r] = signal_ptrs[r];
   }
-  peer_barrier_kernel<<<1, 32, 0, stream>>>(sp, rank, world, (unsigned int*)epoch, device_status_word());
+  launch_k(peer_barrier_kernel, 1, 32, 0, stream, sp, rank, world, (unsigned int*)epoch, device_status_word());
   return launch_status("peer_barrier_kernel");
 }
 
@@ -160,7 +163,7 @@ extern "C" int llnv_peer_allreduce_max(float* vals, int n, void* const* slot_ptr
     sl.p[r] = slot_ptrs[r];
     sg.p[r] = signal_ptrs[r];
   }
-  peer_allreduce_max_kernel<<<1, 32, 0, stream>>>(vals, n, sl, sg, rank, world, (unsigned int*)epoch, device_status_word());
+  launch_k(peer_allreduce_max_kernel, 1, 32, 0, stream, vals, n, sl, sg, rank, world, (unsigned int*)epoch, device_status_word());
   return launch_status("peer_allreduce_max_kernel");
 }
 
@@ -183,7 +186,7 @@ extern "C" int llnv_scatter_2d(const void* src, int64_t src_shard_bytes, int64_t
   int64_t blocks = (total + 255) / 256;
   const int64_t cap = (int64_t)sm_count() * 8 / shards + 1;
   if (blocks > cap) blocks = cap;
-  scatter_2d_kernel<<<dim3((unsigned)blocks, (unsigned)shards), 256, 0, stream>>>((const uint8_t*)src, src_shard_bytes, src_pitch, dp,
+  launch_k(scatter_2d_kernel, dim3((unsigned)blocks, (unsigned)shards), 256, 0, stream, (const uint8_t*)src, src_shard_bytes, src_pitch, dp,
                                                                                  dst_pitch, rows, vec);
   return launch_status("scatter_2d_kernel");
 }

@@ -38,6 +38,7 @@ namespace {
 // ---- tensor amax ----------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) amax_bf16_kernel(const uint16_t* __restrict__ x, int64_t M, int64_t K,
                                                         int64_t ldx, float* __restrict__ amax) {
+  pdl_wait();
   const int64_t vec_per_row = K >> 3;
   const int64_t total = M * vec_per_row;
   uint32_t m = 0;   // two 15-bit magnitudes, compared as unsigned 16-bit lanes
@@ -352,6 +353,7 @@ __global__ void __launch_bounds__(256) quantize_nvfp4_kernel(const uint16_t* x, 
                                                              int64_t ldx, const float* amax_ptr,
                                                              uint8_t* codes, uint8_t* sf,
                                                              const Prologue pr, uint16_t* __restrict__ y_out, int64_t ldy) {
+  pdl_wait();
   if (blockIdx.z == 1) {          // second tensor of a two-tensor launch
     x = pr.x2;
     amax_ptr = pr.amax2;
@@ -441,6 +443,7 @@ template <int MODE, int WPR>
 __global__ void __launch_bounds__(256) ln_stats_amax_kernel(const uint16_t* __restrict__ x, int64_t M, int64_t C, int64_t ldx,
                                                             float eps, Prologue pr, float* __restrict__ row_stats,
                                                             float* __restrict__ amax) {
+  pdl_wait();
   constexpr int kVec = 16 / WPR;              // 16-byte vectors per lane: C <= 4096
   constexpr int kRows = 8 / WPR;              // rows per CTA
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -582,6 +585,7 @@ __global__ void __launch_bounds__(256) ln_stats_amax_kernel(const uint16_t* __re
 // IEEE division (used by the test-suite to pin the range on which the fast path may rely on it).
 template <int D>
 __global__ void div_const_selftest_kernel(uint32_t first, uint64_t count, unsigned long long* mismatches) {
+  pdl_wait();
   unsigned long long bad = 0;
   for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (uint64_t)gridDim.x * blockDim.x) {
     const float x = __uint_as_float(first + (uint32_t)i);
@@ -602,11 +606,11 @@ int launch_quantize(int rule, dim3 grid, cudaStream_t stream, const uint16_t* x,
     grid.x = (unsigned)((K + 63) / 64);
   }
   switch (rule) {
-    case LLNV_RULE_STATIC_6: quantize_nvfp4_kernel<LLNV_RULE_STATIC_6, MODE><<<grid, threads, 0, stream>>>(x, M, K, ldx, amax, codes, sf, pr, y_out, ldy); break;
-    case LLNV_RULE_STATIC_4: quantize_nvfp4_kernel<LLNV_RULE_STATIC_4, MODE><<<grid, threads, 0, stream>>>(x, M, K, ldx, amax, codes, sf, pr, y_out, ldy); break;
-    case LLNV_RULE_MAE: quantize_nvfp4_kernel<LLNV_RULE_MAE, MODE><<<grid, threads, 0, stream>>>(x, M, K, ldx, amax, codes, sf, pr, y_out, ldy); break;
-    case LLNV_RULE_MSE: quantize_nvfp4_kernel<LLNV_RULE_MSE, MODE><<<grid, threads, 0, stream>>>(x, M, K, ldx, amax, codes, sf, pr, y_out, ldy); break;
-    default: quantize_nvfp4_kernel<LLNV_RULE_ABS_MAX, MODE><<<grid, threads, 0, stream>>>(x, M, K, ldx, amax, codes, sf, pr, y_out, ldy); break;
+    case LLNV_RULE_STATIC_6: launch_k(quantize_nvfp4_kernel<LLNV_RULE_STATIC_6, MODE>, grid, threads, 0, stream, x, M, K, ldx, amax, codes, sf, pr, y_out, ldy); break;
+    case LLNV_RULE_STATIC_4: launch_k(quantize_nvfp4_kernel<LLNV_RULE_STATIC_4, MODE>, grid, threads, 0, stream, x, M, K, ldx, amax, codes, sf, pr, y_out, ldy); break;
+    case LLNV_RULE_MAE: launch_k(quantize_nvfp4_kernel<LLNV_RULE_MAE, MODE>, grid, threads, 0, stream, x, M, K, ldx, amax, codes, sf, pr, y_out, ldy); break;
+    case LLNV_RULE_MSE: launch_k(quantize_nvfp4_kernel<LLNV_RULE_MSE, MODE>, grid, threads, 0, stream, x, M, K, ldx, amax, codes, sf, pr, y_out, ldy); break;
+    default: launch_k(quantize_nvfp4_kernel<LLNV_RULE_ABS_MAX, MODE>, grid, threads, 0, stream, x, M, K, ldx, amax, codes, sf, pr, y_out, ldy); break;
   }
   return launch_status("quantize_nvfp4_kernel");
 }
@@ -643,10 +647,10 @@ int ln_quantize_impl(int mode, const void* x, int64_t M, int64_t C, int64_t ldx,
     // warps per row: four when that leaves every lane at least one 16-byte vector (C a multiple of 1024), else one
     const bool split = C % 1024 == 0;
     const unsigned sblocks = split ? (unsigned)((M + 1) / 2) : (unsigned)((M + 7) / 8);
-    if (mode == kAdaLN && split) ln_stats_amax_kernel<kAdaLN, 4><<<sblocks, 256, 0, stream>>>((const uint16_t*)x, M, C, ldx, eps, pr, row_stats, amax);
-    else if (mode == kAdaLN) ln_stats_amax_kernel<kAdaLN, 1><<<sblocks, 256, 0, stream>>>((const uint16_t*)x, M, C, ldx, eps, pr, row_stats, amax);
-    else if (split) ln_stats_amax_kernel<kAffineLN, 4><<<sblocks, 256, 0, stream>>>((const uint16_t*)x, M, C, ldx, eps, pr, row_stats, amax);
-    else ln_stats_amax_kernel<kAffineLN, 1><<<sblocks, 256, 0, stream>>>((const uint16_t*)x, M, C, ldx, eps, pr, row_stats, amax);
+    if (mode == kAdaLN && split) launch_k(ln_stats_amax_kernel<kAdaLN, 4>, sblocks, 256, 0, stream, (const uint16_t*)x, M, C, ldx, eps, pr, row_stats, amax);
+    else if (mode == kAdaLN) launch_k(ln_stats_amax_kernel<kAdaLN, 1>, sblocks, 256, 0, stream, (const uint16_t*)x, M, C, ldx, eps, pr, row_stats, amax);
+    else if (split) launch_k(ln_stats_amax_kernel<kAffineLN, 4>, sblocks, 256, 0, stream, (const uint16_t*)x, M, C, ldx, eps, pr, row_stats, amax);
+    else launch_k(ln_stats_amax_kernel<kAffineLN, 1>, sblocks, 256, 0, stream, (const uint16_t*)x, M, C, ldx, eps, pr, row_stats, amax);
     int rc = launch_status("ln_stats_amax_kernel");
     if (rc != LLNV_OK) return rc;
   }
@@ -675,7 +679,7 @@ extern "C" int llnv_amax_bf16(const void* x, int64_t M, int64_t K, int64_t ldx, 
   int64_t blocks = (total + 256 * 4 - 1) / (256 * 4);
   const int64_t cap = (int64_t)sm_count() * 8;
   if (blocks > cap) blocks = cap;
-  amax_bf16_kernel<<<(unsigned)blocks, 256, 0, stream>>>((const uint16_t*)x, M, K, ldx, amax);
+  launch_k(amax_bf16_kernel, (unsigned)blocks, 256, 0, stream, (const uint16_t*)x, M, K, ldx, amax);
   return launch_status("amax_bf16_kernel");
 }
 
@@ -782,7 +786,7 @@ extern "C" int llnv_selftest_div_const(int divisor, uint32_t first_bits, uint64_
   LLNV_REQUIRE(mismatches && (divisor == 6 || divisor == 1536), "llnv_selftest_div_const: divisor must be 6 or 1536");
   if (count == 0) return LLNV_OK;
   const unsigned blocks = (unsigned)sm_count() * 8;
-  if (divisor == 6) div_const_selftest_kernel<6><<<blocks, 256, 0, stream>>>(first_bits, count, mismatches);
-  else div_const_selftest_kernel<1536><<<blocks, 256, 0, stream>>>(first_bits, count, mismatches);
+  if (divisor == 6) launch_k(div_const_selftest_kernel<6>, blocks, 256, 0, stream, first_bits, count, mismatches);
+  else launch_k(div_const_selftest_kernel<1536>, blocks, 256, 0, stream, first_bits, count, mismatches);
   return launch_status("div_const_selftest_kernel");
 }

@@ -46,6 +46,7 @@ template <int WPR>
 __global__ void __launch_bounds__(256) rmsnorm_rope_kernel(const __grid_constant__ RopeJobs jobs, int64_t S, int64_t C, float eps,
                                                            const float* __restrict__ cosv, const float* __restrict__ sinv,
                                                            int shard_vecs) {
+  pdl_wait();
   const RopeJob& jb = jobs.job[blockIdx.y];
   const uint16_t* __restrict__ x = jb.x;
   const uint16_t* __restrict__ weight = jb.weight;
@@ -227,11 +228,11 @@ int rope_launch_jobs(const RopeJobs& jobs, int njobs, int64_t S, int64_t C, floa
   const int sv = shards > 1 ? (int)(C / shards / 8) : 0;
   // warps per row: as many as leave every warp a whole number of heads and every lane some work
   if (C % 512 == 0 && C >= 2048)
-    rmsnorm_rope_kernel<4><<<dim3((unsigned)((S + 1) / 2), (unsigned)njobs), 256, 0, stream>>>(jobs, S, C, eps, cos, sin, sv);
+    launch_k(rmsnorm_rope_kernel<4>, dim3((unsigned)((S + 1) / 2), (unsigned)njobs), 256, 0, stream, jobs, S, C, eps, cos, sin, sv);
   else if (C % 256 == 0 && C >= 1024)
-    rmsnorm_rope_kernel<2><<<dim3((unsigned)((S + 3) / 4), (unsigned)njobs), 256, 0, stream>>>(jobs, S, C, eps, cos, sin, sv);
+    launch_k(rmsnorm_rope_kernel<2>, dim3((unsigned)((S + 3) / 4), (unsigned)njobs), 256, 0, stream, jobs, S, C, eps, cos, sin, sv);
   else
-    rmsnorm_rope_kernel<1><<<dim3((unsigned)((S + 7) / 8), (unsigned)njobs), 256, 0, stream>>>(jobs, S, C, eps, cos, sin, sv);
+    launch_k(rmsnorm_rope_kernel<1>, dim3((unsigned)((S + 7) / 8), (unsigned)njobs), 256, 0, stream, jobs, S, C, eps, cos, sin, sv);
   return launch_status("rmsnorm_rope_kernel");
 }
 

@@ -82,6 +82,7 @@ struct Elem<false> {
 template <bool BF16, bool VEC>
 __global__ void __launch_bounds__(256) unipc_step_kernel(const void* v_, const void* x_, const void* m0_, const void* m1_, const void* last_,
                                                          void* x0_, void* xs_, void* next_, int64_t n, const __grid_constant__ Coef c) {
+  pdl_wait();
   using E = Elem<BF16>;
   using T = typename E::T;
   const T* v = (const T*)v_;
@@ -180,7 +181,7 @@ extern "C" int llnv_unipc_step(const void* model_output, const void* sample, con
   if (blocks > cap) blocks = cap;
   const dim3 grid((unsigned)blocks);
 #define LLNV_UNIPC_LAUNCH(BF, VEC) \
-  unipc_step_kernel<BF, VEC><<<grid, 256, 0, stream>>>(model_output, sample, x0_prev, x0_older, last_sample, x0_out, sample_out, next_out, n, c)
+  launch_k(unipc_step_kernel<BF, VEC>, grid, 256, 0, stream, model_output, sample, x0_prev, x0_older, last_sample, x0_out, sample_out, next_out, n, c)
   if (dtype == 0) {
     if (vec) LLNV_UNIPC_LAUNCH(true, true);
     else LLNV_UNIPC_LAUNCH(true, false);
