@@ -334,10 +334,10 @@ int llnv_unipc_step(const void* model_output, const void* sample, const void* x0
                     const llnv_unipc_coef* coef, llnv_stream_t stream);
 
 /* Test / benchmark hooks (no counterpart in the reference). */
-/* Kernels are launched with programmatic stream serialization (the next kernel of a stream is
- * scheduled while the previous one drains and waits for it on the device); 0 turns that off, e.g.
- * to time its effect.  Returns the previous setting.  The environment variable LLNV_PDL=0 does the
- * same at load time.  Results do not depend on it. */
+/* 1: launch kernels with programmatic stream serialization (the next kernel of a stream is
+ * scheduled while the previous one drains and waits for it on the device); 0 (default): plain
+ * launches.  Returns the previous setting.  The environment variable LLNV_PDL=1 switches it on at
+ * load time.  Results do not depend on it; on a B200 it measured no gain for graph-replayed chunks. */
 int llnv_set_pdl(int on);
 int llnv_gemm_nvfp4_force_tile_n(int bn);       /* 0 = automatic, 128 or 256 */
 int llnv_gemm_nvfp4_debug(int flags);           /* timing experiments; results become wrong when non-zero */

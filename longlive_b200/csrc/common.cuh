@@ -45,15 +45,16 @@ unsigned int* device_status_word();   // lazily allocated per device (never free
 int sm_count();
 
 // ---- programmatic dependent launch ---------------------------------------------------------
-// Every kernel of the library is launched through launch_k and starts with pdl_wait().  With the
-// "programmatic stream serialization" attribute the grid may be scheduled while the preceding
-// kernel of the stream is still draining (its launch latency, block scheduling and everything a
-// CTA does before pdl_wait() overlap that kernel's tail); pdl_wait() then blocks until the
-// preceding grid has completed and its writes are visible, so the memory semantics are those of an
-// ordinary in-stream launch.  A chunk of the DiT is thousands of short kernels: this takes a
-// microsecond or two off every boundary, in eager mode and inside captured graphs alike.
-// No kernel triggers its dependents early: a dependent grid starts only when every CTA of its
-// predecessor has exited, so a waiting grid never holds SM resources a running grid needs.
+// Every kernel of the library is launched through launch_k and starts with pdl_wait().  When the
+// "programmatic stream serialization" attribute is switched on (llnv_set_pdl(1) or LLNV_PDL=1) a
+// grid may be scheduled while the preceding kernel of the stream is still draining; pdl_wait()
+// then blocks until that grid has completed and its writes are visible, so the memory semantics
+// are those of an ordinary in-stream launch.  No kernel triggers its dependents early: a dependent
+// grid starts only when every CTA of its predecessor has exited, so a waiting grid never holds SM
+// resources a running grid needs.  It is OFF by default: on a B200 the 30-layer chunk replayed as
+// CUDA graphs measured 145.5 ms with it and 145.6 ms without -- kernel boundaries inside a graph
+// are already back to back -- so the default stays the plain launch.  Without the attribute
+// pdl_wait() returns at once.
 bool pdl_enabled();                    // llnv_set_pdl / environment LLNV_PDL=0 turn the attribute off
 
 template <typename... KArgs, typename... Args>

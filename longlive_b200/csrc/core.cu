@@ -52,13 +52,13 @@ int sm_count() {
 }
 
 namespace {
-int g_pdl = -1;                        // -1: not decided yet (environment LLNV_PDL, default on)
+int g_pdl = -1;                        // -1: not decided yet (environment LLNV_PDL=1 turns it on; default off)
 }
 
 bool pdl_enabled() {
   if (g_pdl < 0) {
     const char* e = getenv("LLNV_PDL");
-    g_pdl = (e && e[0] == '0') ? 0 : 1;
+    g_pdl = (e && e[0] == '1') ? 1 : 0;
   }
   return g_pdl != 0;
 }
