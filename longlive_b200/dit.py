@@ -49,6 +49,7 @@ class DiTConfig:
     frames_per_chunk: int = 3
     window_frames: int = 15          # sink + local window, current chunk included
     sink_frames: int = 3
+    global_sink_frames: int = 0      # frames anchored for the whole video (the reference's global_sink_size)
     in_channels: int = 48
     eps: float = 1e-6
 
@@ -154,18 +155,55 @@ class KVCache:
         self.order = list(range(cfg.max_blocks))
         self.filled = 0                       # number of valid blocks, current chunk included
         self.version = 0                      # bumped whenever the set of past blocks changes
+        self.pinned: int | None = None        # slot of the chunk pinned as shot sink at the last scene cut
         self.cfg = cfg
+        if cfg.sink_frames % cfg.frames_per_chunk or cfg.global_sink_frames % cfg.frames_per_chunk:
+            raise ValueError("sink_frames and global_sink_frames must be whole chunks (the cache is a table of chunk blocks)")
+
+    def protected_blocks(self) -> int:
+        """Leading blocks a roll must keep (``effective_sink`` of wan_5b/modules/causal_model.py:498-534):
+        the global sink, plus the pinned chunk once it sits right behind it; a pinned chunk further
+        back floats (the roll moves it forward with the others) and the original sink is no longer
+        kept; without a pinned chunk the larger of global sink and sink."""
+        cfg = self.cfg
+        g = cfg.global_sink_frames // cfg.frames_per_chunk
+        if self.pinned is None:
+            return max(g, cfg.sink_frames // cfg.frames_per_chunk)
+        return g + 1 if self.order.index(self.pinned) == g else g
 
     def begin_chunk(self) -> None:
-        """Make room for a new chunk: grow until full, then evict the oldest non-sink block."""
+        """Make room for a new chunk: grow until full, then evict the oldest block behind the
+        protected prefix (causal_model.py:596-625, 1396-1446: with a table of blocks the roll is a
+        permutation, and the pinned chunk's position follows it by construction)."""
         cfg = self.cfg
         self.version += 1
         if self.filled < cfg.max_blocks:
             self.filled += 1
             return
-        sink_blocks = cfg.sink_frames // cfg.frames_per_chunk
-        victim = self.order.pop(sink_blocks)
+        victim = self.order.pop(self.protected_blocks())
         self.order.append(victim)
+
+    def pin_current(self) -> None:
+        """Scene cut: the chunk just cached becomes the shot sink; it replaces the original sink on the
+        following rolls (pipeline/causal_diffusion_inference.py:659-664, 1026-1042).  A whole chunk is
+        pinned: the reference pins min(sink_size, chunk) frames and its configurations use sink_size >= chunk."""
+        if self.cfg.sink_frames < self.cfg.frames_per_chunk:
+            raise NotImplementedError("pinning less than one chunk")
+        self.pinned = self.current_slot()
+
+    def reset_keep_global(self) -> None:
+        """Scene cut with clean re-cache: drop every block but the global sink; the current chunk
+        becomes the first block behind it and the pin is cleared
+        (``_zero_kv_data``, pipeline/causal_diffusion_inference.py:1044-1052)."""
+        g = self.cfg.global_sink_frames // self.cfg.frames_per_chunk
+        cur = self.current_slot()
+        keep = self.order[:g]
+        if cur in keep:
+            raise RuntimeError("the current chunk lies inside the global sink: nothing to reset")
+        self.order = keep + [cur] + [s for s in self.order if s != cur and s not in keep]
+        self.filled = g + 1
+        self.pinned = None
+        self.version += 1
 
     def past_slots(self) -> list[int]:
         return self.order[: self.filled - 1]
@@ -543,10 +581,13 @@ class CausalDiT:
         return torch.nn.functional.linear(y, self.head_w, self.head_b)
 
     def run_chunk(self, latent_tokens: torch.Tensor, ctx: torch.Tensor, chunk_index: int,
-                  sampling_steps: int = 4, timestep_shift: float = 5.0) -> torch.Tensor:
+                  sampling_steps: int = 4, timestep_shift: float = 5.0, scene_cut: bool = False,
+                  clean_recache: bool = True) -> torch.Tensor:
         """One AR chunk: ``sampling_steps`` denoising forwards, each followed by a UniPC scheduler step,
         then one clean re-cache forward at timestep 0 (pipeline/causal_diffusion_inference.py:566-647;
-        4 steps at shift 5 are the timesteps 999, 937, 833, 624 of configs/inference.yaml)."""
+        4 steps at shift 5 are the timesteps 999, 937, 833, 624 of configs/inference.yaml).  At a
+        ``scene_cut`` the re-cache forward sees only the global sink (``clean_recache``, :621-629) and
+        the chunk is pinned as the new shot sink afterwards (:659-664)."""
         cfg = self.cfg
         self.cache.begin_chunk()
         start_frame = chunk_index * cfg.frames_per_chunk
@@ -560,5 +601,9 @@ class CausalDiT:
             tt = torch.full((F,), float(t), device=self.device)
             flow = self.forward(x_t, tt, ctx, start_frame)
             x_t = sched.step(flow, t, x_t, return_dict=False)[0]
+        if scene_cut and clean_recache:
+            self.cache.reset_keep_global()
         self.forward(x_t, torch.zeros(F, device=self.device), ctx, start_frame)
+        if scene_cut:
+            self.cache.pin_current()
         return x_t

@@ -118,6 +118,41 @@ def test_graph_replay_equals_eager():
                 assert torch.equal(te.scale_factors.view(torch.uint8), tg.scale_factors.view(torch.uint8))
 
 
+def test_scene_cut_clean_recache_and_pinned_sink():
+    """A scene cut with clean re-cache: the re-cache forward sees only the chunk itself, so the cache
+    block it writes equals the block a fresh model writes for the same clean latents at the same
+    position; afterwards the chunk is pinned and replaces the sink, in eager and graph mode alike."""
+    cfg = dit.DiTConfig(**{**CFG, "layers": 2})
+    eager = dit.CausalDiT(cfg, seed=3)
+    graphed = dit.CausalDiT(cfg, seed=3, use_graphs=True)
+    g = torch.Generator().manual_seed(9)
+    raw = torch.randn(cfg.text_len, cfg.text_dim, generator=g).bfloat16().cuda()
+    ctx_e, ctx_g = eager.encode_text(raw), graphed.encode_text(raw)
+    cut = cfg.max_blocks + 1
+    for chunk in range(cut + cfg.max_blocks + 3):
+        lat = torch.randn(cfg.chunk_tokens, cfg.patch_dim, generator=g).bfloat16().cuda()
+        a = eager.run_chunk(lat, ctx_e, chunk, scene_cut=chunk == cut)
+        b = graphed.run_chunk(lat, ctx_g, chunk, scene_cut=chunk == cut)
+        assert torch.equal(a, b), chunk
+        assert eager.cache.order == graphed.cache.order and eager.cache.filled == graphed.cache.filled
+        if chunk == cut:
+            assert eager.cache.filled == 1 and eager.cache.pinned == eager.cache.current_slot()
+            pinned, clean = eager.cache.pinned, a
+            # a fresh model that caches the same clean latents at the same frame position writes the same block
+            fresh = dit.CausalDiT(cfg, seed=3)
+            fresh.cache.begin_chunk()
+            fresh.forward(clean, torch.zeros(cfg.frames_per_chunk, device="cuda"), fresh.encode_text(raw), chunk * cfg.frames_per_chunk)
+            for layer in range(cfg.layers):
+                for side in ("k", "v"):
+                    te, tf = getattr(eager.cache, side)[layer][pinned], getattr(fresh.cache, side)[layer][fresh.cache.current_slot()]
+                    assert torch.equal(te.values, tf.values) and torch.equal(te.amax, tf.amax)
+    assert eager.cache.pinned == pinned and eager.cache.order[0] == pinned          # the pinned chunk became the sink
+    for layer in range(cfg.layers):
+        for slot in range(cfg.max_blocks):
+            te, tg = eager.cache.k[layer][slot], graphed.cache.k[layer][slot]
+            assert torch.equal(te.values, tg.values) and torch.equal(te.amax, tg.amax)
+
+
 def test_checkpoint_round_trip(tmp_path):
     """A model saved in the reference's NVFP4 generator format and loaded into a model with other
     weights reproduces the first model's forward bit for bit; bf16 master weights are quantized on load."""
