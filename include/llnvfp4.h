@@ -298,6 +298,19 @@ int llnv_gemm_nvfp4_grouped(const void* a_codes, const void* a_sf, const float* 
                             const llnv_epilogue_t* epilogue, void* const* d, const int64_t* ldd, float* const* out_amax,
                             llnv_stream_t stream);
 
+/* ---- bf16 Linear of the unquantized edge layers ------------------------------------------------ */
+
+/* d[M, N] = act(a[M, K] . w[N, K]^T + bias), bf16 in and out, fp32 accumulation on tcgen05
+ * (kind::f16): torch.nn.functional.linear for the layers the reference's NVFP4 filter leaves in
+ * bf16 -- patch embedding (the Conv3d of wan_5b/modules/causal_model.py:1052-1056 applied to
+ * patchified tokens), text_embedding, time_embedding, time_projection (:1057-1066) and head.head
+ * (wan_5b/modules/model.py Head, called at causal_model.py:1648-1651).  bias (N values) may be NULL.
+ * act: 0 none, 1 GELU(tanh), 2 SiLU, applied to the bf16-rounded sum as the reference's separate
+ * activation module does.  lda / ldw / ldd: row strides in elements.  K, N and the strides must be
+ * multiples of 8; a, w, d 16-byte aligned. */
+int llnv_linear_bf16(const void* a, int64_t lda, const void* w, int64_t ldw, const void* bias, int act, int64_t M, int64_t N,
+                     int64_t K, void* d, int64_t ldd, llnv_stream_t stream);
+
 /* ---- flow-matching UniPC scheduler step ------------------------------------------------------ */
 
 /* Scalars of one scheduler step, computed on the host in fp32 exactly as the reference computes

@@ -1,0 +1,227 @@
+// bf16 Linear for the layers the reference leaves unquantized: D[M, N] = act(A[M, K] . W[N, K]^T + bias).
+//
+// The NVFP4 filter of the reference keeps the edges of the DiT in bf16 (patch embedding, time and
+// text embeddings, time projection, head: wan_5b/modules/causal_model.py:1052-1071, 1535-1573,
+// 1648-1651; utils/quant.py filters them out of quantize_model).  They are small GEMMs with one
+// long and one short dimension (2640 x 3072 x 192 and 2640 x 192 x 3072 per forward), so this is a
+// plain tile kernel, not a persistent one: one CTA per 128 x BN output tile, a TMA ring of
+// 128-byte-swizzled K-major tiles of A and W (64 channels per stage), tcgen05.mma kind::f16 with
+// the fp32 accumulator in TMEM, and an epilogue that adds the bias in fp32, rounds to bf16 (the
+// rounding point of the reference's fused-bias GEMM), applies the activation on the rounded value
+// (the reference's activation is a separate bf16 op) and stores 64 contiguous bytes per thread.
+// Rows beyond M and channels beyond K are zero-filled by TMA; stores are masked.
+//
+// Warps: 0 = TMA producer, 1 = TMEM allocation + MMA issue, 2..5 = epilogue (TMEM lane quarter
+// warp % 4).  Every wait is bounded (mbar_wait): on a timeout the kernel records where it gave up
+// in the status word, the other roles drain, TMEM is freed and the kernel returns.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace llnv {
+namespace {
+
+using namespace sm100;
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  const float u = k0 * (x + k1 * x * x * x);
+  return __fdividef(x, 1.f + __expf(-2.f * u));
+}
+
+constexpr int kBM = 128, kBK = 64, kStagesLin = 4, kThreadsLin = 192;
+constexpr int kATile = kBM * kBK * 2;                       // 16 KB
+
+struct LinParams {
+  int64_t M, N, K;
+  const uint16_t* bias;
+  uint16_t* d;
+  int64_t ldd;
+  int act;                                                  // 0 none, 1 GELU(tanh), 2 SiLU
+  unsigned int* status;
+};
+
+template <int BN>
+struct LinCfg {
+  static constexpr int kBTile = BN * kBK * 2;
+  static constexpr int kStageBytes = kATile + kBTile;
+  static constexpr int kBarOff = kStagesLin * kStageBytes;
+  static constexpr int kSmemBytes = kBarOff + 256 + 1024;   // barriers + slack for the 1024-byte alignment
+};
+
+__device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.f + __expf(-x)); }
+
+template <int BN>
+__global__ void __launch_bounds__(kThreadsLin, 1)
+linear_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const LinParams p) {
+  pdl_wait();
+  using Cfg = LinCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + Cfg::kBarOff);
+  uint64_t* empty = full + kStagesLin;
+  uint64_t* acc_full = empty + kStagesLin;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN;
+  const int m0 = blockIdx.y * kBM;
+  const int nk = (int)((p.K + kBK - 1) / kBK);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStagesLin; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0u;
+    fence_barrier_init();
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      for (int ks = 0; ks < nk; ++ks) {
+        const int s = ks % kStagesLin;
+        const uint32_t ph = (uint32_t)((ks / kStagesLin) & 1);
+        if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, p.status, 1100u)) break;
+        mbar_arrive_expect_tx(&full[s], Cfg::kStageBytes);
+        tma_load_2d(smem + s * Cfg::kStageBytes, &tmA, ks * kBK, m0, &full[s]);
+        tma_load_2d(smem + s * Cfg::kStageBytes + kATile, &tmB, ks * kBK, n0, &full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc_bf16(kBM, BN, 0, 0);
+      bool ok = true;
+      for (int ks = 0; ks < nk && ok; ++ks) {
+        const int s = ks % kStagesLin;
+        const uint32_t ph = (uint32_t)((ks / kStagesLin) & 1);
+        ok = mbar_wait(&full[s], ph, abort_flag, p.status, 1101u);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smem + s * Cfg::kStageBytes);
+        const uint32_t b_addr = a_addr + kATile;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)          // 16 channels per MMA = 32 bytes along the swizzled row
+          mma_f16_ss(tmem_base, make_kmajor_sw128_desc(a_addr + j * 32), make_kmajor_sw128_desc(b_addr + j * 32), idesc,
+                     (uint32_t)((ks | j) != 0));
+        tc_commit(&empty[s]);
+      }
+      if (ok) tc_commit(acc_full);
+    }
+  } else {
+    const int q = warp & 3;                                  // TMEM lanes 32 q .. 32 q + 31
+    const int64_t row = (int64_t)m0 + q * 32 + lane;
+    if (mbar_wait(acc_full, 0u, abort_flag, p.status, 1102u)) {
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+        tmem_ld_wait();
+        const int64_t col = (int64_t)n0 + c * 32;
+        uint32_t out[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float y0 = __uint_as_float(r[e]), y1 = __uint_as_float(r[e + 1]);
+          if (p.bias) {
+            if (col + e < p.N) y0 += __uint_as_float((uint32_t)__ldg(p.bias + col + e) << 16);
+            if (col + e + 1 < p.N) y1 += __uint_as_float((uint32_t)__ldg(p.bias + col + e + 1) << 16);
+          }
+          if (p.act) {
+            round_bf16x2(y0, y1);
+            if (p.act == 1) {
+              y0 = gelu_tanh(y0);
+              y1 = gelu_tanh(y1);
+            } else {
+              y0 = silu(y0);
+              y1 = silu(y1);
+            }
+          }
+          out[e >> 1] = pack_bf16x2(y0, y1);
+        }
+        if (row < p.M) {
+          uint16_t* dst = p.d + row * p.ldd + col;
+          if (col + 32 <= p.N) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) reinterpret_cast<uint4*>(dst)[v] = make_uint4(out[4 * v], out[4 * v + 1], out[4 * v + 2], out[4 * v + 3]);
+          } else {
+            for (int e = 0; e < 32 && col + e < p.N; ++e) dst[e] = (uint16_t)(out[e >> 1] >> ((e & 1) * 16));
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);         // let copies in flight land before the CTA exits
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, BN);
+  }
+}
+
+template <int BN>
+int launch_linear(const CUtensorMap& tmA, const CUtensorMap& tmB, const LinParams& p, cudaStream_t stream) {
+  using Cfg = LinCfg<BN>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  LLNV_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    LLNV_CUDA(cudaFuncSetAttribute(linear_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    attr_set[dev] = true;
+  }
+  const dim3 grid((unsigned)((p.N + BN - 1) / BN), (unsigned)((p.M + kBM - 1) / kBM));
+  launch_k(linear_bf16_kernel<BN>, grid, kThreadsLin, Cfg::kSmemBytes, stream, tmA, tmB, p);
+  return launch_status("linear_bf16_kernel");
+}
+
+}  // namespace
+}  // namespace llnv
+
+using namespace llnv;
+
+extern "C" int llnv_linear_bf16(const void* a, int64_t lda, const void* w, int64_t ldw, const void* bias, int act, int64_t M, int64_t N,
+                                int64_t K, void* d, int64_t ldd, llnv_stream_t stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  LLNV_REQUIRE(M >= 0 && N > 0 && K > 0, "llnv_linear_bf16: bad sizes M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
+  LLNV_REQUIRE(act >= 0 && act <= 2, "llnv_linear_bf16: act is 0 (none), 1 (GELU tanh) or 2 (SiLU), got %d", act);
+  if (M == 0) return LLNV_OK;
+  LLNV_REQUIRE(a && w && d, "llnv_linear_bf16: null tensor");
+  LLNV_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && lda >= K && ldw >= K,
+               "llnv_linear_bf16: K and the row strides of a and w must be multiples of 8 elements (16 bytes)");
+  LLNV_REQUIRE(ldd % 8 == 0 && ldd >= N && N % 8 == 0, "llnv_linear_bf16: N and the row stride of d must be multiples of 8 elements");
+  LLNV_REQUIRE((((uintptr_t)a | (uintptr_t)w | (uintptr_t)d) & 15) == 0 && ((uintptr_t)bias & 1) == 0,
+               "llnv_linear_bf16: a, w and d must be 16-byte aligned");
+  LinParams p;
+  p.M = M, p.N = N, p.K = K;
+  p.bias = (const uint16_t*)bias;
+  p.d = (uint16_t*)d;
+  p.ldd = ldd;
+  p.act = act;
+  p.status = device_status_word();
+  // narrow tiles when the wide ones would leave most SMs without a CTA
+  const int64_t row_tiles = (M + kBM - 1) / kBM;
+  const bool narrow = N <= 64 || row_tiles * ((N + 127) / 128) * 2 <= sm_count();
+  CUtensorMap tmA, tmB;
+  int rc = cached_tensor_map(&tmA, 1, a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, kBM, kBK, 3);
+  if (rc != LLNV_OK) return rc;
+  rc = cached_tensor_map(&tmB, 1, w, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, narrow ? 64 : 128, kBK, 3);
+  if (rc != LLNV_OK) return rc;
+  return narrow ? launch_linear<64>(tmA, tmB, p, stream) : launch_linear<128>(tmA, tmB, p, stream);
+}

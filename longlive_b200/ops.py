@@ -218,6 +218,36 @@ def scatter_2d(src, src_shard_bytes, dst_ptrs, dst_pitch, rows, row_bytes):
                                           dst_pitch, rows, row_bytes, len(dst_ptrs), _stream(src)))
 
 
+_LINEAR_ACT = {None: 0, "none": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def linear_bf16(x, w, bias=None, act=None, out=None):
+    """``act(x @ w.T + bias)`` for bf16 ``x`` [M, K], ``w`` [N, K], ``bias`` [N] on the tcgen05 bf16 kernel
+    (``llnv_linear_bf16``): the Linear of the layers the reference keeps in bf16.  ``act``: None,
+    "gelu_tanh" or "silu".  Unit column strides; K, N and the row strides multiples of 8."""
+    _require_cuda(x, "x")
+    if act not in _LINEAR_ACT:
+        raise ValueError(f"act must be one of {sorted(k for k in _LINEAR_ACT if k)} or None")
+    for name, t in (("x", x), ("w", w)):
+        if t.dim() != 2 or t.dtype != torch.bfloat16 or t.stride(1) != 1:
+            raise RuntimeError(f"{name} must be a 2-D bfloat16 tensor with unit column stride")
+    if x.shape[1] != w.shape[1]:
+        raise RuntimeError(f"x is [M, {x.shape[1]}] but w is [N, {w.shape[1]}]")
+    m, k = x.shape
+    n = w.shape[0]
+    if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != n or not bias.is_contiguous()):
+        raise RuntimeError("bias must be a contiguous bfloat16 tensor of N values")
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    elif out.shape != (m, n) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
+        raise RuntimeError("out must be bfloat16 [M, N] with unit column stride")
+    with torch.cuda.device(x.device):
+        _check(_lib.lib().llnv_linear_bf16(x.data_ptr(), x.stride(0) if m > 1 else max(k, x.stride(0)), w.data_ptr(), w.stride(0),
+                                           None if bias is None else bias.data_ptr(), _LINEAR_ACT[act], m, n, k, out.data_ptr(),
+                                           out.stride(0) if m > 1 else max(n, out.stride(0)), _stream(x)))
+    return out
+
+
 def peer_barrier(signal_ptrs, rank, epoch):
     """Stream-ordered barrier over the GPUs whose signal areas are ``signal_ptrs`` (``llnv_peer_barrier``)."""
     with torch.cuda.device(epoch.device):
