@@ -401,7 +401,8 @@ def bench_dit_chunk(dev, rank, world, group, steps: int, sync_amax: bool = True,
     from longlive_b200 import _lib, dit
 
     cfg = dit.DiTConfig()
-    model = dit.CausalDiT(cfg, device=dev, seed=0, sp_group=group, sync_amax=sync_amax, use_graphs=use_graphs)
+    model = dit.CausalDiT(cfg, device=dev, seed=0, sp_group=group, sync_amax=sync_amax, use_graphs=use_graphs,
+                          edge_linear=os.environ.get("LLNV_EDGE_LINEAR", "own"))
     gen = torch.Generator(device=dev).manual_seed(7)
     ctx = model.encode_text(torch.randn(cfg.text_len, cfg.text_dim, generator=gen, device=dev).bfloat16())
     lat_full = torch.randn(cfg.chunk_tokens, cfg.patch_dim, generator=gen, device=dev).bfloat16()

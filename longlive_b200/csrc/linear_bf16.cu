@@ -8,8 +8,12 @@
 // 128-byte-swizzled K-major tiles of A and W (64 channels per stage), tcgen05.mma kind::f16 with
 // the fp32 accumulator in TMEM, and an epilogue that adds the bias in fp32, rounds to bf16 (the
 // rounding point of the reference's fused-bias GEMM), applies the activation on the rounded value
-// (the reference's activation is a separate bf16 op) and stores 64 contiguous bytes per thread.
-// Rows beyond M and channels beyond K are zero-filled by TMA; stores are masked.
+// (the reference's activation is a separate bf16 op), writes 32 x 64 blocks into shared memory in
+// the 128-byte swizzle and hands them to TMA stores.  Rows beyond M and channels beyond K are
+// zero-filled by the TMA loads; the TMA stores clip rows beyond M and columns beyond N.  The ring
+// depth is chosen per launch: grids that cover the SMs more than once get at most 4 stages so that
+// two CTAs share an SM, grids of fewer CTAs than SMs (long K, short N) a ring as deep as shared
+// memory allows, since each CTA then has to keep its SM's share of HBM bandwidth busy alone.
 //
 // Warps: 0 = TMA producer, 1 = TMEM allocation + MMA issue, 2..5 = epilogue (TMEM lane quarter
 // warp % 4).  Every wait is bounded (mbar_wait): on a timeout the kernel records where it gave up
@@ -30,7 +34,7 @@ __device__ __forceinline__ float gelu_tanh(float x) {
   return __fdividef(x, 1.f + __expf(-2.f * u));
 }
 
-constexpr int kBM = 128, kBK = 64, kStagesLin = 4, kThreadsLin = 192;
+constexpr int kBM = 128, kBK = 64, kMaxStagesLin = 8, kThreadsLin = 192;
 constexpr int kATile = kBM * kBK * 2;                       // 16 KB
 
 struct LinParams {
@@ -39,6 +43,7 @@ struct LinParams {
   uint16_t* d;
   int64_t ldd;
   int act;                                                  // 0 none, 1 GELU(tanh), 2 SiLU
+  int stages;                                               // ring depth, 1 .. kMaxStagesLin
   unsigned int* status;
 };
 
@@ -46,22 +51,25 @@ template <int BN>
 struct LinCfg {
   static constexpr int kBTile = BN * kBK * 2;
   static constexpr int kStageBytes = kATile + kBTile;
-  static constexpr int kBarOff = kStagesLin * kStageBytes;
-  static constexpr int kSmemBytes = kBarOff + 256 + 1024;   // barriers + slack for the 1024-byte alignment
+  // the epilogue reuses the first stage: 4 warps x (BN / 64) blocks of 32 rows x 128 bytes
+  static_assert(4 * (BN / 64) * 4096 <= kStageBytes, "epilogue staging must fit one stage");
+  static constexpr int smem_bytes(int stages) { return stages * kStageBytes + 256 + 1024; }   // + barriers + alignment slack
 };
 
 __device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.f + __expf(-x)); }
 
 template <int BN>
 __global__ void __launch_bounds__(kThreadsLin, 1)
-linear_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const LinParams p) {
+linear_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                   const __grid_constant__ CUtensorMap tmD, const LinParams p) {
   pdl_wait();
   using Cfg = LinCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + Cfg::kBarOff);
-  uint64_t* empty = full + kStagesLin;
-  uint64_t* acc_full = empty + kStagesLin;
+  const int stages = p.stages;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + stages * Cfg::kStageBytes);
+  uint64_t* empty = full + kMaxStagesLin;
+  uint64_t* acc_full = empty + kMaxStagesLin;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -71,7 +79,7 @@ linear_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   const int nk = (int)((p.K + kBK - 1) / kBK);
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kStagesLin; ++i) {
+    for (int i = 0; i < stages; ++i) {
       mbar_init(&full[i], 1);
       mbar_init(&empty[i], 1);
     }
@@ -80,6 +88,7 @@ linear_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     fence_barrier_init();
     prefetch_tensormap(&tmA);
     prefetch_tensormap(&tmB);
+    prefetch_tensormap(&tmD);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, BN);
@@ -93,8 +102,8 @@ linear_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   if (warp == 0) {
     if (elect_one()) {
       for (int ks = 0; ks < nk; ++ks) {
-        const int s = ks % kStagesLin;
-        const uint32_t ph = (uint32_t)((ks / kStagesLin) & 1);
+        const int s = ks % stages;
+        const uint32_t ph = (uint32_t)((ks / stages) & 1);
         if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, p.status, 1100u)) break;
         mbar_arrive_expect_tx(&full[s], Cfg::kStageBytes);
         tma_load_2d(smem + s * Cfg::kStageBytes, &tmA, ks * kBK, m0, &full[s]);
@@ -106,8 +115,8 @@ linear_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       constexpr uint32_t idesc = make_idesc_bf16(kBM, BN, 0, 0);
       bool ok = true;
       for (int ks = 0; ks < nk && ok; ++ks) {
-        const int s = ks % kStagesLin;
-        const uint32_t ph = (uint32_t)((ks / kStagesLin) & 1);
+        const int s = ks % stages;
+        const uint32_t ph = (uint32_t)((ks / stages) & 1);
         ok = mbar_wait(&full[s], ph, abort_flag, p.status, 1101u);
         if (!ok) break;
         tc_fence_after();
@@ -123,45 +132,51 @@ linear_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     }
   } else {
     const int q = warp & 3;                                  // TMEM lanes 32 q .. 32 q + 31
-    const int64_t row = (int64_t)m0 + q * 32 + lane;
+    const int row0 = m0 + q * 32;
     if (mbar_wait(acc_full, 0u, abort_flag, p.status, 1102u)) {
       tc_fence_after();
+      // every load of the ring has been consumed by now: stage 0 is free for the output blocks
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), r);
+      for (int c = 0; c < BN / 64; ++c) {
+        uint32_t r[2][32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 64), r[0]);
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 64 + 32), r[1]);
         tmem_ld_wait();
-        const int64_t col = (int64_t)n0 + c * 32;
-        uint32_t out[16];
+        const int64_t col = (int64_t)n0 + c * 64;
+        uint8_t* buf = smem + (q * (BN / 64) + c) * 4096;     // 32 rows x 128 bytes, 128-byte swizzle
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float y0 = __uint_as_float(r[e]), y1 = __uint_as_float(r[e + 1]);
-          if (p.bias) {
-            if (col + e < p.N) y0 += __uint_as_float((uint32_t)__ldg(p.bias + col + e) << 16);
-            if (col + e + 1 < p.N) y1 += __uint_as_float((uint32_t)__ldg(p.bias + col + e + 1) << 16);
-          }
-          if (p.act) {
-            round_bf16x2(y0, y1);
-            if (p.act == 1) {
-              y0 = gelu_tanh(y0);
-              y1 = gelu_tanh(y1);
-            } else {
-              y0 = silu(y0);
-              y1 = silu(y1);
+        for (int v8 = 0; v8 < 8; ++v8) {
+          uint32_t w4[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int cc = v8 * 8 + 2 * e;
+            float y0 = __uint_as_float(r[cc >> 5][cc & 31]), y1 = __uint_as_float(r[(cc + 1) >> 5][(cc + 1) & 31]);
+            if (p.bias) {
+              if (col + cc < p.N) y0 += __uint_as_float((uint32_t)__ldg(p.bias + col + cc) << 16);
+              if (col + cc + 1 < p.N) y1 += __uint_as_float((uint32_t)__ldg(p.bias + col + cc + 1) << 16);
             }
+            if (p.act) {
+              round_bf16x2(y0, y1);
+              if (p.act == 1) {
+                y0 = gelu_tanh(y0);
+                y1 = gelu_tanh(y1);
+              } else {
+                y0 = silu(y0);
+                y1 = silu(y1);
+              }
+            }
+            w4[e] = pack_bf16x2(y0, y1);
           }
-          out[e >> 1] = pack_bf16x2(y0, y1);
+          *reinterpret_cast<uint4*>(buf + lane * 128 + ((v8 ^ (lane & 7)) << 4)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
         }
-        if (row < p.M) {
-          uint16_t* dst = p.d + row * p.ldd + col;
-          if (col + 32 <= p.N) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) reinterpret_cast<uint4*>(dst)[v] = make_uint4(out[4 * v], out[4 * v + 1], out[4 * v + 2], out[4 * v + 3]);
-          } else {
-            for (int e = 0; e < 32 && col + e < p.N; ++e) dst[e] = (uint16_t)(out[e >> 1] >> ((e & 1) * 16));
-          }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0 && row0 < p.M && col < p.N) {
+          tma_store_2d(&tmD, buf, (int)col, row0);
+          bulk_commit();
         }
       }
+      if (lane == 0) bulk_wait<0>();
     }
   }
   tc_fence_before();
@@ -177,17 +192,17 @@ linear_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 }
 
 template <int BN>
-int launch_linear(const CUtensorMap& tmA, const CUtensorMap& tmB, const LinParams& p, cudaStream_t stream) {
+int launch_linear(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD, const LinParams& p, cudaStream_t stream) {
   using Cfg = LinCfg<BN>;
   static bool attr_set[64] = {};
   int dev = 0;
   LLNV_CUDA(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    LLNV_CUDA(cudaFuncSetAttribute(linear_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    LLNV_CUDA(cudaFuncSetAttribute(linear_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::smem_bytes(BN == 128 ? 6 : 8)));
     attr_set[dev] = true;
   }
   const dim3 grid((unsigned)((p.N + BN - 1) / BN), (unsigned)((p.M + kBM - 1) / kBM));
-  launch_k(linear_bf16_kernel<BN>, grid, kThreadsLin, Cfg::kSmemBytes, stream, tmA, tmB, p);
+  launch_k(linear_bf16_kernel<BN>, grid, kThreadsLin, (size_t)Cfg::smem_bytes(p.stages), stream, tmA, tmB, tmD, p);
   return launch_status("linear_bf16_kernel");
 }
 
@@ -215,13 +230,20 @@ extern "C" int llnv_linear_bf16(const void* a, int64_t lda, const void* w, int64
   p.ldd = ldd;
   p.act = act;
   p.status = device_status_word();
+
   // narrow tiles when the wide ones would leave most SMs without a CTA
   const int64_t row_tiles = (M + kBM - 1) / kBM;
-  const bool narrow = N <= 64 || row_tiles * ((N + 127) / 128) * 2 <= sm_count();
-  CUtensorMap tmA, tmB;
+  const bool narrow = N <= 64 || row_tiles * ((N + 127) / 128) < 2 * (int64_t)sm_count();
+  const int64_t ctas = row_tiles * ((N + (narrow ? 63 : 127)) / (narrow ? 64 : 128));
+  const int64_t nk = (K + kBK - 1) / kBK;
+  const int64_t deep = ctas <= sm_count() ? (narrow ? 8 : 6) : 4;
+  p.stages = (int)(nk < deep ? nk : deep);
+  CUtensorMap tmA, tmB, tmD;
   int rc = cached_tensor_map(&tmA, 1, a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, kBM, kBK, 3);
   if (rc != LLNV_OK) return rc;
   rc = cached_tensor_map(&tmB, 1, w, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, narrow ? 64 : 128, kBK, 3);
   if (rc != LLNV_OK) return rc;
-  return narrow ? launch_linear<64>(tmA, tmB, p, stream) : launch_linear<128>(tmA, tmB, p, stream);
+  rc = cached_tensor_map(&tmD, 1, d, (uint64_t)M, (uint64_t)N, (uint64_t)ldd, 32, 64, 3);
+  if (rc != LLNV_OK) return rc;
+  return narrow ? launch_linear<64>(tmA, tmB, tmD, p, stream) : launch_linear<128>(tmA, tmB, tmD, p, stream);
 }

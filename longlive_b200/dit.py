@@ -217,8 +217,11 @@ class KVCache:
 
 class CausalDiT:
     def __init__(self, cfg: DiTConfig | None = None, device="cuda", seed: int = 0, sp_group=None, sync_amax: bool = True,
-                 cache_text_kv: bool = True, use_graphs: bool = False, peer_exchange: bool = True):
+                 cache_text_kv: bool = True, use_graphs: bool = False, peer_exchange: bool = True, edge_linear: str = "own"):
         self.cfg = cfg = cfg or DiTConfig()
+        if edge_linear not in ("own", "library"):
+            raise ValueError("edge_linear is 'own' (llnv_linear_bf16) or 'library' (torch.nn.functional.linear, i.e. cuBLAS)")
+        self.edge_linear = edge_linear
         self.use_graphs = use_graphs
         self.device = torch.device(device)
         self.group = sp_group
@@ -352,12 +355,27 @@ class CausalDiT:
         else:
             ops.layernorm_quantize_nvfp4(x, w, b, MSE, self.cfg.eps, **kw)
 
+    def _edge(self, x, w, b, act=None, out=None):
+        """A bf16 Linear of an unquantized edge layer: the library's tcgen05 kernel, or cuBLAS through
+        PyTorch (kept selectable: for these few small GEMMs cuBLAS is the faster of the two)."""
+        if self.edge_linear == "own":
+            return ops.linear_bf16(x, w, b, act=act, out=out)
+        y = torch.nn.functional.linear(x, w, b)
+        if act == "gelu_tanh":
+            y = torch.nn.functional.gelu(y, approximate="tanh")
+        elif act == "silu":
+            y = torch.nn.functional.silu(y)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+
     # ---- text context -------------------------------------------------------------------------
     def encode_text(self, ctx_raw: torch.Tensor) -> torch.Tensor:
         """[text_len, text_dim] -> [text_len, dim] (text_embedding MLP, wan_5b/modules/causal_model.py:1568-1573)."""
-        h = torch.nn.functional.gelu(torch.nn.functional.linear(ctx_raw, self.text_w0, self.text_b0), approximate="tanh")
+        h = self._edge(ctx_raw.contiguous(), self.text_w0, self.text_b0, act="gelu_tanh")
         self.text_kv = None
-        return torch.nn.functional.linear(h, self.text_w1, self.text_b1).contiguous()
+        return self._edge(h, self.text_w1, self.text_b1).contiguous()
 
     def _text_kv(self, layer: int, blk: Block, ctx: torch.Tensor):
         """Cross-attention K (RMS-normed) and V of the text context.  The reference recomputes them on
@@ -506,9 +524,8 @@ class CausalDiT:
         freqs = torch.pow(10000.0, -torch.arange(half, device=self.device, dtype=torch.float64) / half)
         ang = t.to(torch.float64)[:, None] * freqs[None]
         emb = torch.cat([ang.cos(), ang.sin()], dim=1).to(torch.bfloat16)
-        lin = torch.nn.functional.linear
-        e = lin(torch.nn.functional.silu(lin(emb, self.time_w0, self.time_b0)), self.time_w1, self.time_b1)
-        e0 = lin(torch.nn.functional.silu(e), self.tproj_w, self.tproj_b).view(-1, 6, cfg.dim)
+        e = self._edge(self._edge(emb, self.time_w0, self.time_b0, act="silu"), self.time_w1, self.time_b1)
+        e0 = self._edge(torch.nn.functional.silu(e), self.tproj_w, self.tproj_b).view(-1, 6, cfg.dim)
         return e, e0
 
     def _set_rope(self, start_frame: int) -> None:
@@ -563,8 +580,7 @@ class CausalDiT:
 
     def _forward_impl(self, latent_tokens: torch.Tensor, t: torch.Tensor, ctx: torch.Tensor) -> torch.Tensor:
         cfg = self.cfg
-        x = torch.nn.functional.linear(latent_tokens, self.patch_w, self.patch_b)
-        self.x_a.copy_(x)
+        self._edge(latent_tokens, self.patch_w, self.patch_b, out=self.x_a)       # patch embedding, causal_model.py:1535-1540
         e, e0 = self.time_embed(t)
         cos, sin = self.cos_buf, self.sin_buf
         self._ran_eager = True
@@ -578,7 +594,7 @@ class CausalDiT:
         frame = (torch.arange(self.Sl, device=self.device) + self.rank * self.Sl) // cfg.frame_tokens
         xn = torch.nn.functional.layer_norm(cur.float(), (cfg.dim,), eps=cfg.eps)
         y = (xn * (1 + hm[frame, 1]) + hm[frame, 0]).bfloat16()
-        return torch.nn.functional.linear(y, self.head_w, self.head_b)
+        return self._edge(y, self.head_w, self.head_b)
 
     def run_chunk(self, latent_tokens: torch.Tensor, ctx: torch.Tensor, chunk_index: int,
                   sampling_steps: int = 4, timestep_shift: float = 5.0, scene_cut: bool = False,
