@@ -311,6 +311,18 @@ int llnv_gemm_nvfp4_grouped(const void* a_codes, const void* a_sf, const float* 
 int llnv_linear_bf16(const void* a, int64_t lda, const void* w, int64_t ldw, const void* bias, int act, int64_t M, int64_t N,
                      int64_t K, void* d, int64_t ldd, llnv_stream_t stream);
 
+/* ---- latent <-> token layout ----------------------------------------------------------------- */
+
+/* bf16 latent [C, F, 2h, 2w] (element strides stride_c and stride_f, image axes contiguous) to
+ * tokens [F*h*w, 4*C] with features ordered (c, kh, kw) -- the view of the input the patch-embedding
+ * Conv3d with kernel and stride (1, 2, 2) takes (wan_5b/modules/causal_model.py:1052-1056, 1535-1540) --
+ * and back, which is the reference's unpatchify (causal_model.py:1835-1858) for a head whose rows
+ * are stored in that feature order.  ldt: token row stride in elements.  h, w: token grid. */
+int llnv_patchify(const void* latent, int64_t stride_c, int64_t stride_f, void* tokens, int64_t ldt, int C, int F, int h, int w,
+                  llnv_stream_t stream);
+int llnv_unpatchify(const void* tokens, int64_t ldt, void* latent, int64_t stride_c, int64_t stride_f, int C, int F, int h, int w,
+                    llnv_stream_t stream);
+
 /* ---- flow-matching UniPC scheduler step ------------------------------------------------------ */
 
 /* Scalars of one scheduler step, computed on the host in fp32 exactly as the reference computes

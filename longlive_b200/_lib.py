@@ -12,7 +12,7 @@ EXPORTS = [
     "llnv_version", "llnv_last_error", "llnv_check_status", "llnv_amax_bf16", "llnv_quantize_nvfp4",
     "llnv_kv_dequant", "llnv_dequantize_nvfp4", "llnv_gemm_nvfp4", "llnv_gemm_nvfp4_grouped", "llnv_adaln_quantize_nvfp4",
     "llnv_layernorm_quantize_nvfp4", "llnv_gemm_nvfp4_force_tile_n", "llnv_gemm_nvfp4_debug", "llnv_selftest_div_const",
-    "llnv_adaln_quantize_nvfp4_static", "llnv_static_max_rows", "llnv_rmsnorm_rope", "llnv_attention_bf16", "llnv_attention_bf16_ex", "llnv_quantize_nvfp4_ex", "llnv_quantize_nvfp4_pair", "llnv_rmsnorm_rope_ex", "llnv_rmsnorm_rope_scatter", "llnv_rmsnorm_rope_qk", "llnv_scatter_2d", "llnv_peer_barrier", "llnv_peer_allreduce_max", "llnv_attention_key_splits", "llnv_attention_workspace_bytes", "llnv_adaln_quantize_nvfp4_ex", "llnv_layernorm_quantize_nvfp4_ex", "llnv_unipc_step", "llnv_set_pdl", "llnv_linear_bf16",
+    "llnv_adaln_quantize_nvfp4_static", "llnv_static_max_rows", "llnv_rmsnorm_rope", "llnv_attention_bf16", "llnv_attention_bf16_ex", "llnv_quantize_nvfp4_ex", "llnv_quantize_nvfp4_pair", "llnv_rmsnorm_rope_ex", "llnv_rmsnorm_rope_scatter", "llnv_rmsnorm_rope_qk", "llnv_scatter_2d", "llnv_peer_barrier", "llnv_peer_allreduce_max", "llnv_attention_key_splits", "llnv_attention_workspace_bytes", "llnv_adaln_quantize_nvfp4_ex", "llnv_layernorm_quantize_nvfp4_ex", "llnv_unipc_step", "llnv_set_pdl", "llnv_linear_bf16", "llnv_patchify", "llnv_unpatchify",
 ]
 
 
@@ -82,6 +82,8 @@ def lib() -> C.CDLL:
         l.llnv_peer_barrier.argtypes = [p, i32, i32, p, p]
         l.llnv_peer_allreduce_max.argtypes = [p, i32, p, p, i32, i32, p, p]
         l.llnv_set_pdl.argtypes = [i32]
+        l.llnv_patchify.argtypes = [p, i64, i64, p, i64, i32, i32, i32, i32, p]
+        l.llnv_unpatchify.argtypes = [p, i64, p, i64, i64, i32, i32, i32, i32, p]
         l.llnv_linear_bf16.argtypes = [p, i64, p, i64, p, i32, i64, i64, i64, p, i64, p]
         l.llnv_unipc_step.argtypes = [p, p, p, p, p, p, p, p, i64, i32, p, p]
         for name in EXPORTS:

@@ -16,6 +16,12 @@ of the generator wrapper.
 same thing the reference's ``quantize_model_with_filter`` does after loading a bf16 checkpoint).
 The patch embedding is stored as the Conv3d weight [dim, C_in, 1, 2, 2]; flattened it is the
 [dim, C_in * 4] matrix applied to tokens whose features are ordered (channel, kh, kw).
+The reference's head emits the features of a token in the order (kh, kw, channel), which its
+``unpatchify`` turns back into a latent (wan_5b/modules/causal_model.py:1851-1857); the model here
+keeps latents patchified between the forwards of a chunk, so the rows of ``head.head`` are
+permuted on load into the input order (channel, kh, kw) -- the head then writes the flow
+prediction in the layout of its input and the scheduler step needs no unpatchify / patchify pair --
+and permuted back on save.
 """
 from __future__ import annotations
 
@@ -40,6 +46,11 @@ BLOCK_VECTORS = (("norm_q", "self_attn.norm_q.weight"), ("norm_k", "self_attn.no
 EDGE_LINEARS = (("time_w0", "time_b0", "time_embedding.0"), ("time_w1", "time_b1", "time_embedding.2"),
                 ("tproj_w", "tproj_b", "time_projection.1"), ("text_w0", "text_b0", "text_embedding.0"),
                 ("text_w1", "text_b1", "text_embedding.2"), ("head_w", "head_b", "head.head"))
+
+
+def head_row_order(in_channels: int, patch: int = 4) -> torch.Tensor:
+    """Index array p with ``w_model = w_reference[p]``: model row c * patch + k is the reference's row k * C + c."""
+    return torch.arange(patch * in_channels).view(patch, in_channels).t().reshape(-1)
 
 
 def is_nvfp4_state_dict(state_dict: object) -> bool:
@@ -99,6 +110,9 @@ def state_dict_of(model, prefix: str = "model.") -> dict:
     for w, b, path in EDGE_LINEARS:
         sd[f"{prefix}{path}.weight"] = getattr(model, w)
         sd[f"{prefix}{path}.bias"] = getattr(model, b)
+    inv = torch.argsort(head_row_order(cfg.in_channels)).to(model.head_w.device)
+    sd[f"{prefix}head.head.weight"] = model.head_w[inv]
+    sd[f"{prefix}head.head.bias"] = model.head_b[inv]
     return sd
 
 
@@ -168,6 +182,11 @@ def load_state_dict_into(model, state_dict: Mapping, prefix: str = "model.", wei
             t = take(key)
             if t is not None:
                 _copy(getattr(model, attr), t, key)
+    if f"{prefix}head.head.weight" in used:
+        order = head_row_order(model.cfg.in_channels).to(model.head_w.device)
+        model.head_w.copy_(model.head_w[order])
+        if f"{prefix}head.head.bias" in used:
+            model.head_b.copy_(model.head_b[order])
     for blk in model.blocks:
         blk.fuse_qkv()
     model.modulation_all = torch.stack([blk.modulation for blk in model.blocks], 0)

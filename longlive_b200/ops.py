@@ -248,6 +248,41 @@ def linear_bf16(x, w, bias=None, act=None, out=None):
     return out
 
 
+def _latent_view(latent, channels_first):
+    if latent.dim() != 4 or latent.dtype != torch.bfloat16 or latent.stride(3) != 1 or latent.stride(2) != latent.shape[3]:
+        raise RuntimeError("latent must be a 4-D bfloat16 tensor whose two image axes are contiguous")
+    if latent.shape[2] % 2 or latent.shape[3] % 2:
+        raise RuntimeError("latent height and width must be even (patch 1 x 2 x 2)")
+    c_ax, f_ax = (0, 1) if channels_first else (1, 0)
+    return latent.shape[c_ax], latent.shape[f_ax], latent.stride(c_ax), latent.stride(f_ax), latent.shape[2] // 2, latent.shape[3] // 2
+
+
+def patchify(latent, channels_first=True, out=None):
+    """bf16 latent [C, F, H, W] (or [F, C, H, W] with ``channels_first=False``) -> tokens [F*H/2*W/2, 4*C],
+    features ordered (c, kh, kw): the input of the patch embedding (``llnv_patchify``)."""
+    _require_cuda(latent, "latent")
+    C, F, sc, sf, h, w = _latent_view(latent, channels_first)
+    if out is None:
+        out = torch.empty((F * h * w, 4 * C), dtype=torch.bfloat16, device=latent.device)
+    elif out.shape != (F * h * w, 4 * C) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
+        raise RuntimeError("out must be bfloat16 [F*h*w, 4*C] with unit column stride")
+    with torch.cuda.device(latent.device):
+        _check(_lib.lib().llnv_patchify(latent.data_ptr(), sc, sf, out.data_ptr(), out.stride(0), C, F, h, w, _stream(latent)))
+    return out
+
+
+def unpatchify(tokens, out, channels_first=True):
+    """Tokens [F*h*w, 4*C] (features (c, kh, kw)) -> the bf16 latent ``out`` [C, F, 2h, 2w] (or [F, C, 2h, 2w]);
+    the inverse of ``patchify`` (``llnv_unpatchify``)."""
+    _require_cuda(tokens, "tokens")
+    C, F, sc, sf, h, w = _latent_view(out, channels_first)
+    if tokens.shape != (F * h * w, 4 * C) or tokens.dtype != torch.bfloat16 or tokens.stride(1) != 1 or tokens.device != out.device:
+        raise RuntimeError("tokens must be bfloat16 [F*h*w, 4*C] with unit column stride on the device of out")
+    with torch.cuda.device(tokens.device):
+        _check(_lib.lib().llnv_unpatchify(tokens.data_ptr(), tokens.stride(0), out.data_ptr(), sc, sf, C, F, h, w, _stream(tokens)))
+    return out
+
+
 def peer_barrier(signal_ptrs, rank, epoch):
     """Stream-ordered barrier over the GPUs whose signal areas are ``signal_ptrs`` (``llnv_peer_barrier``)."""
     with torch.cuda.device(epoch.device):

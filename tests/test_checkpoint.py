@@ -32,3 +32,17 @@ def test_expected_keys_follow_the_reference_module_tree():
     assert len(keys) == 2 * per_block + 3 + 6 * 2
     bf16 = ck.expected_keys(cfg, quantized=False)
     assert "model.blocks.0.ffn.0.weight" in bf16 and not any("quantized_weight" in k for k in bf16)
+
+
+def test_head_row_order_folds_unpatchify_and_patchify():
+    """A head with permuted rows emits, per token, what the reference's head + unpatchify + patchify
+    (Conv3d feature order) would: (kh, kw, channel) -> [C, F, H, W] -> (channel, kh, kw)."""
+    C, f, h, w = 5, 2, 3, 4
+    g = torch.Generator().manual_seed(0)
+    u = torch.randn(f * h * w, 4 * C, generator=g)                        # reference head output, features (kh, kw, c)
+    lat = torch.einsum("fhwpqrc->cfphqwr", u.view(f, h, w, 1, 2, 2, C)).reshape(C, f, 2 * h, 2 * w)   # unpatchify
+    # patchify as the Conv3d with kernel (1, 2, 2) sees it: token (f, hh, ww), features (c, kh, kw)
+    tok = lat.view(C, f, h, 2, w, 2).permute(1, 2, 4, 0, 3, 5).reshape(f * h * w, 4 * C)
+    assert torch.equal(u[:, ck.head_row_order(C)], tok)
+    inv = torch.argsort(ck.head_row_order(C))
+    assert torch.equal(tok[:, inv], u)
