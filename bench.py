@@ -418,14 +418,25 @@ def bench_dit_chunk(dev, rank, world, group, steps: int, sync_amax: bool = True,
     torch.cuda.synchronize(dev)
     if world > 1:
         dist.barrier()
+    # every finished chunk leaves through the streaming hand-off (unpatchify into a ring slot, copy to
+    # pinned host memory on a side stream); with token shards each rank would hand off a partial image
+    handoff = None
+    if world == 1:
+        from longlive_b200.handoff import LatentHandoff
+        handoff = LatentHandoff(cfg.in_channels, cfg.frames_per_chunk, 2 * cfg.grid_h, 2 * cfg.grid_w, device=dev, target="host", depth=3)
     times = []
     for _ in range(steps):
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
-        model.run_chunk(lat, ctx, chunk)
+        out = model.run_chunk(lat, ctx, chunk)
+        if handoff is not None:
+            handoff.push(out)
         e.record()
         torch.cuda.synchronize(dev)
         times.append(s.elapsed_time(e))
+        if handoff is not None:
+            seq, _host_latent = handoff.pop()
+            handoff.release(seq)
         chunk += 1
     assert _lib.lib().llnv_check_status(None) == 0, _lib.lib().llnv_last_error()
     exchange = "producer kernels store into peer memory (NVLink), own barrier" if model.arena is not None else "NCCL all-to-all"
@@ -448,6 +459,7 @@ def bench_dit_chunk(dev, rank, world, group, steps: int, sync_amax: bool = True,
             "amax_sync": bool(world > 1 and sync_amax), "cuda_graphs": bool(use_graphs), "scaling": "strong",
             "exchange": ("none" if world == 1 else exchange),
             "kv_cache_bytes_per_rank": model.cache.bytes(),
+            "handoff": (None if handoff is None else {"target": "pinned host", "bytes_per_chunk": handoff.bytes_per_chunk, "in_timed_region": True}),
             "data": "synthetic, random-init weights"}
 
 
