@@ -466,6 +466,7 @@ def bench_dit_chunk(dev, rank, world, group, steps: int, sync_amax: bool = True,
 def run_kernel_case(spec: str, iters: int):
     """Run one kernel on one shape a few times (used for ncu captures and quick timing):
     gemm:MxNxK[:tile]   quantize:MxK[:rule]   kvdequant:BLOCKSxTOKENSxHEADS   attention:LQxLKxHEADS   ropenorm:TOKENSxHEADS
+    linear:MxNxK  (the bf16 Linear of the edge layers)
     unipc:ELEMENTS[:f32]  (the scheduler step with order-2 corrector and predictor: 5 tensors read, 3 written)"""
     import torch
 
@@ -525,6 +526,14 @@ def run_kernel_case(spec: str, iters: int):
         amax = torch.empty(1, dtype=torch.float32, device=dev)
         fn = lambda: ops.rmsnorm_rope(x, w, cos, sin, out=out, out_smooth=sm, amax_out=amax)
         work, unit = s_ * heads * 128 * 6 / 1e9, "GB/s"
+    elif kind == "linear":
+        m, n, k = d
+        x = torch.randn(m, k, generator=gen, device=dev).bfloat16()
+        w = (torch.randn(n, k, generator=gen, device=dev) * 0.02).bfloat16()
+        b = torch.randn(n, generator=gen, device=dev).bfloat16()
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+        fn = lambda: ops.linear_bf16(x, w, b, out=out)
+        work, unit = 2.0 * m * n * k / 1e12, "TFLOP/s"
     elif kind == "unipc":
         import ctypes
         from longlive_b200.scheduler import FlowUniPCMultistepScheduler
