@@ -5,15 +5,16 @@
 // 1648-1651; utils/quant.py filters them out of quantize_model).  They are small GEMMs with one
 // long and one short dimension (2640 x 3072 x 192 and 2640 x 192 x 3072 per forward), so this is a
 // plain tile kernel, not a persistent one: one CTA per 128 x BN output tile, a TMA ring of
-// 128-byte-swizzled K-major tiles of A and W (64 channels per stage), tcgen05.mma kind::f16 with
+// 128-byte-swizzled K-major tiles of A and W (two 64-channel blocks per stage, so that 256
+// contiguous bytes of every operand row are fetched together), tcgen05.mma kind::f16 with
 // the fp32 accumulator in TMEM, and an epilogue that adds the bias in fp32, rounds to bf16 (the
 // rounding point of the reference's fused-bias GEMM), applies the activation on the rounded value
 // (the reference's activation is a separate bf16 op), writes 32 x 64 blocks into shared memory in
 // the 128-byte swizzle and hands them to TMA stores.  Rows beyond M and channels beyond K are
 // zero-filled by the TMA loads; the TMA stores clip rows beyond M and columns beyond N.  The ring
-// depth is chosen per launch: grids that cover the SMs more than once get at most 4 stages so that
-// two CTAs share an SM, grids of fewer CTAs than SMs (long K, short N) a ring as deep as shared
-// memory allows, since each CTA then has to keep its SM's share of HBM bandwidth busy alone.
+// depth is chosen per launch: about 100 KB of ring for grids that cover the SMs more than once (two
+// CTAs per SM), 192 KB for grids of fewer CTAs than SMs (long K, short N), where each CTA has to
+// keep its SM's share of HBM bandwidth busy alone.
 //
 // Warps: 0 = TMA producer, 1 = TMEM allocation + MMA issue, 2..5 = epilogue (TMEM lane quarter
 // warp % 4).  Every wait is bounded (mbar_wait): on a timeout the kernel records where it gave up
@@ -35,7 +36,9 @@ __device__ __forceinline__ float gelu_tanh(float x) {
 }
 
 constexpr int kBM = 128, kBK = 64, kMaxStagesLin = 8, kThreadsLin = 192;
-constexpr int kATile = kBM * kBK * 2;                       // 16 KB
+// a stage holds `sub` (1 or 2) consecutive 64-channel blocks of both operands; with 2, 256 contiguous
+// bytes of every row are fetched together, which halves the DRAM pages a tile touches per byte (long K)
+constexpr int kATile = kBM * kBK * 2;                       // 16 KB per 64-channel block
 
 struct LinParams {
   int64_t M, N, K;
@@ -44,16 +47,17 @@ struct LinParams {
   int64_t ldd;
   int act;                                                  // 0 none, 1 GELU(tanh), 2 SiLU
   int stages;                                               // ring depth, 1 .. kMaxStagesLin
+  int sub;                                                  // 64-channel blocks per stage, 1 or 2
   unsigned int* status;
 };
 
 template <int BN>
 struct LinCfg {
   static constexpr int kBTile = BN * kBK * 2;
-  static constexpr int kStageBytes = kATile + kBTile;
+  static constexpr int kBlockBytes = kATile + kBTile;
   // the epilogue reuses the first stage: 4 warps x (BN / 64) blocks of 32 rows x 128 bytes
-  static_assert(4 * (BN / 64) * 4096 <= kStageBytes, "epilogue staging must fit one stage");
-  static constexpr int smem_bytes(int stages) { return stages * kStageBytes + 256 + 1024; }   // + barriers + alignment slack
+  static_assert(4 * (BN / 64) * 4096 <= kBlockBytes, "epilogue staging must fit one block of a stage");
+  static constexpr int smem_bytes(int blocks) { return blocks * kBlockBytes + 256 + 1024; }   // + barriers + alignment slack
 };
 
 __device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.f + __expf(-x)); }
@@ -66,8 +70,9 @@ linear_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   using Cfg = LinCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  const int stages = p.stages;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + stages * Cfg::kStageBytes);
+  const int stages = p.stages, sub = p.sub;
+  const int stage_bytes = sub * Cfg::kBlockBytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + stages * stage_bytes);
   uint64_t* empty = full + kMaxStagesLin;
   uint64_t* acc_full = empty + kMaxStagesLin;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
@@ -76,7 +81,7 @@ linear_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BN;
   const int m0 = blockIdx.y * kBM;
-  const int nk = (int)((p.K + kBK - 1) / kBK);
+  const int nk = (int)((p.K + sub * kBK - 1) / (sub * kBK));     // stages of `sub` blocks; channels beyond K are zero-filled
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < stages; ++i) {
@@ -105,9 +110,11 @@ linear_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         const int s = ks % stages;
         const uint32_t ph = (uint32_t)((ks / stages) & 1);
         if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, p.status, 1100u)) break;
-        mbar_arrive_expect_tx(&full[s], Cfg::kStageBytes);
-        tma_load_2d(smem + s * Cfg::kStageBytes, &tmA, ks * kBK, m0, &full[s]);
-        tma_load_2d(smem + s * Cfg::kStageBytes + kATile, &tmB, ks * kBK, n0, &full[s]);
+        mbar_arrive_expect_tx(&full[s], stage_bytes);
+        for (int u = 0; u < sub; ++u) {
+          tma_load_2d(smem + s * stage_bytes + u * Cfg::kBlockBytes, &tmA, (ks * sub + u) * kBK, m0, &full[s]);
+          tma_load_2d(smem + s * stage_bytes + u * Cfg::kBlockBytes + kATile, &tmB, (ks * sub + u) * kBK, n0, &full[s]);
+        }
       }
     }
   } else if (warp == 1) {
@@ -120,12 +127,14 @@ linear_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         ok = mbar_wait(&full[s], ph, abort_flag, p.status, 1101u);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(smem + s * Cfg::kStageBytes);
-        const uint32_t b_addr = a_addr + kATile;
+        for (int u = 0; u < sub; ++u) {
+          const uint32_t a_addr = smem_u32(smem + s * stage_bytes + u * Cfg::kBlockBytes);
+          const uint32_t b_addr = a_addr + kATile;
 #pragma unroll
-        for (int j = 0; j < 4; ++j)          // 16 channels per MMA = 32 bytes along the swizzled row
-          mma_f16_ss(tmem_base, make_kmajor_sw128_desc(a_addr + j * 32), make_kmajor_sw128_desc(b_addr + j * 32), idesc,
-                     (uint32_t)((ks | j) != 0));
+          for (int j = 0; j < 4; ++j)        // 16 channels per MMA = 32 bytes along the swizzled row
+            mma_f16_ss(tmem_base, make_kmajor_sw128_desc(a_addr + j * 32), make_kmajor_sw128_desc(b_addr + j * 32), idesc,
+                       (uint32_t)((ks | u | j) != 0));
+        }
         tc_commit(&empty[s]);
       }
       if (ok) tc_commit(acc_full);
@@ -202,7 +211,7 @@ int launch_linear(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensor
     attr_set[dev] = true;
   }
   const dim3 grid((unsigned)((p.N + BN - 1) / BN), (unsigned)((p.M + kBM - 1) / kBM));
-  launch_k(linear_bf16_kernel<BN>, grid, kThreadsLin, (size_t)Cfg::smem_bytes(p.stages), stream, tmA, tmB, tmD, p);
+  launch_k(linear_bf16_kernel<BN>, grid, kThreadsLin, (size_t)Cfg::smem_bytes(p.stages * p.sub), stream, tmA, tmB, tmD, p);
   return launch_status("linear_bf16_kernel");
 }
 
@@ -235,8 +244,10 @@ extern "C" int llnv_linear_bf16(const void* a, int64_t lda, const void* w, int64
   const int64_t row_tiles = (M + kBM - 1) / kBM;
   const bool narrow = N <= 64 || row_tiles * ((N + 127) / 128) < 2 * (int64_t)sm_count();
   const int64_t ctas = row_tiles * ((N + (narrow ? 63 : 127)) / (narrow ? 64 : 128));
-  const int64_t nk = (K + kBK - 1) / kBK;
-  const int64_t deep = ctas <= sm_count() ? (narrow ? 8 : 6) : 4;
+  p.sub = K >= 512 ? 2 : 1;
+  const int64_t nk = (K + p.sub * kBK - 1) / (p.sub * kBK);
+  const int64_t blocks = ctas <= sm_count() ? (narrow ? 8 : 6) : 4;       // 64-channel blocks the ring may hold (192 KB / 96-128 KB)
+  const int64_t deep = blocks / p.sub;
   p.stages = (int)(nk < deep ? nk : deep);
   CUtensorMap tmA, tmB, tmD;
   int rc = cached_tensor_map(&tmA, 1, a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, kBM, kBK, 3);

@@ -13,7 +13,7 @@
 // fp32) before the next one uses it; fp32 scalars stay fp32; a division by a scalar is a
 // multiplication by its fp32 reciprocal; the corrector / predictor weights (rho) arrive already
 // rounded to the latents' dtype.  Products and sums use the non-contracting intrinsics so that no
-// multiply-add is fused.  The scalar coefficients are computed on the host.
+// multiply-add is fused; values are processed in pairs so that a bf16 rounding is half a paired conversion.  The scalar coefficients are computed on the host.
 #include "common.cuh"
 
 namespace llnv {
@@ -33,31 +33,54 @@ __device__ __forceinline__ float rnd(float x) {
   return x;
 }
 
+// Two values per call: the bf16 rounding of a pair is one cvt.rn.bf16x2.f32 (the scalar conversion
+// issues on the quarter-rate XU pipe and made the kernel instruction-bound).
+struct P2 {
+  float a, b;
+};
 template <bool BF16>
-__device__ __forceinline__ void step_element(const Coef& c, float v, float x, float m0p, float m1p, float last, float& x0_out,
-                                             float& xs_out, float& next_out) {
-  const float x0 = rnd<BF16>(__fsub_rn(x, rnd<BF16>(__fmul_rn(c.sigma, v))));
-  float xs = x;
+__device__ __forceinline__ P2 R(P2 v) {
+  if constexpr (BF16) round_bf16x2(v.a, v.b);
+  return v;
+}
+__device__ __forceinline__ P2 mul_s(float s, P2 v) { return {__fmul_rn(s, v.a), __fmul_rn(s, v.b)}; }
+__device__ __forceinline__ P2 sub2(P2 x, P2 y) { return {__fsub_rn(x.a, y.a), __fsub_rn(x.b, y.b)}; }
+__device__ __forceinline__ P2 add2(P2 x, P2 y) { return {__fadd_rn(x.a, y.a), __fadd_rn(x.b, y.b)}; }
+
+template <bool BF16>
+__device__ __forceinline__ void step_pair(const Coef& c, P2 v, P2 x, P2 m0p, P2 m1p, P2 last, P2& x0_out, P2& xs_out, P2& next_out) {
+  const P2 x0 = R<BF16>(sub2(x, R<BF16>(mul_s(c.sigma, v))));
+  P2 xs = x;
   if (c.use_corrector) {
-    const float xt = rnd<BF16>(__fsub_rn(rnd<BF16>(__fmul_rn(c.cc1, last)), rnd<BF16>(__fmul_rn(c.cc2, m0p))));
-    float res = rnd<BF16>(__fmul_rn(c.c_rho1, rnd<BF16>(__fsub_rn(x0, m0p))));
+    const P2 xt = R<BF16>(sub2(R<BF16>(mul_s(c.cc1, last)), R<BF16>(mul_s(c.cc2, m0p))));
+    P2 res = R<BF16>(mul_s(c.c_rho1, R<BF16>(sub2(x0, m0p))));
     if (c.corrector_order == 2) {
-      const float d1 = rnd<BF16>(__fmul_rn(rnd<BF16>(__fsub_rn(m1p, m0p)), c.c_inv_rk));
-      res = rnd<BF16>(__fadd_rn(rnd<BF16>(__fmul_rn(c.c_rho0, d1)), res));
+      const P2 d1 = R<BF16>(mul_s(c.c_inv_rk, R<BF16>(sub2(m1p, m0p))));
+      res = R<BF16>(add2(R<BF16>(mul_s(c.c_rho0, d1)), res));
     }
-    xs = rnd<BF16>(__fsub_rn(xt, rnd<BF16>(__fmul_rn(c.cc3, res))));
+    xs = R<BF16>(sub2(xt, R<BF16>(mul_s(c.cc3, res))));
   }
-  const float xt = rnd<BF16>(__fsub_rn(rnd<BF16>(__fmul_rn(c.pc1, xs)), rnd<BF16>(__fmul_rn(c.pc2, x0))));
-  float next;
+  const P2 xt = R<BF16>(sub2(R<BF16>(mul_s(c.pc1, xs)), R<BF16>(mul_s(c.pc2, x0))));
+  P2 next;
   if (c.predictor_order == 2) {
-    const float d1 = rnd<BF16>(__fmul_rn(rnd<BF16>(__fsub_rn(m0p, x0)), c.p_inv_rk));
-    next = rnd<BF16>(__fsub_rn(xt, rnd<BF16>(__fmul_rn(c.pc3, rnd<BF16>(__fmul_rn(0.5f, d1))))));
+    const P2 d1 = R<BF16>(mul_s(c.p_inv_rk, R<BF16>(sub2(m0p, x0))));
+    next = R<BF16>(sub2(xt, R<BF16>(mul_s(c.pc3, R<BF16>(mul_s(0.5f, d1))))));
   } else {
-    next = rnd<BF16>(__fsub_rn(xt, c.p_zero));
+    next = R<BF16>(sub2(xt, P2{c.p_zero, c.p_zero}));
   }
   x0_out = x0;
   xs_out = xs;
   next_out = next;
+}
+
+template <bool BF16>
+__device__ __forceinline__ void step_element(const Coef& c, float v, float x, float m0p, float m1p, float last, float& x0_out,
+                                             float& xs_out, float& next_out) {
+  P2 o0, o1, o2;
+  step_pair<BF16>(c, {v, v}, {x, x}, {m0p, m0p}, {m1p, m1p}, {last, last}, o0, o1, o2);
+  x0_out = o0.a;
+  xs_out = o1.a;
+  next_out = o2.a;
 }
 
 template <bool BF16>
@@ -68,6 +91,7 @@ struct Elem<true> {
   static constexpr int kVec = 8;
   static __device__ __forceinline__ float load(const T* p) { return __uint_as_float((uint32_t)*p << 16); }
   static __device__ __forceinline__ void store(T* p, float f) { *p = (T)f2bf(f); }
+  static __device__ __forceinline__ void store2(T* p, P2 v) { *reinterpret_cast<uint32_t*>(p) = pack_bf16x2(v.a, v.b); }
 };
 template <>
 struct Elem<false> {
@@ -75,6 +99,10 @@ struct Elem<false> {
   static constexpr int kVec = 4;
   static __device__ __forceinline__ float load(const T* p) { return *p; }
   static __device__ __forceinline__ void store(T* p, float f) { *p = f; }
+  static __device__ __forceinline__ void store2(T* p, P2 v) {
+    p[0] = v.a;
+    p[1] = v.b;
+  }
 };
 
 // The output pointers may equal input pointers (the x0 history rotates in place, the next sample
@@ -108,12 +136,13 @@ __global__ void __launch_bounds__(256) unipc_step_kernel(const void* v_, const v
       if (need_m1) *reinterpret_cast<uint4*>(q) = reinterpret_cast<const uint4*>(m1)[i];
       if (c.use_corrector) *reinterpret_cast<uint4*>(l) = reinterpret_cast<const uint4*>(last)[i];
 #pragma unroll
-      for (int j = 0; j < V; ++j) {
-        float o0, o1, o2;
-        step_element<BF16>(c, E::load(a + j), E::load(b + j), E::load(p + j), E::load(q + j), E::load(l + j), o0, o1, o2);
-        E::store(r0 + j, o0);
-        E::store(r1 + j, o1);
-        E::store(r2 + j, o2);
+      for (int j = 0; j < V; j += 2) {
+        P2 o0, o1, o2;
+        step_pair<BF16>(c, {E::load(a + j), E::load(a + j + 1)}, {E::load(b + j), E::load(b + j + 1)}, {E::load(p + j), E::load(p + j + 1)},
+                        {E::load(q + j), E::load(q + j + 1)}, {E::load(l + j), E::load(l + j + 1)}, o0, o1, o2);
+        E::store2(r0 + j, o0);
+        E::store2(r1 + j, o1);
+        E::store2(r2 + j, o2);
       }
       reinterpret_cast<uint4*>(x0o)[i] = *reinterpret_cast<uint4*>(r0);
       reinterpret_cast<uint4*>(xso)[i] = *reinterpret_cast<uint4*>(r1);
