@@ -589,11 +589,13 @@ class CausalDiT:
         for li, blk in enumerate(self.blocks):
             self.block_forward(li, cur, nxt, em_all[li], ctx, cos, sin)
             cur, nxt = nxt, cur
-        # head: LayerNorm, modulate with (head.modulation + e), project (causal_model.py:1648)
-        hm = (self.head_mod + e.unsqueeze(1)).float()                   # [F, 2, dim]
-        frame = (torch.arange(self.Sl, device=self.device) + self.rank * self.Sl) // cfg.frame_tokens
-        xn = torch.nn.functional.layer_norm(cur.float(), (cfg.dim,), eps=cfg.eps)
-        y = (xn * (1 + hm[frame, 1]) + hm[frame, 0]).bfloat16()
+        # head: LayerNorm, modulate with (head.modulation + e), project (CausalHead.forward, causal_model.py:950-959):
+        # the same bf16 rounding points as a block's adaLN, so the quantizer's load-side transform produces y
+        # (its NVFP4 output goes to scratch and is not used: the head Linear stays bf16)
+        hm = self.head_mod + e.unsqueeze(1)                             # [F, 2, dim]: shift, scale
+        a = self.act_c
+        _, _, _, y = ops.adaln_quantize_nvfp4(cur, hm[:, 1], hm[:, 0], cfg.frame_tokens, MSE, cfg.eps, want_y=True, codes=a.codes,
+                                              sf=a.sf, amax=a.amax, row_stats=self.row_stats, row_offset=self.rank * self.Sl)
         return self._edge(y, self.head_w, self.head_b)
 
     def run_chunk(self, latent_tokens: torch.Tensor, ctx: torch.Tensor, chunk_index: int,
