@@ -81,7 +81,7 @@ def _bits(t: torch.Tensor) -> np.ndarray:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the LongLive checkout")
     args = ap.parse_args()
     Scheduler = _load_scheduler(args.reference)
     out = {}
