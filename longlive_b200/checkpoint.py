@@ -192,6 +192,7 @@ def load_state_dict_into(model, state_dict: Mapping, prefix: str = "model.", wei
     model.modulation_all = torch.stack([blk.modulation for blk in model.blocks], 0)
     model.text_kv = None                       # cached text K/V belong to the old weights
     model._graphs.clear()                      # captured graphs hold the old weight addresses
+    model._time_cache.clear()                  # cached time embeddings belong to the old weights
     return [k for k in sd if k not in used]
 
 

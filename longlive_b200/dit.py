@@ -305,6 +305,7 @@ class CausalDiT:
         self._rope_frame: int | None = None
         self._graphs: dict = {}
         self._scheduler = None
+        self._time_cache: dict = {}
         self._graph_pool = None
         self._ran_eager = False
 
@@ -537,7 +538,24 @@ class CausalDiT:
         self.sin_buf.copy_(sin[lo:hi])
         self._rope_frame = start_frame
 
-    def forward(self, latent_tokens: torch.Tensor, t: torch.Tensor, ctx: torch.Tensor, start_frame: int) -> torch.Tensor:
+    def _time_inputs(self, t: torch.Tensor, t_key):
+        """(e, per-layer modulation) of the timesteps ``t``.  They depend on the timesteps and the weights
+        only, and a video runs the same few timesteps in every chunk, so with a host-side key for ``t``
+        (``t_key``, e.g. the tuple of its values) they are computed once and kept; the reference recomputes
+        the time MLP and the time projection in every forward (causal_model.py:1561-1564)."""
+        if t_key is None:
+            e, e0 = self.time_embed(t)
+            return e, self.modulation_all + e0.unsqueeze(0)     # [layers, F, 6, dim], causal_model.py:863 for every block at once
+        hit = self._time_cache.get(t_key)
+        if hit is None:
+            if len(self._time_cache) >= 64:
+                self._time_cache.clear()
+                self._graphs.clear()                             # captured graphs read the dropped tensors
+            e, e0 = self.time_embed(t)
+            hit = self._time_cache[t_key] = (e, self.modulation_all + e0.unsqueeze(0))
+        return hit
+
+    def forward(self, latent_tokens: torch.Tensor, t: torch.Tensor, ctx: torch.Tensor, start_frame: int, t_key=None) -> torch.Tensor:
         """latent_tokens: [Sl, patch_dim] (my token shard of the patchified chunk) -> [Sl, patch_dim].
 
         With ``use_graphs`` the whole forward (about a thousand launches, the collectives included)
@@ -548,17 +566,18 @@ class CausalDiT:
         set-up such as the text K/V and the communicators must not happen inside a capture)."""
         self._set_rope(start_frame)
         if not self.use_graphs:
-            out = self._forward_impl(latent_tokens, t, ctx)
+            out = self._forward_impl(latent_tokens, t, ctx, self._time_inputs(t, t_key) if t_key is not None else None)
             self._window_version = self.cache.version
             return out
         self.g_lat.copy_(latent_tokens)
         self.g_t.copy_(t)
+        tin = self._time_inputs(t, t_key) if t_key is not None else None     # outside any capture: the tensors outlive the graphs
         fresh = self._window_version != self.cache.version        # this forward also dequantizes the past blocks
-        key = (tuple(self.cache.order), self.cache.filled, ctx.data_ptr(), fresh)
+        key = (tuple(self.cache.order), self.cache.filled, ctx.data_ptr(), fresh, t_key)
         entry = self._graphs.get(key)
         if entry is None:
             if not self._ran_eager or self.cache.filled < self.cfg.max_blocks:
-                out = self._forward_impl(self.g_lat, self.g_t, ctx)
+                out = self._forward_impl(self.g_lat, self.g_t, ctx, tin)
                 self._window_version = self.cache.version
                 return out
             if self._graph_pool is None:
@@ -566,7 +585,7 @@ class CausalDiT:
             graph = torch.cuda.CUDAGraph()
             torch.cuda.synchronize(self.device)
             with torch.cuda.graph(graph, pool=self._graph_pool, capture_error_mode="thread_local"):
-                out = self._forward_impl(self.g_lat, self.g_t, ctx)
+                out = self._forward_impl(self.g_lat, self.g_t, ctx, tin)
             entry = self._graphs[key] = (graph, out)
         entry[0].replay()
         self._window_version = self.cache.version
@@ -578,14 +597,13 @@ class CausalDiT:
         self._graphs.clear()
         self._graph_pool = None
 
-    def _forward_impl(self, latent_tokens: torch.Tensor, t: torch.Tensor, ctx: torch.Tensor) -> torch.Tensor:
+    def _forward_impl(self, latent_tokens: torch.Tensor, t: torch.Tensor, ctx: torch.Tensor, time_inputs=None) -> torch.Tensor:
         cfg = self.cfg
         self._edge(latent_tokens, self.patch_w, self.patch_b, out=self.x_a)       # patch embedding, causal_model.py:1535-1540
-        e, e0 = self.time_embed(t)
+        e, em_all = time_inputs if time_inputs is not None else self._time_inputs(t, None)
         cos, sin = self.cos_buf, self.sin_buf
         self._ran_eager = True
         cur, nxt = self.x_a, self.x_b
-        em_all = self.modulation_all + e0.unsqueeze(0)                  # [layers, F, 6, dim], causal_model.py:863 for every block at once
         for li, blk in enumerate(self.blocks):
             self.block_forward(li, cur, nxt, em_all[li], ctx, cos, sin)
             cur, nxt = nxt, cur
@@ -617,11 +635,11 @@ class CausalDiT:
         x_t = latent_tokens
         for t in sched.timesteps.tolist():
             tt = torch.full((F,), float(t), device=self.device)
-            flow = self.forward(x_t, tt, ctx, start_frame)
+            flow = self.forward(x_t, tt, ctx, start_frame, t_key=(float(t),) * F)
             x_t = sched.step(flow, t, x_t, return_dict=False)[0]
         if scene_cut and clean_recache:
             self.cache.reset_keep_global()
-        self.forward(x_t, torch.zeros(F, device=self.device), ctx, start_frame)
+        self.forward(x_t, torch.zeros(F, device=self.device), ctx, start_frame, t_key=(0.0,) * F)
         if scene_cut:
             self.cache.pin_current()
         return x_t
