@@ -54,7 +54,7 @@ def _worker(rank, world, port, q, use_graphs=False, peer=False):
         kp = par.cache.k[0][cur_p].dequantize(torch.float32).view(cfg.chunk_tokens, hl, 128)
         ok = ok and torch.equal(kp, kr[:, rank * hl:(rank + 1) * hl])
         if use_graphs:
-            ok = ok and len(par._graphs) == 10
+            ok = ok and len(par._graphs) == 12     # 2 table states x (5 timesteps of a chunk + the extra forward)
         torch.cuda.synchronize()
         par.close()
         q.put((rank, "ok" if ok else "mismatch"))
