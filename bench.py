@@ -466,6 +466,7 @@ def bench_dit_chunk(dev, rank, world, group, steps: int, sync_amax: bool = True,
 def run_kernel_case(spec: str, iters: int):
     """Run one kernel on one shape a few times (used for ncu captures and quick timing):
     gemm:MxNxK[:tile]   quantize:MxK[:rule]   kvdequant:BLOCKSxTOKENSxHEADS   attention:LQxLKxHEADS   ropenorm:TOKENSxHEADS
+    attnkv:LQxBLOCKSxTOKENSxHEADS[:twostep]  (attention over BLOCKS NVFP4 cache blocks + one bf16 chunk; twostep = dequantize, then attend)
     linear:MxNxK  (the bf16 Linear of the edge layers)
     unipc:ELEMENTS[:f32]  (the scheduler step with order-2 corrector and predictor: 5 tensors read, 3 written)"""
     import torch
@@ -486,10 +487,8 @@ def run_kernel_case(spec: str, iters: int):
         xq = L.quantize_to_fp4(torch.randn(m, k, generator=gen, device=dev).bfloat16())
         wq = L.quantize_to_fp4((torch.randn(n, k, generator=gen, device=dev) * 0.02).bfloat16())
         out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
-        if opt:
-            lib.llnv_gemm_nvfp4_force_tile_n(int(opt))
         fn = lambda: ops.gemm_nvfp4(xq.values, xq.scale_factors, xq.amax, 3, wq.values, wq.scale_factors, wq.amax, 3,
-                                    m, n, k, out=out)
+                                    m, n, k, out=out, tile=int(opt or 0))
         work, unit = 2.0 * m * n * k / 1e12, "TFLOP/s"
     elif kind == "quantize":
         m, k = d
@@ -515,6 +514,28 @@ def run_kernel_case(spec: str, iters: int):
         out = torch.empty_like(q)
         fn = lambda: ops.attention_bf16(q, k, v, heads, out=out)
         work, unit = 4.0 * lq * lk * heads * 128 / 1e12, "TFLOP/s"
+    elif kind == "attnkv":
+        # chunk attention reading the NVFP4 cache: LQ queries, BLOCKS cached blocks of TOKENS tokens + a bf16 chunk of TOKENS
+        lq, blocks, tokens, heads = d
+        kq = [L.quantize_to_fp4(torch.randn(tokens * heads, 128, generator=gen, device=dev).bfloat16()) for _ in range(blocks)]
+        vq = [L.quantize_to_fp4(torch.randn(tokens * heads, 128, generator=gen, device=dev).bfloat16()) for _ in range(blocks)]
+        q = torch.randn(lq, heads * 128, generator=gen, device=dev).bfloat16()
+        kc = torch.randn(tokens, heads * 128, generator=gen, device=dev).bfloat16()
+        vc = torch.randn(tokens, heads * 128, generator=gen, device=dev).bfloat16()
+        out = torch.empty_like(q)
+        if opt == "twostep":      # the unfused form it replaces: dequantize every block into a bf16 window, then attend
+            win_k = torch.empty((blocks + 1) * tokens, heads * 128, dtype=torch.bfloat16, device=dev)
+            win_v = torch.empty_like(win_k)
+            win_k[blocks * tokens:] = kc
+            win_v[blocks * tokens:] = vc
+
+            def fn():
+                L.dequantize_kv_cache(kq, blocks, heads, tokens, torch.bfloat16, dev, out=win_k[: blocks * tokens].view(1, -1, heads, 128))
+                L.dequantize_kv_cache(vq, blocks, heads, tokens, torch.bfloat16, dev, out=win_v[: blocks * tokens].view(1, -1, heads, 128))
+                ops.attention_bf16(q, win_k, win_v, heads, out=out)
+        else:
+            fn = lambda: ops.attention_nvfp4kv(q, kq, vq, tokens, kc, vc, heads, out=out)
+        work, unit = 4.0 * lq * (blocks + 1) * tokens * heads * 128 / 1e12, "TFLOP/s"
     elif kind == "ropenorm":
         s_, heads = d
         x = torch.randn(s_, heads * 128, generator=gen, device=dev).bfloat16()

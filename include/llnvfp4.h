@@ -50,6 +50,12 @@ enum { LLNV_DEQ_FUSED = 0, LLNV_DEQ_PYTORCH = 1, LLNV_DEQ_TRITON = 2 };
 int llnv_version(void);
 const char* llnv_last_error(void);
 
+/* One-time set-up for the current device: allocates the 16-byte device status word (the only device
+ * memory the library itself owns besides the fixed scratch array of llnv_adaln_quantize_nvfp4_static).
+ * Every entry point does this lazily on its first use on a device; call it at start-up when the first
+ * use could otherwise fall inside a stream capture, where an allocation is not allowed. */
+int llnv_init_device(void);
+
 /* Reads and clears the device-side status word that kernels with bounded waits write when a
  * wait gives up.  Synchronises `stream`.  Returns LLNV_OK or LLNV_E_TIMEOUT. */
 int llnv_check_status(llnv_stream_t stream);
@@ -196,6 +202,12 @@ int llnv_scatter_2d(const void* src, int64_t src_shard_bytes, int64_t src_pitch,
  * is bounded; a rank that gives up records LLNV_E_TIMEOUT for llnv_check_status and returns. */
 int llnv_peer_barrier(void* const* signal_ptrs, int rank, int world, void* epoch, llnv_stream_t stream);
 
+/* Number of polls after which llnv_peer_barrier / llnv_peer_allreduce_max give up (process-wide, read at
+ * launch; 0 restores the default of about four million polls, a few seconds).  Returns the previous
+ * value.  After a timeout the kernel returns normally, llnv_check_status reports LLNV_E_TIMEOUT and
+ * whatever the consumers of that barrier read is undefined. */
+int llnv_set_peer_poll_limit(unsigned int max_polls);
+
 /* MAX all-reduce of n <= 32 device floats over the group, in place, fused with that barrier (same
  * signal areas and epoch; counts as one barrier).  slot_ptrs[r] is rank r's slot area: 2 * 8 * 32
  * floats of symmetric memory.  Used for the per-tensor amax values of the quantizers, so that a
@@ -248,6 +260,28 @@ int llnv_attention_bf16_ex(const void* q, int64_t Lq, int64_t ldq, const void* k
                            int key_splits, void* workspace, int64_t workspace_bytes, float* out_amax,
                            llnv_stream_t stream);
 int llnv_attention_key_splits(int64_t Lq, int64_t Lk, int heads);
+
+/* The chunk attention reading the NVFP4 KV cache directly: the window is `num_blocks` cached blocks
+ * (oldest first; block b holds block_token_size tokens x heads rows of 128 channels, token-major /
+ * head-minor, as an NVFP4 matrix [rows_padded, 128] with swizzled scales and one fp32 amax) followed by
+ * the current chunk in bf16 (k_cur / v_cur: [L_cur, heads*128], row strides ldk / ldv; L_cur may be 0).
+ * Stands in for the reference's dequantize-every-block-then-attend sequence: dequantize_kv_cache on all
+ * max_blocks blocks of K and of V (utils/quant.py:731-768, utils/kernel/kv_dequant_cuda.cu:59-107; call
+ * sites wan_5b/modules/causal_model.py:557-600, 628-652), window assembly with torch.cat (:673-724) and
+ * attention() (:781, wan_5b/modules/attention.py:241-254).  Here the cached keys and values are decoded
+ * inside the attention kernel's load stage, with the rounding of the fused dequantize kernel
+ * (LLNV_DEQ_FUSED), so no bf16 copy of the cache exists and the result equals llnv_kv_dequant followed
+ * by llnv_attention_bf16_ex on the concatenated window bit for bit.
+ *   k_codes / k_sf / k_amax / v_*: HOST arrays of num_blocks (<= 16) DEVICE pointers, passed to the kernel
+ *   as launch parameters.  Codes must be 16-byte aligned.  num_blocks == 0 is llnv_attention_bf16_ex on
+ *   the current chunk.  key_splits / workspace / out_amax as in llnv_attention_bf16_ex, with
+ *   Lk = num_blocks * block_token_size + L_cur. */
+int llnv_attention_nvfp4kv(const void* q, int64_t Lq, int64_t ldq, const void* const* k_codes, const void* const* k_sf,
+                           const float* const* k_amax, const void* const* v_codes, const void* const* v_sf,
+                           const float* const* v_amax, int num_blocks, int block_token_size, float e2m1_max,
+                           float e4m3_max, const void* k_cur, const void* v_cur, int64_t L_cur, int64_t ldk, int64_t ldv,
+                           int heads, float scale, void* out, int64_t ldo, int key_splits, void* workspace,
+                           int64_t workspace_bytes, float* out_amax, llnv_stream_t stream);
 int64_t llnv_attention_workspace_bytes(int64_t Lq, int heads, int key_splits);
 
 /* Fused epilogue of the W4A4 GEMM.  All pointers are device pointers and optional (NULL = skip).
@@ -285,6 +319,17 @@ int llnv_gemm_nvfp4(const void* a_codes, const void* a_sf, const float* a_amax, 
                     const void* b_codes, const void* b_sf, const float* b_amax, int b_rule,
                     int64_t M, int64_t N, int64_t K, const llnv_epilogue_t* epilogue,
                     void* d, int64_t ldd, llnv_stream_t stream);
+
+/* llnv_gemm_nvfp4 with the tiling chosen by the caller instead of by shape (all tilings give the same
+ * bits: same products, same accumulation order along K): LLNV_GEMM_TILE_AUTO, 128 / 192 / 256 = one
+ * CTA per 128 x tile output tile (a width that does not divide N falls back to the automatic choice),
+ * LLNV_GEMM_TILE_PAIR = one 256 x 256 tile per pair of SMs (cta_group::2; needs N % 256 == 0).  The
+ * reference fixes one CUTLASS tile shape at compile time (fouroversix/src/fouroversix/csrc/fp4_gemm.cu:67-84). */
+enum { LLNV_GEMM_TILE_AUTO = 0, LLNV_GEMM_TILE_PAIR = 2 };
+int llnv_gemm_nvfp4_ex(const void* a_codes, const void* a_sf, const float* a_amax, int a_rule,
+                       const void* b_codes, const void* b_sf, const float* b_amax, int b_rule,
+                       int64_t M, int64_t N, int64_t K, const llnv_epilogue_t* epilogue,
+                       void* d, int64_t ldd, int tile, llnv_stream_t stream);
 
 /* Two or three Linears that share their input in one launch: B is the concatenation along N of
  * `groups` weight matrices of N_each rows (codes and swizzled scales concatenated, b_amax one fp32
@@ -364,8 +409,6 @@ int llnv_unipc_step(const void* model_output, const void* sample, const void* x0
  * launches.  Returns the previous setting.  The environment variable LLNV_PDL=1 switches it on at
  * load time.  Results do not depend on it; on a B200 it measured no gain for graph-replayed chunks. */
 int llnv_set_pdl(int on);
-int llnv_gemm_nvfp4_force_tile_n(int bn);       /* 0 = automatic, 128 or 256 */
-int llnv_gemm_nvfp4_debug(int flags);           /* timing experiments; results become wrong when non-zero */
 int llnv_selftest_div_const(int divisor, uint32_t first_bits, uint64_t count, unsigned long long* mismatches,
                             llnv_stream_t stream);
 

@@ -190,7 +190,7 @@ def load_state_dict_into(model, state_dict: Mapping, prefix: str = "model.", wei
     for blk in model.blocks:
         blk.fuse_qkv()
     model.modulation_all = torch.stack([blk.modulation for blk in model.blocks], 0)
-    model.text_kv = None                       # cached text K/V belong to the old weights
+    model._prompts = []                        # cached text K/V belong to the old weights
     model._graphs.clear()                      # captured graphs hold the old weight addresses
     model._time_cache.clear()                  # cached time embeddings belong to the old weights
     return [k for k in sd if k not in used]

@@ -22,7 +22,23 @@
 //              After the last tile the same warps normalise O and store it through swizzled
 //              shared memory (the Q tile's buffer) with TMA.
 // All mbarrier waits are bounded (sm100.cuh).
+//
+// NVFP4 key/value cache (attention_kernel<true>, llnv_attention_nvfp4kv).  The window is a list of
+// segments: cached NVFP4 blocks (E2M1 codes, E4M3 scale per 16 channels, one fp32 amax per block,
+// rows ordered token-major / head-minor) followed by the current chunk in bf16.  The cached part is
+// never materialised in global memory: four more warps (12-15) decode it inside the load stage.
+// Decode thread i owns key row i of a 128-key tile: it reads the row's 64 code bytes and 8 scale
+// bytes of K and of V straight from the cache block (prefetched one tile ahead into registers),
+// converts with the rounding of the standalone dequantize kernel,
+//     bf16( (e2m1 * e4m3) * (amax * fp32(1 / (6 * 256))) ),
+// and writes the bf16 row into the 128-byte-swizzled K / V stage the MMAs read -- the same bytes a
+// TMA load of the dequantized window would have put there, so the result equals dequantize-then-
+// attention bit for bit.  A tile that holds the last cached keys and the first keys of the current
+// chunk is also built by these warps (they copy the bf16 rows); tiles that lie entirely in the
+// current chunk come from TMA as before.  With 16 warps the register file is re-divided after
+// start-up (setmaxnreg): load/MMA warpgroup 56, decode warpgroup 104, softmax warpgroups 176.
 #include <cuda.h>
+#include <cuda_fp4.h>
 
 #include "common.cuh"
 #include "sm100.cuh"
@@ -46,7 +62,19 @@ constexpr uint32_t kBarOff = kVOff + kStages * kTileBytes;
 constexpr uint32_t kSmemBytes = kBarOff + 1024;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kSCol = 0, kOCol = 256;      // S_h at kSCol + 128 h, O_h at kOCol + 128 h
-constexpr int kThreads = 320;
+constexpr int kThreads = 320;            // bf16 window: load, MMA, 2 x 4 softmax warps
+constexpr int kThreadsFused = 512;       // NVFP4 window: four warpgroups (load + MMA, softmax a, softmax b, decode)
+constexpr int kMaxKvBlocks = 16;
+
+// Device pointers of the cached blocks of one layer (oldest first), passed as launch parameters.
+struct KvTable {
+  const uint8_t* k_codes[kMaxKvBlocks];
+  const uint8_t* k_sf[kMaxKvBlocks];
+  const float* k_amax[kMaxKvBlocks];
+  const uint8_t* v_codes[kMaxKvBlocks];
+  const uint8_t* v_sf[kMaxKvBlocks];
+  const float* v_amax[kMaxKvBlocks];
+};
 
 struct AttnParams {
   int64_t Lq, Lk;
@@ -59,7 +87,64 @@ struct AttnParams {
   float* part_o;               // [nsplit][Lq][heads][128] fp32
   float* part_ml;              // [nsplit][Lq][heads][2]   fp32: exponent offset m (raw score units), sum l
   float* out_amax;             // optional: max |out| over all written elements (zeroed by the host before the launch)
+  // NVFP4 window (attention_kernel<true>): the first n_cached keys live in cache blocks of block_tokens
+  // tokens each, the remaining Lk - n_cached keys are the bf16 tensors the K / V tensor maps describe
+  int64_t n_cached;
+  int block_tokens;
+  float inv_denom;             // fp32(1 / (e2m1_max * e4m3_max))
+  const uint16_t* k_cur;       // current chunk, bf16 [Lk - n_cached, heads * 128]: rows of the tile shared with the cache
+  const uint16_t* v_cur;
+  int64_t ldk, ldv;
 };
+
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+
+// One key row of a cached block as it arrives from global memory: 64 code bytes, 8 scale bytes.
+struct CodedRow {
+  uint4 c[4];
+  uint32_t sf[2];
+  float g;                      // amax * fp32(1 / (e2m1_max * e4m3_max)) of the row's block
+};
+
+// Decode one cached row (128 channels) into row i of a K / V stage: two halves of 64 channels, rows of
+// 128 bytes, 16-byte chunks XOR-swizzled with the row index as a TMA load with the 128-byte swizzle
+// writes them.  Arithmetic as decode16<LLNV_DEQ_FUSED> of the standalone dequantize kernel.
+__device__ __forceinline__ void decode_row_to_stage(const CodedRow& r, uint8_t* stage, int i) {
+  const uint32_t words[16] = {r.c[0].x, r.c[0].y, r.c[0].z, r.c[0].w, r.c[1].x, r.c[1].y, r.c[1].z, r.c[1].w,
+                              r.c[2].x, r.c[2].y, r.c[2].z, r.c[2].w, r.c[3].x, r.c[3].y, r.c[3].z, r.c[3].w};
+  const F2 g2 = f2_splat(r.g);
+#pragma unroll
+  for (int b = 0; b < 8; ++b) {                       // 16 channels per scale
+    const F2 s2 = f2_splat(e4m3_to_float((r.sf[b >> 2] >> (8 * (b & 3))) & 0xFFu));
+#pragma unroll
+    for (int wi = 0; wi < 2; ++wi) {                  // 8 channels = one 16-byte chunk of the bf16 row
+      const uint32_t w = words[2 * b + wi];
+      uint32_t o[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const __half2_raw h2 = __nv_cvt_fp4x2_to_halfraw2((__nv_fp4x2_storage_t)((w >> (8 * e)) & 0xFFu), __NV_E2M1);
+        const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+        const F2 d = f2_mul(f2_mul(F2{v.x, v.y}, s2), g2);
+        o[e] = pack_bf16x2(d.x, d.y);
+      }
+      const int chunk = 2 * b + wi;                   // 0..15
+      *reinterpret_cast<uint4*>(stage + (chunk >> 3) * kHalfBytes + i * 128 + (((chunk & 7) ^ (i & 7)) << 4)) =
+          make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+// Row i of a stage from 128 bf16 values in global memory (src == nullptr: zeros).
+__device__ __forceinline__ void copy_row_to_stage(const uint16_t* src, uint8_t* stage, int i) {
+#pragma unroll
+  for (int chunk = 0; chunk < 16; ++chunk) {
+    const uint4 v = src ? __ldg(reinterpret_cast<const uint4*>(src) + chunk) : make_uint4(0u, 0u, 0u, 0u);
+    *reinterpret_cast<uint4*>(stage + (chunk >> 3) * kHalfBytes + i * 128 + (((chunk & 7) ^ (i & 7)) << 4)) = v;
+  }
+}
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -110,11 +195,15 @@ __device__ __forceinline__ float ex2_poly(float x) {
 #define LLNV_ATTN_POLY_MOD 8        // every 8th score takes the FMA-pipe exp2 (measured best; 4 is already slower, 0 = none)
 #endif
 
-// 10 warps put three warps on some schedulers, whose 16 K-register files then allow 168 registers per thread
-__global__ void __launch_bounds__(kThreads, 1)
+// bf16 window: 10 warps put three warps on some schedulers, whose 16 K-register files then allow 168
+// registers per thread.  NVFP4 window: 16 warps start with 128 registers each and re-divide them.
+template <bool FUSED>
+__global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const AttnParams p) {
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const AttnParams p,
+                 const __grid_constant__ KvTable tab) {
   pdl_wait();
+  constexpr int kSoftmaxWarp0 = FUSED ? 4 : 2;       // first softmax warp (its TMEM lane quarter is warp % 4)
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* q_full = reinterpret_cast<uint64_t*>(smem + kBarOff);
   uint64_t* k_full = q_full + 1;
@@ -133,6 +222,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int j0 = (int)((int64_t)blockIdx.z * nt_all / p.nsplit);                  // first key tile of this split
   const int nt = (int)((int64_t)(blockIdx.z + 1) * nt_all / p.nsplit) - j0;       // >= 1: the host keeps nsplit <= nt_all
   const int n_half = ((int64_t)qt * kBQ + kHQ < p.Lq) ? 2 : 1;     // the second half may lie entirely beyond Lq
+  // key tiles [0, nd) of this split hold cached keys and are built by the decode warps, the rest come from TMA
+  int nd = 0;
+  if (FUSED) {
+    const int64_t cached_tiles = (p.n_cached + kBK - 1) / kBK - j0;
+    nd = cached_tiles <= 0 ? 0 : (cached_tiles < nt ? (int)cached_tiles : nt);
+  }
 
   if ((smem_u32(smem) & 1023u) != 0) {
     if (threadIdx.x == 0 && p.status && atomicCAS(p.status, 0u, 2u) == 0u) p.status[1] = 901u;
@@ -166,6 +261,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // NVFP4 window: the register file is re-divided at the top of every warpgroup's branch (all four warps of
+  // a warpgroup execute the same instruction; an increase waits for the other warpgroups' releases):
+  // 16 warps x 32 x 128 registers at launch = 128 x (56 + 104 + 2 x 176).
+  if (FUSED && warp < 4) setmaxnreg_dec<56>();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -179,14 +278,23 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int j = 0; j < nt; ++j) {
         const int s = j % kStages;
         const uint32_t ph = (uint32_t)((j / kStages) & 1);
+        if (j < nd) {
+          // a tile the decode warps build: only follow the stage's phases, one by one, so that the parity
+          // this thread waits for below can never be mistaken for that of an earlier use of the stage
+          mbar_wait(&k_empty[s], ph ^ 1u, abort_flag, p.status, 102u);
+          mbar_wait(&v_empty[s], ph ^ 1u, abort_flag, p.status, 103u);
+          continue;
+        }
+        // row of the tile's first key in the tensor the K / V maps describe (the whole window, or the current chunk)
+        const int krow = (j0 + j) * kBK - (FUSED ? (int)p.n_cached : 0);
         mbar_wait(&k_empty[s], ph ^ 1u, abort_flag, p.status, 100u);
         mbar_arrive_expect_tx(&k_full[s], kTileBytes);
-        tma_load_2d(smem + kKOff + s * kTileBytes, &tmK, col, (j0 + j) * kBK, &k_full[s]);
-        tma_load_2d(smem + kKOff + s * kTileBytes + kHalfBytes, &tmK, col + 64, (j0 + j) * kBK, &k_full[s]);
+        tma_load_2d(smem + kKOff + s * kTileBytes, &tmK, col, krow, &k_full[s]);
+        tma_load_2d(smem + kKOff + s * kTileBytes + kHalfBytes, &tmK, col + 64, krow, &k_full[s]);
         mbar_wait(&v_empty[s], ph ^ 1u, abort_flag, p.status, 101u);
         mbar_arrive_expect_tx(&v_full[s], kTileBytes);
-        tma_load_2d(smem + kVOff + s * kTileBytes, &tmV, col, (j0 + j) * kBK, &v_full[s]);
-        tma_load_2d(smem + kVOff + s * kTileBytes + kHalfBytes, &tmV, col + 64, (j0 + j) * kBK, &v_full[s]);
+        tma_load_2d(smem + kVOff + s * kTileBytes, &tmV, col, krow, &v_full[s]);
+        tma_load_2d(smem + kVOff + s * kTileBytes + kHalfBytes, &tmV, col + 64, krow, &v_full[s]);
       }
     }
   } else if (warp == 1) {
@@ -242,10 +350,67 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
     }
-  } else {
+  } else if (FUSED && warp >= 12) {
+    // ------------------------------------------------------------------ NVFP4 decode (warps 12..15)
+    setmaxnreg_dec<104>();
+    const int i = (int)threadIdx.x - 384;               // key row of the tile this thread builds
+    const int H = p.heads;
+    // where key row i of tile j lives: 0 = cache block (fetched into `row`), 1 = current chunk, 2 = beyond the window
+    auto fetch = [&](int j, CodedRow& kr, CodedRow& vr, int64_t& cur_row) -> int {
+      const int64_t key = (int64_t)(j0 + j) * kBK + i;
+      if (key >= p.n_cached) {
+        cur_row = key - p.n_cached;
+        return key < p.Lk ? 1 : 2;
+      }
+      const int b = (int)(key / p.block_tokens);
+      const int64_t r = (key - (int64_t)b * p.block_tokens) * H + head;      // row of the block: token-major, head-minor
+      const int64_t sf_off = (r >> 7) * 1024 + (r & 31) * 16 + ((r & 127) >> 5) * 4;   // scale columns 0..3; 4..7 are 512 bytes on
+      const uint4* kc = reinterpret_cast<const uint4*>(tab.k_codes[b] + r * 64);
+      const uint4* vc = reinterpret_cast<const uint4*>(tab.v_codes[b] + r * 64);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        kr.c[c] = __ldg(kc + c);
+        vr.c[c] = __ldg(vc + c);
+      }
+      kr.sf[0] = __ldg(reinterpret_cast<const uint32_t*>(tab.k_sf[b] + sf_off));
+      kr.sf[1] = __ldg(reinterpret_cast<const uint32_t*>(tab.k_sf[b] + sf_off + 512));
+      vr.sf[0] = __ldg(reinterpret_cast<const uint32_t*>(tab.v_sf[b] + sf_off));
+      vr.sf[1] = __ldg(reinterpret_cast<const uint32_t*>(tab.v_sf[b] + sf_off + 512));
+      kr.g = __fmul_rn(__ldg(tab.k_amax[b]), p.inv_denom);
+      vr.g = __fmul_rn(__ldg(tab.v_amax[b]), p.inv_denom);
+      return 0;
+    };
+    CodedRow k_nxt, v_nxt;
+    int64_t cur_nxt = 0;
+    int kind_nxt = 2;
+    if (nd > 0) kind_nxt = fetch(0, k_nxt, v_nxt, cur_nxt);
+    for (int j = 0; j < nd; ++j) {
+      const int s = j % kStages;
+      const uint32_t ph = (uint32_t)((j / kStages) & 1);
+      const CodedRow k_row = k_nxt, v_row = v_nxt;
+      const int64_t cur_row = cur_nxt;
+      const int kind = kind_nxt;
+      if (j + 1 < nd) kind_nxt = fetch(j + 1, k_nxt, v_nxt, cur_nxt);       // in flight while this tile is decoded
+      mbar_wait(&k_empty[s], ph ^ 1u, abort_flag, p.status, 400u);
+      uint8_t* kst = smem + kKOff + s * kTileBytes;
+      if (kind == 0) decode_row_to_stage(k_row, kst, i);
+      else copy_row_to_stage(kind == 1 ? p.k_cur + cur_row * p.ldk + (int64_t)head * kD : nullptr, kst, i);
+      fence_proxy_async();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (i == 0) mbar_arrive(&k_full[s]);
+      mbar_wait(&v_empty[s], ph ^ 1u, abort_flag, p.status, 401u);
+      uint8_t* vst = smem + kVOff + s * kTileBytes;
+      if (kind == 0) decode_row_to_stage(v_row, vst, i);
+      else copy_row_to_stage(kind == 1 ? p.v_cur + cur_row * p.ldv + (int64_t)head * kD : nullptr, vst, i);
+      fence_proxy_async();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (i == 0) mbar_arrive(&v_full[s]);
+    }
+  } else if (warp >= kSoftmaxWarp0 && warp < kSoftmaxWarp0 + 8) {
     // ------------------------------------------------------------------ softmax + epilogue
+    if (FUSED) setmaxnreg_inc<176>();
     const int q = warp & 3;
-    const int half = warp >= 6 ? 1 : 0;
+    const int half = warp >= kSoftmaxWarp0 + 4 ? 1 : 0;
     const uint32_t lane_base = (uint32_t)(q * 32) << 16;
     const float c = p.scale_log2;
     if (half < n_half) {
@@ -465,44 +630,55 @@ extern "C" int64_t llnv_attention_workspace_bytes(int64_t Lq, int heads, int key
   return (int64_t)key_splits * Lq * heads * (kD + 2) * (int64_t)sizeof(float);
 }
 
-extern "C" int llnv_attention_bf16_ex(const void* q, int64_t Lq, int64_t ldq, const void* k, const void* v, int64_t Lk,
-                                      int64_t ldk, int64_t ldv, int heads, float scale, void* out, int64_t ldo,
-                                      int key_splits, void* workspace, int64_t workspace_bytes, float* out_amax,
-                                      llnv_stream_t stream_) {
-  cudaStream_t stream = (cudaStream_t)stream_;
-  LLNV_REQUIRE(key_splits >= 1 && key_splits <= 64, "llnv_attention_bf16: key_splits must be in 1..64 (got %d)", key_splits);
-  LLNV_REQUIRE(Lk <= 0 || key_splits <= (Lk + kBK - 1) / kBK, "llnv_attention_bf16: more key splits (%d) than key tiles of 128", key_splits);
+namespace {
+
+// Shared host side of the two entry points.  kv == nullptr: k / v are the whole window (bf16).  Otherwise the window
+// is kv's cache blocks (n_cached keys) followed by the bf16 tensors k / v of Lk - n_cached keys.
+int attention_launch(const void* q, int64_t Lq, int64_t ldq, const void* k, const void* v, int64_t Lk, int64_t ldk, int64_t ldv,
+                     int heads, float scale, void* out, int64_t ldo, int key_splits, void* workspace, int64_t workspace_bytes,
+                     float* out_amax, const KvTable* kv, int64_t n_cached, int block_tokens, float inv_denom, cudaStream_t stream,
+                     const char* who) {
+  LLNV_REQUIRE(key_splits >= 1 && key_splits <= 64, "%s: key_splits must be in 1..64 (got %d)", who, key_splits);
+  LLNV_REQUIRE(Lk <= 0 || key_splits <= (Lk + kBK - 1) / kBK, "%s: more key splits (%d) than key tiles of 128", who, key_splits);
   if (key_splits > 1) {
     LLNV_REQUIRE(workspace != nullptr && ((uintptr_t)workspace & 15) == 0 &&
                      workspace_bytes >= llnv_attention_workspace_bytes(Lq, heads, key_splits),
-                 "llnv_attention_bf16: key splits need a 16-byte aligned workspace of llnv_attention_workspace_bytes() bytes");
+                 "%s: key splits need a 16-byte aligned workspace of llnv_attention_workspace_bytes() bytes", who);
   }
-  LLNV_REQUIRE(q && k && v && out, "llnv_attention_bf16: null pointer");
-  LLNV_REQUIRE(Lq >= 0 && Lk > 0 && heads > 0, "llnv_attention_bf16: need Lq >= 0, Lk > 0, heads > 0 (Lq=%lld Lk=%lld heads=%d)",
+  const int64_t L_cur = Lk - n_cached;               // keys held in bf16
+  LLNV_REQUIRE(q && out && (L_cur == 0 || (k && v)), "%s: null pointer", who);
+  LLNV_REQUIRE(Lq >= 0 && Lk > 0 && L_cur >= 0 && heads > 0, "%s: need Lq >= 0, Lk > 0, heads > 0 (Lq=%lld Lk=%lld heads=%d)", who,
                (long long)Lq, (long long)Lk, heads);
   const int64_t C = (int64_t)heads * kD;
-  LLNV_REQUIRE(ldq >= C && ldk >= C && ldv >= C && ldo >= C && ldq % 8 == 0 && ldk % 8 == 0 && ldv % 8 == 0 && ldo % 8 == 0,
-               "llnv_attention_bf16: row strides must be >= heads*128 and multiples of 8");
+  LLNV_REQUIRE(ldq >= C && ldo >= C && ldq % 8 == 0 && ldo % 8 == 0 && (L_cur == 0 || (ldk >= C && ldv >= C && ldk % 8 == 0 && ldv % 8 == 0)),
+               "%s: row strides must be >= heads*128 and multiples of 8", who);
   LLNV_REQUIRE(((uintptr_t)q & 15) == 0 && ((uintptr_t)k & 15) == 0 && ((uintptr_t)v & 15) == 0 && ((uintptr_t)out & 15) == 0,
-               "llnv_attention_bf16: pointers must be 16-byte aligned");
-  LLNV_REQUIRE(heads <= 65535, "llnv_attention_bf16: too many heads");
+               "%s: pointers must be 16-byte aligned", who);
+  LLNV_REQUIRE(heads <= 65535, "%s: too many heads", who);
   if (out_amax) LLNV_CUDA(cudaMemsetAsync(out_amax, 0, sizeof(float), stream));
   if (Lq == 0) return LLNV_OK;
   CUtensorMap tmQ, tmK, tmV, tmO;
   int rc = cached_tensor_map(&tmQ, 1, q, (uint64_t)Lq, (uint64_t)C, (uint64_t)ldq, 128, 64, 3);
   if (rc != LLNV_OK) return rc;
-  rc = cached_tensor_map(&tmK, 1, k, (uint64_t)Lk, (uint64_t)C, (uint64_t)ldk, 128, 64, 3);
-  if (rc != LLNV_OK) return rc;
-  rc = cached_tensor_map(&tmV, 1, v, (uint64_t)Lk, (uint64_t)C, (uint64_t)ldv, 128, 64, 3);
-  if (rc != LLNV_OK) return rc;
+  if (L_cur > 0) {
+    rc = cached_tensor_map(&tmK, 1, k, (uint64_t)L_cur, (uint64_t)C, (uint64_t)ldk, 128, 64, 3);
+    if (rc != LLNV_OK) return rc;
+    rc = cached_tensor_map(&tmV, 1, v, (uint64_t)L_cur, (uint64_t)C, (uint64_t)ldv, 128, 64, 3);
+    if (rc != LLNV_OK) return rc;
+  } else {
+    tmK = tmQ;                  // never used: every key tile is built by the decode warps
+    tmV = tmQ;
+  }
   rc = cached_tensor_map(&tmO, 1, out, (uint64_t)Lq, (uint64_t)C, (uint64_t)ldo, 32, 64, 3);
   if (rc != LLNV_OK) return rc;
-  static bool attr_set[64] = {};
+  static bool attr_set[2][64] = {};
   int dev = 0;
   LLNV_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    LLNV_CUDA(cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-    attr_set[dev] = true;
+  const int fused = kv != nullptr ? 1 : 0;
+  if (dev >= 0 && dev < 64 && !attr_set[fused][dev]) {
+    if (fused) LLNV_CUDA(cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+    else LLNV_CUDA(cudaFuncSetAttribute(attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+    attr_set[fused][dev] = true;
   }
   AttnParams p;
   p.Lq = Lq;
@@ -514,14 +690,68 @@ extern "C" int llnv_attention_bf16_ex(const void* q, int64_t Lq, int64_t ldq, co
   p.part_o = key_splits > 1 ? (float*)workspace : nullptr;
   p.part_ml = key_splits > 1 ? (float*)workspace + (int64_t)key_splits * Lq * heads * kD : nullptr;
   p.out_amax = key_splits > 1 ? nullptr : out_amax;
+  p.n_cached = n_cached;
+  p.block_tokens = block_tokens > 0 ? block_tokens : 1;
+  p.inv_denom = inv_denom;
+  p.k_cur = (const uint16_t*)k;
+  p.v_cur = (const uint16_t*)v;
+  p.ldk = ldk;
+  p.ldv = ldv;
   dim3 grid((unsigned)((Lq + kBQ - 1) / kBQ), (unsigned)heads, (unsigned)key_splits);
-  launch_k(attention_kernel, grid, kThreads, kSmemBytes, stream, tmQ, tmK, tmV, tmO, p);
+  static const KvTable no_blocks = {};
+  if (fused) launch_k(attention_kernel<true>, grid, kThreadsFused, kSmemBytes, stream, tmQ, tmK, tmV, tmO, p, *kv);
+  else launch_k(attention_kernel<false>, grid, kThreads, kSmemBytes, stream, tmQ, tmK, tmV, tmO, p, no_blocks);
   int st = launch_status("attention_kernel");
   if (st != LLNV_OK || key_splits == 1) return st;
   const int64_t units = Lq * heads;
   launch_k(attention_combine_kernel, (unsigned)((units + 7) / 8), 256, 0, stream, p.part_o, p.part_ml, key_splits, Lq, heads, p.scale_log2,
                                                                            (uint16_t*)out, ldo, out_amax);
   return launch_status("attention_combine_kernel");
+}
+
+}  // namespace
+
+extern "C" int llnv_attention_bf16_ex(const void* q, int64_t Lq, int64_t ldq, const void* k, const void* v, int64_t Lk,
+                                      int64_t ldk, int64_t ldv, int heads, float scale, void* out, int64_t ldo,
+                                      int key_splits, void* workspace, int64_t workspace_bytes, float* out_amax,
+                                      llnv_stream_t stream) {
+  LLNV_REQUIRE(k && v, "llnv_attention_bf16: null pointer");
+  return attention_launch(q, Lq, ldq, k, v, Lk, ldk, ldv, heads, scale, out, ldo, key_splits, workspace, workspace_bytes, out_amax,
+                          nullptr, 0, 0, 0.f, (cudaStream_t)stream, "llnv_attention_bf16");
+}
+
+extern "C" int llnv_attention_nvfp4kv(const void* q, int64_t Lq, int64_t ldq, const void* const* k_codes, const void* const* k_sf,
+                                      const float* const* k_amax, const void* const* v_codes, const void* const* v_sf,
+                                      const float* const* v_amax, int num_blocks, int block_token_size, float e2m1_max,
+                                      float e4m3_max, const void* k_cur, const void* v_cur, int64_t L_cur, int64_t ldk, int64_t ldv,
+                                      int heads, float scale, void* out, int64_t ldo, int key_splits, void* workspace,
+                                      int64_t workspace_bytes, float* out_amax, llnv_stream_t stream) {
+  const char* who = "llnv_attention_nvfp4kv";
+  LLNV_REQUIRE(num_blocks >= 0 && num_blocks <= kMaxKvBlocks, "%s: 0 to %d cache blocks (got %d)", who, kMaxKvBlocks, num_blocks);
+  LLNV_REQUIRE(L_cur >= 0 && (num_blocks > 0 || L_cur > 0), "%s: the window is empty", who);
+  if (num_blocks == 0)
+    return attention_launch(q, Lq, ldq, k_cur, v_cur, L_cur, ldk, ldv, heads, scale, out, ldo, key_splits, workspace, workspace_bytes,
+                            out_amax, nullptr, 0, 0, 0.f, (cudaStream_t)stream, who);
+  LLNV_REQUIRE(k_codes && k_sf && k_amax && v_codes && v_sf && v_amax, "%s: null pointer table", who);
+  LLNV_REQUIRE(block_token_size > 0 && heads > 0, "%s: block_token_size and heads must be positive", who);
+  LLNV_REQUIRE(e2m1_max > 0 && e4m3_max > 0, "%s: e2m1_max and e4m3_max must be positive", who);
+  KvTable tab = {};
+  for (int b = 0; b < num_blocks; ++b) {
+    LLNV_REQUIRE(k_codes[b] && k_sf[b] && k_amax[b] && v_codes[b] && v_sf[b] && v_amax[b], "%s: null pointer in block %d", who, b);
+    LLNV_REQUIRE(((uintptr_t)k_codes[b] & 15) == 0 && ((uintptr_t)v_codes[b] & 15) == 0 && ((uintptr_t)k_sf[b] & 3) == 0 &&
+                     ((uintptr_t)v_sf[b] & 3) == 0,
+                 "%s: codes of block %d must be 16-byte, scales 4-byte aligned", who, b);
+    tab.k_codes[b] = (const uint8_t*)k_codes[b];
+    tab.k_sf[b] = (const uint8_t*)k_sf[b];
+    tab.k_amax[b] = k_amax[b];
+    tab.v_codes[b] = (const uint8_t*)v_codes[b];
+    tab.v_sf[b] = (const uint8_t*)v_sf[b];
+    tab.v_amax[b] = v_amax[b];
+  }
+  const int64_t n_cached = (int64_t)num_blocks * block_token_size;
+  const float inv_denom = (float)(1.0 / ((double)e2m1_max * (double)e4m3_max));
+  return attention_launch(q, Lq, ldq, k_cur, v_cur, n_cached + L_cur, ldk, ldv, heads, scale, out, ldo, key_splits, workspace,
+                          workspace_bytes, out_amax, &tab, n_cached, block_token_size, inv_denom, (cudaStream_t)stream, who);
 }
 
 extern "C" int llnv_attention_bf16(const void* q, int64_t Lq, int64_t ldq, const void* k, const void* v, int64_t Lk,

@@ -71,7 +71,16 @@ extern "C" int llnv_set_pdl(int on) {
   return before;
 }
 
-extern "C" int llnv_version(void) { return 1; }
+extern "C" int llnv_version(void) { return 2; }
+
+extern "C" int llnv_init_device(void) {
+  if (!llnv::device_status_word()) {
+    llnv::set_error("llnv_init_device: could not allocate the device status word");
+    return LLNV_E_CUDA;
+  }
+  llnv::sm_count();
+  return LLNV_OK;
+}
 
 extern "C" const char* llnv_last_error(void) { return llnv::g_err; }
 

@@ -20,7 +20,6 @@ struct GemmParams {
   __nv_bfloat16* d;
   int64_t ldd;
   unsigned int* status;
-  int debug;               // timing experiments only: bit0 skip scale copies, bit1 one MMA per stage, bit2 skip stores
   // Grouped launch (1-CTA kernel): B is the concatenation along N of up to three weight matrices
   // of group_cols rows each, every one with its own tensor amax (b_amax[g]), output matrix and
   // optional output amax; 0 = one ordinary GEMM.

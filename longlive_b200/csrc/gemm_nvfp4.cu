@@ -180,17 +180,15 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             const uint32_t b_lo = a_lo + (C::kABytes >> 4);
             const uint32_t sfa_lo = (smem_base + s * C::kStageBytes + C::kABytes + C::kBBytes) >> 4;
             const uint32_t sfb_lo = sfa_lo + (C::kSfaBytes >> 4);
-            if (!(p.debug & 1) || kb == 0) {
 #pragma unroll
-              for (int g = 0; g < 4; ++g) {
-                tmem_cp_sf(tmem_base + C::kSfaCol + 4 * g, ((uint64_t)kSfHi << 32) | (sfa_lo + 32 * g));
+            for (int g = 0; g < 4; ++g) {
+              tmem_cp_sf(tmem_base + C::kSfaCol + 4 * g, ((uint64_t)kSfHi << 32) | (sfa_lo + 32 * g));
 #pragma unroll
-                for (int h = 0; h < C::kSfbAtoms; ++h)
-                  tmem_cp_sf(tmem_base + C::kSfbCol + C::kSfbColsPerK * g + 4 * h, ((uint64_t)kSfHi << 32) | (sfb_lo + 128 * h + 32 * g));
-              }
+              for (int h = 0; h < C::kSfbAtoms; ++h)
+                tmem_cp_sf(tmem_base + C::kSfbCol + C::kSfbColsPerK * g + 4 * h, ((uint64_t)kSfHi << 32) | (sfb_lo + 128 * h + 32 * g));
             }
 #pragma unroll
-            for (int k = 0; k < ((p.debug & 2) ? 1 : 4); ++k) {
+            for (int k = 0; k < 4; ++k) {
               // 64 E2M1 elements = 32 bytes further along K inside the 128-byte swizzled row
               mma_nvf4(d_tmem, ((uint64_t)kOpHi << 32) | (a_lo + 2 * k), ((uint64_t)kOpHi << 32) | (b_lo + 2 * k), idesc,
                        tmem_base + C::kSfaCol + 4 * k, tmem_base + C::kSfbCol + C::kSfbColsPerK * k + sfb_col0, (kb | k) != 0 ? 1u : 0u);
@@ -266,7 +264,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       auto finish_chunk = [&](int c0, const uint32_t (&pkc)[32]) {
         const uint32_t b = C::kAcc == 1 ? (uint32_t)(c0 >> 6) : (chunk & 1u);
         uint8_t* buf = my_stage + b * 4096;
-        if (row0 < p.M && !(p.debug & 4)) {
+        if (row0 < p.M) {
           if (C::kAcc == 1) {
             if (has_res) {
               mbar_wait(&my_res_bar[b], (res_phase >> b) & 1u, abort_flag, p.status, 301u);
@@ -289,7 +287,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           epilogue_packed<EPI>(pkc, bias, grow, col, buf, lane, want_amax, row_ok, local_amax);
           fence_proxy_async();
           __syncwarp();
-          if (lane == 0 && !(p.debug & 8)) {
+          if (lane == 0) {
             tma_store_2d(tm_out, buf, (int)(col - gcol0), row0);  // rows beyond M are clipped by the tensor map
             bulk_commit();
           }
@@ -374,9 +372,6 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
 // ---- host side ------------------------------------------------------------------------------
 
-int g_forced_bn = 0;
-int g_debug = 0;
-
 int get_codes_map(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
   return cached_tensor_map(out, 0, ptr, rows, row_bytes, row_bytes, box_rows, BK_BYTES, 3);
 }
@@ -409,20 +404,6 @@ int gemm_nvfp4_pair(const void* a_codes, const void* a_sf, const void* b_codes, 
 
 using namespace llnv;
 
-// Test/benchmark hook: force the kernel: 128 / 256 = one CTA per tile with that N tile, 2 = CTA pairs
-// (256 x 256 tile per pair); 0 restores the automatic choice.
-extern "C" int llnv_gemm_nvfp4_force_tile_n(int bn) {
-  LLNV_REQUIRE(bn == 0 || bn == 2 || bn == 128 || bn == 192 || bn == 256, "llnv_gemm_nvfp4_force_tile_n: tile must be 0, 2, 128, 192 or 256");
-  g_forced_bn = bn;
-  return LLNV_OK;
-}
-
-// Timing experiments only (results become wrong): see GemmParams::debug.
-extern "C" int llnv_gemm_nvfp4_debug(int flags) {
-  g_debug = flags;
-  return LLNV_OK;
-}
-
 namespace {
 
 // groups == 1: one GEMM into d.  groups == 2 or 3: B holds that many weight matrices of N / groups rows
@@ -430,7 +411,7 @@ namespace {
 // and its output amax, if wanted, to amax_groups[g].
 int gemm_run(const void* a_codes, const void* a_sf, const float* a_amax, int a_rule, const void* b_codes, const void* b_sf,
              const float* b_amax, int b_rule, int64_t M, int64_t N, int64_t K, const llnv_epilogue_t* epilogue, void* d, int64_t ldd,
-             cudaStream_t stream, int groups, void* const* d_groups, const int64_t* ldd_groups, float* const* amax_groups) {
+             cudaStream_t stream, int groups, void* const* d_groups, const int64_t* ldd_groups, float* const* amax_groups, int tile) {
   LLNV_REQUIRE(a_codes && a_sf && b_codes && b_sf && d, "llnv_gemm_nvfp4: null pointer");
   LLNV_REQUIRE(M >= 0 && N > 0 && K > 0, "llnv_gemm_nvfp4: bad shape M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
   LLNV_REQUIRE(N % 128 == 0, "llnv_gemm_nvfp4: N must be a multiple of 128 (got %lld)", (long long)N);
@@ -438,6 +419,9 @@ int gemm_run(const void* a_codes, const void* a_sf, const float* a_amax, int a_r
   LLNV_REQUIRE(ldd >= N / groups && ldd % 8 == 0 && ((uintptr_t)d & 15) == 0, "llnv_gemm_nvfp4: d must be 16-byte aligned with ldd a multiple of 8");
   LLNV_REQUIRE(((uintptr_t)a_sf & 15) == 0 && ((uintptr_t)b_sf & 15) == 0, "llnv_gemm_nvfp4: scale arrays must be 16-byte aligned");
   LLNV_REQUIRE(a_rule >= 0 && a_rule <= 4 && b_rule >= 0 && b_rule <= 4, "llnv_gemm_nvfp4: unknown scale rule");
+  LLNV_REQUIRE(tile == LLNV_GEMM_TILE_AUTO || tile == LLNV_GEMM_TILE_PAIR || tile == 128 || tile == 192 || tile == 256,
+               "llnv_gemm_nvfp4: tile must be 0 (automatic), 128, 192, 256 or LLNV_GEMM_TILE_PAIR (got %d)", tile);
+  
   llnv_epilogue_t epi;
   memset(&epi, 0, sizeof(epi));
   if (epilogue) epi = *epilogue;
@@ -456,9 +440,9 @@ int gemm_run(const void* a_codes, const void* a_sf, const float* a_amax, int a_r
   // less than one wave of 256-wide tiles: 192-wide ones fill more SMs (and overlap their epilogue
   // with the next main loop); with more tiles the lower operand traffic of the 256-wide tile wins
   else if (bn == 256 && N % 192 == 0 && (groups == 1 || group_cols % 192 == 0) && ((M + 127) / 128) * (N / 256) <= (int64_t)sm_count()) bn = 192;
-  if (g_forced_bn == 128) bn = 128;
-  if (g_forced_bn == 192 && N % 192 == 0 && (groups == 1 || group_cols % 192 == 0)) bn = 192;
-  if (g_forced_bn == 256 && N % 256 == 0 && (groups == 1 || group_cols % 256 == 0)) bn = 256;
+  if (tile == 128) bn = 128;
+  if (tile == 192 && N % 192 == 0 && (groups == 1 || group_cols % 192 == 0)) bn = 192;
+  if (tile == 256 && N % 256 == 0 && (groups == 1 || group_cols % 256 == 0)) bn = 256;
 
   const uint64_t mp = (uint64_t)((M + 127) / 128 * 128);
   CUtensorMap tmA, tmB;
@@ -480,7 +464,6 @@ int gemm_run(const void* a_codes, const void* a_sf, const float* a_amax, int a_r
   p.d = (__nv_bfloat16*)d;
   p.ldd = ldd;
   p.status = device_status_word();
-  p.debug = g_debug;
   CUtensorMap tmD, tmR;
   GroupMaps gmaps;
   memset(&gmaps, 0, sizeof(gmaps));
@@ -503,8 +486,8 @@ int gemm_run(const void* a_codes, const void* a_sf, const float* a_amax, int a_r
   const int variant = (epi.bias ? kEpiBias : 0) | (epi.act == 1 ? kEpiGelu : 0) | (epi.residual ? kEpiRes : 0);
   // CTA pairs pay off when the K loop dominates (measured: +13..17 % at K = 14336, no gain at K = 3072)
   const bool pair_ok = N % 256 == 0;
-  const bool pair_auto = g_forced_bn == 0 && K >= 8192 && M >= 1024 && groups == 1;
-  if (pair_ok && groups == 1 && (g_forced_bn == 2 || pair_auto)) return gemm_nvfp4_pair(a_codes, a_sf, b_codes, b_sf, p, tmD, tmR, variant, stream);
+  const bool pair_auto = tile == 0 && K >= 8192 && M >= 1024 && groups == 1;
+  if (pair_ok && groups == 1 && (tile == 2 || pair_auto)) return gemm_nvfp4_pair(a_codes, a_sf, b_codes, b_sf, p, tmD, tmR, variant, stream);
 #define LLNV_GEMM_CASE(V)                                                                   \
   case V:                                                                                   \
     return bn == 256   ? launch<256, V>(tmA, tmB, tmD, tmR, p, stream, gmaps)                     \
@@ -531,7 +514,14 @@ extern "C" int llnv_gemm_nvfp4(const void* a_codes, const void* a_sf, const floa
                                const void* b_sf, const float* b_amax, int b_rule, int64_t M, int64_t N, int64_t K,
                                const llnv_epilogue_t* epilogue, void* d, int64_t ldd, llnv_stream_t stream) {
   return gemm_run(a_codes, a_sf, a_amax, a_rule, b_codes, b_sf, b_amax, b_rule, M, N, K, epilogue, d, ldd, (cudaStream_t)stream, 1, nullptr,
-                  nullptr, nullptr);
+                  nullptr, nullptr, LLNV_GEMM_TILE_AUTO);
+}
+
+extern "C" int llnv_gemm_nvfp4_ex(const void* a_codes, const void* a_sf, const float* a_amax, int a_rule, const void* b_codes,
+                                  const void* b_sf, const float* b_amax, int b_rule, int64_t M, int64_t N, int64_t K,
+                                  const llnv_epilogue_t* epilogue, void* d, int64_t ldd, int tile, llnv_stream_t stream) {
+  return gemm_run(a_codes, a_sf, a_amax, a_rule, b_codes, b_sf, b_amax, b_rule, M, N, K, epilogue, d, ldd, (cudaStream_t)stream, 1, nullptr,
+                  nullptr, nullptr, tile);
 }
 
 extern "C" int llnv_gemm_nvfp4_grouped(const void* a_codes, const void* a_sf, const float* a_amax, int a_rule, const void* b_codes,
@@ -551,5 +541,5 @@ extern "C" int llnv_gemm_nvfp4_grouped(const void* a_codes, const void* a_sf, co
       if (out_amax[g]) LLNV_CUDA(cudaMemsetAsync(out_amax[g], 0, sizeof(float), (cudaStream_t)stream));
   }
   return gemm_run(a_codes, a_sf, a_amax, a_rule, b_codes, b_sf, b_amax, b_rule, M, N_each * groups, K, epilogue, d[0], ldd[0],
-                  (cudaStream_t)stream, groups, d, ldd, out_amax);
+                  (cudaStream_t)stream, groups, d, ldd, out_amax, LLNV_GEMM_TILE_AUTO);
 }

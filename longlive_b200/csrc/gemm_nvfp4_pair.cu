@@ -226,7 +226,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster_addr(mapa_u32(&tempty_bar[b], 0));
           }
-          if (row0 < p.M && !(p.debug & 4)) {
+          if (row0 < p.M) {
             if (has_res) {
               if (c0 + 64 < 128 && lane == 0) {
                 bulk_wait_read<0>();

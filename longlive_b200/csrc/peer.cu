@@ -19,22 +19,25 @@
 // replays correctly): thread r of the single CTA stores e into flag[my_rank] of rank r
 // (st.release.sys), then polls its own flag[r] until it is >= e (ld.acquire.sys).  Epochs only
 // grow, so a rank that is already one barrier ahead cannot be missed.  The poll is bounded: after
-// kPeerPolls polls the kernel records a timeout in the status word (read by llnv_check_status) and
-// returns; it never traps and never spins forever.
+// max_polls polls (a launch parameter; llnv_set_peer_poll_limit, default a few seconds) the kernel
+// records a timeout in the status word (read by llnv_check_status) and returns; it never traps and
+// never spins forever.  What a consumer reads after a timed-out barrier is undefined, so callers
+// check the status before they use a step's results (CausalDiT.run_chunk does, once per chunk).
 #include "common.cuh"
 
 namespace llnv {
 namespace {
 
-constexpr uint32_t kPeerPolls = 1u << 22;     // a few seconds of polling before giving up
+constexpr uint32_t kDefaultPeerPolls = 1u << 22;     // a few seconds of polling before giving up
 constexpr int kMaxPeers = 8;
+uint32_t g_peer_polls = kDefaultPeerPolls;
 
 struct PeerPtrs {
   void* p[kMaxPeers];
 };
 
 __global__ void __launch_bounds__(32) peer_barrier_kernel(PeerPtrs signals, int rank, int world, unsigned int* epoch,
-                                                          unsigned int* status) {
+                                                          unsigned int* status, uint32_t max_polls) {
   pdl_wait();
   __shared__ unsigned int e_sh;
   if (threadIdx.x == 0) e_sh = *epoch + 1u;
@@ -47,7 +50,7 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(PeerPtrs signals, int 
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(e) : "memory");
     const unsigned int* mine = reinterpret_cast<const unsigned int*>(signals.p[rank]) + r;
     ok = false;
-    for (uint32_t i = 0; i < kPeerPolls; ++i) {
+    for (uint32_t i = 0; i < max_polls; ++i) {
       unsigned int v;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
       if ((int)(v - e) >= 0) {
@@ -71,7 +74,8 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(PeerPtrs signals, int 
 // arrays alternate with the epoch, so a rank that is already in the next reduction cannot overwrite
 // values a slower rank has not read yet (it cannot be two reductions ahead: each one is a barrier).
 __global__ void __launch_bounds__(32) peer_allreduce_max_kernel(float* __restrict__ vals, int n, PeerPtrs slots, PeerPtrs signals,
-                                                                int rank, int world, unsigned int* epoch, unsigned int* status) {
+                                                                int rank, int world, unsigned int* epoch, unsigned int* status,
+                                                                uint32_t max_polls) {
   pdl_wait();
   __shared__ unsigned int e_sh;
   if (threadIdx.x == 0) e_sh = *epoch + 1u;
@@ -87,7 +91,7 @@ __global__ void __launch_bounds__(32) peer_allreduce_max_kernel(float* __restric
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(e) : "memory");
     const unsigned int* mine = reinterpret_cast<const unsigned int*>(signals.p[rank]) + r;
     ok = false;
-    for (uint32_t i = 0; i < kPeerPolls; ++i) {
+    for (uint32_t i = 0; i < max_polls; ++i) {
       unsigned int v;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
       if ((int)(v - e) >= 0) {
@@ -137,6 +141,12 @@ __global__ void __launch_bounds__(256) scatter_2d_kernel(const uint8_t* __restri
 
 using namespace llnv;
 
+extern "C" int llnv_set_peer_poll_limit(unsigned int max_polls) {
+  const unsigned int before = g_peer_polls;
+  g_peer_polls = max_polls ? max_polls : kDefaultPeerPolls;
+  return (int)(before > 0x7FFFFFFFu ? 0x7FFFFFFFu : before);
+}
+
 extern "C" int llnv_peer_barrier(void* const* signal_ptrs, int rank, int world, void* epoch, llnv_stream_t stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   LLNV_REQUIRE(signal_ptrs && epoch, "llnv_peer_barrier: null pointer");
@@ -146,7 +156,7 @@ extern "C" int llnv_peer_barrier(void* const* signal_ptrs, int rank, int world, 
     LLNV_REQUIRE(signal_ptrs[r] != nullptr && ((uintptr_t)signal_ptrs[r] & 3) == 0, "llnv_peer_barrier: bad signal pointer of rank %d", r);
     sp.p[r] = signal_ptrs[r];
   }
-  launch_k(peer_barrier_kernel, 1, 32, 0, stream, sp, rank, world, (unsigned int*)epoch, device_status_word());
+  launch_k(peer_barrier_kernel, 1, 32, 0, stream, sp, rank, world, (unsigned int*)epoch, device_status_word(), g_peer_polls);
   return launch_status("peer_barrier_kernel");
 }
 
@@ -163,7 +173,7 @@ extern "C" int llnv_peer_allreduce_max(float* vals, int n, void* const* slot_ptr
     sl.p[r] = slot_ptrs[r];
     sg.p[r] = signal_ptrs[r];
   }
-  launch_k(peer_allreduce_max_kernel, 1, 32, 0, stream, vals, n, sl, sg, rank, world, (unsigned int*)epoch, device_status_word());
+  launch_k(peer_allreduce_max_kernel, 1, 32, 0, stream, vals, n, sl, sg, rank, world, (unsigned int*)epoch, device_status_word(), g_peer_polls);
   return launch_status("peer_allreduce_max_kernel");
 }
 

@@ -8,9 +8,9 @@ block table instead of copying slots.  Random-init weights of the reference's sh
 embedding, time/text MLPs and the head are plain bf16 torch ops (outside the hot path).
 
 Per block and forward (S tokens of the chunk, window = cached blocks + current chunk):
-  adaLN(e0,e1)+quantize -> q,k,v GEMMs(+bias; v also emits its amax and lands in the V window)
-  -> RMSNorm+RoPE (q) / RMSNorm+RoPE+k_smooth+amax (k, smoothed copy lands in the K window)
-  -> NVFP4 cache blocks dequantized into the window -> attention -> quantize -> o GEMM(+bias,
+  adaLN(e0,e1)+quantize -> q,k,v GEMMs(+bias; v also emits its amax)
+  -> RMSNorm+RoPE (q) / RMSNorm+RoPE+k_smooth+amax (k)
+  -> attention over [NVFP4 cache blocks, decoded inside the kernel | current chunk] -> quantize -> o GEMM(+bias,
   gate e2, residual) -> LayerNorm+quantize -> cross q GEMM -> RMSNorm -> attention over the text
   K/V -> quantize -> o GEMM(+bias, residual) -> adaLN(e3,e4)+quantize -> FFN GEMM(+bias, GELU, amax)
   -> quantize (amax given) -> FFN GEMM(+bias, gate e5, residual); then the rotated keys and the
@@ -255,47 +255,42 @@ class CausalDiT:
         self.q_buf, self.k_buf, self.v_buf = bf(Sl, c), bf(Sl, c), bf(Sl, c)
         self.q_rot, self.k_rot, self.k_smooth = bf(Sl, c), bf(Sl, c), bf(Sl, c)
         self.attn_out = bf(S, self.Cl)
-        Lk = cfg.window_frames * cfg.frame_tokens
         self.arena = None
+        self.check_peer_status = True         # run_chunk raises ops.DeviceTimeout when a peer barrier gave up
         if self.P > 1:
             P_, Cl_ = self.P, self.Cl
             if peer_exchange:
                 # exchange targets in symmetric memory: peers store into them directly (longlive_b200/csrc/peer.cu)
-                layout = {"q_h": S * Cl_ * 2, "kr_h": S * Cl_ * 2, "attn_sh": S * Cl_ * 2}
-                for li in range(cfg.layers):
-                    layout[f"win_k{li}"] = Lk * Cl_ * 2
-                    layout[f"win_v{li}"] = Lk * Cl_ * 2
+                layout = {name: S * Cl_ * 2 for name in ("q_h", "kr_h", "cur_k", "cur_v", "attn_sh")}
                 self.arena = sp.PeerArena.create(sp_group, dev, layout)
             if self.arena is not None:
                 self.q_h, self.kr_h = self.arena.tensor("q_h", (S, Cl_)), self.arena.tensor("kr_h", (S, Cl_))
+                self.cur_k, self.cur_v = self.arena.tensor("cur_k", (S, Cl_)), self.arena.tensor("cur_v", (S, Cl_))
                 self.attn_sh = self.arena.tensor("attn_sh", (P_, Sl, Cl_))
             else:
                 # NCCL exchange: send / receive layouts [rank][my tokens][that rank's heads] and
                 # [all tokens][my heads], written and read in place by the kernels on either side
                 self.q_sh, self.kr_sh, self.ks_sh, self.v_sh = bf(P_, Sl, Cl_), bf(P_, Sl, Cl_), bf(P_, Sl, Cl_), bf(P_, Sl, Cl_)
                 self.q_h, self.kr_h = bf(S, Cl_), bf(S, Cl_)
+                self.cur_k, self.cur_v = bf(S, Cl_), bf(S, Cl_)
                 self.attn_sh = bf(P_, Sl, Cl_)
+        else:
+            self.cur_k, self.cur_v = bf(S, self.Cl), bf(S, self.Cl)
         self.x_a, self.x_b, self.x1, self.x2 = bf(Sl, c), bf(Sl, c), bf(Sl, c), bf(Sl, c)
         self.hidden = bf(Sl, cfg.ffn_dim)
         self.cq_buf, self.cq_n = bf(Sl, c), bf(Sl, c)
         self.ck_buf, self.cv_buf, self.ck_n = bf(cfg.text_len, c), bf(cfg.text_len, c), bf(cfg.text_len, c)
         self.cattn = bf(Sl, c)
-        # One bf16 attention window per layer.  The past blocks of a window do not change during
-        # the forwards of a chunk, so they are dequantized from the NVFP4 cache once per chunk (by the
-        # first forward after the block table moved) instead of once per forward as the reference does
-        # (causal_model.py:591-600); 2 x 81 MB per layer at full size.
-        if self.arena is not None:
-            self.win_k = [self.arena.tensor(f"win_k{li}", (Lk, self.Cl)) for li in range(cfg.layers)]
-            self.win_v = [self.arena.tensor(f"win_v{li}", (Lk, self.Cl)) for li in range(cfg.layers)]
-        else:
-            self.win_k = [bf(Lk, self.Cl) for _ in range(cfg.layers)]
-            self.win_v = [bf(Lk, self.Cl) for _ in range(cfg.layers)]
-        self._window_version = -1             # cache.version whose past blocks the windows hold
+        # The attention window is never materialised: the attention kernel decodes the NVFP4 cache blocks
+        # of the layer in its load stage and reads the current chunk's smoothed keys / values from cur_k /
+        # cur_v ([all chunk tokens, my heads], one pair shared by all layers; the reference dequantizes every
+        # block into a bf16 window per layer and forward, causal_model.py:557-600).
         self.kv_amax = torch.zeros(2, dtype=torch.float32, device=dev)      # [k, v]: reduced with one collective
         self.k_amax, self.v_amax = self.kv_amax[0:1], self.kv_amax[1:2]
         self.h_amax = torch.zeros(1, dtype=torch.float32, device=dev)
         self.modulation_all = torch.stack([b.modulation for b in self.blocks], 0)       # [layers, 1, 6, dim]
-        self.text_kv: list | None = None
+        self._prompts: list = []              # cached cross-attention K / V per prompt tensor, most recent last
+        self._prompt_serial = 0
         self.cache = KVCache(cfg, Hl, dev)
         # static inputs of a forward (a captured graph reads these addresses on every replay)
         self.g_lat = bf(Sl, cfg.patch_dim)
@@ -375,25 +370,47 @@ class CausalDiT:
     def encode_text(self, ctx_raw: torch.Tensor) -> torch.Tensor:
         """[text_len, text_dim] -> [text_len, dim] (text_embedding MLP, wan_5b/modules/causal_model.py:1568-1573)."""
         h = self._edge(ctx_raw.contiguous(), self.text_w0, self.text_b0, act="gelu_tanh")
-        self.text_kv = None
         return self._edge(h, self.text_w1, self.text_b1).contiguous()
+
+    MAX_PROMPTS = 4
+
+    def _prompt(self, ctx: torch.Tensor) -> dict:
+        """The cache entry of a prompt: the context tensor itself (object identity plus its in-place
+        modification counter), so two prompts encoded up front never share cached K / V, and a tensor
+        that was freed and whose address was reused cannot be mistaken for the old prompt (the entry
+        keeps the tensor alive).  Entries carry a serial number that is part of a captured graph's key;
+        when the oldest of MAX_PROMPTS entries is dropped, the graphs captured for it go with it."""
+        for ent in self._prompts:
+            if ent["ctx"] is ctx and ent["version"] == ctx._version:
+                return ent
+        self._prompt_serial += 1
+        ent = {"ctx": ctx, "version": ctx._version, "serial": self._prompt_serial, "kv": [None] * self.cfg.layers}
+        self._prompts.append(ent)
+        while len(self._prompts) > self.MAX_PROMPTS:
+            old = self._prompts.pop(0)
+            self._graphs = {k: g for k, g in self._graphs.items() if k[2] != old["serial"]}
+        return ent
 
     def _text_kv(self, layer: int, blk: Block, ctx: torch.Tensor):
         """Cross-attention K (RMS-normed) and V of the text context.  The reference recomputes them on
-        every call (causal_model.py:229-235); they depend only on the prompt, so they are cached."""
-        if self.cache_text_kv and self.text_kv is not None and self.text_kv[layer] is not None:
-            return self.text_kv[layer]
+        every call (causal_model.py:229-235); they depend only on the prompt, so they are cached per
+        prompt tensor (``_prompt``)."""
+        ent = self._prompt(ctx) if self.cache_text_kv else None
+        if ent is not None and ent["kv"][layer] is not None:
+            return ent["kv"][layer]
         cfg = self.cfg
         if layer == 0 or not self.cache_text_kv:
             ops.quantize_nvfp4(ctx, MSE, self.act_t.amax, self.act_t.codes, self.act_t.sf, amax_given=False)
         k = self._gemm(self.act_t, cfg.text_len, blk.ck, None if self.cache_text_kv else self.ck_buf)
         v = self._gemm(self.act_t, cfg.text_len, blk.cv, None if self.cache_text_kv else self.cv_buf)
         kn, _, _ = ops.rmsnorm_rope(k, blk.cnorm_k, eps=cfg.eps, out=None if self.cache_text_kv else self.ck_n)
-        if self.cache_text_kv:
-            if self.text_kv is None:
-                self.text_kv = [None] * cfg.layers
-            self.text_kv[layer] = (kn, v)
+        if ent is not None:
+            ent["kv"][layer] = (kn, v)
         return kn, v
+
+    def _text_ready(self, ctx: torch.Tensor) -> bool:
+        """True when a forward with this prompt computes no text K / V (nothing to cache, or all cached)."""
+        return not self.cache_text_kv or all(kv is not None for kv in self._prompt(ctx)["kv"])
 
     # ---- one block ----------------------------------------------------------------------------
     def block_forward(self, li: int, x: torch.Tensor, x_out: torch.Tensor, e: torch.Tensor, ctx, cos, sin):
@@ -403,12 +420,10 @@ class CausalDiT:
         roff = self.rank * Sl
         # -- self attention
         self._adaln_quantize(x, e[:, 1], e[:, 0], self.act_c)
-        n_past = len(cache.past_slots())
         T = cfg.chunk_tokens
-        win_k, win_v = self.win_k[li], self.win_v[li]
-        cur_k, cur_v = win_k[n_past * T:(n_past + 1) * T], win_v[n_past * T:(n_past + 1) * T]
+        cur_k, cur_v = self.cur_k, self.cur_v
         ck, cv = cache.k[li][cache.current_slot()], cache.v[li][cache.current_slot()]
-        # q, k and v projections in one grouped launch; V lands in the window (one GPU) or in v_buf, with its amax
+        # q, k and v projections in one grouped launch; V lands in cur_v (one GPU) or in v_buf, with its amax
         v_out = cur_v if self.P == 1 else self.v_buf
         v_am = cv.amax if self.P == 1 else self.v_amax
         if blk.qkv_ok:
@@ -428,13 +443,14 @@ class CausalDiT:
         elif self.arena is not None:
             # tokens -> heads over peer memory: every producer stores each head shard at its final
             # address on the rank that owns those heads (q, rotated keys for the cache, smoothed keys
-            # and values in that rank's window); one barrier makes all of it visible
+            # and values of the chunk); one barrier makes all of it visible.  The buffers are shared by
+            # all layers: a rank overwrites them for the next layer only after the barrier behind this
+            # layer's attention, which every rank reaches after its attention kernel has finished.
             ar, Cl = self.arena, self.Cl
             row_off = self.rank * Sl * Cl * 2                   # my token block inside an [S, Cl] buffer
-            cur_off = n_past * T * Cl * 2 + row_off            # ... inside the current-chunk part of a window
             ops.rmsnorm_rope_qk(self.q_buf, blk.norm_q, ar.ptrs("q_h", row_off), Cl, self.k_buf, blk.norm_k, ar.ptrs("kr_h", row_off), Cl,
-                                ar.ptrs(f"win_k{li}", cur_off), Cl, self.k_amax, cos, sin, cfg.eps)
-            ops.scatter_2d(self.v_buf, Cl * 2, ar.ptrs(f"win_v{li}", cur_off), Cl * 2, Sl, Cl * 2)
+                                ar.ptrs("cur_k", row_off), Cl, self.k_amax, cos, sin, cfg.eps)
+            ops.scatter_2d(self.v_buf, Cl * 2, ar.ptrs("cur_v", row_off), Cl * 2, Sl, Cl * 2)
             # the barrier that publishes the stores above also carries the K / V amax: its group maximum
             # is the tensor scale of every rank's cache block (and the one a single GPU would use)
             ar.allreduce_max_(self.kv_amax)
@@ -456,21 +472,14 @@ class CausalDiT:
             for w in (w_q, w_ks, w_kr, w_v):
                 w.wait()
             q_h, k_for_cache, v_for_cache = self.q_h, self.kr_h, cur_v
-        if n_past and self._window_version != cache.version:
-            slots = cache.past_slots()
-            ops.kv_dequant([cache.k[li][s].values for s in slots], [cache.k[li][s].scale_factors for s in slots],
-                           [cache.k[li][s].amax for s in slots], self.Hl, T, torch.bfloat16, 6, 256, ops.DEQ_FUSED,
-                           out=win_k[: n_past * T])
-            ops.kv_dequant([cache.v[li][s].values for s in slots], [cache.v[li][s].scale_factors for s in slots],
-                           [cache.v[li][s].amax for s in slots], self.Hl, T, torch.bfloat16, 6, 256, ops.DEQ_FUSED,
-                           out=win_v[: n_past * T])
-        lk = (n_past + 1) * T
+        past = cache.past_slots()
         # The attention epilogue also produces max |out|.  Across a sequence-parallel group that is
         # the amax of (all tokens, my heads), which bounds the (my tokens, all heads) tensor quantized
         # after the exchange only once it is MAX-reduced: the peer-memory barrier after the exchange
         # does that for free; with the NCCL exchange it is used only under sync_amax.
         fused_amax = self.P == 1 or self.sync_amax or self.arena is not None
-        ops.attention_bf16(q_h, win_k[:lk], win_v[:lk], self.Hl, out=self.attn_out, out_amax=self.act_c.amax if fused_amax else None)
+        ops.attention_nvfp4kv(q_h, [cache.k[li][s] for s in past], [cache.v[li][s] for s in past], T, cur_k, cur_v, self.Hl,
+                              out=self.attn_out, out_amax=self.act_c.amax if fused_amax else None)
         # cache write: rotated (un-smoothed) keys and values of the chunk, straight into the slot
         if self.P == 1:
             kv_given = True
@@ -566,20 +575,18 @@ class CausalDiT:
         set-up such as the text K/V and the communicators must not happen inside a capture)."""
         self._set_rope(start_frame)
         if not self.use_graphs:
-            out = self._forward_impl(latent_tokens, t, ctx, self._time_inputs(t, t_key) if t_key is not None else None)
-            self._window_version = self.cache.version
-            return out
+            return self._forward_impl(latent_tokens, t, ctx, self._time_inputs(t, t_key) if t_key is not None else None)
         self.g_lat.copy_(latent_tokens)
         self.g_t.copy_(t)
         tin = self._time_inputs(t, t_key) if t_key is not None else None     # outside any capture: the tensors outlive the graphs
-        fresh = self._window_version != self.cache.version        # this forward also dequantizes the past blocks
-        key = (tuple(self.cache.order), self.cache.filled, ctx.data_ptr(), fresh, t_key)
+        prompt_key = self._prompt(ctx)["serial"] if self.cache_text_kv else ctx.data_ptr()
+        key = (tuple(self.cache.order), self.cache.filled, prompt_key, t_key)
         entry = self._graphs.get(key)
         if entry is None:
-            if not self._ran_eager or self.cache.filled < self.cfg.max_blocks:
-                out = self._forward_impl(self.g_lat, self.g_t, ctx, tin)
-                self._window_version = self.cache.version
-                return out
+            # eager when one-time set-up is still due (first forward, the text K / V of a new prompt) or
+            # while the window still fills: none of that may happen inside a capture
+            if not self._ran_eager or self.cache.filled < self.cfg.max_blocks or not self._text_ready(ctx):
+                return self._forward_impl(self.g_lat, self.g_t, ctx, tin)
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
             graph = torch.cuda.CUDAGraph()
@@ -588,7 +595,6 @@ class CausalDiT:
                 out = self._forward_impl(self.g_lat, self.g_t, ctx, tin)
             entry = self._graphs[key] = (graph, out)
         entry[0].replay()
-        self._window_version = self.cache.version
         return entry[1]
 
     def close(self) -> None:
@@ -642,4 +648,8 @@ class CausalDiT:
         self.forward(x_t, torch.zeros(F, device=self.device), ctx, start_frame, t_key=(0.0,) * F)
         if scene_cut:
             self.cache.pin_current()
+        if self.arena is not None and self.check_peer_status:
+            # a peer barrier that gave up (a rank that is seconds late) leaves this chunk's exchange buffers
+            # undefined: find out here, once per chunk, instead of returning a wrong chunk silently
+            ops.check_status(self.device)
         return x_t

@@ -13,7 +13,23 @@ DEQ_FUSED, DEQ_PYTORCH, DEQ_TRITON = 0, 1, 2
 
 
 def _stream(t: torch.Tensor) -> int:
+    _lib.init_device(t.device.index if t.device.index is not None else torch.cuda.current_device())
     return torch.cuda.current_stream(t.device).cuda_stream
+
+
+class DeviceTimeout(RuntimeError):
+    """A bounded device-side wait gave up (``LLNV_E_TIMEOUT``): results of the affected step are invalid."""
+
+
+def check_status(device=None) -> None:
+    """Synchronise the current stream of ``device`` and raise ``DeviceTimeout`` if a kernel's bounded wait
+    (an mbarrier wait, a peer barrier) gave up since the last check (``llnv_check_status``; clears the flag)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().llnv_check_status(torch.cuda.current_stream(dev).cuda_stream)
+    if rc == -3:
+        raise DeviceTimeout(_lib.lib().llnv_last_error().decode("utf-8", "replace"))
+    _check(rc)
 
 
 def _require_cuda(t: torch.Tensor, name: str) -> None:
@@ -326,6 +342,60 @@ def attention_bf16(q, k, v, heads, scale=None, out=None, key_splits=None, out_am
     return out
 
 
+def attention_nvfp4kv(q, k_blocks, v_blocks, block_tokens, k_cur, v_cur, heads, scale=None, out=None, key_splits=None,
+                      out_amax=None, e2m1_max=6.0, e4m3_max=256.0):
+    """Chunk attention over [cached NVFP4 blocks ... | current chunk (bf16)] without dequantizing the cache to
+    memory (``llnv_attention_nvfp4kv``).  ``k_blocks`` / ``v_blocks``: cache blocks oldest first, each with
+    ``values`` (uint8 [rows_padded, 64]), ``scale_factors`` and ``amax`` (a ``QuantizedTensor`` of
+    ``block_tokens * heads`` rows of 128 channels, token-major / head-minor).  ``k_cur`` / ``v_cur``: bf16
+    [L_cur, heads*128] (or None when the window is the cache alone).  Result: bf16 [Lq, heads*128], equal bit
+    for bit to dequantizing the blocks into a window and calling ``attention_bf16`` on it."""
+    _require_cuda(q, "q")
+    if q.dim() != 2 or q.dtype != torch.bfloat16 or q.stride(1) != 1 or q.shape[1] != heads * 128:
+        raise RuntimeError("q must be bfloat16 [tokens, heads*128] with unit column stride")
+    n = len(k_blocks)
+    if len(v_blocks) != n:
+        raise RuntimeError("k_blocks and v_blocks must have the same length")
+    for b in list(k_blocks) + list(v_blocks):
+        v = b.values
+        if v.dtype != torch.uint8 or v.dim() != 2 or v.shape[1] != 64 or not v.is_contiguous() or v.shape[0] < block_tokens * heads:
+            raise RuntimeError("a cache block must be contiguous uint8 [rows_padded, 64] covering block_tokens * heads rows")
+        if v.device != q.device or b.scale_factors.device != q.device or b.amax.device != q.device or b.amax.dtype != torch.float32:
+            raise RuntimeError("cache blocks must live on the device of q, with float32 amax")
+    l_cur = 0
+    if k_cur is not None:
+        for name, t in (("k_cur", k_cur), ("v_cur", v_cur)):
+            if t is None or t.dim() != 2 or t.dtype != torch.bfloat16 or t.stride(1) != 1 or t.shape[1] != heads * 128:
+                raise RuntimeError(f"{name} must be bfloat16 [tokens, heads*128] with unit column stride")
+        if k_cur.shape[0] != v_cur.shape[0]:
+            raise RuntimeError("k_cur and v_cur must have the same number of tokens")
+        l_cur = k_cur.shape[0]
+    lk = n * block_tokens + l_cur
+    if out is None:
+        out = torch.empty((q.shape[0], heads * 128), dtype=torch.bfloat16, device=q.device)
+    if scale is None:
+        scale = 128 ** -0.5
+    lib = _lib.lib()
+    tab = lambda blocks, f: _ptr_table([f(b).data_ptr() for b in blocks]) if n else None
+    with torch.cuda.device(q.device):
+        if key_splits is None:
+            key_splits = lib.llnv_attention_key_splits(q.shape[0], lk, heads)
+        ws, ws_bytes = None, 0
+        if key_splits > 1:
+            ws_bytes = lib.llnv_attention_workspace_bytes(q.shape[0], heads, key_splits)
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+        _check(lib.llnv_attention_nvfp4kv(
+            q.data_ptr(), q.shape[0], q.stride(0),
+            tab(k_blocks, lambda b: b.values), tab(k_blocks, lambda b: b.scale_factors), tab(k_blocks, lambda b: b.amax),
+            tab(v_blocks, lambda b: b.values), tab(v_blocks, lambda b: b.scale_factors), tab(v_blocks, lambda b: b.amax),
+            n, int(block_tokens), float(e2m1_max), float(e4m3_max),
+            k_cur.data_ptr() if l_cur else None, v_cur.data_ptr() if l_cur else None, l_cur,
+            k_cur.stride(0) if l_cur else 0, v_cur.stride(0) if l_cur else 0, heads, float(scale), out.data_ptr(), out.stride(0),
+            int(key_splits), ws.data_ptr() if ws is not None else None, ws_bytes,
+            out_amax.data_ptr() if out_amax is not None else None, _stream(q)))
+    return out
+
+
 def dequantize_nvfp4(codes, sf, amax, rows, cols, cols_padded, dtype, e2m1_max, e4m3_max, rounding=DEQ_PYTORCH):
     _require_cuda(codes, "codes")
     out = torch.empty((rows, cols), dtype=dtype, device=codes.device)
@@ -371,8 +441,9 @@ def kv_dequant(values, scale_factors, amax, num_heads, block_token_size, dtype, 
 
 
 def gemm_nvfp4(a_codes, a_sf, a_amax, a_rule, b_codes, b_sf, b_amax, b_rule, m, n, k, *, out=None, alpha=None,
-               bias=None, act=0, residual=None, gate=None, frame_rows=0, out_amax=None, row_offset=0):
-    """``epilogue(alpha * A @ B^T)`` -> bf16 [m, n]; see ``llnv_gemm_nvfp4`` in include/llnvfp4.h."""
+               bias=None, act=0, residual=None, gate=None, frame_rows=0, out_amax=None, row_offset=0, tile=0):
+    """``epilogue(alpha * A @ B^T)`` -> bf16 [m, n]; see ``llnv_gemm_nvfp4`` in include/llnvfp4.h.
+    ``tile``: 0 = tiling chosen by shape, 128 / 192 / 256 = that tile width, 2 = CTA-pair kernel."""
     _require_cuda(a_codes, "a_codes")
     dev = a_codes.device
     if out is None:
@@ -391,11 +462,11 @@ def gemm_nvfp4(a_codes, a_sf, a_amax, a_rule, b_codes, b_sf, b_amax, b_rule, m, 
         epi.row_offset = int(row_offset)
     epi.out_amax = out_amax.data_ptr() if out_amax is not None else None
     with torch.cuda.device(dev):
-        _check(_lib.lib().llnv_gemm_nvfp4(a_codes.data_ptr(), a_sf.data_ptr(),
-                                          a_amax.data_ptr() if a_amax is not None else None, a_rule,
-                                          b_codes.data_ptr(), b_sf.data_ptr(),
-                                          b_amax.data_ptr() if b_amax is not None else None, b_rule,
-                                          m, n, k, C.byref(epi), out.data_ptr(), out.stride(0), _stream(a_codes)))
+        _check(_lib.lib().llnv_gemm_nvfp4_ex(a_codes.data_ptr(), a_sf.data_ptr(),
+                                             a_amax.data_ptr() if a_amax is not None else None, a_rule,
+                                             b_codes.data_ptr(), b_sf.data_ptr(),
+                                             b_amax.data_ptr() if b_amax is not None else None, b_rule,
+                                             m, n, k, C.byref(epi), out.data_ptr(), out.stride(0), int(tile), _stream(a_codes)))
     return out
 
 

@@ -376,16 +376,21 @@ def k_smooth(k: np.ndarray) -> np.ndarray:
 
 
 def dequantize_kv_cache(blocks, num_heads: int, block_token_size: int, rule="mse",
-                        mode: int = DEQ_FUSED_CUDA) -> np.ndarray:
-    """List of per-block (codes, scales, amax) -> bf16-valued [1, blocks*T, H, 128].
+                        mode: int = DEQ_FUSED_CUDA, dtype: str = "bf16") -> np.ndarray:
+    """List of per-block (codes, scales, amax) -> [1, blocks*T, H, 128] fp32 array holding the values of
+    the output dtype ("bf16", "fp16" or "fp32": the fp32 product rounded once to that type).
 
     utils/quant.py:731-768; the default rounding is that of the fused CUDA kernel the
-    reference calls first (utils/kernel/kv_dequant_cuda.cu:59-107).
+    reference calls first (utils/kernel/kv_dequant_cuda.cu:59-107; output cast :216-240).
     """
     rows = num_heads * block_token_size
     outs = []
     for codes, sf, amax in blocks:
-        d = dequantize(codes, sf, amax, rule, (rows, 128), mode, out_bf16=True)
+        d = dequantize(codes, sf, amax, rule, (rows, 128), mode, out_bf16=dtype == "bf16")
+        if dtype == "fp16":
+            d = d.astype(np.float16).astype(f32)
+        elif dtype not in ("bf16", "fp32"):
+            raise ValueError(dtype)
         outs.append(d.reshape(block_token_size, num_heads, 128))
     return np.concatenate(outs, axis=0)[None]
 

@@ -150,3 +150,114 @@ def test_attention_full_window_properties():
     torch.cuda.synchronize()
     assert _lib.lib().llnv_check_status(None) == 0, _lib.lib().llnv_last_error()
     assert float((a - b).abs().max()) <= 2.0 ** -8 + 2.0 ** -6 * float(a.abs().max())
+
+
+# ---- NVFP4 K/V decoded inside the attention kernel ----------------------------------------------------
+
+def _cache_blocks(n, T, heads, gen, scale=1.0):
+    return [L.quantize_to_fp4((torch.randn(T * heads, 128, generator=gen, device="cuda") * scale * (1 + 0.5 * i)).bfloat16())
+            for i in range(n)]
+
+
+def _dequant_then_attention(q, kq, vq, T, k_cur, v_cur, heads, key_splits=None, out_amax=None):
+    """Today's two-step form: llnv_kv_dequant into one bf16 window, then llnv_attention_bf16_ex on it."""
+    n = len(kq)
+    l_cur = 0 if k_cur is None else k_cur.shape[0]
+    lk = n * T + l_cur
+    win_k = torch.empty(lk, heads * 128, dtype=torch.bfloat16, device="cuda")
+    win_v = torch.empty_like(win_k)
+    if n:
+        L.dequantize_kv_cache(kq, n, heads, T, torch.bfloat16, "cuda", out=win_k[: n * T].view(1, n * T, heads, 128))
+        L.dequantize_kv_cache(vq, n, heads, T, torch.bfloat16, "cuda", out=win_v[: n * T].view(1, n * T, heads, 128))
+    if l_cur:
+        win_k[n * T:] = k_cur
+        win_v[n * T:] = v_cur
+    return ops.attention_bf16(q, win_k, win_v, heads, key_splits=key_splits, out_amax=out_amax)
+
+
+@pytest.mark.parametrize("heads,T,blocks,l_cur,lq,splits", [
+    (2, 96, 2, 96, 96, 1),          # cached keys end inside a tile: one tile mixes cache rows and current-chunk rows
+    (1, 128, 3, 128, 256, 1),       # tile-aligned segments
+    (3, 80, 5, 80, 300, 1),         # blocks shorter than a tile: a tile spans three cache blocks
+    (2, 200, 2, 0, 130, 1),         # the window is the cache alone, ragged last tile
+    (2, 264, 4, 264, 264, 3),       # key splits: a split may start in the cache and end in the current chunk
+    (4, 330, 4, 330, 330, 2),
+    (2, 96, 0, 200, 96, 1),         # no cached block yet (first chunk)
+])
+def test_nvfp4kv_attention_is_bit_identical_to_dequant_then_attention(heads, T, blocks, l_cur, lq, splits):
+    g = torch.Generator(device="cuda").manual_seed(heads * 1000 + T + blocks)
+    kq, vq = _cache_blocks(blocks, T, heads, g), _cache_blocks(blocks, T, heads, g, scale=2.0)
+    q = torch.randn(lq, heads * 128, generator=g, device="cuda").bfloat16()
+    k_cur = torch.randn(l_cur, heads * 128, generator=g, device="cuda").bfloat16() if l_cur else None
+    v_cur = torch.randn(l_cur, heads * 128, generator=g, device="cuda").bfloat16() if l_cur else None
+    am_a = torch.full((1,), 9.0, device="cuda")
+    am_b = torch.full((1,), 9.0, device="cuda")
+    ref = _dequant_then_attention(q, kq, vq, T, k_cur, v_cur, heads, key_splits=splits, out_amax=am_a)
+    out = ops.attention_nvfp4kv(q, kq, vq, T, k_cur, v_cur, heads, key_splits=splits, out_amax=am_b)
+    torch.cuda.synchronize()
+    assert _lib.lib().llnv_check_status(None) == 0, _lib.lib().llnv_last_error()
+    assert torch.equal(out, ref)
+    assert torch.equal(am_a, am_b)
+
+
+def test_nvfp4kv_attention_strided_current_chunk_and_arguments():
+    heads, T = 2, 64
+    g = torch.Generator(device="cuda").manual_seed(4)
+    kq, vq = _cache_blocks(2, T, heads, g), _cache_blocks(2, T, heads, g)
+    q = torch.randn(100, heads * 128, generator=g, device="cuda").bfloat16()
+    wide = torch.randn(70, 2 * heads * 128 + 64, generator=g, device="cuda").bfloat16()
+    k_cur, v_cur = wide[:, : heads * 128], wide[:, heads * 128 + 64:]          # row stride larger than heads * 128
+    out = ops.attention_nvfp4kv(q, kq, vq, T, k_cur, v_cur, heads)
+    assert torch.equal(out, _dequant_then_attention(q, kq, vq, T, k_cur.contiguous(), v_cur.contiguous(), heads))
+    with pytest.raises(RuntimeError, match="cache block"):
+        ops.attention_nvfp4kv(q, kq, vq, 4 * T, k_cur, v_cur, heads)                 # blocks too small for that many tokens
+    with pytest.raises(RuntimeError, match="same length"):
+        ops.attention_nvfp4kv(q, kq, vq[:1], T, k_cur, v_cur, heads)
+    with pytest.raises(RuntimeError, match="0 to 16 cache blocks"):
+        ops.attention_nvfp4kv(q, kq * 9, vq * 9, T, k_cur, v_cur, heads)
+
+
+def test_config3_window_attention_full_size_vs_oracle():
+    """The benchmark's attention configuration: 24 heads, a chunk of 2640 queries at frames 12-14, window = 4
+    cached NVFP4 blocks of 2640 tokens (RoPE'd at their frame positions, frames 0-11) + the current chunk
+    (k_smooth-ed keys) = 13200 keys.  Cache write and attention run at full size on the GPU; the oracle
+    (dequantize with the fused rounding, fp32 attention) checks 2 of the 24 heads, and the cache blocks bit for bit."""
+    heads, T, blocks, fh, fw = 24, 2640, 4, 22, 40
+    C = heads * 128
+    g = torch.Generator(device="cuda").manual_seed(33)
+    ones = torch.ones(C, dtype=torch.bfloat16, device="cuda")
+    kq, vq = [], []
+    for b in range(blocks):
+        cos, sin = (torch.from_numpy(t).cuda() for t in O.rope_tables(3 * b, 3, fh, fw))
+        k_raw = torch.randn(T, C, generator=g, device="cuda").bfloat16()
+        v_raw = torch.randn(T, C, generator=g, device="cuda").bfloat16()
+        k_rot, _, _ = ops.rmsnorm_rope(k_raw, None, cos, sin)
+        kq.append(L.quantize_to_fp4(k_rot.reshape(T * heads, 128)))
+        vq.append(L.quantize_to_fp4(v_raw.reshape(T * heads, 128)))
+        if b == 1:      # the written block is the oracle's quantization of the rotated keys, bit for bit
+            # (the rotation itself is compared with the oracle in tests/test_gpu_rope_norm.py: equal up to one bf16 ulp)
+            oc, osf, oam = O.quantize_nvfp4(k_rot.float().cpu().numpy().reshape(T * heads, 128), "mse")
+            assert np.array_equal(kq[-1].values.cpu().numpy(), oc) and np.array_equal(util.u8(kq[-1].scale_factors), osf)
+            assert float(kq[-1].amax.item()) == float(oam)
+    cos, sin = (torch.from_numpy(t).cuda() for t in O.rope_tables(12, 3, fh, fw))
+    q_raw = torch.randn(T, C, generator=g, device="cuda").bfloat16()
+    k_raw = torch.randn(T, C, generator=g, device="cuda").bfloat16()
+    v_new = torch.randn(T, C, generator=g, device="cuda").bfloat16()
+    q_rot, _, _ = ops.rmsnorm_rope(q_raw, None, cos, sin)
+    k_rot, k_sm, _ = ops.rmsnorm_rope(k_raw, None, cos, sin, want_smooth=True)
+    out = ops.attention_nvfp4kv(q_rot, kq, vq, T, k_sm, v_new, heads)
+    torch.cuda.synchronize()
+    assert _lib.lib().llnv_check_status(None) == 0, _lib.lib().llnv_last_error()
+    sel = [5, 23]
+    def head_blocks(qs):
+        outs = []
+        for t in qs:
+            d = O.dequantize(t.values.cpu().numpy(), util.u8(t.scale_factors), np.float32(t.amax.item()), "mse", (T * heads, 128),
+                             O.DEQ_FUSED_CUDA, out_bf16=True)
+            outs.append(d.reshape(T, heads, 128)[:, sel])
+        return np.concatenate(outs, 0)
+    kw = np.concatenate([head_blocks(kq), k_sm.float().cpu().numpy().reshape(T, heads, 128)[:, sel]], 0)
+    vw = np.concatenate([head_blocks(vq), v_new.float().cpu().numpy().reshape(T, heads, 128)[:, sel]], 0)
+    ref = O.attention(q_rot.float().cpu().numpy().reshape(T, heads, 128)[:, sel], kw, vw)
+    got = out.view(T, heads, 128)[:, sel]
+    check(got, ref)

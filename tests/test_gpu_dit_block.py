@@ -108,7 +108,7 @@ def test_graph_replay_equals_eager():
         a = eager.run_chunk(lat, ctx_e, chunk)
         b = graphed.run_chunk(lat, ctx_g, chunk)
         assert torch.equal(a, b), chunk
-    assert len(graphed._graphs) == 5 * period        # per table state: one graph per timestep of a chunk (the first also refreshes the windows)
+    assert len(graphed._graphs) == 5 * period        # per table state: one graph per timestep of a chunk
     assert eager.cache.order == graphed.cache.order
     for layer in range(cfg.layers):
         for slot in range(cfg.max_blocks):

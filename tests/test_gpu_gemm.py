@@ -41,19 +41,16 @@ def oracle_matmul(xq, wq, m, n, k):
 @pytest.mark.parametrize("tile_n", [128, 256, 2])     # 2 = CTA-pair kernel (256 x 256 tile per pair)
 @pytest.mark.parametrize("m,n,k", [(128, 256, 256), (200, 256, 512), (880, 512, 3072), (130, 1024, 1024), (512, 3072, 3072)])
 def test_gemm_matches_oracle(m, n, k, tile_n):
-    _lib.lib().llnv_gemm_nvfp4_force_tile_n(tile_n)
-    try:
-        x = util.config_activation(m, k, seed=m + k)
-        w = util.config_weight(n, k, seed=n)
-        xq = L.quantize_to_fp4(x.cuda())
-        wq = L.quantize_to_fp4(w.cuda())
-        y = L.fp4_matmul(xq, wq)
-        torch.cuda.synchronize()
-        assert _lib.lib().llnv_check_status(None) == 0
-        assert y.shape == (m, n) and y.dtype == torch.bfloat16
-        check_close(y, O.bf16_round(oracle_matmul(xq, wq, m, n, k)), k)
-    finally:
-        _lib.lib().llnv_gemm_nvfp4_force_tile_n(0)
+    x = util.config_activation(m, k, seed=m + k)
+    w = util.config_weight(n, k, seed=n)
+    xq = L.quantize_to_fp4(x.cuda())
+    wq = L.quantize_to_fp4(w.cuda())
+    y = ops.gemm_nvfp4(xq.values, xq.scale_factors, xq.amax, 3, wq.values, wq.scale_factors, wq.amax, 3, m, n, k, tile=tile_n)
+    torch.cuda.synchronize()
+    assert _lib.lib().llnv_check_status(None) == 0
+    assert y.shape == (m, n) and y.dtype == torch.bfloat16
+    check_close(y, O.bf16_round(oracle_matmul(xq, wq, m, n, k)), k)
+    assert torch.equal(y, L.fp4_matmul(xq, wq))          # the public entry (automatic tiling) gives the same bits
 
 
 def test_gemm_small_fixture(golden):
@@ -149,14 +146,10 @@ def test_pair_kernel_fused_epilogues_match_single_cta_kernel():
     lib = _lib.lib()
     outs = {}
     for tile in (256, 2):
-        lib.llnv_gemm_nvfp4_force_tile_n(tile)
-        try:
-            a1 = torch.zeros(1, dtype=torch.float32, device="cuda")
-            a2 = torch.zeros(1, dtype=torch.float32, device="cuda")
-            outs[tile] = (ops.gemm_nvfp4(*args), ops.gemm_nvfp4(*args, bias=bias, act=1, out_amax=a1),
-                          ops.gemm_nvfp4(*args, bias=bias, residual=resid, gate=gate, frame_rows=m // frames, out_amax=a2), a1, a2)
-        finally:
-            lib.llnv_gemm_nvfp4_force_tile_n(0)
+        a1 = torch.zeros(1, dtype=torch.float32, device="cuda")
+        a2 = torch.zeros(1, dtype=torch.float32, device="cuda")
+        outs[tile] = (ops.gemm_nvfp4(*args, tile=tile), ops.gemm_nvfp4(*args, bias=bias, act=1, out_amax=a1, tile=tile),
+                      ops.gemm_nvfp4(*args, bias=bias, residual=resid, gate=gate, frame_rows=m // frames, out_amax=a2, tile=tile), a1, a2)
     torch.cuda.synchronize()
     assert lib.llnv_check_status(None) == 0, lib.llnv_last_error()
     for a, b in zip(outs[256], outs[2]):
@@ -186,11 +179,8 @@ def test_gemm_192_wide_tiles(m, n, k):
     args = (xq.values, xq.scale_factors, xq.amax, 3, wq.values, wq.scale_factors, wq.amax, 3, m, n, k)
     outs = {}
     for tile in (192, 128):
-        lib.llnv_gemm_nvfp4_force_tile_n(tile)
-        try:
-            outs[tile] = (ops.gemm_nvfp4(*args), ops.gemm_nvfp4(*args, bias=bias, act=1), ops.gemm_nvfp4(*args, bias=bias, residual=resid))
-        finally:
-            lib.llnv_gemm_nvfp4_force_tile_n(0)
+        outs[tile] = (ops.gemm_nvfp4(*args, tile=tile), ops.gemm_nvfp4(*args, bias=bias, act=1, tile=tile),
+                      ops.gemm_nvfp4(*args, bias=bias, residual=resid, tile=tile))
     torch.cuda.synchronize()
     assert lib.llnv_check_status(None) == 0, lib.llnv_last_error()
     check_close(outs[192][0], O.bf16_round(oracle_matmul(xq, wq, m, n, k)), k)
@@ -237,13 +227,48 @@ def test_gemm_full_size_tilings_agree():
     lib = _lib.lib()
     outs = []
     for tile in (256, 192, 128, 2):
-        lib.llnv_gemm_nvfp4_force_tile_n(tile)
-        try:
-            outs.append(ops.gemm_nvfp4(*args))
-        finally:
-            lib.llnv_gemm_nvfp4_force_tile_n(0)
+        outs.append(ops.gemm_nvfp4(*args, tile=tile))
     torch.cuda.synchronize()
     assert lib.llnv_check_status(None) == 0, lib.llnv_last_error()
     for o in outs[1:]:
         assert torch.equal(o, outs[0])
     assert torch.isfinite(outs[0].float()).all()
+
+
+def _sampled_oracle(xq, wq, m, n, k, rows):
+    """Oracle result for a sample of output rows (every row of A meets all of B, so sampled rows still cover every
+    N tile, every K block and every scale atom of B; the sample spreads over all M tiles and lanes)."""
+    a = O.dequantize(xq.values.cpu().numpy(), util.u8(xq.scale_factors), np.float32(xq.amax.item()), xq.scale_rule.value, (m, k))
+    b = O.dequantize(wq.values.cpu().numpy(), util.u8(wq.scale_factors), np.float32(wq.amax.item()), wq.scale_rule.value, (n, k))
+    return a[rows] @ b.T
+
+
+@pytest.mark.parametrize("m,n,k,tiles", [
+    (2640, 14336, 3072, (0, 256, 2)),      # ffn.0 of the DiT block
+    (2640, 3072, 14336, (0, 256, 2)),      # ffn.2 (the automatic choice is the CTA-pair kernel)
+    (10560, 3072, 3072, (0, 2)),           # q/k/v/o at the largest token count of the sweep
+    (10560, 14336, 3072, (0,)),
+    (880, 3072, 14336, (0, 128)),
+])
+def test_gemm_benchmark_shapes_match_oracle(m, n, k, tiles):
+    """The FFN shapes and the M = 10560 shapes of the benchmark sweep against the oracle's dequantize-then-fp32-matmul
+    (not merely against another tiling): 264 output rows, 8 from every 33rd part of M with the last M tile included."""
+    x = util.config_activation(m, k, seed=m + k).cuda()
+    w = util.config_weight(n, k, seed=n + k).cuda()
+    xq, wq = L.quantize_to_fp4(x), L.quantize_to_fp4(w)
+    del x, w
+    step = m // 33
+    rows = np.unique(np.concatenate([np.arange(i * step + (i * 37) % 97, i * step + (i * 37) % 97 + 8) for i in range(33)] + [np.arange(m - 8, m)]))
+    rows = rows[rows < m]
+    ref = O.bf16_round(_sampled_oracle(xq, wq, m, n, k, rows))
+    args = (xq.values, xq.scale_factors, xq.amax, 3, wq.values, wq.scale_factors, wq.amax, 3, m, n, k)
+    first = None
+    for tile in tiles:
+        y = ops.gemm_nvfp4(*args, tile=tile)
+        torch.cuda.synchronize()
+        assert _lib.lib().llnv_check_status(None) == 0, _lib.lib().llnv_last_error()
+        check_close(y[torch.from_numpy(rows).cuda()], ref, k)
+        if first is None:
+            first = y
+        else:
+            assert torch.equal(y, first)

@@ -122,11 +122,12 @@ def test_kv_dequant_matches_oracle_and_fixture(golden):
     ref = O.dequantize_kv_cache([(b.values.cpu().numpy(), util.u8(b.scale_factors), np.float32(b.amax.item()))
                                  for b in blocks + [qt]], H, T, "mse", O.DEQ_FUSED_CUDA)
     assert np.array_equal(util.torch_bf16_bits(fused), O.bf16_bits(ref))
-    for dt in (torch.float16, torch.float32):
+    for dt, name in ((torch.float16, "fp16"), (torch.float32, "fp32")):
         o = L.dequantize_kv_cache(blocks, 3, H, T, dt, "cuda")
-        r32 = O.dequantize_kv_cache([(b.values.cpu().numpy(), util.u8(b.scale_factors), np.float32(b.amax.item()))
-                                     for b in blocks], H, T, "mse", O.DEQ_FUSED_CUDA)
+        ref = O.dequantize_kv_cache([(b.values.cpu().numpy(), util.u8(b.scale_factors), np.float32(b.amax.item()))
+                                     for b in blocks], H, T, "mse", O.DEQ_FUSED_CUDA, dtype=name)
         assert o.dtype == dt and o.shape == (1, 3 * T, H, 128)
+        assert np.array_equal(o.float().cpu().numpy().view(np.uint32), ref.view(np.uint32))      # bit for bit
 
 
 def test_kv_slot_helpers():

@@ -1,6 +1,7 @@
-"""Sequence parallelism on real GPUs (needs >= 2): a token/head-sharded run of the DiT block stack
+"""Sequence parallelism on real GPUs (2, 4 or 8 of them): a token/head-sharded run of the DiT block stack
 must reproduce the single-GPU result bit for bit when the per-tensor amax values are MAX-reduced
-(all per-token kernels see the same rows, attention sees the same heads, quantizers the same scale)."""
+(all per-token kernels see the same rows, attention sees the same heads, quantizers the same scale).
+Plus, on one GPU, the give-up path of the peer barrier's bounded wait."""
 import os
 import socket
 import sys
@@ -11,7 +12,8 @@ import torch
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
-CFG = dict(dim=512, ffn_dim=1024, heads=4, layers=2, text_len=128, text_dim=64, freq_dim=32, grid_h=4, grid_w=6,
+# 8 heads and 72 chunk tokens divide by every world size tested
+CFG = dict(dim=1024, ffn_dim=1024, heads=8, layers=2, text_len=128, text_dim=64, freq_dim=32, grid_h=4, grid_w=6,
            frames_per_chunk=3, window_frames=9, sink_frames=3, in_channels=4)
 
 
@@ -55,6 +57,8 @@ def _worker(rank, world, port, q, use_graphs=False, peer=False):
         ok = ok and torch.equal(kp, kr[:, rank * hl:(rank + 1) * hl])
         if use_graphs:
             ok = ok and len(par._graphs) == 12     # 2 table states x (5 timesteps of a chunk + the extra forward)
+        from longlive_b200 import ops
+        ops.check_status(dev)                      # no bounded wait gave up on this rank
         torch.cuda.synchronize()
         par.close()
         q.put((rank, "ok" if ok else "mismatch"))
@@ -65,16 +69,18 @@ def _worker(rank, world, port, q, use_graphs=False, peer=False):
         dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("use_graphs,peer", [(False, False), (True, False), (False, True), (True, True)])
-def test_sequence_parallel_matches_single_gpu(use_graphs, peer):
+def test_sequence_parallel_matches_single_gpu(use_graphs, peer, world):
     """peer=False exchanges with NCCL all-to-alls, peer=True with stores into the other GPU's
     symmetric memory and the library's own barrier."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, use_graphs, peer)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, use_graphs, peer)) for r in range(world)]
     for p in procs:
         p.start()
     results = sorted(q.get(timeout=600) for _ in procs)
@@ -82,4 +88,35 @@ def test_sequence_parallel_matches_single_gpu(use_graphs, peer):
         p.join(timeout=60)
         if p.is_alive():
             p.kill()
-    assert results == [(0, "ok"), (1, "ok")], results
+    assert results == [(r, "ok") for r in range(world)], results
+
+
+def test_peer_barrier_gives_up_and_reports_timeout():
+    """The bounded wait of the peer barrier, on one GPU: the barrier is launched as rank 0 of a world of two whose
+    second signal area nobody writes, with a short poll limit.  The kernel must return by itself, llnv_check_status
+    must report the timeout (code 3, where 700) once and clear it, and the context must stay usable."""
+    from longlive_b200 import _lib, ops
+    lib = _lib.lib()
+    dev = torch.device("cuda", 0)
+    mine = torch.zeros(64, dtype=torch.int32, device=dev)          # rank 0's signal area (flag r written by rank r)
+    theirs = torch.zeros(64, dtype=torch.int32, device=dev)        # stands for rank 1's area; nobody plays rank 1
+    epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+    ops.check_status(dev)
+    lib.llnv_set_peer_poll_limit(20000)
+    try:
+        ops.peer_barrier([mine.data_ptr(), theirs.data_ptr()], 0, epoch)
+        with pytest.raises(ops.DeviceTimeout, match="code=3 where=700"):
+            ops.check_status(dev)
+        ops.check_status(dev)                                      # reported once, then clear
+        assert int(epoch.item()) == 1 and int(theirs[0].item()) == 1 and int(mine[0].item()) == 1
+        vals = torch.tensor([1.0, 2.0], device=dev)
+        slots = torch.zeros(2 * 8 * 32, dtype=torch.float32, device=dev)
+        ops.peer_allreduce_max(vals, [slots.data_ptr(), slots.data_ptr()], [mine.data_ptr(), theirs.data_ptr()], 0, epoch)
+        with pytest.raises(ops.DeviceTimeout, match="code=3 where=701"):
+            ops.check_status(dev)
+    finally:
+        lib.llnv_set_peer_poll_limit(0)
+    # a world of one needs no peer and must pass
+    ops.peer_barrier([mine.data_ptr()], 0, epoch)
+    ops.check_status(dev)
+    assert torch.equal(torch.ones(4, device=dev) * 2, torch.full((4,), 2.0, device=dev))
