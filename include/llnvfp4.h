@@ -273,7 +273,8 @@ int llnv_attention_key_splits(int64_t Lq, int64_t Lk, int heads);
  * (LLNV_DEQ_FUSED), so no bf16 copy of the cache exists and the result equals llnv_kv_dequant followed
  * by llnv_attention_bf16_ex on the concatenated window bit for bit.
  *   k_codes / k_sf / k_amax / v_*: HOST arrays of num_blocks (<= 16) DEVICE pointers, passed to the kernel
- *   as launch parameters.  Codes must be 16-byte aligned.  num_blocks == 0 is llnv_attention_bf16_ex on
+ *   as launch parameters.  Codes must be 16-byte aligned, block_token_size >= 128 (a 128-key tile then
+ *   touches at most two blocks) and heads * 64 a multiple of 16.  num_blocks == 0 is llnv_attention_bf16_ex on
  *   the current chunk.  key_splits / workspace / out_amax as in llnv_attention_bf16_ex, with
  *   Lk = num_blocks * block_token_size + L_cur. */
 int llnv_attention_nvfp4kv(const void* q, int64_t Lq, int64_t ldq, const void* const* k_codes, const void* const* k_sf,

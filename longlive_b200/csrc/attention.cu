@@ -27,15 +27,24 @@
 // segments: cached NVFP4 blocks (E2M1 codes, E4M3 scale per 16 channels, one fp32 amax per block,
 // rows ordered token-major / head-minor) followed by the current chunk in bf16.  The cached part is
 // never materialised in global memory: four more warps (12-15) decode it inside the load stage.
-// Decode thread i owns key row i of a 128-key tile: it reads the row's 64 code bytes and 8 scale
-// bytes of K and of V straight from the cache block (prefetched one tile ahead into registers),
-// converts with the rounding of the standalone dequantize kernel,
+// The TMA producer loads the 128 x 64-byte code tile of the stage's next key tile (one box per cache
+// block the tile touches, at most two) into the tail of the K / V stage itself, which is free at
+// that point; decode thread i owns key row i: it reads the row's 64 code bytes from there and its 8
+// scale bytes from global memory (prefetched one tile ahead) and writes the bf16 row over the stage
+// in the 128-byte-swizzled layout the MMAs read -- the same bytes a TMA load of the dequantized
+// window would have put there, so the result equals dequantize-then-attention bit for bit.  (Row
+// loads issued by the decode threads themselves -- 64 bytes per thread, every lane in another cache
+// line -- kept the load/store unit busy for longer than the decode itself; one TMA box per tile
+// does not touch it.)  The value of a code is that of the standalone dequantize kernel,
 //     bf16( (e2m1 * e4m3) * (amax * fp32(1 / (6 * 256))) ),
-// and writes the bf16 row into the 128-byte-swizzled K / V stage the MMAs read -- the same bytes a
-// TMA load of the dequantized window would have put there, so the result equals dequantize-then-
-// attention bit for bit.  A tile that holds the last cached keys and the first keys of the current
-// chunk is also built by these warps (they copy the bf16 rows); tiles that lie entirely in the
-// current chunk come from TMA as before.  With 16 warps the register file is re-divided after
+// which for one cache block depends only on (scale byte, code): when a tile first touches a cache
+// block the decode warps compute, with exactly that arithmetic, the eight bf16 magnitudes of each of
+// the 128 scale bytes into a 2 KiB shared-memory table (byte-split for prmt), and a row is then
+// decoded with byte permutes alone: per 16 channels one 16-byte table read, per 8 channels four
+// lookups, the sign bits, four interleaves.  No conversion or multiply runs per element, so the
+// decode stays off the special-function pipe the softmax's exp2 lives on.  A tile that holds the
+// last cached keys and the first keys of the current chunk is also built by these warps (they copy
+// the bf16 rows); tiles that lie entirely in the current chunk come from TMA as before.  With 16 warps the register file is re-divided after
 // start-up (setmaxnreg): load/MMA warpgroup 56, decode warpgroup 104, softmax warpgroups 176.
 #include <cuda.h>
 #include <cuda_fp4.h>
@@ -60,6 +69,14 @@ constexpr uint32_t kKOff = 2 * kTileBytes;
 constexpr uint32_t kVOff = kKOff + kStages * kTileBytes;
 constexpr uint32_t kBarOff = kVOff + kStages * kTileBytes;
 constexpr uint32_t kSmemBytes = kBarOff + 1024;
+// NVFP4 window: decode tables behind the barriers, kTabSlots cache blocks x (K, V) x 128 scale bytes x 16 bytes
+constexpr int kTabSlots = 2;                      // a tile of 128 keys touches at most two cache blocks (blocks hold >= 128 tokens)
+constexpr uint32_t kCodeBytes = 128 * 64;         // code tile of one cache block: 128 key rows x 64 bytes, 64-byte swizzle
+constexpr uint32_t kCodeOff = kTileBytes - 2 * kCodeBytes;      // two code tiles in the tail of the stage they expand into
+constexpr uint32_t kTabOff = kBarOff + 1024;
+constexpr uint32_t kTabBytes = kTabSlots * 2 * 128 * 16;
+constexpr uint32_t kSmemBytesFused = kTabOff + kTabBytes;
+static_assert(kSmemBytesFused <= 232448, "more shared memory than one CTA may use");
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kSCol = 0, kOCol = 256;      // S_h at kSCol + 128 h, O_h at kOCol + 128 h
 constexpr int kThreads = 320;            // bf16 window: load, MMA, 2 x 4 softmax warps
@@ -68,12 +85,13 @@ constexpr int kMaxKvBlocks = 16;
 
 // Device pointers of the cached blocks of one layer (oldest first), passed as launch parameters.
 struct KvTable {
-  const uint8_t* k_codes[kMaxKvBlocks];
   const uint8_t* k_sf[kMaxKvBlocks];
   const float* k_amax[kMaxKvBlocks];
-  const uint8_t* v_codes[kMaxKvBlocks];
   const uint8_t* v_sf[kMaxKvBlocks];
   const float* v_amax[kMaxKvBlocks];
+  // codes of block b viewed as [block_tokens, heads * 64 bytes]: box = 128 tokens x the 64 bytes of one head
+  CUtensorMap k_codes[kMaxKvBlocks];
+  CUtensorMap v_codes[kMaxKvBlocks];
 };
 
 struct AttnParams {
@@ -102,47 +120,99 @@ __device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.
 template <int N>
 __device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
-// One key row of a cached block as it arrives from global memory: 64 code bytes, 8 scale bytes.
-struct CodedRow {
-  uint4 c[4];
-  uint32_t sf[2];
-  float g;                      // amax * fp32(1 / (e2m1_max * e4m3_max)) of the row's block
+// What a decode thread keeps of its key row between the prefetch and the decode.
+struct RowInfo {
+  uint32_t ksf[2], vsf[2];      // the row's 8 K and 8 V scale bytes
+  int64_t cur_row;              // kind 1: row of the current chunk
+  int kind;                     // 0 = cache block, 1 = current chunk, 2 = beyond the window
+  int code_row;                 // kind 0: row inside the staged code tiles (128.. = second tile)
+  int slot;                     // kind 0: decode table slot of the row's cache block
+  float kg, vg;                 // kind 0: amax * fp32(1 / (e2m1_max * e4m3_max)) of the row's K / V block (arithmetic decode)
 };
 
-// Decode one cached row (128 channels) into row i of a K / V stage: two halves of 64 channels, rows of
-// 128 bytes, 16-byte chunks XOR-swizzled with the row index as a TMA load with the 128-byte swizzle
-// writes them.  Arithmetic as decode16<LLNV_DEQ_FUSED> of the standalone dequantize kernel.
-__device__ __forceinline__ void decode_row_to_stage(const CodedRow& r, uint8_t* stage, int i) {
-  const uint32_t words[16] = {r.c[0].x, r.c[0].y, r.c[0].z, r.c[0].w, r.c[1].x, r.c[1].y, r.c[1].z, r.c[1].w,
-                              r.c[2].x, r.c[2].y, r.c[2].z, r.c[2].w, r.c[3].x, r.c[3].y, r.c[3].z, r.c[3].w};
-  const F2 g2 = f2_splat(r.g);
+// Decode table of one (cache block, scale byte): the bf16 magnitudes of the eight E2M1 magnitudes
+// {0, .5, 1, 1.5, 2, 3, 4, 6} under that scale, computed as decode16<LLNV_DEQ_FUSED> of the standalone
+// dequantize kernel computes them, stored byte-split: x = low bytes of magnitudes 0..3, y = low bytes of
+// 4..7, z / w = the high bytes.
+__device__ __forceinline__ uint4 decode_table_entry(uint32_t scale_byte, float g) {
+  const float s = e4m3_to_float(scale_byte);
+  const float mags[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+  uint32_t pk[4];
 #pragma unroll
-  for (int b = 0; b < 8; ++b) {                       // 16 channels per scale
-    const F2 s2 = f2_splat(e4m3_to_float((r.sf[b >> 2] >> (8 * (b & 3))) & 0xFFu));
+  for (int m = 0; m < 4; ++m)
+    pk[m] = pack_bf16x2(__fmul_rn(__fmul_rn(mags[2 * m], s), g), __fmul_rn(__fmul_rn(mags[2 * m + 1], s), g));
+  uint4 t;
+  t.x = __byte_perm(pk[0], pk[1], 0x6420);
+  t.y = __byte_perm(pk[2], pk[3], 0x6420);
+  t.z = __byte_perm(pk[0], pk[1], 0x7531);
+  t.w = __byte_perm(pk[2], pk[3], 0x7531);
+  return t;
+}
+
+// How a decode thread turns codes into bf16 (all three give the same bits):
+//   0  table lookups with byte permutes only (integer pipe),
+//   1  convert and multiply every element as the standalone dequantize kernel does (conversion + FMA pipes),
+//   2  even 16-byte chunks by lookup, odd ones by arithmetic, to spread the work over both groups of pipes.
+#ifndef LLNV_ATTN_DECODE_MODE
+#define LLNV_ATTN_DECODE_MODE 0
+#endif
+
+// 8 codes (one word) -> 8 bf16 (16 bytes) by arithmetic: bf16((e2m1 * s) * g), decode16<LLNV_DEQ_FUSED> of dequant.cu
+__device__ __forceinline__ uint4 decode_word_arith(uint32_t w, float s, float g) {
+  const F2 s2 = f2_splat(s), g2 = f2_splat(g);
+  uint32_t o[4];
 #pragma unroll
-    for (int wi = 0; wi < 2; ++wi) {                  // 8 channels = one 16-byte chunk of the bf16 row
-      const uint32_t w = words[2 * b + wi];
-      uint32_t o[4];
+  for (int e = 0; e < 4; ++e) {
+    const __half2_raw h2 = __nv_cvt_fp4x2_to_halfraw2((__nv_fp4x2_storage_t)((w >> (8 * e)) & 0xFFu), __NV_E2M1);
+    const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+    const F2 d = f2_mul(f2_mul(F2{v.x, v.y}, s2), g2);
+    o[e] = pack_bf16x2(d.x, d.y);
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// Decode 64 channels (code words w[0..7], scale bytes in sf) of a cached row into row i of one half of a K / V
+// stage: rows of 128 bytes, 16-byte chunks XOR-swizzled with the row index as a TMA load with the 128-byte
+// swizzle writes them.  `tab` is the row's block's table (128 entries of 16 bytes) in shared memory.
+__device__ __forceinline__ void decode_half_row(const uint32_t (&w8)[8], uint32_t sf, const uint8_t* tab, float g, uint8_t* half,
+                                                int i) {
+  constexpr int kMode = LLNV_ATTN_DECODE_MODE;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const __half2_raw h2 = __nv_cvt_fp4x2_to_halfraw2((__nv_fp4x2_storage_t)((w >> (8 * e)) & 0xFFu), __NV_E2M1);
-        const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&h2));
-        const F2 d = f2_mul(f2_mul(F2{v.x, v.y}, s2), g2);
-        o[e] = pack_bf16x2(d.x, d.y);
+  for (int b = 0; b < 4; ++b) {                       // 16 channels per scale
+    // table entry of scale byte b (bit 7 of a UE4M3 scale is never set): byte * 16 with one shift and one mask
+    const uint32_t toff = (b == 0 ? sf << 4 : sf >> (8 * b - 4)) & 0x7F0u;
+    uint4 t = make_uint4(0u, 0u, 0u, 0u);
+    if (kMode != 1) t = *reinterpret_cast<const uint4*>(tab + toff);
+    float s = 0.f;
+    if (kMode != 0) s = e4m3_to_float((sf >> (8 * b)) & 0xFFu);
+#pragma unroll
+    for (int wi = 0; wi < 2; ++wi) {                  // 8 codes = one 16-byte chunk of the bf16 row
+      const uint32_t w = w8[2 * b + wi];
+      if (kMode == 1 || (kMode == 2 && wi == 1)) {
+        *reinterpret_cast<uint4*>(half + i * 128 + (((2 * b + wi) ^ (i & 7)) << 4)) = decode_word_arith(w, s, g);
+        continue;
       }
-      const int chunk = 2 * b + wi;                   // 0..15
-      *reinterpret_cast<uint4*>(stage + (chunk >> 3) * kHalfBytes + i * 128 + (((chunk & 7) ^ (i & 7)) << 4)) =
-          make_uint4(o[0], o[1], o[2], o[3]);
+      const uint32_t sel = w & 0x77777777u;           // magnitude indices of codes 0..3 (low half) and 4..7
+      const uint32_t selb = sel >> 16;
+      const uint32_t w4 = w << 4;                     // bit 7 of byte k: sign of code 2k (of w: sign of code 2k+1)
+      const uint32_t lo_a = __byte_perm(t.x, t.y, sel), lo_b = __byte_perm(t.x, t.y, selb);
+      uint32_t hi_a = __byte_perm(t.z, t.w, sel), hi_b = __byte_perm(t.z, t.w, selb);
+      hi_a |= __byte_perm(w4, w, 0x5140) & 0x80808080u;
+      hi_b |= __byte_perm(w4, w, 0x7362) & 0x80808080u;
+      const int chunk = 2 * b + wi;                   // 0..7
+      *reinterpret_cast<uint4*>(half + i * 128 + ((chunk ^ (i & 7)) << 4)) =
+          make_uint4(__byte_perm(lo_a, hi_a, 0x5140), __byte_perm(lo_a, hi_a, 0x7362), __byte_perm(lo_b, hi_b, 0x5140),
+                     __byte_perm(lo_b, hi_b, 0x7362));
     }
   }
 }
 
-// Row i of a stage from 128 bf16 values in global memory (src == nullptr: zeros).
-__device__ __forceinline__ void copy_row_to_stage(const uint16_t* src, uint8_t* stage, int i) {
+// Row i of one half of a stage from 64 bf16 values in global memory (src == nullptr: zeros).
+__device__ __forceinline__ void copy_half_row(const uint16_t* src, uint8_t* half, int i) {
 #pragma unroll
-  for (int chunk = 0; chunk < 16; ++chunk) {
+  for (int chunk = 0; chunk < 8; ++chunk) {
     const uint4 v = src ? __ldg(reinterpret_cast<const uint4*>(src) + chunk) : make_uint4(0u, 0u, 0u, 0u);
-    *reinterpret_cast<uint4*>(stage + (chunk >> 3) * kHalfBytes + i * 128 + (((chunk & 7) ^ (i & 7)) << 4)) = v;
+    *reinterpret_cast<uint4*>(half + i * 128 + ((chunk ^ (i & 7)) << 4)) = v;
   }
 }
 
@@ -213,7 +283,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* s_full = v_empty + kStages;        // [2 halves]
   uint64_t* p_ready = s_full + 2;              // [2 halves]
   uint64_t* pv_done = p_ready + 2;             // [2 halves]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
+  uint64_t* kc_full = pv_done + 2;             // [kStages] code tiles of a K stage have landed (NVFP4 window)
+  uint64_t* vc_full = kc_full + kStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(vc_full + kStages);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -240,6 +312,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
+      mbar_init(&kc_full[i], 1);
+      mbar_init(&vc_full[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
@@ -279,10 +353,21 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int s = j % kStages;
         const uint32_t ph = (uint32_t)((j / kStages) & 1);
         if (j < nd) {
-          // a tile the decode warps build: only follow the stage's phases, one by one, so that the parity
-          // this thread waits for below can never be mistaken for that of an earlier use of the stage
+          // a tile the decode warps build: its codes go into the tail of the (free) stage, one box of 128 token
+          // rows per cache block the tile touches; rows beyond a block's end arrive as zeros and are not used
+          const int64_t key0 = (int64_t)(j0 + j) * kBK;
+          const int b0 = (int)(key0 / p.block_tokens);
+          const int tok0 = (int)(key0 - (int64_t)b0 * p.block_tokens);
+          const bool two = tok0 + kBK > p.block_tokens && (int64_t)(b0 + 1) * p.block_tokens < p.n_cached;
+          const uint32_t bytes = two ? 2 * kCodeBytes : kCodeBytes;
           mbar_wait(&k_empty[s], ph ^ 1u, abort_flag, p.status, 102u);
+          mbar_arrive_expect_tx(&kc_full[s], bytes);
+          tma_load_2d(smem + kKOff + s * kTileBytes + kCodeOff, &tab.k_codes[b0], head * 64, tok0, &kc_full[s]);
+          if (two) tma_load_2d(smem + kKOff + s * kTileBytes + kCodeOff + kCodeBytes, &tab.k_codes[b0 + 1], head * 64, 0, &kc_full[s]);
           mbar_wait(&v_empty[s], ph ^ 1u, abort_flag, p.status, 103u);
+          mbar_arrive_expect_tx(&vc_full[s], bytes);
+          tma_load_2d(smem + kVOff + s * kTileBytes + kCodeOff, &tab.v_codes[b0], head * 64, tok0, &vc_full[s]);
+          if (two) tma_load_2d(smem + kVOff + s * kTileBytes + kCodeOff + kCodeBytes, &tab.v_codes[b0 + 1], head * 64, 0, &vc_full[s]);
           continue;
         }
         // row of the tile's first key in the tensor the K / V maps describe (the whole window, or the current chunk)
@@ -353,58 +438,109 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   } else if (FUSED && warp >= 12) {
     // ------------------------------------------------------------------ NVFP4 decode (warps 12..15)
     setmaxnreg_dec<104>();
-    const int i = (int)threadIdx.x - 384;               // key row of the tile this thread builds
+    const int i = (int)threadIdx.x - 384;               // key row of the tile this thread builds; also its table entry
     const int H = p.heads;
-    // where key row i of tile j lives: 0 = cache block (fetched into `row`), 1 = current chunk, 2 = beyond the window
-    auto fetch = [&](int j, CodedRow& kr, CodedRow& vr, int64_t& cur_row) -> int {
-      const int64_t key = (int64_t)(j0 + j) * kBK + i;
-      if (key >= p.n_cached) {
-        cur_row = key - p.n_cached;
-        return key < p.Lk ? 1 : 2;
+    const int T = p.block_tokens;
+    const int n_cached = (int)p.n_cached, Lk = (int)p.Lk;      // the host keeps the window below 2^31 keys
+    uint8_t* tabs = smem + kTabOff;
+    // (block, token) of the first key of the tile being fetched, advanced tile by tile (no divisions in the loop)
+    int fb = (int)(((int64_t)j0 * kBK) / T);
+    int ft = (int)((int64_t)j0 * kBK - (int64_t)fb * T);
+    int fkey = j0 * kBK;
+    // where key row i of the next tile lives, and its scale bytes (global loads, consumed one tile later)
+    auto fetch = [&](RowInfo& r) {
+      const int key = fkey + i;
+      if (key >= n_cached) {
+        r.cur_row = key - n_cached;
+        r.kind = key < Lk ? 1 : 2;
+      } else {
+        const bool second = ft + i >= T;                  // the row lies in the next cache block: second staged code tile
+        const int b = second ? fb + 1 : fb;
+        const int tok = second ? ft + i - T : ft + i;
+        r.kind = 0;
+        r.code_row = second ? 128 + tok : i;
+        r.slot = b % kTabSlots;
+        const int row = tok * H + head;                   // row of the block: token-major, head-minor
+        const int sf_off = (row >> 7) * 1024 + (row & 31) * 16 + ((row & 127) >> 5) * 4;   // scale columns 0..3; 4..7 are 512 bytes on
+        r.ksf[0] = __ldg(reinterpret_cast<const uint32_t*>(tab.k_sf[b] + sf_off));
+        r.ksf[1] = __ldg(reinterpret_cast<const uint32_t*>(tab.k_sf[b] + sf_off + 512));
+        r.vsf[0] = __ldg(reinterpret_cast<const uint32_t*>(tab.v_sf[b] + sf_off));
+        r.vsf[1] = __ldg(reinterpret_cast<const uint32_t*>(tab.v_sf[b] + sf_off + 512));
+        if (LLNV_ATTN_DECODE_MODE != 0) {
+          r.kg = __fmul_rn(__ldg(tab.k_amax[b]), p.inv_denom);
+          r.vg = __fmul_rn(__ldg(tab.v_amax[b]), p.inv_denom);
+        }
       }
-      const int b = (int)(key / p.block_tokens);
-      const int64_t r = (key - (int64_t)b * p.block_tokens) * H + head;      // row of the block: token-major, head-minor
-      const int64_t sf_off = (r >> 7) * 1024 + (r & 31) * 16 + ((r & 127) >> 5) * 4;   // scale columns 0..3; 4..7 are 512 bytes on
-      const uint4* kc = reinterpret_cast<const uint4*>(tab.k_codes[b] + r * 64);
-      const uint4* vc = reinterpret_cast<const uint4*>(tab.v_codes[b] + r * 64);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        kr.c[c] = __ldg(kc + c);
-        vr.c[c] = __ldg(vc + c);
-      }
-      kr.sf[0] = __ldg(reinterpret_cast<const uint32_t*>(tab.k_sf[b] + sf_off));
-      kr.sf[1] = __ldg(reinterpret_cast<const uint32_t*>(tab.k_sf[b] + sf_off + 512));
-      vr.sf[0] = __ldg(reinterpret_cast<const uint32_t*>(tab.v_sf[b] + sf_off));
-      vr.sf[1] = __ldg(reinterpret_cast<const uint32_t*>(tab.v_sf[b] + sf_off + 512));
-      kr.g = __fmul_rn(__ldg(tab.k_amax[b]), p.inv_denom);
-      vr.g = __fmul_rn(__ldg(tab.v_amax[b]), p.inv_denom);
-      return 0;
+      fkey += kBK;
+      ft += kBK;
+      if (ft >= T) { ft -= T; ++fb; }
     };
-    CodedRow k_nxt, v_nxt;
-    int64_t cur_nxt = 0;
-    int kind_nxt = 2;
-    if (nd > 0) kind_nxt = fetch(0, k_nxt, v_nxt, cur_nxt);
+    // one of K / V of a tile: expand the staged codes (or copy the current chunk's rows) into stage `st`
+    auto build = [&](const RowInfo& row, int kv, uint32_t sf0, uint32_t sf1, uint8_t* st, uint64_t* codes_full, uint64_t* full,
+                     uint32_t ph) {
+      // the stage is free and its code tiles have landed (the producer waited for the stage before it loaded them)
+      mbar_wait(codes_full, ph, abort_flag, p.status, 400u + kv);
+      // Both barriers below are executed by all 128 threads outside any divergent branch: a tile that mixes cache
+      // rows and current-chunk rows splits a warp between the two branches, and bar.sync needs converged warps.
+      uint32_t w[16];
+      const uint16_t* src = nullptr;
+      const uint8_t* tb = tabs + row.slot * 4096 + kv * 2048;
+      if (row.kind == 0) {
+        // 64-byte rows, 16-byte chunks XOR-swizzled with bits 1-2 of the row index (TMA's 64-byte swizzle)
+        const uint8_t* cr = st + kCodeOff + row.code_row * 64;
+        const int sw = (row.code_row >> 1) & 3;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const uint4 v4 = *reinterpret_cast<const uint4*>(cr + ((c ^ sw) << 4));
+          w[4 * c] = v4.x; w[4 * c + 1] = v4.y; w[4 * c + 2] = v4.z; w[4 * c + 3] = v4.w;
+        }
+        // channels 0..63 go into the first half of the stage, which holds no codes: no need to wait for the others
+        const uint32_t lo8[8] = {w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]};
+        decode_half_row(lo8, sf0, tb, kv ? row.vg : row.kg, st, i);
+      } else {
+        if (row.kind == 1) src = (kv ? p.v_cur + row.cur_row * p.ldv : p.k_cur + row.cur_row * p.ldk) + (int64_t)head * kD;
+        copy_half_row(src, st, i);
+      }
+      __syncwarp();
+      asm volatile("bar.sync 1, 128;" ::: "memory");      // every thread has read its codes: the tail may be overwritten
+      if (row.kind == 0) {
+        const uint32_t hi8[8] = {w[8], w[9], w[10], w[11], w[12], w[13], w[14], w[15]};
+        decode_half_row(hi8, sf1, tb, kv ? row.vg : row.kg, st + kHalfBytes, i);
+      } else {
+        copy_half_row(src ? src + 64 : nullptr, st + kHalfBytes, i);
+      }
+      fence_proxy_async();
+      __syncwarp();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (i == 0) mbar_arrive(full);
+    };
+    // decode tables exist for cache blocks up to `built`; (lb, lt) = (block, token) of the last key of the current tile
+    int built = fb - 1;
+    int lb = (int)(((int64_t)j0 * kBK + kBK - 1) / T);
+    int lt = (int)((int64_t)j0 * kBK + kBK - 1 - (int64_t)lb * T);
+    const int last_block = n_cached > 0 ? (n_cached - 1) / T : 0;
+    RowInfo nxt;
+    nxt.kind = 2;
+    if (nd > 0) fetch(nxt);
     for (int j = 0; j < nd; ++j) {
       const int s = j % kStages;
       const uint32_t ph = (uint32_t)((j / kStages) & 1);
-      const CodedRow k_row = k_nxt, v_row = v_nxt;
-      const int64_t cur_row = cur_nxt;
-      const int kind = kind_nxt;
-      if (j + 1 < nd) kind_nxt = fetch(j + 1, k_nxt, v_nxt, cur_nxt);       // in flight while this tile is decoded
-      mbar_wait(&k_empty[s], ph ^ 1u, abort_flag, p.status, 400u);
-      uint8_t* kst = smem + kKOff + s * kTileBytes;
-      if (kind == 0) decode_row_to_stage(k_row, kst, i);
-      else copy_row_to_stage(kind == 1 ? p.k_cur + cur_row * p.ldk + (int64_t)head * kD : nullptr, kst, i);
-      fence_proxy_async();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (i == 0) mbar_arrive(&k_full[s]);
-      mbar_wait(&v_empty[s], ph ^ 1u, abort_flag, p.status, 401u);
-      uint8_t* vst = smem + kVOff + s * kTileBytes;
-      if (kind == 0) decode_row_to_stage(v_row, vst, i);
-      else copy_row_to_stage(kind == 1 ? p.v_cur + cur_row * p.ldv + (int64_t)head * kD : nullptr, vst, i);
-      fence_proxy_async();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (i == 0) mbar_arrive(&v_full[s]);
+      const RowInfo row = nxt;
+      if (j + 1 < nd) fetch(nxt);                         // in flight while this tile is decoded
+      const int b_hi = lb < last_block ? lb : last_block;
+      lt += kBK;
+      if (lt >= T) { lt -= T; ++lb; }
+      if (b_hi > built) {               // the same for all 128 threads
+        for (int b = built + 1; b <= b_hi; ++b) {
+          uint8_t* tb = tabs + (b % kTabSlots) * 4096;
+          *reinterpret_cast<uint4*>(tb + i * 16) = decode_table_entry((uint32_t)i, __fmul_rn(__ldg(tab.k_amax[b]), p.inv_denom));
+          *reinterpret_cast<uint4*>(tb + 2048 + i * 16) = decode_table_entry((uint32_t)i, __fmul_rn(__ldg(tab.v_amax[b]), p.inv_denom));
+        }
+        built = b_hi;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+      build(row, 0, row.ksf[0], row.ksf[1], smem + kKOff + s * kTileBytes, &kc_full[s], &k_full[s], ph);
+      build(row, 1, row.vsf[0], row.vsf[1], smem + kVOff + s * kTileBytes, &vc_full[s], &v_full[s], ph);
     }
   } else if (warp >= kSoftmaxWarp0 && warp < kSoftmaxWarp0 + 8) {
     // ------------------------------------------------------------------ softmax + epilogue
@@ -676,7 +812,7 @@ int attention_launch(const void* q, int64_t Lq, int64_t ldq, const void* k, cons
   LLNV_CUDA(cudaGetDevice(&dev));
   const int fused = kv != nullptr ? 1 : 0;
   if (dev >= 0 && dev < 64 && !attr_set[fused][dev]) {
-    if (fused) LLNV_CUDA(cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+    if (fused) LLNV_CUDA(cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytesFused));
     else LLNV_CUDA(cudaFuncSetAttribute(attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
     attr_set[fused][dev] = true;
   }
@@ -698,8 +834,8 @@ int attention_launch(const void* q, int64_t Lq, int64_t ldq, const void* k, cons
   p.ldk = ldk;
   p.ldv = ldv;
   dim3 grid((unsigned)((Lq + kBQ - 1) / kBQ), (unsigned)heads, (unsigned)key_splits);
-  static const KvTable no_blocks = {};
-  if (fused) launch_k(attention_kernel<true>, grid, kThreadsFused, kSmemBytes, stream, tmQ, tmK, tmV, tmO, p, *kv);
+  static const KvTable no_blocks = {};      // the bf16 kernel never reads it
+  if (fused) launch_k(attention_kernel<true>, grid, kThreadsFused, kSmemBytesFused, stream, tmQ, tmK, tmV, tmO, p, *kv);
   else launch_k(attention_kernel<false>, grid, kThreads, kSmemBytes, stream, tmQ, tmK, tmV, tmO, p, no_blocks);
   int st = launch_status("attention_kernel");
   if (st != LLNV_OK || key_splits == 1) return st;
@@ -733,20 +869,23 @@ extern "C" int llnv_attention_nvfp4kv(const void* q, int64_t Lq, int64_t ldq, co
     return attention_launch(q, Lq, ldq, k_cur, v_cur, L_cur, ldk, ldv, heads, scale, out, ldo, key_splits, workspace, workspace_bytes,
                             out_amax, nullptr, 0, 0, 0.f, (cudaStream_t)stream, who);
   LLNV_REQUIRE(k_codes && k_sf && k_amax && v_codes && v_sf && v_amax, "%s: null pointer table", who);
-  LLNV_REQUIRE(block_token_size > 0 && heads > 0, "%s: block_token_size and heads must be positive", who);
+  LLNV_REQUIRE(block_token_size >= 128 && heads > 0, "%s: block_token_size must be at least 128 (got %d) and heads positive", who,
+               block_token_size);
   LLNV_REQUIRE(e2m1_max > 0 && e4m3_max > 0, "%s: e2m1_max and e4m3_max must be positive", who);
-  KvTable tab = {};
+  static thread_local KvTable tab;          // 4.5 KiB, copied into the launch parameters
   for (int b = 0; b < num_blocks; ++b) {
     LLNV_REQUIRE(k_codes[b] && k_sf[b] && k_amax[b] && v_codes[b] && v_sf[b] && v_amax[b], "%s: null pointer in block %d", who, b);
     LLNV_REQUIRE(((uintptr_t)k_codes[b] & 15) == 0 && ((uintptr_t)v_codes[b] & 15) == 0 && ((uintptr_t)k_sf[b] & 3) == 0 &&
                      ((uintptr_t)v_sf[b] & 3) == 0,
                  "%s: codes of block %d must be 16-byte, scales 4-byte aligned", who, b);
-    tab.k_codes[b] = (const uint8_t*)k_codes[b];
     tab.k_sf[b] = (const uint8_t*)k_sf[b];
     tab.k_amax[b] = k_amax[b];
-    tab.v_codes[b] = (const uint8_t*)v_codes[b];
     tab.v_sf[b] = (const uint8_t*)v_sf[b];
     tab.v_amax[b] = v_amax[b];
+    // byte tensor [tokens, heads * 64], box 128 tokens x 64 bytes, 64-byte swizzle
+    int rc = cached_tensor_map(&tab.k_codes[b], 0, k_codes[b], (uint64_t)block_token_size, (uint64_t)heads * 64, (uint64_t)heads * 64, 128, 64, 2);
+    if (rc == LLNV_OK) rc = cached_tensor_map(&tab.v_codes[b], 0, v_codes[b], (uint64_t)block_token_size, (uint64_t)heads * 64, (uint64_t)heads * 64, 128, 64, 2);
+    if (rc != LLNV_OK) return rc;
   }
   const int64_t n_cached = (int64_t)num_blocks * block_token_size;
   const float inv_denom = (float)(1.0 / ((double)e2m1_max * (double)e4m3_max));

@@ -159,6 +159,9 @@ class KVCache:
         self.cfg = cfg
         if cfg.sink_frames % cfg.frames_per_chunk or cfg.global_sink_frames % cfg.frames_per_chunk:
             raise ValueError("sink_frames and global_sink_frames must be whole chunks (the cache is a table of chunk blocks)")
+        if cfg.chunk_tokens < 128:
+            raise ValueError("a cache block (one chunk) must hold at least 128 tokens: the attention kernel decodes 128-key tiles "
+                             "that may touch at most two blocks")
 
     def protected_blocks(self) -> int:
         """Leading blocks a roll must keep (``effective_sink`` of wan_5b/modules/causal_model.py:498-534):

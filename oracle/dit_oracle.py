@@ -3,8 +3,10 @@
 Composes the functions of ``nvfp4_oracle`` in the order of the reference's block
 (wan_5b/modules/causal_model.py:829-930; self-attention :327-791 with the quantized-cache branch
 :628-652; cross-attention :197-295; cache update :1371-1483).  Parity status: the individual
-steps are pinned by the fixtures of ``tests/golden`` (see ``nvfp4_oracle``); the composition
-itself is unpinned in the reference (no block-level test exists there).
+steps are pinned by the fixtures of ``tests/golden`` (see ``nvfp4_oracle``), and the composition is
+pinned by ``tests/golden/dit_block.npz``: inputs, weights, outputs and cache blocks of the reference's own
+``CausalWanAttentionBlock`` run on CPU for four consecutive chunks (``tests/golden/make_golden_block.py``;
+checked by ``tests/test_dit_oracle_golden.py``).
 """
 from __future__ import annotations
 
@@ -25,9 +27,12 @@ def linear(x, w_q, w_shape, bias):
     return O.linear_forward(x, w_q, w_shape, bias, "mse", "mse")
 
 
-def block_forward(x, e, p, ctx_kn, ctx_v, cos, sin, past_k, past_v, heads, frame_tokens, chunk_tokens, eps=1e-6):
+def block_forward(x, e, p, ctx_kn, ctx_v, cos, sin, past_k, past_v, heads, frame_tokens, chunk_tokens, eps=1e-6,
+                  deq_mode=O.DEQ_FUSED_CUDA):
     """x: [S, C]; e: [F, 6, C]; p: dict of weights (quantized triples + shapes, biases, norm weights);
-    past_k / past_v: lists of quantized cache blocks.  Returns (x_out, new_k_block, new_v_block)."""
+    past_k / past_v: lists of quantized cache blocks; deq_mode: which of the reference's dequantize roundings
+    the cached blocks take (its fused CUDA kernel by default, DEQ_PYTORCH for its CPU path).
+    Returns (x_out, new_k_block, new_v_block)."""
     s, c = x.shape
     frame = np.arange(s) // frame_tokens
     y = O.adaln_modulate(x, e[:, 1], e[:, 0], frame_tokens, eps)
@@ -38,7 +43,7 @@ def block_forward(x, e, p, ctx_kn, ctx_v, cos, sin, past_k, past_v, heads, frame
     kn = O.rms_norm(k, p["norm_k"], eps)
     qr = O.rope_apply(qn.reshape(s, heads, 128), cos, sin)
     kr = O.rope_apply(kn.reshape(s, heads, 128), cos, sin)
-    attn = O.window_attention(qr, kr, v.reshape(s, heads, 128), past_k, past_v, heads, chunk_tokens)
+    attn = O.window_attention(qr, kr, v.reshape(s, heads, 128), past_k, past_v, heads, chunk_tokens, mode=deq_mode)
     new_k = O.quantize_nvfp4(kr.reshape(s * heads, 128), "mse")
     new_v = O.quantize_nvfp4(v.reshape(s * heads, 128), "mse")
     o = linear(attn.reshape(s, c), p["o"], (c, c), p["o_b"])

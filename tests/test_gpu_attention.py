@@ -176,10 +176,11 @@ def _dequant_then_attention(q, kq, vq, T, k_cur, v_cur, heads, key_splits=None, 
 
 
 @pytest.mark.parametrize("heads,T,blocks,l_cur,lq,splits", [
-    (2, 96, 2, 96, 96, 1),          # cached keys end inside a tile: one tile mixes cache rows and current-chunk rows
-    (1, 128, 3, 128, 256, 1),       # tile-aligned segments
-    (3, 80, 5, 80, 300, 1),         # blocks shorter than a tile: a tile spans three cache blocks
+    (2, 136, 2, 96, 96, 1),         # cached keys end inside a tile: one tile mixes cache rows and current-chunk rows
+    (1, 128, 3, 128, 256, 1),       # tile-aligned segments (the smallest block the kernel accepts)
+    (3, 130, 5, 80, 300, 1),        # every tile spans two cache blocks; five blocks cycle through the two table slots
     (2, 200, 2, 0, 130, 1),         # the window is the cache alone, ragged last tile
+    (2, 250, 3, 7, 64, 1),          # the current chunk is a few rows inside the last decoded tile
     (2, 264, 4, 264, 264, 3),       # key splits: a split may start in the cache and end in the current chunk
     (4, 330, 4, 330, 330, 2),
     (2, 96, 0, 200, 96, 1),         # no cached block yet (first chunk)
@@ -201,7 +202,7 @@ def test_nvfp4kv_attention_is_bit_identical_to_dequant_then_attention(heads, T, 
 
 
 def test_nvfp4kv_attention_strided_current_chunk_and_arguments():
-    heads, T = 2, 64
+    heads, T = 2, 128
     g = torch.Generator(device="cuda").manual_seed(4)
     kq, vq = _cache_blocks(2, T, heads, g), _cache_blocks(2, T, heads, g)
     q = torch.randn(100, heads * 128, generator=g, device="cuda").bfloat16()
@@ -215,6 +216,8 @@ def test_nvfp4kv_attention_strided_current_chunk_and_arguments():
         ops.attention_nvfp4kv(q, kq, vq[:1], T, k_cur, v_cur, heads)
     with pytest.raises(RuntimeError, match="0 to 16 cache blocks"):
         ops.attention_nvfp4kv(q, kq * 9, vq * 9, T, k_cur, v_cur, heads)
+    with pytest.raises(RuntimeError, match="at least 128"):
+        ops.attention_nvfp4kv(q, kq, vq, 64, k_cur, v_cur, heads)
 
 
 def test_config3_window_attention_full_size_vs_oracle():

@@ -1,5 +1,5 @@
 """One causal DiT block (and two consecutive chunks through the rolling NVFP4 cache) against the
-CPU oracle composition, on a reduced configuration (dim 256, 2 heads, FFN 512, 24 tokens/frame).
+CPU oracle composition, on a reduced configuration (dim 256, 2 heads, FFN 512, 48 tokens/frame: 144-token cache blocks).
 
 Tolerance: every stage matches its oracle to within a bf16 ulp, but a one-ulp difference ahead of
 a quantizer can flip an E2M1 code (a ~6 % change of that element), so block outputs are compared
@@ -16,7 +16,7 @@ from tests import util
 
 pytestmark = pytest.mark.gpu
 
-CFG = dict(dim=256, ffn_dim=512, heads=2, layers=1, text_len=128, text_dim=64, freq_dim=32, grid_h=4, grid_w=6,
+CFG = dict(dim=256, ffn_dim=512, heads=2, layers=1, text_len=128, text_dim=64, freq_dim=32, grid_h=6, grid_w=8,
            frames_per_chunk=3, window_frames=9, sink_frames=3, in_channels=4)
 
 

@@ -12,8 +12,8 @@ import torch
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
-# 8 heads and 72 chunk tokens divide by every world size tested
-CFG = dict(dim=1024, ffn_dim=1024, heads=8, layers=2, text_len=128, text_dim=64, freq_dim=32, grid_h=4, grid_w=6,
+# 8 heads and 144 chunk tokens divide by every world size tested; cache blocks hold >= 128 tokens
+CFG = dict(dim=1024, ffn_dim=1024, heads=8, layers=2, text_len=128, text_dim=64, freq_dim=32, grid_h=6, grid_w=8,
            frames_per_chunk=3, window_frames=9, sink_frames=3, in_channels=4)
 
 
