@@ -197,8 +197,10 @@ def load_state_dict_into(model, state_dict: Mapping, prefix: str = "model.", wei
 
 
 def load_checkpoint(model, path: str, use_ema: bool = False, strict: bool = True) -> list[str]:
-    """``torch.load`` a checkpoint file and load its generator into ``model``."""
-    ckpt = torch.load(path, map_location="cpu", weights_only=False)
+    """``torch.load`` a checkpoint file and load its generator into ``model``.  The file is read with
+    ``weights_only=True``: the format holds tensors and plain containers only, so nothing in it needs unpickling
+    arbitrary objects (the reference's loader passes ``weights_only=False``)."""
+    ckpt = torch.load(path, map_location="cpu", weights_only=True)
     rule = "mse"
     if isinstance(ckpt, Mapping) and isinstance(ckpt.get("quantization"), Mapping):
         rule = ckpt["quantization"].get("weight_scale_rule") or ckpt["quantization"].get("scale_rule") or rule

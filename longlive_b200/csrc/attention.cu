@@ -122,12 +122,10 @@ __device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.
 
 // What a decode thread keeps of its key row between the prefetch and the decode.
 struct RowInfo {
-  uint32_t ksf[2], vsf[2];      // the row's 8 K and 8 V scale bytes
-  int64_t cur_row;              // kind 1: row of the current chunk
+  uint32_t ksf[2], vsf[2];      // kind 0: the row's 8 K and 8 V scale bytes
   int kind;                     // 0 = cache block, 1 = current chunk, 2 = beyond the window
-  int code_row;                 // kind 0: row inside the staged code tiles (128.. = second tile)
-  int slot;                     // kind 0: decode table slot of the row's cache block
-  float kg, vg;                 // kind 0: amax * fp32(1 / (e2m1_max * e4m3_max)) of the row's K / V block (arithmetic decode)
+  int where;                    // kind 0: row inside the staged code tiles (128.. = second tile) | table slot << 8;
+                                // kind 1: row of the current chunk
 };
 
 // Decode table of one (cache block, scale byte): the bf16 magnitudes of the eight E2M1 magnitudes
@@ -149,70 +147,51 @@ __device__ __forceinline__ uint4 decode_table_entry(uint32_t scale_byte, float g
   return t;
 }
 
-// How a decode thread turns codes into bf16 (all three give the same bits):
-//   0  table lookups with byte permutes only (integer pipe),
-//   1  convert and multiply every element as the standalone dequantize kernel does (conversion + FMA pipes),
-//   2  even 16-byte chunks by lookup, odd ones by arithmetic, to spread the work over both groups of pipes.
-#ifndef LLNV_ATTN_DECODE_MODE
-#define LLNV_ATTN_DECODE_MODE 0
-#endif
-
-// 8 codes (one word) -> 8 bf16 (16 bytes) by arithmetic: bf16((e2m1 * s) * g), decode16<LLNV_DEQ_FUSED> of dequant.cu
-__device__ __forceinline__ uint4 decode_word_arith(uint32_t w, float s, float g) {
-  const F2 s2 = f2_splat(s), g2 = f2_splat(g);
-  uint32_t o[4];
-#pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    const __half2_raw h2 = __nv_cvt_fp4x2_to_halfraw2((__nv_fp4x2_storage_t)((w >> (8 * e)) & 0xFFu), __NV_E2M1);
-    const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&h2));
-    const F2 d = f2_mul(f2_mul(F2{v.x, v.y}, s2), g2);
-    o[e] = pack_bf16x2(d.x, d.y);
-  }
-  return make_uint4(o[0], o[1], o[2], o[3]);
+// 8 codes (one word) -> 8 bf16 (16 bytes) with the table entry `t` of the codes' scale byte: four byte lookups
+// (low / high bytes of codes 0..3 and 4..7), the sign bits, four interleaves.
+__device__ __forceinline__ uint4 decode_word(uint32_t w, const uint4& t) {
+  const uint32_t sel = w & 0x77777777u;             // magnitude indices of codes 0..3 (low half) and 4..7
+  const uint32_t selb = sel >> 16;
+  const uint32_t w4 = w << 4;                       // bit 7 of byte k: sign of code 2k (of w: sign of code 2k+1)
+  const uint32_t lo_a = __byte_perm(t.x, t.y, sel), lo_b = __byte_perm(t.x, t.y, selb);
+  uint32_t hi_a = __byte_perm(t.z, t.w, sel), hi_b = __byte_perm(t.z, t.w, selb);
+  hi_a |= __byte_perm(w4, w, 0x5140) & 0x80808080u;
+  hi_b |= __byte_perm(w4, w, 0x7362) & 0x80808080u;
+  return make_uint4(__byte_perm(lo_a, hi_a, 0x5140), __byte_perm(lo_a, hi_a, 0x7362), __byte_perm(lo_b, hi_b, 0x5140),
+                    __byte_perm(lo_b, hi_b, 0x7362));
 }
 
-// Decode 64 channels (code words w[0..7], scale bytes in sf) of a cached row into row i of one half of a K / V
-// stage: rows of 128 bytes, 16-byte chunks XOR-swizzled with the row index as a TMA load with the 128-byte
-// swizzle writes them.  `tab` is the row's block's table (128 entries of 16 bytes) in shared memory.
-__device__ __forceinline__ void decode_half_row(const uint32_t (&w8)[8], uint32_t sf, const uint8_t* tab, float g, uint8_t* half,
-                                                int i) {
-  constexpr int kMode = LLNV_ATTN_DECODE_MODE;
+// Decode a cached row (code words w[0..15], scale bytes sf0 | sf1) into row i of a K / V stage: two halves of 64
+// channels, rows of 128 bytes, 16-byte chunks XOR-swizzled with the row index as a TMA load with the 128-byte
+// swizzle writes them.  `tab` is the row's block's table (128 entries of 16 bytes) in shared memory.  The loop
+// over the four 32-channel groups stays rolled (the words rotate through w[0..3]): unrolled, this code and the
+// softmax's together overflow the instruction cache.
+__device__ __forceinline__ void decode_row(uint32_t (&w)[16], uint32_t sf0, uint32_t sf1, const uint8_t* tab, uint8_t* stage, int i) {
+  uint8_t* dst = stage + i * 128;
+  const int x = i & 7;
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {                       // 32 channels: two scale bytes, four 16-byte chunks
+    const uint32_t sfw = (c & 2 ? sf1 : sf0) >> (16 * (c & 1));
+    // table entries of the two scale bytes (bit 7 of a UE4M3 scale is never set): byte * 16
+    const uint4 t0 = *reinterpret_cast<const uint4*>(tab + ((sfw << 4) & 0x7F0u));
+    const uint4 t1 = *reinterpret_cast<const uint4*>(tab + ((sfw >> 4) & 0x7F0u));
+    uint8_t* half = dst + (c >> 1) * kHalfBytes;
+    const int k0 = (c & 1) * 4;                       // first chunk of the group inside its half
+    *reinterpret_cast<uint4*>(half + (((k0 + 0) ^ x) << 4)) = decode_word(w[0], t0);
+    *reinterpret_cast<uint4*>(half + (((k0 + 1) ^ x) << 4)) = decode_word(w[1], t0);
+    *reinterpret_cast<uint4*>(half + (((k0 + 2) ^ x) << 4)) = decode_word(w[2], t1);
+    *reinterpret_cast<uint4*>(half + (((k0 + 3) ^ x) << 4)) = decode_word(w[3], t1);
 #pragma unroll
-  for (int b = 0; b < 4; ++b) {                       // 16 channels per scale
-    // table entry of scale byte b (bit 7 of a UE4M3 scale is never set): byte * 16 with one shift and one mask
-    const uint32_t toff = (b == 0 ? sf << 4 : sf >> (8 * b - 4)) & 0x7F0u;
-    uint4 t = make_uint4(0u, 0u, 0u, 0u);
-    if (kMode != 1) t = *reinterpret_cast<const uint4*>(tab + toff);
-    float s = 0.f;
-    if (kMode != 0) s = e4m3_to_float((sf >> (8 * b)) & 0xFFu);
-#pragma unroll
-    for (int wi = 0; wi < 2; ++wi) {                  // 8 codes = one 16-byte chunk of the bf16 row
-      const uint32_t w = w8[2 * b + wi];
-      if (kMode == 1 || (kMode == 2 && wi == 1)) {
-        *reinterpret_cast<uint4*>(half + i * 128 + (((2 * b + wi) ^ (i & 7)) << 4)) = decode_word_arith(w, s, g);
-        continue;
-      }
-      const uint32_t sel = w & 0x77777777u;           // magnitude indices of codes 0..3 (low half) and 4..7
-      const uint32_t selb = sel >> 16;
-      const uint32_t w4 = w << 4;                     // bit 7 of byte k: sign of code 2k (of w: sign of code 2k+1)
-      const uint32_t lo_a = __byte_perm(t.x, t.y, sel), lo_b = __byte_perm(t.x, t.y, selb);
-      uint32_t hi_a = __byte_perm(t.z, t.w, sel), hi_b = __byte_perm(t.z, t.w, selb);
-      hi_a |= __byte_perm(w4, w, 0x5140) & 0x80808080u;
-      hi_b |= __byte_perm(w4, w, 0x7362) & 0x80808080u;
-      const int chunk = 2 * b + wi;                   // 0..7
-      *reinterpret_cast<uint4*>(half + i * 128 + ((chunk ^ (i & 7)) << 4)) =
-          make_uint4(__byte_perm(lo_a, hi_a, 0x5140), __byte_perm(lo_a, hi_a, 0x7362), __byte_perm(lo_b, hi_b, 0x5140),
-                     __byte_perm(lo_b, hi_b, 0x7362));
-    }
+    for (int k = 0; k < 12; ++k) w[k] = w[k + 4];
   }
 }
 
-// Row i of one half of a stage from 64 bf16 values in global memory (src == nullptr: zeros).
-__device__ __forceinline__ void copy_half_row(const uint16_t* src, uint8_t* half, int i) {
-#pragma unroll
-  for (int chunk = 0; chunk < 8; ++chunk) {
+// Row i of a stage from 128 bf16 values in global memory (src == nullptr: zeros).
+__device__ __forceinline__ void copy_row(const uint16_t* src, uint8_t* stage, int i) {
+#pragma unroll 4
+  for (int chunk = 0; chunk < 16; ++chunk) {
     const uint4 v = src ? __ldg(reinterpret_cast<const uint4*>(src) + chunk) : make_uint4(0u, 0u, 0u, 0u);
-    *reinterpret_cast<uint4*>(half + i * 128 + ((chunk ^ (i & 7)) << 4)) = v;
+    *reinterpret_cast<uint4*>(stage + (chunk >> 3) * kHalfBytes + i * 128 + (((chunk & 7) ^ (i & 7)) << 4)) = v;
   }
 }
 
@@ -340,46 +319,61 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   // 16 warps x 32 x 128 registers at launch = 128 x (56 + 104 + 2 x 176).
   if (FUSED && warp < 4) setmaxnreg_dec<56>();
 
-  if (warp == 0) {
+  if (warp == 0 || (FUSED && warp == 2)) {
     // ------------------------------------------------------------------ TMA producer
+    // bf16 window: warp 0 loads Q, then K and V tile by tile.  NVFP4 window: warp 0 loads Q and feeds the K
+    // stages, warp 2 feeds the V stages, so that neither side queues behind the other's stage becoming free.
+    const bool do_k = warp == 0, do_v = FUSED ? warp == 2 : true;
     if (elect_one()) {
       const int col = head * kD;
-      mbar_arrive_expect_tx(q_full, n_half * kTileBytes);
-      for (int h = 0; h < n_half; ++h) {
-        tma_load_2d(smem + kQOff + h * kTileBytes, &tmQ, col, qt * kBQ + h * kHQ, q_full);
-        tma_load_2d(smem + kQOff + h * kTileBytes + kHalfBytes, &tmQ, col + 64, qt * kBQ + h * kHQ, q_full);
+      if (do_k) {
+        mbar_arrive_expect_tx(q_full, n_half * kTileBytes);
+        for (int h = 0; h < n_half; ++h) {
+          tma_load_2d(smem + kQOff + h * kTileBytes, &tmQ, col, qt * kBQ + h * kHQ, q_full);
+          tma_load_2d(smem + kQOff + h * kTileBytes + kHalfBytes, &tmQ, col + 64, qt * kBQ + h * kHQ, q_full);
+        }
       }
+      // (block, token) of the first key of tile j, advanced tile by tile
+      int b0 = FUSED ? (int)(((int64_t)j0 * kBK) / p.block_tokens) : 0;
+      int tok0 = FUSED ? (int)((int64_t)j0 * kBK - (int64_t)b0 * p.block_tokens) : 0;
       for (int j = 0; j < nt; ++j) {
         const int s = j % kStages;
         const uint32_t ph = (uint32_t)((j / kStages) & 1);
         if (j < nd) {
           // a tile the decode warps build: its codes go into the tail of the (free) stage, one box of 128 token
           // rows per cache block the tile touches; rows beyond a block's end arrive as zeros and are not used
-          const int64_t key0 = (int64_t)(j0 + j) * kBK;
-          const int b0 = (int)(key0 / p.block_tokens);
-          const int tok0 = (int)(key0 - (int64_t)b0 * p.block_tokens);
           const bool two = tok0 + kBK > p.block_tokens && (int64_t)(b0 + 1) * p.block_tokens < p.n_cached;
           const uint32_t bytes = two ? 2 * kCodeBytes : kCodeBytes;
-          mbar_wait(&k_empty[s], ph ^ 1u, abort_flag, p.status, 102u);
-          mbar_arrive_expect_tx(&kc_full[s], bytes);
-          tma_load_2d(smem + kKOff + s * kTileBytes + kCodeOff, &tab.k_codes[b0], head * 64, tok0, &kc_full[s]);
-          if (two) tma_load_2d(smem + kKOff + s * kTileBytes + kCodeOff + kCodeBytes, &tab.k_codes[b0 + 1], head * 64, 0, &kc_full[s]);
-          mbar_wait(&v_empty[s], ph ^ 1u, abort_flag, p.status, 103u);
-          mbar_arrive_expect_tx(&vc_full[s], bytes);
-          tma_load_2d(smem + kVOff + s * kTileBytes + kCodeOff, &tab.v_codes[b0], head * 64, tok0, &vc_full[s]);
-          if (two) tma_load_2d(smem + kVOff + s * kTileBytes + kCodeOff + kCodeBytes, &tab.v_codes[b0 + 1], head * 64, 0, &vc_full[s]);
+          if (do_k) {
+            mbar_wait(&k_empty[s], ph ^ 1u, abort_flag, p.status, 102u);
+            mbar_arrive_expect_tx(&kc_full[s], bytes);
+            tma_load_2d(smem + kKOff + s * kTileBytes + kCodeOff, &tab.k_codes[b0], head * 64, tok0, &kc_full[s]);
+            if (two) tma_load_2d(smem + kKOff + s * kTileBytes + kCodeOff + kCodeBytes, &tab.k_codes[b0 + 1], head * 64, 0, &kc_full[s]);
+          }
+          if (do_v) {
+            mbar_wait(&v_empty[s], ph ^ 1u, abort_flag, p.status, 103u);
+            mbar_arrive_expect_tx(&vc_full[s], bytes);
+            tma_load_2d(smem + kVOff + s * kTileBytes + kCodeOff, &tab.v_codes[b0], head * 64, tok0, &vc_full[s]);
+            if (two) tma_load_2d(smem + kVOff + s * kTileBytes + kCodeOff + kCodeBytes, &tab.v_codes[b0 + 1], head * 64, 0, &vc_full[s]);
+          }
+          tok0 += kBK;
+          if (tok0 >= p.block_tokens) { tok0 -= p.block_tokens; ++b0; }
           continue;
         }
         // row of the tile's first key in the tensor the K / V maps describe (the whole window, or the current chunk)
         const int krow = (j0 + j) * kBK - (FUSED ? (int)p.n_cached : 0);
-        mbar_wait(&k_empty[s], ph ^ 1u, abort_flag, p.status, 100u);
-        mbar_arrive_expect_tx(&k_full[s], kTileBytes);
-        tma_load_2d(smem + kKOff + s * kTileBytes, &tmK, col, krow, &k_full[s]);
-        tma_load_2d(smem + kKOff + s * kTileBytes + kHalfBytes, &tmK, col + 64, krow, &k_full[s]);
-        mbar_wait(&v_empty[s], ph ^ 1u, abort_flag, p.status, 101u);
-        mbar_arrive_expect_tx(&v_full[s], kTileBytes);
-        tma_load_2d(smem + kVOff + s * kTileBytes, &tmV, col, krow, &v_full[s]);
-        tma_load_2d(smem + kVOff + s * kTileBytes + kHalfBytes, &tmV, col + 64, krow, &v_full[s]);
+        if (do_k) {
+          mbar_wait(&k_empty[s], ph ^ 1u, abort_flag, p.status, 100u);
+          mbar_arrive_expect_tx(&k_full[s], kTileBytes);
+          tma_load_2d(smem + kKOff + s * kTileBytes, &tmK, col, krow, &k_full[s]);
+          tma_load_2d(smem + kKOff + s * kTileBytes + kHalfBytes, &tmK, col + 64, krow, &k_full[s]);
+        }
+        if (do_v) {
+          mbar_wait(&v_empty[s], ph ^ 1u, abort_flag, p.status, 101u);
+          mbar_arrive_expect_tx(&v_full[s], kTileBytes);
+          tma_load_2d(smem + kVOff + s * kTileBytes, &tmV, col, krow, &v_full[s]);
+          tma_load_2d(smem + kVOff + s * kTileBytes + kHalfBytes, &tmV, col + 64, krow, &v_full[s]);
+        }
       }
     }
   } else if (warp == 1) {
@@ -437,12 +431,15 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else if (FUSED && warp >= 12) {
     // ------------------------------------------------------------------ NVFP4 decode (warps 12..15)
+    // Thread i builds key row i of every tile: first the K stage (the MMAs need it first), then the V stage.
+    // (Two groups of 64 threads building K and V side by side, two rows per thread, measured 9 % slower: the
+    // K tile is on the critical path and took twice as long.)
     setmaxnreg_dec<104>();
     const int i = (int)threadIdx.x - 384;               // key row of the tile this thread builds; also its table entry
     const int H = p.heads;
     const int T = p.block_tokens;
     const int n_cached = (int)p.n_cached, Lk = (int)p.Lk;      // the host keeps the window below 2^31 keys
-    uint8_t* tabs = smem + kTabOff;
+    uint8_t* tabs = smem + kTabOff;                       // slot * 4096 + (K: 0, V: 2048) + entry * 16
     // (block, token) of the first key of the tile being fetched, advanced tile by tile (no divisions in the loop)
     int fb = (int)(((int64_t)j0 * kBK) / T);
     int ft = (int)((int64_t)j0 * kBK - (int64_t)fb * T);
@@ -451,25 +448,20 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     auto fetch = [&](RowInfo& r) {
       const int key = fkey + i;
       if (key >= n_cached) {
-        r.cur_row = key - n_cached;
+        r.where = key - n_cached;
         r.kind = key < Lk ? 1 : 2;
       } else {
         const bool second = ft + i >= T;                  // the row lies in the next cache block: second staged code tile
         const int b = second ? fb + 1 : fb;
         const int tok = second ? ft + i - T : ft + i;
         r.kind = 0;
-        r.code_row = second ? 128 + tok : i;
-        r.slot = b % kTabSlots;
+        r.where = (second ? 128 + tok : i) | ((b % kTabSlots) << 8);
         const int row = tok * H + head;                   // row of the block: token-major, head-minor
         const int sf_off = (row >> 7) * 1024 + (row & 31) * 16 + ((row & 127) >> 5) * 4;   // scale columns 0..3; 4..7 are 512 bytes on
         r.ksf[0] = __ldg(reinterpret_cast<const uint32_t*>(tab.k_sf[b] + sf_off));
         r.ksf[1] = __ldg(reinterpret_cast<const uint32_t*>(tab.k_sf[b] + sf_off + 512));
         r.vsf[0] = __ldg(reinterpret_cast<const uint32_t*>(tab.v_sf[b] + sf_off));
         r.vsf[1] = __ldg(reinterpret_cast<const uint32_t*>(tab.v_sf[b] + sf_off + 512));
-        if (LLNV_ATTN_DECODE_MODE != 0) {
-          r.kg = __fmul_rn(__ldg(tab.k_amax[b]), p.inv_denom);
-          r.vg = __fmul_rn(__ldg(tab.v_amax[b]), p.inv_denom);
-        }
       }
       fkey += kBK;
       ft += kBK;
@@ -480,34 +472,28 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                      uint32_t ph) {
       // the stage is free and its code tiles have landed (the producer waited for the stage before it loaded them)
       mbar_wait(codes_full, ph, abort_flag, p.status, 400u + kv);
-      // Both barriers below are executed by all 128 threads outside any divergent branch: a tile that mixes cache
-      // rows and current-chunk rows splits a warp between the two branches, and bar.sync needs converged warps.
       uint32_t w[16];
-      const uint16_t* src = nullptr;
-      const uint8_t* tb = tabs + row.slot * 4096 + kv * 2048;
       if (row.kind == 0) {
         // 64-byte rows, 16-byte chunks XOR-swizzled with bits 1-2 of the row index (TMA's 64-byte swizzle)
-        const uint8_t* cr = st + kCodeOff + row.code_row * 64;
-        const int sw = (row.code_row >> 1) & 3;
+        const int cr = row.where & 0xFF;
+        const uint8_t* src = st + kCodeOff + cr * 64;
+        const int sw = (cr >> 1) & 3;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          const uint4 v4 = *reinterpret_cast<const uint4*>(cr + ((c ^ sw) << 4));
+          const uint4 v4 = *reinterpret_cast<const uint4*>(src + ((c ^ sw) << 4));
           w[4 * c] = v4.x; w[4 * c + 1] = v4.y; w[4 * c + 2] = v4.z; w[4 * c + 3] = v4.w;
         }
-        // channels 0..63 go into the first half of the stage, which holds no codes: no need to wait for the others
-        const uint32_t lo8[8] = {w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]};
-        decode_half_row(lo8, sf0, tb, kv ? row.vg : row.kg, st, i);
-      } else {
-        if (row.kind == 1) src = (kv ? p.v_cur + row.cur_row * p.ldv : p.k_cur + row.cur_row * p.ldk) + (int64_t)head * kD;
-        copy_half_row(src, st, i);
       }
+      // Both barriers are executed by all 128 threads outside any divergent branch (a tile that mixes cache rows and
+      // current-chunk rows splits a warp between the branches above and below; bar.sync needs converged warps).
       __syncwarp();
-      asm volatile("bar.sync 1, 128;" ::: "memory");      // every thread has read its codes: the tail may be overwritten
+      asm volatile("bar.sync 1, 128;" ::: "memory");      // every thread holds its codes: the stage's tail may be overwritten
       if (row.kind == 0) {
-        const uint32_t hi8[8] = {w[8], w[9], w[10], w[11], w[12], w[13], w[14], w[15]};
-        decode_half_row(hi8, sf1, tb, kv ? row.vg : row.kg, st + kHalfBytes, i);
+        decode_row(w, sf0, sf1, tabs + (row.where >> 8) * 4096 + kv * 2048, st, i);
       } else {
-        copy_half_row(src ? src + 64 : nullptr, st + kHalfBytes, i);
+        const uint16_t* src = nullptr;
+        if (row.kind == 1) src = (kv ? p.v_cur + (int64_t)row.where * p.ldv : p.k_cur + (int64_t)row.where * p.ldk) + (int64_t)head * kD;
+        copy_row(src, st, i);
       }
       fence_proxy_async();
       __syncwarp();
@@ -530,17 +516,18 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const int b_hi = lb < last_block ? lb : last_block;
       lt += kBK;
       if (lt >= T) { lt -= T; ++lb; }
-      if (b_hi > built) {               // the same for all 128 threads
+      if (b_hi > built) {               // the same for all 128 threads; the first barrier of `build` publishes the tables
         for (int b = built + 1; b <= b_hi; ++b) {
           uint8_t* tb = tabs + (b % kTabSlots) * 4096;
           *reinterpret_cast<uint4*>(tb + i * 16) = decode_table_entry((uint32_t)i, __fmul_rn(__ldg(tab.k_amax[b]), p.inv_denom));
           *reinterpret_cast<uint4*>(tb + 2048 + i * 16) = decode_table_entry((uint32_t)i, __fmul_rn(__ldg(tab.v_amax[b]), p.inv_denom));
         }
         built = b_hi;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
       }
-      build(row, 0, row.ksf[0], row.ksf[1], smem + kKOff + s * kTileBytes, &kc_full[s], &k_full[s], ph);
-      build(row, 1, row.vsf[0], row.vsf[1], smem + kVOff + s * kTileBytes, &vc_full[s], &v_full[s], ph);
+#pragma unroll 1
+      for (int kv = 0; kv < 2; ++kv)                      // K, then V: one copy of the build code
+        build(row, kv, kv ? row.vsf[0] : row.ksf[0], kv ? row.vsf[1] : row.ksf[1], smem + (kv ? kVOff : kKOff) + s * kTileBytes,
+              kv ? &vc_full[s] : &kc_full[s], kv ? &v_full[s] : &k_full[s], ph);
     }
   } else if (warp >= kSoftmaxWarp0 && warp < kSoftmaxWarp0 + 8) {
     // ------------------------------------------------------------------ softmax + epilogue

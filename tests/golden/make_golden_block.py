@@ -157,7 +157,10 @@ def main() -> None:
             sd[f"{name}.{k}"] = v.clone()
         sd[f"{name}.bias"] = lin.bias.data.clone()
         masters[f"{name}.weight"] = lin.weight.data.clone()
-    torch.save({"format": NVFP4_CHECKPOINT_FORMAT, "version": NVFP4_CHECKPOINT_VERSION, "generator": sd, "masters": masters},
+    # outer layout of scripts/save_merged_nvfp4_generator.py:220-236 (plus the bf16 masters, for the tests)
+    torch.save({"generator": sd, "checkpoint_format": NVFP4_CHECKPOINT_FORMAT, "checkpoint_version": NVFP4_CHECKPOINT_VERSION,
+                "quantization": {"format": "nvfp4", "backend": "fouroversix", "materialized": True, "dtype": "bfloat16",
+                                 "scale_rule": "mse"}, "masters": masters},
                os.path.join(HERE, "nvfp4_state_dict.pt"))
     print("written:", os.path.join(HERE, "dit_block.npz"), os.path.join(HERE, "nvfp4_state_dict.pt"))
 

@@ -1,9 +1,38 @@
 """Checkpoint format helpers (host logic, no GPU): layouts the reference writes are unwrapped the
 way utils/nvfp4_checkpoint.py does, and the key names follow the causal Wan model's module tree."""
+import os
+
+import numpy as np
 import torch
 
 from longlive_b200 import checkpoint as ck
 from longlive_b200.dit import DiTConfig
+from oracle import nvfp4_oracle as O
+
+FIXTURE = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "nvfp4_state_dict.pt")
+
+
+def test_state_dict_written_by_the_reference_exporter():
+    """``tests/golden/nvfp4_state_dict.pt`` holds the entries the reference's FourOverSixLinear.get_quantized_parameters
+    (fouroversix/src/fouroversix/model/modules/linear.py:233-289) wrote for two Linears, in the exporter's outer layout,
+    plus their bf16 master weights.  The file loads with weights_only=True, is recognised, carries the key names and
+    the metadata layout this package reads, and its codes, scales and amax are what the oracle's quantizer gives for
+    the master weights, bit for bit."""
+    ckpt = torch.load(FIXTURE, map_location="cpu", weights_only=True)
+    assert ckpt["checkpoint_format"] == ck.NVFP4_CHECKPOINT_FORMAT and ckpt["checkpoint_version"] == ck.NVFP4_CHECKPOINT_VERSION
+    sd = ck.unwrap_generator_state_dict(ckpt)
+    assert ck.is_nvfp4_state_dict(sd)
+    assert ckpt["quantization"]["scale_rule"] == "mse"
+    wanted = {k[len("model."):] for k in ck.expected_keys(DiTConfig(layers=1))}
+    assert set(sd) <= wanted, set(sd) - wanted
+    for name, (o, i) in {"blocks.0.self_attn.q": (256, 256), "blocks.0.ffn.0": (512, 256)}.items():
+        meta = sd[f"{name}.quantized_weight_metadata"]
+        assert meta.dtype == torch.int32 and meta.tolist() == [o, i, o, i]          # original rows, cols, padded rows, cols
+        codes, sf, amax = O.quantize_nvfp4(ckpt["masters"][f"{name}.weight"].float().numpy(), "mse")
+        assert np.array_equal(sd[f"{name}.quantized_weight_values"].numpy(), codes)
+        assert np.array_equal(sd[f"{name}.quantized_weight_scale_factors"].view(torch.uint8).numpy(), sf)
+        assert np.float32(sd[f"{name}.quantized_weight_amax"].item()) == amax
+        assert sd[f"{name}.bias"].dtype == torch.bfloat16 and sd[f"{name}.bias"].numel() == o
 
 
 def test_unwrap_and_detect():
