@@ -1,23 +1,29 @@
 #!/usr/bin/env python
-"""Benchmark of the NVFP4 hot path: the W4A4 GEMM shape sweep of one Wan2.2-5B-shaped DiT block.
+"""Benchmark of the NVFP4 hot path of the causal Wan2.2-5B-shaped DiT.
 
     python bench.py --gpus N --steps K --warmup W [--impl reference]
+    torchrun --nproc-per-node N bench.py --gpus N ...        (N > 1: one rank per GPU)
 
-Workload (seeded synthetic tensors with the benchmark's shapes and value distributions):
-q/k/v/o and cross-attention q/o 3072->3072, cross-attention k/v over 512 text tokens, FFN
-3072->14336->3072, for M in {880, 2640, 10560} tokens; activations ~N(0,1) with 0.1 % entries
-x20, weights ~N(0, 0.02), both quantized to NVFP4 with the 4-over-6 MSE rule.
+Headline (`value`): video frames per second of the 30-layer DiT, one step = one autoregressive chunk of 3
+latent frames = 4 denoising forwards + UniPC steps + 1 clean re-cache forward, NVFP4 W4A4 Linears, NVFP4 KV
+cache read by the attention kernel, full 15-frame window (steady state).  N > 1 ranks run the SAME chunk
+sequence-parallel (tokens sharded, heads sharded inside self-attention, one exchange per direction per layer
+over NVLink): strong scaling.  With N > 1 every per-tensor amax is MAX-reduced over the group, so the ranks
+compute bit for bit what one GPU computes; that is checked on the live ranks before timing (`sp_parity`).
+Seeded synthetic tensors and random-init weights of the benchmark's shapes stand in for prompts and checkpoints.
 
-One "step" is one pass over all 30 GEMMs of the sweep.
-  value  W4A4 GEMM TFLOP/s (2*M*N*K with the logical M) with NVFP4 operands resident in HBM,
-         timed with CUDA events around each step, L2 flushed between steps, max over ranks.
-  e2e    the same FLOPs through the public Linear path from HOST buffers: pinned bf16
-         activations -> device, quantize, GEMM + bias, result -> host, all inside the timed region.
-With --gpus N every rank runs the sweep on its own token shard (tokens are sharded across
-ranks for every Linear; there is no collective on this path): weak scaling.
+  value          device-timed (CUDA events per chunk, max over ranks), inputs resident in HBM
+  e2e            the same chunks driven from HOST buffers: pinned latents -> device and the finished chunk
+                 -> pinned host memory inside the timed region (wall clock around synchronised chunks)
+  roofline       the dominant kernel (the chunk attention, about half of a chunk) timed live with CUDA events
+                 at the rank's shape; `chunk_roofline` and `gemm_sweep.roofline` are the whole-chunk and GEMM views
+  gemm_sweep     the W4A4 GEMM shape sweep of one DiT block (M in {880, 2640, 10560}), per rank, no collective
+  rollout        240 latent frames (80 chunks) from an empty cache: fill phase and steady state, p10/p50/p90
+  cpu_baseline   the CPU restatement of the reference's fake-quant block (oracle/, numpy) timed on the host cores
+                 for a bounded sample (one block, one frame of tokens) and extrapolated; N = 1 only
 
---impl reference times the CPU restatement of the reference's dequantize-then-matmul path
-(oracle/, numpy) on the host cores for the same metric, on a bounded sample of the workload.
+--impl reference times that CPU path alone, same metric and unit.
+--kernel-case runs one kernel on one shape (ncu captures, quick timing).
 """
 from __future__ import annotations
 
@@ -34,8 +40,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-DIM, FFN, TEXT = 3072, 14336, 512
+DIM, FFN, TEXT, HEADS, LAYERS = 3072, 14336, 512, 24, 30
 M_SWEEP = (880, 2640, 10560)
+CHUNK_TOKENS, WINDOW_TOKENS, FORWARDS = 2640, 13200, 5
 
 
 def sweep_shapes(m_values=M_SWEEP):
@@ -55,6 +62,14 @@ def flops_of(shapes) -> float:
     return float(sum(2.0 * m * n * k for _, m, n, k in shapes))
 
 
+def chunk_flops():
+    """Algorithmic FLOPs of one chunk in steady state: (FP4 GEMM flops, bf16 attention flops)."""
+    s = CHUNK_TOKENS
+    gemm = LAYERS * (6 * 2.0 * s * DIM * DIM + 2 * 2.0 * s * DIM * FFN)
+    attn = LAYERS * (4.0 * s * WINDOW_TOKENS * DIM + 4.0 * s * TEXT * DIM)
+    return FORWARDS * gemm, FORWARDS * attn
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -63,6 +78,22 @@ def load_peaks():
         return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
                 "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "source": "measured"}
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def dram_traffic(kernel: str, shape: str):
+    """DRAM read+write bytes per launch from the committed ncu summaries (profiles/dram_traffic.md: one row per
+    captured kernel and shape).  None when no capture of that shape is committed."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.md")
+    if not os.path.exists(path):
+        return None
+    for line in open(path):
+        cells = [c.strip() for c in line.strip().strip("|").split("|")]
+        if len(cells) >= 3 and cells[0] == kernel and cells[1] == shape:
+            try:
+                return float(cells[2])
+            except ValueError:
+                return None
+    return None
 
 
 class ClockSampler:
@@ -114,7 +145,6 @@ class ClockSampler:
         except Exception:
             pass
         if sm:
-            # the loop is busy for most samples; use the upper half to skip idle gaps between steps
             out["sm_mhz"] = statistics.median(sm)
             out["sm_max_mhz"] = max(smax)
             out["samples"] = len(sm)
@@ -122,58 +152,80 @@ class ClockSampler:
         return out
 
 
+def percentiles(times):
+    ts = sorted(times)
+    return statistics.median(ts), ts[int(0.1 * (len(ts) - 1))], ts[int(round(0.9 * (len(ts) - 1)))]
+
+
 # ---------------------------------------------------------------------------------------------
-# CPU arm (oracle port): dequantize-then-fp32-matmul on the host cores
+# CPU arm: the oracle's restatement of the reference's fake-quant DiT block on the host cores
 # ---------------------------------------------------------------------------------------------
 
-def cpu_port_tflops(sample_shapes, repeats: int = 1):
-    """Times oracle.fp4_matmul (the reference's PyTorch matmul backend restated in numpy) on
-    pre-quantized operands; returns (TFLOP/s, seconds, description)."""
+def cpu_block_seconds(repeats: int = 1):
+    """Times oracle.dit_oracle.block_forward (the reference's CPU path restated in numpy: quantize every Linear
+    input with the 4-over-6 rule, dequantize-then-fp32-matmul, window attention over dequantized NVFP4 blocks) for
+    ONE block at the benchmark's widths on ONE frame of tokens (880 queries; the window keeps its 4 cached blocks of
+    2640 tokens plus the new frame).  Weight and cache codes are random bytes: their values do not change the work.
+    Returns (seconds per block call, description)."""
     import numpy as np
 
+    from oracle import dit_oracle as DO
     from oracle import nvfp4_oracle as O
 
     rng = np.random.default_rng(0)
-    ops_ = []
-    for name, m, n, k in sample_shapes:
-        x = rng.standard_normal((m, k), dtype=np.float32)
-        x = np.where(rng.random((m, k)) < 0.001, x * 20, x).astype(np.float32)
-        w = (rng.standard_normal((n, k), dtype=np.float32) * 0.02).astype(np.float32)
-        # quantization of the operands is not part of the GEMM metric: use the static rule (one pass)
-        ops_.append((O.quantize_nvfp4(O.bf16_round(x), "static_6"), O.quantize_nvfp4(O.bf16_round(w), "static_6"), (m, k), (n, k)))
+    s, c, f, heads = 880, DIM, FFN, HEADS
+
+    def rand_q(rows, cols):
+        mp = (rows + 127) // 128 * 128
+        codes = rng.integers(0, 256, size=(mp, cols // 2), dtype=np.uint8)
+        sf = rng.integers(0x30, 0x50, size=mp * cols // 16, dtype=np.uint8)
+        return codes, sf, np.float32(1.0)
+
+    p = {"ffn_dim": f}
+    for n_, (o, i) in {"q": (c, c), "k": (c, c), "v": (c, c), "o": (c, c), "cq": (c, c), "co": (c, c), "ffn0": (f, c), "ffn2": (c, f)}.items():
+        p[n_] = rand_q(o, i)
+        p[n_ + "_b"] = np.zeros(o, dtype=np.float32)
+    for n_ in ("norm_q", "norm_k", "cnorm_q", "cnorm_k", "norm3_w"):
+        p[n_] = np.ones(c, dtype=np.float32)
+    p["norm3_b"] = np.zeros(c, dtype=np.float32)
+    x = O.bf16_round(rng.standard_normal((s, c), dtype=np.float32))
+    e = O.bf16_round(rng.standard_normal((1, 6, c), dtype=np.float32) * 0.1)
+    ctx_kn = O.bf16_round(rng.standard_normal((TEXT, heads, 128), dtype=np.float32))
+    ctx_v = O.bf16_round(rng.standard_normal((TEXT, heads, 128), dtype=np.float32))
+    cos, sin = O.rope_tables(12, 1, 22, 40)
+    past = [rand_q(CHUNK_TOKENS * heads, 128) for _ in range(4)]
     t0 = time.perf_counter()
     for _ in range(repeats):
-        for xq, wq, xs, ws in ops_:
-            O.fp4_matmul(xq, wq, xs, ws, "static_6", "static_6")
-    dt = time.perf_counter() - t0
-    fl = flops_of(sample_shapes) * repeats
-    return fl / dt / 1e12, dt, "; ".join(f"{n} {m}x{nn}x{k}" for n, m, nn, k in sample_shapes)
+        DO.block_forward(x, e, p, ctx_kn, ctx_v, cos, sin, past, past, heads, 880, CHUNK_TOKENS)
+    dt = (time.perf_counter() - t0) / repeats
+    return dt, ("oracle/dit_oracle.block_forward (numpy restatement of the reference's CPU fake-quant block): 1 block, 880 query tokens "
+                "(one of the chunk's 3 frames), window of 4 cached NVFP4 blocks + the frame; extrapolated x3 frames x30 layers x5 forwards")
+
+
+def cpu_chunk_fps(repeats: int = 1):
+    dt, desc = cpu_block_seconds(repeats)
+    chunk_s = dt * 3 * LAYERS * FORWARDS
+    return 12.0 / chunk_s, dt, chunk_s, desc
 
 
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample = [s for s in sweep_shapes((880,)) if s[0] in ("self_attn.q", "cross_attn.k", "ffn.0")]
-    for _ in range(max(0, min(args.warmup, 1))):
-        cpu_port_tflops(sample[:1])
-    vals, secs = [], []
-    for _ in range(max(1, min(args.steps, 5))):
-        v, dt, desc = cpu_port_tflops(sample)
-        vals.append(v)
-        secs.append(dt)
-    value = statistics.mean(vals)
+    steps = max(1, min(args.steps, 2))
+    vals = [cpu_chunk_fps(1) for _ in range(steps)]
+    value = statistics.mean(v[0] for v in vals)
+    chunk_s = statistics.mean(v[2] for v in vals)
     cores = os.cpu_count() or 1
     line = {
-        "impl": "reference", "metric": "w4a4_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": len(vals), "warmup": min(args.warmup, 1), "ms_per_step": statistics.mean(secs) * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4 (dequantized to f32 on the CPU)",
-        "data": "synthetic",
-        "config": {"workload": "DiT-block W4A4 GEMM sweep (3072/14336, M in {880,2640,10560}); CPU arm runs a bounded sample",
-                   "l2": "n/a (CPU)"},
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-                         "sample": f"numpy restatement of the reference's dequantize-then-fp32-matmul backend on: {desc}"},
-        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "impl": "reference", "metric": "dit_chunk_video_fps", "value": value, "unit": "frames/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": 0, "ms_per_step": chunk_s * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "nvfp4 fake-quant (dequantized to f32 on the CPU)", "data": "synthetic",
+        "config": {"workload": "30-layer Wan2.2-5B-shaped causal DiT, one AR chunk (3 latent frames, 5 forwards), 15-frame window; "
+                               "the CPU arm times a bounded sample and extrapolates", "l2": "n/a (CPU)"},
+        "cpu_baseline": {"value": value, "unit": "frames/s", "cores": cores, "kind": "port",
+                         "sample": vals[0][3] + f"; {vals[0][1]:.1f} s per block call"},
+        "e2e": {"value": value, "unit": "frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
 
@@ -182,21 +234,53 @@ def run_reference_arm(args):
 # GPU arm
 # ---------------------------------------------------------------------------------------------
 
-def run_gpu_arm(args):
+def sp_parity_check(dev, rank, world, group):
+    """Bit-equality of the sequence-parallel DiT with the single-GPU DiT on the live ranks (reduced configuration,
+    amax MAX-reduced over the group, peer-memory exchange when available): every rank runs both models on the same
+    inputs and compares its token shard of five chunks and its head shard of the last cache block.
+    Returns ('bit-exact' or 'mismatch', exchange kind)."""
+    import torch
+    import torch.distributed as dist
+
+    from longlive_b200 import dit, ops
+
+    cfg = dit.DiTConfig(dim=1024, ffn_dim=1024, heads=8, layers=2, text_len=128, text_dim=64, freq_dim=32, grid_h=6, grid_w=8,
+                        frames_per_chunk=3, window_frames=9, sink_frames=3, in_channels=4)
+    par = dit.CausalDiT(cfg, device=dev, seed=4, sp_group=group, sync_amax=True, use_graphs=True)
+    ref = dit.CausalDiT(cfg, device=dev, seed=4)
+    g = torch.Generator(device=dev).manual_seed(9)
+    raw = torch.randn(cfg.text_len, cfg.text_dim, generator=g, device=dev).bfloat16()
+    ctx_p, ctx_r = par.encode_text(raw), ref.encode_text(raw)
+    sl = cfg.chunk_tokens // world
+    ok = True
+    for chunk in range(5):
+        lat = torch.randn(cfg.chunk_tokens, cfg.patch_dim, generator=g, device=dev).bfloat16()
+        out_r = ref.run_chunk(lat, ctx_r, chunk)
+        out_p = par.run_chunk(lat[rank * sl:(rank + 1) * sl].contiguous(), ctx_p, chunk)
+        ok = ok and bool(torch.equal(out_p, out_r[rank * sl:(rank + 1) * sl]))
+    hl = cfg.heads // world
+    kr = ref.cache.k[0][ref.cache.current_slot()].dequantize(torch.float32).view(cfg.chunk_tokens, cfg.heads, 128)
+    kp = par.cache.k[0][par.cache.current_slot()].dequantize(torch.float32).view(cfg.chunk_tokens, hl, 128)
+    ok = ok and bool(torch.equal(kp, kr[:, rank * hl:(rank + 1) * hl]))
+    ops.check_status(dev)
+    exchange = "peer stores" if par.arena is not None else "nccl"
+    par.close()
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+    del par, ref
+    torch.cuda.empty_cache()
+    return ("bit-exact" if int(flag.item()) == 1 else "mismatch"), exchange
+
+
+def run_gemm_sweep(dev, rank, world, steps, warmup, peaks):
+    """One pass over the 30 GEMMs of the DiT-block shape sweep per step (operands resident, L2 flushed between steps,
+    the 30 launches replayed as one CUDA graph), on every rank independently; beside it the ten GEMMs a block runs on a
+    2640-token chunk, so that the large-M shapes cannot hide them."""
     import torch
     import torch.distributed as dist
 
     import longlive_b200 as L
-    from longlive_b200 import _lib, ops
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    lib = _lib.lib()
+    from longlive_b200 import ops
 
     shapes = sweep_shapes()
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
@@ -207,28 +291,127 @@ def run_gpu_arm(args):
         return torch.where(mask, x * 20, x).bfloat16()
 
     cfg = L.QuantizationConfig(scale_rule="mse")
-    weights = {}
+    weights, acts, outs = {}, {}, {}
     for name, m, n, k in shapes:
         if (name, n, k) not in weights:
-            w = (torch.randn(n, k, generator=gen, device=dev) * 0.02).bfloat16()
-            weights[(name, n, k)] = (L.quantize_to_fp4(w, cfg), torch.zeros(n, dtype=torch.bfloat16, device=dev))
-            del w
-    acts = {}
-    for name, m, n, k in shapes:
+            weights[(name, n, k)] = L.quantize_to_fp4((torch.randn(n, k, generator=gen, device=dev) * 0.02).bfloat16(), cfg)
         if (m, k) not in acts:
             acts[(m, k)] = L.quantize_to_fp4(activation(m, k), cfg)
-    outs = {}
-    for name, m, n, k in shapes:
         if (m, n) not in outs:
             outs[(m, n)] = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
 
-    def gemm_step():
-        for name, m, n, k in shapes:
-            xq = acts[(m, k)]
-            wq, _ = weights[(name, n, k)]
-            ops.gemm_nvfp4(xq.values, xq.scale_factors, xq.amax, 3, wq.values, wq.scale_factors, wq.amax, 3, m, n, k,
-                           out=outs[(m, n)])
+    def graph_of(sel):
+        def step():
+            for name, m, n, k in sel:
+                xq, wq = acts[(m, k)], weights[(name, n, k)]
+                ops.gemm_nvfp4(xq.values, xq.scale_factors, xq.amax, 3, wq.values, wq.scale_factors, wq.amax, 3, m, n, k, out=outs[(m, n)])
+        step()
+        torch.cuda.synchronize(dev)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, capture_error_mode="thread_local"):
+            step()
+        return g
+
+    def timed(g, n_steps):
+        for _ in range(max(warmup, 3)):
+            flush.fill_(1)
+            g.replay()
+        torch.cuda.synchronize(dev)
+        total = 0.0
+        for i in range(n_steps):
+            flush.fill_(i & 0xFF)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            g.replay()
+            e.record()
+            torch.cuda.synchronize(dev)
+            total += s.elapsed_time(e)
+        ms = total / n_steps
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    fp4_peak = 4.0 * peaks["bf16_tflops"]
+    ms_all = timed(graph_of(shapes), steps)
+    dit_shapes = [s for s in shapes if s[1] in (CHUNK_TOKENS, TEXT)][:10]       # the 10 GEMMs a chunk forward runs per block
+    ms_dit = timed(graph_of(dit_shapes), steps)
+    tf_all = flops_of(shapes) / (ms_all * 1e-3) / 1e12
+    tf_dit = flops_of(dit_shapes) / (ms_dit * 1e-3) / 1e12
+    del flush
+    return {
+        "metric": "w4a4_gemm_tflops", "unit": "TFLOP/s per GPU", "value": tf_all, "ms_per_step": ms_all, "steps": steps,
+        "workload": "q/k/v/o + cross q/o 3072x3072, cross k/v M=512, FFN 3072<->14336; M in {880,2640,10560}; 30 GEMMs per step, "
+                    "every rank on its own operands, no collective",
+        "flops_per_step": flops_of(shapes), "l2": "flushed between timed steps (256 MiB write)",
+        "roofline": {"bound": "tensor", "achieved": tf_all, "peak": fp4_peak, "unit": "TFLOP/s", "frac": tf_all / fp4_peak,
+                     "traffic": dram_traffic("gemm_nvfp4_kernel", "2640x14336x3072"), "traffic_case": "M=2640 N=14336 K=3072 launch (profiles/dram_traffic.md)",
+                     "peak_note": f"4 x {peaks['source']} dense bf16 burst peak ({peaks['bf16_tflops']} TFLOP/s): no FP4 entry is measured; nominal dense FP4 is 9000",
+                     "kernel": "gemm_nvfp4_kernel", "frac_of_nominal_9pf": tf_all / 9000.0},
+        "m2640_only": {"value": tf_dit, "ms_per_step": ms_dit, "frac": tf_dit / fp4_peak, "frac_of_nominal_9pf": tf_dit / 9000.0,
+                       "workload": "the 10 GEMMs one block runs on a 2640-token chunk (cross k/v at M=512)", "flops_per_step": flops_of(dit_shapes)},
+    }
+
+
+def attention_roofline(dev, rank, world, peaks, iters=8):
+    """The chunk attention at the rank's shape (2640 queries, 4 cached NVFP4 blocks + the bf16 chunk, 24 / N heads),
+    timed live with CUDA events on the launching stream, L2 flushed between launches."""
+    import torch
+
+    import longlive_b200 as L
+    from longlive_b200 import ops
+
+    heads, t, blocks = HEADS // world, CHUNK_TOKENS, 4
+    gen = torch.Generator(device=dev).manual_seed(3)
+    kq = [L.quantize_to_fp4(torch.randn(t * heads, 128, generator=gen, device=dev).bfloat16()) for _ in range(blocks)]
+    vq = [L.quantize_to_fp4(torch.randn(t * heads, 128, generator=gen, device=dev).bfloat16()) for _ in range(blocks)]
+    q = torch.randn(t, heads * 128, generator=gen, device=dev).bfloat16()
+    kc = torch.randn(t, heads * 128, generator=gen, device=dev).bfloat16()
+    vc = torch.randn(t, heads * 128, generator=gen, device=dev).bfloat16()
+    out = torch.empty_like(q)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for _ in range(3):
+        ops.attention_nvfp4kv(q, kq, vq, t, kc, vc, heads, out=out)
+    torch.cuda.synchronize(dev)
+    times = []
+    for i in range(iters):
+        flush.fill_(i)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        ops.attention_nvfp4kv(q, kq, vq, t, kc, vc, heads, out=out)
+        e.record()
+        torch.cuda.synchronize(dev)
+        times.append(s.elapsed_time(e))
+    ms = statistics.mean(times)
+    fl = 4.0 * t * (blocks + 1) * t * heads * 128
+    achieved = fl / (ms * 1e-3) / 1e12
+    peak = peaks["bf16_tflops"]
+    return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+            "traffic": dram_traffic("attention_kernel<fused>", f"2640x4x2640x{heads}"), "kernel": "attention_kernel<true> (NVFP4 K/V decoded in the load stage)",
+            "shape": f"{t} queries x {(blocks + 1) * t} keys x {heads} heads", "avg_launch_us": ms * 1e3, "launches_timed": iters,
+            "algorithmic_flops_per_launch": fl,
+            "peak_note": f"{peaks['source']} dense bf16 burst peak (cuBLAS GEMM); the kernel's MMAs are bf16 (kind::f16)"}
+
+
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    from longlive_b200 import _lib, dit, ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", device_id=dev)
+    group = dist.group.WORLD if world > 1 else None
+    lib = _lib.lib()
+    peaks = load_peaks()
 
     def sync_all():
         torch.cuda.synchronize(dev)
@@ -236,231 +419,175 @@ def run_gpu_arm(args):
             dist.barrier()
             torch.cuda.synchronize(dev)
 
-    # The 30 launches of a step are captured once in a CUDA graph and replayed: a step is short
-    # enough (about a millisecond) that launching from Python would otherwise bound it, more so
-    # with several ranks sharing the host.
-    gemm_step()
-    torch.cuda.synchronize(dev)
-    step_graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(step_graph, capture_error_mode="thread_local"):
-        gemm_step()
-    for _ in range(max(args.warmup, 3)):
-        flush.fill_(1)
-        step_graph.replay()
-    sync_all()
-    assert lib.llnv_check_status(None) == 0, lib.llnv_last_error()
-
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    sync_all()
-    wall0 = time.perf_counter()
-    for i in range(args.steps):
-        flush.fill_(i & 0xFF)          # evict the 126 MB L2 (not timed)
-        starts[i].record()
-        step_graph.replay()
-        ends[i].record()
-    sync_all()
-    wall = time.perf_counter() - wall0
-    step_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
-    total_ms = sum(step_ms)
-    if world > 1:
-        t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    def max_over_ranks(vals):
+        if world == 1:
+            return list(vals)
+        t = torch.tensor(list(vals), dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms = float(t.item())
-    ms_per_step = total_ms / args.steps
-    fl_step = flops_of(shapes)
-    value = fl_step * world / (ms_per_step * 1e-3) / 1e12
-    assert lib.llnv_check_status(None) == 0, lib.llnv_last_error()
+        return [float(v) for v in t.tolist()]
 
-    # ---- end to end through the public Linear path, host buffers -------------------------------
-    e2e_steps = max(1, min(args.steps, 3))
-    host_in = {}
-    for name, m, n, k in shapes:
-        if (m, k) not in host_in:
-            host_in[(m, k)] = torch.randn(m, k, dtype=torch.bfloat16).pin_memory()
-    torch.cuda.current_stream(dev).synchronize()
-    host_out = {}
-    for name, m, n, k in shapes:
-        if (m, n) not in host_out:
-            host_out[(m, n)] = torch.empty(m, n, dtype=torch.bfloat16).pin_memory()
-    h2d = sum(m * k * 2 for _, m, n, k in shapes)
-    d2h = sum(m * n * 2 for _, m, n, k in shapes)
-
-    # Three streams: host->device copies, quantize + GEMM, device->host copies, chained with events so
-    # that the copies of neighbouring GEMMs overlap the compute (PCIe is full duplex).
-    st_in, st_cmp, st_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-    dev_in = [torch.empty(m, k, dtype=torch.bfloat16, device=dev) for _, m, n, k in shapes]
-    dev_out = [torch.empty(m, n, dtype=torch.bfloat16, device=dev) for _, m, n, k in shapes]
-    step_done = torch.cuda.Event()
-
-    def e2e_step():
-        st_in.wait_event(step_done)                    # buffers of the previous step are free again
-        st_cmp.wait_event(step_done)
-        for i, (name, m, n, k) in enumerate(shapes):
-            with torch.cuda.stream(st_in):
-                dev_in[i].copy_(host_in[(m, k)], non_blocking=True)
-                ev_in = torch.cuda.Event()
-                ev_in.record(st_in)
-            with torch.cuda.stream(st_cmp):
-                st_cmp.wait_event(ev_in)
-                wq, bias = weights[(name, n, k)]
-                L.fp4_matmul(L.quantize_to_fp4(dev_in[i], cfg), wq, bias=bias, out=dev_out[i])
-                ev_c = torch.cuda.Event()
-                ev_c.record(st_cmp)
-            with torch.cuda.stream(st_out):
-                st_out.wait_event(ev_c)
-                host_out[(m, n)].copy_(dev_out[i], non_blocking=True)
-        step_done.record(st_out)
-        torch.cuda.current_stream(dev).wait_event(step_done)
-
-    e2e_step()
-    sync_all()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_step()
-    sync_all()
-    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    sp_parity, sp_exchange = (None, "none")
     if world > 1:
-        t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
-    e2e_value = fl_step * world / e2e_s / 1e12
-    clocks = sampler.stop() if rank == 0 else {}
+        sp_parity, sp_exchange = sp_parity_check(dev, rank, world, group)
 
-    dit_chunk = None
-    if not args.no_dit:
-        del flush
-        torch.cuda.empty_cache()
-        grp = dist.group.WORLD if world > 1 else None
-        # Sequence-parallel ranks quantize their own token shard with its own tensor scale, as the
-        # reference's sequence-parallel path does (it has no amax exchange).  The variant with every
-        # amax MAX-reduced over the group reproduces the 1-GPU codes bit for bit and is timed beside it.
-        dit_chunk = bench_dit_chunk(dev, rank, world, grp, args.chunk_steps, sync_amax=False)
-        if world > 1:
-            torch.cuda.empty_cache()
-            synced = bench_dit_chunk(dev, rank, world, grp, min(3, args.chunk_steps), sync_amax=True)
-            dit_chunk["bit_identical_to_1gpu_amax_allreduce"] = {"value": synced["value"], "ms_per_chunk": synced["ms_per_chunk"]}
-        torch.cuda.empty_cache()
-        eager = bench_dit_chunk(dev, rank, world, grp, min(3, args.chunk_steps), sync_amax=False, use_graphs=False)
-        dit_chunk["eager_launches"] = {"value": eager["value"], "ms_per_chunk": eager["ms_per_chunk"]}
-
-    if rank == 0:
-        peaks = load_peaks()
-        fp4_peak = 4.0 * peaks["bf16_tflops"]
-        per_gpu = value / world
-        line = {
-            "metric": "w4a4_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3 block scale, f32 accumulate, bf16 out)", "data": "synthetic",
-            "config": {"workload": "DiT-block W4A4 GEMM sweep: q/k/v/o + cross q/o 3072x3072, cross k/v M=512, FFN 3072<->14336; "
-                                   "M in {880,2640,10560}; 30 GEMMs per step",
-                       "flops_per_step": fl_step, "l2": "flushed between timed steps (256 MiB write)",
-                       "launches": "the 30 GEMM launches of a step replayed as one CUDA graph",
-                       "parallelism": f"tokens sharded over {world} rank(s), no collective"},
-            "clocks": clocks,
-            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "steps": e2e_steps, "ms_per_step": e2e_s * 1e3},
-            "gpu_launches": len(shapes) * args.steps,
-            "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": fp4_peak, "unit": "TFLOP/s",
-                         "frac": per_gpu / fp4_peak,
-                         "traffic": 51.3e6, "traffic_case": "dram read+write of one captured launch, M=2640 N=14336 K=3072 "
-                                                            "(profiles/gemm_nvfp4_kernel__2640x14336x3072.md); algorithmic "
-                                                            "operand+output bytes of that launch: 105 MB, of which 52 MB of output "
-                                                            "stay dirty in L2",
-                         "peak_note": f"4 x {peaks['source']} dense bf16 burst peak ({peaks['bf16_tflops']} TFLOP/s); "
-                                      "no FP4 entry is measured; nominal dense FP4 is 9000",
-                         "kernel": "gemm_nvfp4_kernel", "frac_of_nominal_9pf": per_gpu / 9000.0},
-            "wall_s_timed_region": wall,
-        }
-        if dit_chunk is not None:
-            line["dit_chunk"] = dit_chunk
-        if world == 1 and not args.no_cpu_baseline:
-            sample = [s for s in sweep_shapes((880,)) if s[0] in ("self_attn.q", "cross_attn.k", "ffn.0")]
-            v, dt, desc = cpu_port_tflops(sample, repeats=8)
-            line["cpu_baseline"] = {"value": v, "unit": "TFLOP/s", "cores": os.cpu_count() or 1, "kind": "port",
-                                    "sample": f"numpy restatement of the reference's dequantize-then-fp32-matmul backend, "
-                                              f"{dt:.1f} s for 8 passes over: {desc}"}
-        print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
-
-
-def bench_dit_chunk(dev, rank, world, group, steps: int, sync_amax: bool = True, use_graphs: bool = True):
-    """Second headline of the benchmark: one AR chunk (3 latent frames, 4 denoising forwards + 1
-    clean re-cache forward) of the 30-layer random-init Wan2.2-5B-shaped causal DiT with NVFP4
-    W4A4 linears and the NVFP4 KV cache in steady state (full 15-frame window).  With N > 1 ranks
-    the chunk is sequence-parallel over the N GPUs (tokens sharded, heads sharded inside
-    self-attention, NCCL all-to-all at the attention boundary): strong scaling.  DiT only (no T5,
-    no VAE); video fps = 4 * 3 latent frames / chunk time."""
-    import torch
-    import torch.distributed as dist
-
-    from longlive_b200 import _lib, dit
-
+    # ---- the chunk, steady state ---------------------------------------------------------------------------
     cfg = dit.DiTConfig()
-    model = dit.CausalDiT(cfg, device=dev, seed=0, sp_group=group, sync_amax=sync_amax, use_graphs=use_graphs,
+    sync_amax = world > 1 and not args.per_shard_scales
+    model = dit.CausalDiT(cfg, device=dev, seed=0, sp_group=group, sync_amax=sync_amax, use_graphs=not args.eager,
                           edge_linear=os.environ.get("LLNV_EDGE_LINEAR", "own"))
     gen = torch.Generator(device=dev).manual_seed(7)
     ctx = model.encode_text(torch.randn(cfg.text_len, cfg.text_dim, generator=gen, device=dev).bfloat16())
-    lat_full = torch.randn(cfg.chunk_tokens, cfg.patch_dim, generator=gen, device=dev).bfloat16()
     sl = cfg.chunk_tokens // world
+    lat_full = torch.randn(cfg.chunk_tokens, cfg.patch_dim, generator=gen, device=dev).bfloat16()
     lat = lat_full[rank * sl:(rank + 1) * sl].contiguous()
-    chunk = 0
-    # fill the window, then one full period of the rolling block table (each of its states is
-    # captured as a CUDA graph on first use; the timed chunks below are replays)
-    period = cfg.max_blocks - cfg.sink_frames // cfg.frames_per_chunk
-    for _ in range(cfg.max_blocks + period):
-        model.run_chunk(lat, ctx, chunk)
-        chunk += 1
-    torch.cuda.synchronize(dev)
-    if world > 1:
-        dist.barrier()
-    # every finished chunk leaves through the streaming hand-off (unpatchify into a ring slot, copy to
-    # pinned host memory on a side stream); with token shards each rank would hand off a partial image
     handoff = None
     if world == 1:
         from longlive_b200.handoff import LatentHandoff
         handoff = LatentHandoff(cfg.in_channels, cfg.frames_per_chunk, 2 * cfg.grid_h, 2 * cfg.grid_w, device=dev, target="host", depth=3)
+    chunk = 0
+    # fill the window, then one full period of the rolling block table (each of its states is captured as a CUDA
+    # graph on first use); at least `warmup` chunks in total
+    period = cfg.max_blocks - cfg.sink_frames // cfg.frames_per_chunk
+    launches0 = lib.llnv_launch_count()
+    model.run_chunk(lat, ctx, chunk)
+    chunk += 1
+    launches_per_chunk = lib.llnv_launch_count() - launches0             # eager chunk: every kernel of 5 forwards + 4 scheduler steps
+    for _ in range(max(cfg.max_blocks + period - 1, args.warmup)):
+        model.run_chunk(lat, ctx, chunk)
+        chunk += 1
+    sync_all()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     times = []
-    for _ in range(steps):
+    wall0 = time.perf_counter()
+    for _ in range(args.steps):
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
         s.record()
         out = model.run_chunk(lat, ctx, chunk)
-        if handoff is not None:
-            handoff.push(out)
         e.record()
         torch.cuda.synchronize(dev)
         times.append(s.elapsed_time(e))
-        if handoff is not None:
-            seq, _host_latent = handoff.pop()
-            handoff.release(seq)
         chunk += 1
-    assert _lib.lib().llnv_check_status(None) == 0, _lib.lib().llnv_last_error()
-    exchange = "producer kernels store into peer memory (NVLink), own barrier" if model.arena is not None else "NCCL all-to-all"
+    wall = time.perf_counter() - wall0
+    ops.check_status(dev)
+    med, p10, p90 = max_over_ranks(percentiles(times))
+    total_ms = max_over_ranks([sum(times)])[0]
+    ms_per_step = total_ms / args.steps
+    value = 12.0 / (ms_per_step * 1e-3)
+
+    # ---- end to end from host buffers ----------------------------------------------------------------------
+    e2e_steps = max(1, min(args.steps, 5))
+    host_lat = lat.cpu().pin_memory()
+    dev_lat = torch.empty_like(lat)
+    host_out = torch.empty_like(host_lat).pin_memory()
+    sync_all()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        dev_lat.copy_(host_lat, non_blocking=True)                       # this chunk's noise latents, pinned host -> device
+        out = model.run_chunk(dev_lat, ctx, chunk)
+        if handoff is not None:
+            handoff.push(out)                                            # unpatchify + side-stream copy to pinned host memory
+            seq, _host = handoff.pop()                                   # waits for that copy
+            handoff.release(seq)
+        else:
+            host_out.copy_(out, non_blocking=True)                       # the rank's token shard of the finished chunk
+            torch.cuda.synchronize(dev)
+        chunk += 1
+    sync_all()
+    e2e_s = max_over_ranks([(time.perf_counter() - t0) / e2e_steps])[0]
+    clocks = sampler.stop() if rank == 0 else {}
+    h2d = lat.numel() * 2
+    d2h = handoff.bytes_per_chunk if handoff is not None else lat.numel() * 2
+    kv_bytes = model.cache.bytes()
+    cur_bytes = (model.cur_k.numel() + model.cur_v.numel()) * 2
+    exchange = "none" if world == 1 else ("producer kernels store into peer memory (NVLink), own barrier" if model.arena is not None else "NCCL all-to-all")
     model.close()
-    ts = sorted(times)
-    stats = [statistics.median(times), ts[int(0.1 * (len(ts) - 1))], ts[int(round(0.9 * (len(ts) - 1)))]]
+    del model
+    torch.cuda.empty_cache()
+
+    # ---- rollout from an empty cache (240 latent frames) ---------------------------------------------------
+    rollout = None
+    if not args.no_rollout:
+        m2 = dit.CausalDiT(cfg, device=dev, seed=0, sp_group=group, sync_amax=sync_amax, use_graphs=not args.eager)
+        ctx2 = m2.encode_text(torch.randn(cfg.text_len, cfg.text_dim, generator=gen, device=dev).bfloat16())
+        rt = []
+        for c in range(args.rollout_chunks):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            m2.run_chunk(lat, ctx2, c)
+            e.record()
+            torch.cuda.synchronize(dev)
+            rt.append(s.elapsed_time(e))
+        ops.check_status(dev)
+        rt = max_over_ranks(rt)
+        fill_n = cfg.max_blocks + period                                 # chunks that run eagerly or capture a graph
+        steady = rt[fill_n:] if len(rt) > fill_n + 2 else rt
+        smed, sp10, sp90 = percentiles(steady)
+        rollout = {"chunks": len(rt), "latent_frames": 3 * len(rt), "total_s": sum(rt) * 1e-3, "video_fps_whole_rollout": 12.0 * len(rt) / (sum(rt) * 1e-3),
+                   "fill_phase_chunks": fill_n, "fill_phase_ms_per_chunk": [round(v, 2) for v in rt[:fill_n]],
+                   "steady_ms_per_chunk_p50": smed, "steady_ms_per_chunk_p10": sp10, "steady_ms_per_chunk_p90": sp90,
+                   "note": "cache starts empty; the window grows for 5 chunks, then the block table rolls; the first pass over each table "
+                           "state captures its CUDA graphs"}
+        m2.close()
+        del m2
+        torch.cuda.empty_cache()
+
+    attn = attention_roofline(dev, rank, world, peaks)
+    gemm = None if args.no_gemm_sweep else run_gemm_sweep(dev, rank, world, max(3, min(args.steps, 10)), args.warmup, peaks)
+
+    if rank == 0:
+        gemm_fl, attn_fl = chunk_flops()
+        fp4_peak = 4.0 * peaks["bf16_tflops_sustained"]
+        ideal_s = (gemm_fl / (fp4_peak * 1e12) + attn_fl / (peaks["bf16_tflops_sustained"] * 1e12)) / world
+        line = {
+            "metric": "dit_chunk_video_fps", "value": value, "unit": "frames/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(cfg.max_blocks + period, args.warmup + 1), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "nvfp4 W4A4 Linears (f32 accumulate, bf16 out) + bf16 attention over an NVFP4 KV cache",
+            "data": "synthetic, random-init weights",
+            "config": {"workload": "30-layer Wan2.2-5B-shaped causal DiT (dim 3072, FFN 14336, 24 heads), one AR chunk = 3 latent frames "
+                                   "(2640 tokens) x (4 denoising forwards + UniPC steps + 1 re-cache forward), window 15 frames (13200 keys), "
+                                   "512 text tokens; BASELINE config 4 at N=1, config 5's steady state at N>1",
+                       "l2": "inputs larger than L2: a chunk streams 2.9 GB of NVFP4 weights five times",
+                       "launches": "CUDA graph per (block-table state, timestep)" if not args.eager else "eager launches",
+                       "parallelism": "single GPU" if world == 1 else f"sequence-parallel over {world} GPUs (tokens / heads), exchange: {exchange}",
+                       "amax_sync": bool(sync_amax), "latent_fps": 3.0 / (ms_per_step * 1e-3)},
+            "ms_per_chunk_p50": med, "ms_per_chunk_p10": p10, "ms_per_chunk_p90": p90,
+            "clocks": clocks,
+            "e2e": {"value": 12.0 / e2e_s, "unit": "frames/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                    "ms_per_step": e2e_s * 1e3,
+                    "path": "CausalDiT.run_chunk from a pinned host latent; finished chunk through LatentHandoff to pinned host memory"
+                            if world == 1 else "CausalDiT.run_chunk from pinned host latents; every rank copies its token shard of the chunk to pinned host memory"},
+            "gpu_launches": int(launches_per_chunk) * args.steps,
+            "gpu_launches_note": f"{int(launches_per_chunk)} kernels of this library per chunk (counted on an eagerly launched chunk; timed chunks replay them from graphs)",
+            "roofline": attn,
+            "chunk_roofline": {"bound": "tensor", "algorithmic_flops_fp4_gemm": gemm_fl, "algorithmic_flops_bf16_attention": attn_fl,
+                               "ideal_ms_per_chunk": ideal_s * 1e3, "frac": ideal_s / (ms_per_step * 1e-3),
+                               "peak_note": f"GEMM flops at 4 x {peaks['source']} sustained bf16 peak ({peaks['bf16_tflops_sustained']} TFLOP/s), "
+                                            f"attention flops at that peak, divided over {world} GPU(s)"},
+            "memory": {"kv_cache_bytes_per_rank": kv_bytes, "current_chunk_kv_bytes_per_rank": cur_bytes,
+                       "note": "no bf16 copy of the cache exists: the attention kernel decodes the NVFP4 blocks in its load stage"},
+            "wall_s_timed_region": wall,
+        }
+        if sp_parity is not None:
+            line["sp_parity"] = sp_parity
+            line["sp_parity_note"] = f"reduced-configuration DiT, {world} ranks vs 1 GPU on every rank, amax MAX-reduced, exchange: {sp_exchange}"
+            line["nvlink_bytes_sent_per_rank_per_chunk"] = int(5 * (cfg.chunk_tokens // world) * cfg.dim * 2 * (world - 1) / world) * cfg.layers * 5
+        if rollout is not None:
+            line["rollout"] = rollout
+        if gemm is not None:
+            line["gemm_sweep"] = gemm
+        if world == 1 and not args.no_cpu_baseline:
+            fps, dt, chunk_s, desc = cpu_chunk_fps(1)
+            line["cpu_baseline"] = {"value": fps, "unit": "frames/s", "cores": os.cpu_count() or 1, "kind": "port",
+                                    "sample": desc + f"; {dt:.1f} s per block call -> {chunk_s:.0f} s per chunk"}
+        print(json.dumps(line))
     if world > 1:
-        t = torch.tensor(stats, dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        stats = [float(v) for v in t.tolist()]
-    ms = stats[0]
-    # bytes every rank stores into other ranks' memory per chunk: q, rotated k, smoothed k, v and the
-    # attention output, each [2640 / P tokens, 3072 channels] bf16 per block and forward, (P - 1) / P of it remote
-    nvlink = 0 if world == 1 else int(5 * (cfg.chunk_tokens // world) * cfg.dim * 2 * (world - 1) / world) * cfg.layers * 5
-    return {"metric": "dit_chunk_video_fps", "value": 12.0 / (ms * 1e-3), "unit": "frames/s", "latent_fps": 3.0 / (ms * 1e-3),
-            "ms_per_chunk": ms, "ms_per_chunk_p10": stats[1], "ms_per_chunk_p90": stats[2], "chunks_timed": steps,
-            "nvlink_bytes_sent_per_rank_per_chunk": nvlink, "layers": cfg.layers, "forwards_per_chunk": 5,
-            "window_tokens": cfg.window_frames * cfg.frame_tokens, "chunk_tokens": cfg.chunk_tokens,
-            "parallelism": f"sequence-parallel over {world} GPU(s)" if world > 1 else "single GPU",
-            "amax_sync": bool(world > 1 and sync_amax), "cuda_graphs": bool(use_graphs), "scaling": "strong",
-            "exchange": ("none" if world == 1 else exchange),
-            "kv_cache_bytes_per_rank": model.cache.bytes(),
-            "handoff": (None if handoff is None else {"target": "pinned host", "bytes_per_chunk": handoff.bytes_per_chunk, "in_timed_region": True}),
-            "data": "synthetic, random-init weights"}
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def run_kernel_case(spec: str, iters: int):
@@ -593,12 +720,17 @@ def main():
     ap.add_argument("--kernel-case", default=None, help="run one kernel case instead of the benchmark (see run_kernel_case)")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=8, help="AR chunks timed (two periods of the rolling block table)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-dit", action="store_true", help="skip the 30-layer DiT chunk measurement")
-    ap.add_argument("--chunk-steps", type=int, default=8, help="AR chunks timed for the dit_chunk figure (two periods of the rolling block table)")
+    ap.add_argument("--no-gemm-sweep", action="store_true")
+    ap.add_argument("--no-rollout", action="store_true")
+    ap.add_argument("--rollout-chunks", type=int, default=80, help="chunks of the from-empty rollout (80 = 240 latent frames)")
+    ap.add_argument("--eager", action="store_true", help="launch every kernel eagerly instead of replaying CUDA graphs")
+    ap.add_argument("--per-shard-scales", action="store_true",
+                    help="N > 1: every rank quantizes its token shard with its own tensor scale (what the reference's "
+                         "sequence-parallel path does; valid NVFP4, not bit-identical to one GPU) instead of reducing amax")
     args = ap.parse_args()
     if args.kernel_case:
         run_kernel_case(args.kernel_case, args.iters)

@@ -405,6 +405,9 @@ int llnv_unipc_step(const void* model_output, const void* sample, const void* x0
                     const llnv_unipc_coef* coef, llnv_stream_t stream);
 
 /* Test / benchmark hooks (no counterpart in the reference). */
+/* Number of kernels the library has launched in this process (every launch, captured ones included, is counted
+ * when it is issued; a replayed graph is not re-counted). */
+unsigned long long llnv_launch_count(void);
 /* 1: launch kernels with programmatic stream serialization (the next kernel of a stream is
  * scheduled while the previous one drains and waits for it on the device); 0 (default): plain
  * launches.  Returns the previous setting.  The environment variable LLNV_PDL=1 switches it on at

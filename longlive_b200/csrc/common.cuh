@@ -56,6 +56,7 @@ int sm_count();
 // are already back to back -- so the default stays the plain launch.  Without the attribute
 // pdl_wait() returns at once.
 bool pdl_enabled();                    // llnv_set_pdl / environment LLNV_PDL=0 turn the attribute off
+void count_launch();                   // llnv_launch_count(): kernels launched by the library since it was loaded
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
@@ -69,6 +70,7 @@ inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  count_launch();
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

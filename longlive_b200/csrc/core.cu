@@ -1,4 +1,5 @@
 // Library-wide plumbing: error strings, device status word, cached device properties.
+#include <atomic>
 #include <cstring>
 #include <mutex>
 
@@ -52,6 +53,11 @@ int sm_count() {
 }
 
 namespace {
+std::atomic<unsigned long long> g_launches{0};
+}
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+namespace {
 int g_pdl = -1;                        // -1: not decided yet (environment LLNV_PDL=1 turns it on; default off)
 }
 
@@ -72,6 +78,8 @@ extern "C" int llnv_set_pdl(int on) {
 }
 
 extern "C" int llnv_version(void) { return 2; }
+
+extern "C" unsigned long long llnv_launch_count(void) { return llnv::g_launches.load(std::memory_order_relaxed); }
 
 extern "C" int llnv_init_device(void) {
   if (!llnv::device_status_word()) {
