@@ -295,6 +295,13 @@ int64_t llnv_attention_workspace_bytes(int64_t Lq, int heads, int key_splits);
  *   y  = bf16(residual[m,n] + bf16(y * gate[f,n])) if residual (gate NULL -> y added as is),
  *        f = (m + row_offset) / frame_rows
  *   out_amax = max(out_amax, |y|)                  if out_amax (atomic, caller zeroes it)
+ *   (q_codes, q_sf) = quantize_nvfp4(y, amax = *q_amax)   if q_codes: the NVFP4 form of y, so that the Linear that
+ *        consumes y needs no separate quantize pass (the reference quantizes the input of every Linear in its own
+ *        kernels, fouroversix/src/fouroversix/model/modules/linear.py:45-46, and its GEMM has no epilogue at all,
+ *        fouroversix/src/fouroversix/csrc/fp4_gemm.cu:64-86).  The tensor amax must be known before the GEMM runs
+ *        (the reference's quantizer accepts a given amax: quantize/pytorch/reference.py:244, 262); codes and scales
+ *        are then bit for bit those of llnv_quantize_nvfp4(y, amax_given = 1).  Rule: LLNV_RULE_MSE.  Not combinable
+ *        with residual.  With q_codes set, d may be NULL: the bf16 result is then not written at all.
  */
 typedef struct {
   const float* alpha;     /* device scalar; NULL -> amax_a*amax_b/(6*Ea*6*Eb) from the rules */
@@ -307,6 +314,10 @@ typedef struct {
   int32_t frame_rows;     /* rows per frame for the gate lookup */
   float* out_amax;        /* fp32 scalar, atomic max of |out| */
   int32_t row_offset;     /* added to m before the gate's frame lookup (token shards) */
+  void* q_codes;          /* uint8 [Mp, N/2], Mp = M rounded up to 128 (rows M..Mp-1 are written as zeros) */
+  void* q_sf;             /* e4m3 bytes, Mp*N/16, 128x4 swizzled */
+  const float* q_amax;    /* device fp32: the tensor amax the codes are scaled with (read, not computed) */
+  int32_t q_rule;         /* LLNV_RULE_MSE */
 } llnv_epilogue_t;
 
 /* D[M, N] = epilogue(alpha * A[M, K] * B[N, K]^T), A and B NVFP4 (codes [rows_padded, K/2],

@@ -21,7 +21,8 @@ class Epilogue(C.Structure):
     _fields_ = [
         ("alpha", C.c_void_p), ("bias", C.c_void_p), ("act", C.c_int32), ("residual", C.c_void_p),
         ("ldr", C.c_int64), ("gate", C.c_void_p), ("gate_stride", C.c_int64), ("frame_rows", C.c_int32),
-        ("out_amax", C.c_void_p), ("row_offset", C.c_int32),
+        ("out_amax", C.c_void_p), ("row_offset", C.c_int32), ("q_codes", C.c_void_p), ("q_sf", C.c_void_p),
+        ("q_amax", C.c_void_p), ("q_rule", C.c_int32),
     ]
 
 

@@ -4,6 +4,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "quant_block.cuh"
 #include "sm100.cuh"
 
 namespace llnv {
@@ -25,6 +26,19 @@ struct GemmParams {
   // optional output amax; 0 = one ordinary GEMM.
   int64_t group_cols;
   float* group_amax[3];
+  // Requantized output (epilogue variants with kEpiQuant): NVFP4 codes [Mp, N/2] and swizzled scales of the
+  // epilogue's bf16 result, quantized with the 4-over-6 MSE rule under the tensor amax *q_amax supplied by the caller.
+  uint8_t* q_codes;
+  uint8_t* q_sf;
+  const float* q_amax;
+  int store_bf16;          // 0: the bf16 result itself is not written (d may be null)
+};
+
+// Where one thread's row of a 64-column chunk goes when the epilogue requantizes (kEpiQuant).
+struct QuantOut {
+  quant::QuantConsts qc;
+  uint8_t* codes;          // this row's 32 code bytes of the chunk
+  uint32_t* sf;            // this row's 4 scale bytes of the chunk (one word of the swizzled atom)
 };
 
 struct GroupMaps {
@@ -45,7 +59,7 @@ __device__ __forceinline__ float gelu_tanh(float x) {
 
 // epilogue variants (compile-time, so that the plain path stays a handful of instructions per
 // element and the whole epilogue fits the instruction cache)
-constexpr int kEpiBias = 1, kEpiGelu = 2, kEpiRes = 4;
+constexpr int kEpiBias = 1, kEpiGelu = 2, kEpiRes = 4, kEpiQuant = 8;
 
 // First step of every epilogue: alpha * accumulator, rounded to bf16 (the reference's GEMM returns
 // bf16 before bias / activation / residual are applied), packed two columns per word.  After this
@@ -65,8 +79,13 @@ __device__ __forceinline__ void drain_chunk(const uint32_t (&r)[2][32], float al
 template <int EPI>
 __device__ __forceinline__ void epilogue_packed(const uint32_t (&pk)[32], const uint16_t* __restrict__ bias,
                                                 const uint16_t* __restrict__ grow, int64_t col, uint8_t* buf, int lane,
-                                                bool want_amax, bool row_ok, float& local_amax) {
+                                                bool want_amax, bool row_ok, float& local_amax, const QuantOut* qo = nullptr,
+                                                bool store_bf16 = true) {
   constexpr bool has_res = (EPI & kEpiRes) != 0;
+  constexpr bool has_quant = (EPI & kEpiQuant) != 0;
+  uint32_t qw[8];                     // the 16 bf16 values of the quantization block being assembled
+  uint32_t qc_words[8];               // the chunk's 32 code bytes
+  uint32_t qsf = 0;                   // the chunk's 4 scale bytes
 #pragma unroll
   for (int v8 = 0; v8 < 8; ++v8) {    // 8 columns (16 bytes) at a time
     uint4* slot = reinterpret_cast<uint4*>(buf + lane * 128 + ((v8 ^ (lane & 7)) << 4));
@@ -133,7 +152,25 @@ __device__ __forceinline__ void epilogue_packed(const uint32_t (&pk)[32], const 
     ov.y = pack2(y[2], y[3]);
     ov.z = pack2(y[4], y[5]);
     ov.w = pack2(y[6], y[7]);
-    *slot = ov;
+    if (!has_quant || store_bf16) *slot = ov;
+    if (has_quant) {
+      // two 8-column units make one 16-element quantization block: the block quantizer of the standalone kernel,
+      // on the bf16 values just produced, with the tensor amax given up front
+      const int h = (v8 & 1) * 4;
+      qw[h] = ov.x; qw[h + 1] = ov.y; qw[h + 2] = ov.z; qw[h + 3] = ov.w;
+      if (v8 & 1) {
+        uint32_t c_lo = 0, c_hi = 0, sfb = 0;
+        if (row_ok) quant::quant_block<LLNV_RULE_MSE>(qw, qo->qc, c_lo, c_hi, sfb);     // rows beyond M: zero codes and scales
+        qc_words[v8 - 1] = c_lo;
+        qc_words[v8] = c_hi;
+        qsf |= sfb << (8 * (v8 >> 1));
+      }
+    }
+  }
+  if (has_quant) {
+    reinterpret_cast<uint4*>(qo->codes)[0] = make_uint4(qc_words[0], qc_words[1], qc_words[2], qc_words[3]);
+    reinterpret_cast<uint4*>(qo->codes)[1] = make_uint4(qc_words[4], qc_words[5], qc_words[6], qc_words[7]);
+    *qo->sf = qsf;
   }
 }
 

@@ -211,6 +211,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       if (p.N >= 3 * p.group_cols) alpha2 = __fdiv_rn(__fmul_rn(__ldg(p.a_amax), __ldg(p.b_amax + 2)), p.alpha_denom);
     }
     float amax0 = 0.f, amax1 = 0.f, amax2 = 0.f;
+    quant::QuantConsts qconsts = {};
+    if constexpr ((EPI & kEpiQuant) != 0) qconsts = quant::make_consts<LLNV_RULE_MSE>(__ldg(p.q_amax));
     const uint16_t* bias = reinterpret_cast<const uint16_t*>(p.epi.bias);
     constexpr bool has_res = (EPI & kEpiRes) != 0;
     const uint16_t* gate = reinterpret_cast<const uint16_t*>(p.epi.gate);
@@ -284,13 +286,29 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             __syncwarp();
           }
           const int64_t col = (int64_t)nt * BN + c0;
-          epilogue_packed<EPI>(pkc, bias, grow, col, buf, lane, want_amax, row_ok, local_amax);
+          if constexpr ((EPI & kEpiQuant) != 0) {
+            // codes [Mp, N/2] row-major; scales in 512-byte atoms of 128 rows x 4 scale columns (64 elements)
+            QuantOut qo;
+            qo.qc = qconsts;
+            qo.codes = p.q_codes + row * (p.N >> 1) + (col >> 1);
+            qo.sf = reinterpret_cast<uint32_t*>(p.q_sf + ((int64_t)mt * (p.N >> 6) + (col >> 6)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4);
+            epilogue_packed<EPI>(pkc, bias, grow, col, buf, lane, want_amax, row_ok, local_amax, &qo, p.store_bf16 != 0);
+          } else {
+            epilogue_packed<EPI>(pkc, bias, grow, col, buf, lane, want_amax, row_ok, local_amax);
+          }
           fence_proxy_async();
           __syncwarp();
-          if (lane == 0) {
+          if (lane == 0 && ((EPI & kEpiQuant) == 0 || p.store_bf16)) {
             tma_store_2d(tm_out, buf, (int)(col - gcol0), row0);  // rows beyond M are clipped by the tensor map
             bulk_commit();
           }
+        } else if constexpr ((EPI & kEpiQuant) != 0) {
+          // a group of 32 padding rows (M..Mp-1): zero codes and zero scales, as the standalone quantizer writes them
+          const int64_t col = (int64_t)nt * BN + c0;
+          uint4* cz = reinterpret_cast<uint4*>(p.q_codes + row * (p.N >> 1) + (col >> 1));
+          cz[0] = make_uint4(0u, 0u, 0u, 0u);
+          cz[1] = make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint32_t*>(p.q_sf + ((int64_t)mt * (p.N >> 6) + (col >> 6)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4) = 0u;
         }
       };
       const uint32_t acc_tmem = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
@@ -412,11 +430,11 @@ namespace {
 int gemm_run(const void* a_codes, const void* a_sf, const float* a_amax, int a_rule, const void* b_codes, const void* b_sf,
              const float* b_amax, int b_rule, int64_t M, int64_t N, int64_t K, const llnv_epilogue_t* epilogue, void* d, int64_t ldd,
              cudaStream_t stream, int groups, void* const* d_groups, const int64_t* ldd_groups, float* const* amax_groups, int tile) {
-  LLNV_REQUIRE(a_codes && a_sf && b_codes && b_sf && d, "llnv_gemm_nvfp4: null pointer");
+  LLNV_REQUIRE(a_codes && a_sf && b_codes && b_sf, "llnv_gemm_nvfp4: null pointer");
   LLNV_REQUIRE(M >= 0 && N > 0 && K > 0, "llnv_gemm_nvfp4: bad shape M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
   LLNV_REQUIRE(N % 128 == 0, "llnv_gemm_nvfp4: N must be a multiple of 128 (got %lld)", (long long)N);
   LLNV_REQUIRE(K % 256 == 0, "llnv_gemm_nvfp4: K must be a multiple of 256 (got %lld)", (long long)K);
-  LLNV_REQUIRE(ldd >= N / groups && ldd % 8 == 0 && ((uintptr_t)d & 15) == 0, "llnv_gemm_nvfp4: d must be 16-byte aligned with ldd a multiple of 8");
+  LLNV_REQUIRE(d == nullptr || (ldd >= N / groups && ldd % 8 == 0 && ((uintptr_t)d & 15) == 0), "llnv_gemm_nvfp4: d must be 16-byte aligned with ldd a multiple of 8");
   LLNV_REQUIRE(((uintptr_t)a_sf & 15) == 0 && ((uintptr_t)b_sf & 15) == 0, "llnv_gemm_nvfp4: scale arrays must be 16-byte aligned");
   LLNV_REQUIRE(a_rule >= 0 && a_rule <= 4 && b_rule >= 0 && b_rule <= 4, "llnv_gemm_nvfp4: unknown scale rule");
   LLNV_REQUIRE(tile == LLNV_GEMM_TILE_AUTO || tile == LLNV_GEMM_TILE_PAIR || tile == 128 || tile == 192 || tile == 256,
@@ -431,6 +449,15 @@ int gemm_run(const void* a_codes, const void* a_sf, const float* a_amax, int a_r
   if (epi.bias) LLNV_REQUIRE(((uintptr_t)epi.bias & 15) == 0, "llnv_gemm_nvfp4: bias must be 16-byte aligned");
   if (epi.gate) LLNV_REQUIRE(((uintptr_t)epi.gate & 15) == 0 && epi.gate_stride % 8 == 0, "llnv_gemm_nvfp4: gate must be 16-byte aligned with a stride that is a multiple of 8");
   if (epi.gate) LLNV_REQUIRE(epi.residual && epi.frame_rows > 0 && epi.gate_stride >= N, "llnv_gemm_nvfp4: gate needs residual, frame_rows > 0 and gate_stride >= N");
+  const bool requant = epi.q_codes != nullptr;
+  if (requant) {
+    LLNV_REQUIRE(epi.q_sf && epi.q_amax, "llnv_gemm_nvfp4: requantized output needs q_codes, q_sf and q_amax");
+    LLNV_REQUIRE(epi.q_rule == LLNV_RULE_MSE, "llnv_gemm_nvfp4: the epilogue requantizes with the 4-over-6 MSE rule only (got rule %d)", epi.q_rule);
+    LLNV_REQUIRE(!epi.residual && groups == 1, "llnv_gemm_nvfp4: requantized output cannot be combined with a residual or a grouped launch");
+    LLNV_REQUIRE(((uintptr_t)epi.q_codes & 15) == 0 && ((uintptr_t)epi.q_sf & 3) == 0, "llnv_gemm_nvfp4: q_codes must be 16-byte, q_sf 4-byte aligned");
+    LLNV_REQUIRE(N % 64 == 0, "llnv_gemm_nvfp4: requantized output needs N %% 64 == 0");
+  }
+  LLNV_REQUIRE(d != nullptr || requant, "llnv_gemm_nvfp4: null output pointer");
   if (M == 0) return LLNV_OK;
 
   const int64_t group_cols = groups > 1 ? N / groups : 0;
@@ -464,6 +491,14 @@ int gemm_run(const void* a_codes, const void* a_sf, const float* a_amax, int a_r
   p.d = (__nv_bfloat16*)d;
   p.ldd = ldd;
   p.status = device_status_word();
+  p.q_codes = (uint8_t*)epi.q_codes;
+  p.q_sf = (uint8_t*)epi.q_sf;
+  p.q_amax = epi.q_amax;
+  p.store_bf16 = d != nullptr ? 1 : 0;
+  if (d == nullptr) {           // the output map is never used; describe the codes buffer so that the encode succeeds
+    d = epi.q_codes;
+    ldd = N;
+  }
   CUtensorMap tmD, tmR;
   GroupMaps gmaps;
   memset(&gmaps, 0, sizeof(gmaps));
@@ -483,9 +518,9 @@ int gemm_run(const void* a_codes, const void* a_sf, const float* a_amax, int a_r
     rc = get_out_map(&tmR, epi.residual, (uint64_t)M, (uint64_t)N, (uint64_t)epi.ldr);
     if (rc != LLNV_OK) return rc;
   }
-  const int variant = (epi.bias ? kEpiBias : 0) | (epi.act == 1 ? kEpiGelu : 0) | (epi.residual ? kEpiRes : 0);
+  const int variant = (epi.bias ? kEpiBias : 0) | (epi.act == 1 ? kEpiGelu : 0) | (epi.residual ? kEpiRes : 0) | (requant ? kEpiQuant : 0);
   // CTA pairs pay off when the K loop dominates (measured: +13..17 % at K = 14336, no gain at K = 3072)
-  const bool pair_ok = N % 256 == 0;
+  const bool pair_ok = N % 256 == 0 && !requant;
   const bool pair_auto = tile == 0 && K >= 8192 && M >= 1024 && groups == 1;
   if (pair_ok && groups == 1 && (tile == 2 || pair_auto)) return gemm_nvfp4_pair(a_codes, a_sf, b_codes, b_sf, p, tmD, tmR, variant, stream);
 #define LLNV_GEMM_CASE(V)                                                                   \
@@ -502,6 +537,10 @@ int gemm_run(const void* a_codes, const void* a_sf, const float* a_amax, int a_r
     LLNV_GEMM_CASE(5)
     LLNV_GEMM_CASE(6)
     LLNV_GEMM_CASE(7)
+    LLNV_GEMM_CASE(8)       // requantized output: plain, + bias, + GELU, + bias + GELU
+    LLNV_GEMM_CASE(9)
+    LLNV_GEMM_CASE(10)
+    LLNV_GEMM_CASE(11)
   }
 #undef LLNV_GEMM_CASE
   set_error("llnv_gemm_nvfp4: internal dispatch error");

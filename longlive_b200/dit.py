@@ -159,9 +159,7 @@ class KVCache:
         self.cfg = cfg
         if cfg.sink_frames % cfg.frames_per_chunk or cfg.global_sink_frames % cfg.frames_per_chunk:
             raise ValueError("sink_frames and global_sink_frames must be whole chunks (the cache is a table of chunk blocks)")
-        if cfg.chunk_tokens < 128:
-            raise ValueError("a cache block (one chunk) must hold at least 128 tokens: the attention kernel decodes 128-key tiles "
-                             "that may touch at most two blocks")
+
 
     def protected_blocks(self) -> int:
         """Leading blocks a roll must keep (``effective_sink`` of wan_5b/modules/causal_model.py:498-534):
@@ -220,10 +218,15 @@ class KVCache:
 
 class CausalDiT:
     def __init__(self, cfg: DiTConfig | None = None, device="cuda", seed: int = 0, sp_group=None, sync_amax: bool = True,
-                 cache_text_kv: bool = True, use_graphs: bool = False, peer_exchange: bool = True, edge_linear: str = "own"):
+                 cache_text_kv: bool = True, use_graphs: bool = False, peer_exchange: bool = True, edge_linear: str = "own",
+                 ffn_requant: str = "two_pass"):
         self.cfg = cfg = cfg or DiTConfig()
         if edge_linear not in ("own", "library"):
             raise ValueError("edge_linear is 'own' (llnv_linear_bf16) or 'library' (torch.nn.functional.linear, i.e. cuBLAS)")
+        if ffn_requant not in ("two_pass", "single_pass"):
+            raise ValueError("ffn_requant is 'two_pass' (the reference's rounding: GEMM writes the bf16 hidden and its amax, a second "
+                             "kernel quantizes it) or 'single_pass' (the GEMM epilogue quantizes with the previous forward's amax)")
+        self.ffn_requant = ffn_requant
         self.edge_linear = edge_linear
         self.use_graphs = use_graphs
         self.device = torch.device(device)
@@ -232,6 +235,9 @@ class CausalDiT:
         self.sync_amax = sync_amax and self.P > 1
         self.cache_text_kv = cache_text_kv
         assert cfg.chunk_tokens % self.P == 0 and cfg.heads % self.P == 0, "tokens and heads must divide by the SP size"
+        if cfg.chunk_tokens < 128:
+            raise ValueError("a cache block (one chunk) must hold at least 128 tokens: the attention kernel decodes 128-key tiles "
+                             "that may touch at most two blocks")
         gen = torch.Generator(device=self.device).manual_seed(seed)          # same weights on every rank
         self.blocks = [Block(cfg, gen, self.device) for _ in range(cfg.layers)]
         c = cfg.dim
@@ -291,6 +297,11 @@ class CausalDiT:
         self.kv_amax = torch.zeros(2, dtype=torch.float32, device=dev)      # [k, v]: reduced with one collective
         self.k_amax, self.v_amax = self.kv_amax[0:1], self.kv_amax[1:2]
         self.h_amax = torch.zeros(1, dtype=torch.float32, device=dev)
+        # single-pass FFN requantization: per layer the amax the epilogue scales the hidden with (that of the layer's
+        # previous forward) and the amax this forward measures
+        self.ffn_amax_use = torch.zeros(cfg.layers, dtype=torch.float32, device=dev)
+        self.ffn_amax_new = torch.zeros(cfg.layers, dtype=torch.float32, device=dev)
+        self._ffn_calibrated = False
         self.modulation_all = torch.stack([b.modulation for b in self.blocks], 0)       # [layers, 1, 6, dim]
         self._prompts: list = []              # cached cross-attention K / V per prompt tensor, most recent last
         self._prompt_serial = 0
@@ -521,12 +532,33 @@ class CausalDiT:
         self._gemm(self.act_c, Sl, blk.co, x2, residual=x1)
         # -- FFN
         self._adaln_quantize(x2, e[:, 4], e[:, 3], self.act_c)
+        if self.ffn_requant == "single_pass" and self._ffn_calibrated:
+            # The GEMM epilogue quantizes the GELU output itself: the 75.7 MB bf16 hidden is neither written nor re-read
+            # and one launch goes away.  A quantizer needs the tensor amax before its first block; it is taken from this
+            # layer's previous forward (values above it saturate as the quantizer saturates them), and this forward's
+            # amax is measured for the next one.  Not the reference's rounding: 'two_pass' below is.
+            use, new = self.ffn_amax_use[li:li + 1], self.ffn_amax_new[li:li + 1]
+            a = self.act_c
+            new.zero_()
+            ops.gemm_nvfp4(a.codes, a.sf, a.amax, MSE, blk.ffn0.q.values, blk.ffn0.q.scale_factors, blk.ffn0.q.amax,
+                           blk.ffn0.q.scale_rule.cuda_id(), Sl, blk.ffn0.out_f, blk.ffn0.in_f, bias=blk.ffn0.bias, act=1, out_amax=new,
+                           requant=(self.act_f.codes, self.act_f.sf), requant_amax=use, store_out=False)
+            f = self.act_f
+            ops.gemm_nvfp4(f.codes, f.sf, use, MSE, blk.ffn2.q.values, blk.ffn2.q.scale_factors, blk.ffn2.q.amax,
+                           blk.ffn2.q.scale_rule.cuda_id(), Sl, blk.ffn2.out_f, blk.ffn2.in_f, out=x_out, bias=blk.ffn2.bias, residual=x2,
+                           gate=e[:, 5], frame_rows=ft, row_offset=roff)
+            if self.sync_amax:
+                self._allreduce_max(new)
+            use.copy_(new)
+            return x_out
         self.act_f.amax.zero_()
         self._gemm(self.act_c, Sl, blk.ffn0, self.hidden, act=1, out_amax=self.act_f.amax)
         if self.sync_amax:
             self._allreduce_max(self.act_f.amax)
         ops.quantize_nvfp4(self.hidden, MSE, self.act_f.amax, self.act_f.codes, self.act_f.sf, amax_given=True)
         self._gemm(self.act_f, Sl, blk.ffn2, x_out, residual=x2, gate=e[:, 5], frame_rows=ft, row_offset=roff)
+        if self.ffn_requant == "single_pass":
+            self.ffn_amax_use[li:li + 1].copy_(self.act_f.amax)      # calibration: the first forward runs the two-pass form
         return x_out
 
     # ---- whole model ----------------------------------------------------------------------------
@@ -611,11 +643,14 @@ class CausalDiT:
         self._edge(latent_tokens, self.patch_w, self.patch_b, out=self.x_a)       # patch embedding, causal_model.py:1535-1540
         e, em_all = time_inputs if time_inputs is not None else self._time_inputs(t, None)
         cos, sin = self.cos_buf, self.sin_buf
+        ran_before = self._ran_eager
         self._ran_eager = True
         cur, nxt = self.x_a, self.x_b
         for li, blk in enumerate(self.blocks):
             self.block_forward(li, cur, nxt, em_all[li], ctx, cos, sin)
             cur, nxt = nxt, cur
+        if not ran_before:
+            self._ffn_calibrated = True          # every layer's hidden amax is known from here on
         # head: LayerNorm, modulate with (head.modulation + e), project (CausalHead.forward, causal_model.py:950-959):
         # the same bf16 rounding points as a block's adaLN, so the quantizer's load-side transform produces y
         # (its NVFP4 output goes to scratch and is not used: the head Linear stays bf16)

@@ -441,12 +441,18 @@ def kv_dequant(values, scale_factors, amax, num_heads, block_token_size, dtype, 
 
 
 def gemm_nvfp4(a_codes, a_sf, a_amax, a_rule, b_codes, b_sf, b_amax, b_rule, m, n, k, *, out=None, alpha=None,
-               bias=None, act=0, residual=None, gate=None, frame_rows=0, out_amax=None, row_offset=0, tile=0):
+               bias=None, act=0, residual=None, gate=None, frame_rows=0, out_amax=None, row_offset=0, tile=0,
+               requant=None, requant_amax=None, store_out=True):
     """``epilogue(alpha * A @ B^T)`` -> bf16 [m, n]; see ``llnv_gemm_nvfp4`` in include/llnvfp4.h.
-    ``tile``: 0 = tiling chosen by shape, 128 / 192 / 256 = that tile width, 2 = CTA-pair kernel."""
+    ``tile``: 0 = tiling chosen by shape, 128 / 192 / 256 = that tile width, 2 = CTA-pair kernel.
+    ``requant`` = (codes, sf) buffers: the epilogue also writes the NVFP4 form of the result (4-over-6 MSE rule)
+    under the tensor amax ``requant_amax`` (fp32 [1], known before the call); with ``store_out=False`` the bf16
+    result itself is not written and None is returned."""
     _require_cuda(a_codes, "a_codes")
     dev = a_codes.device
-    if out is None:
+    if requant is None and not store_out:
+        raise ValueError("store_out=False needs requant buffers")
+    if out is None and store_out:
         out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
     epi = _lib.Epilogue()
     epi.alpha = alpha.data_ptr() if alpha is not None else None
@@ -461,13 +467,21 @@ def gemm_nvfp4(a_codes, a_sf, a_amax, a_rule, b_codes, b_sf, b_amax, b_rule, m, 
         epi.frame_rows = int(frame_rows)
         epi.row_offset = int(row_offset)
     epi.out_amax = out_amax.data_ptr() if out_amax is not None else None
+    if requant is not None:
+        q_codes, q_sf = requant
+        if requant_amax is None or requant_amax.dtype != torch.float32:
+            raise ValueError("requant needs requant_amax (fp32 [1]): the tensor amax must be known before the GEMM runs")
+        if q_codes.dtype != torch.uint8 or q_codes.numel() < padded_rows(m) * n // 2 or q_sf.numel() < padded_rows(m) * n // 16:
+            raise RuntimeError("requant buffers must hold uint8 [Mp, N/2] codes and Mp*N/16 scale bytes")
+        epi.q_codes, epi.q_sf, epi.q_amax, epi.q_rule = q_codes.data_ptr(), q_sf.data_ptr(), requant_amax.data_ptr(), 3
     with torch.cuda.device(dev):
         _check(_lib.lib().llnv_gemm_nvfp4_ex(a_codes.data_ptr(), a_sf.data_ptr(),
                                              a_amax.data_ptr() if a_amax is not None else None, a_rule,
                                              b_codes.data_ptr(), b_sf.data_ptr(),
                                              b_amax.data_ptr() if b_amax is not None else None, b_rule,
-                                             m, n, k, C.byref(epi), out.data_ptr(), out.stride(0), int(tile), _stream(a_codes)))
-    return out
+                                             m, n, k, C.byref(epi), out.data_ptr() if store_out else None,
+                                             out.stride(0) if store_out else n, int(tile), _stream(a_codes)))
+    return out if store_out else None
 
 
 def gemm_nvfp4_grouped(a_codes, a_sf, a_amax, a_rule, b_codes, b_sf, b_amax, b_rule, m, n_each, k, outs, *, bias=None, act=0,

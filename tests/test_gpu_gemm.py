@@ -272,3 +272,58 @@ def test_gemm_benchmark_shapes_match_oracle(m, n, k, tiles):
             first = y
         else:
             assert torch.equal(y, first)
+
+
+@pytest.mark.parametrize("m,n,k,tile,act", [(300, 512, 768, 0, 1), (300, 512, 768, 256, 0), (264, 768, 512, 192, 1), (2640, 14336, 3072, 0, 1)])
+def test_gemm_epilogue_requantizes_its_output(m, n, k, tile, act):
+    """The epilogue variant that also writes the NVFP4 form of its result, with the tensor amax given up front:
+    codes and scales equal the standalone quantizer's (and the oracle's) on the bf16 result, bit for bit; rows M..Mp-1
+    are zero; the bf16 result is unchanged, or not written at all when the caller does not want it."""
+    x = util.config_activation(m, k, seed=m + 1).cuda()
+    w = util.config_weight(n, k, seed=n + 1).cuda()
+    xq, wq = L.quantize_to_fp4(x), L.quantize_to_fp4(w)
+    g = torch.Generator().manual_seed(3)
+    bias = torch.randn(n, generator=g).bfloat16().cuda()
+    args = (xq.values, xq.scale_factors, xq.amax, 3, wq.values, wq.scale_factors, wq.amax, 3, m, n, k)
+    y = ops.gemm_nvfp4(*args, bias=bias, act=act, tile=tile)
+    # the amax a caller would supply: here the true one and, second, a stale one that is too small (values then
+    # saturate exactly as the quantizer saturates them)
+    for scale in (1.0, 0.5):
+        amax = (y.float().abs().max() * scale).reshape(1).bfloat16().float().contiguous()
+        mp = ops.padded_rows(m)
+        ref_codes, ref_sf, _ = ops.quantize_nvfp4(y, 3, amax.clone(), amax_given=True)
+        codes = torch.full((mp, n // 2), 0xAB, dtype=torch.uint8, device="cuda")
+        sf = torch.full((mp * n // 16,), 0x55, dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
+        y2 = ops.gemm_nvfp4(*args, bias=bias, act=act, tile=tile, requant=(codes, sf), requant_amax=amax)
+        torch.cuda.synchronize()
+        assert _lib.lib().llnv_check_status(None) == 0, _lib.lib().llnv_last_error()
+        assert torch.equal(y2, y)
+        assert torch.equal(codes, ref_codes) and torch.equal(sf.view(torch.uint8), ref_sf.view(torch.uint8))
+        assert int(codes[m:].max().item()) == 0 if mp > m else True
+        codes.fill_(0xAB)
+        none = ops.gemm_nvfp4(*args, bias=bias, act=act, tile=tile, requant=(codes, sf), requant_amax=amax, store_out=False)
+        assert none is None and torch.equal(codes, ref_codes)
+        if m <= 512 and scale == 1.0:        # and the oracle, for the small cases (an amax below the true maximum is outside
+            # what the reference's quantizer defines: its E4M3 cast does not saturate)
+            oc, osf, _ = O.quantize_nvfp4(y.float().cpu().numpy(), "mse", amax=np.float32(amax.item()))
+            assert np.array_equal(codes.cpu().numpy(), oc) and np.array_equal(util.u8(sf), osf)
+    # the consumer GEMM reads the epilogue's codes like any quantized activation
+    w2 = L.quantize_to_fp4(util.config_weight(256, n, seed=9).cuda())
+    a = ops.gemm_nvfp4(codes, sf, amax, 3, w2.values, w2.scale_factors, w2.amax, 3, m, 256, n)
+    b = ops.gemm_nvfp4(ref_codes, ref_sf, amax, 3, w2.values, w2.scale_factors, w2.amax, 3, m, 256, n)
+    assert torch.equal(a, b)
+
+
+def test_gemm_requant_argument_checks():
+    x = L.quantize_to_fp4(torch.zeros(128, 256, dtype=torch.bfloat16, device="cuda"))
+    w = L.quantize_to_fp4(torch.zeros(256, 256, dtype=torch.bfloat16, device="cuda"))
+    args = (x.values, x.scale_factors, x.amax, 3, w.values, w.scale_factors, w.amax, 3, 128, 256, 256)
+    codes = torch.zeros(128, 128, dtype=torch.uint8, device="cuda")
+    sf = torch.zeros(128 * 16, dtype=torch.uint8, device="cuda")
+    amax = torch.ones(1, device="cuda")
+    with pytest.raises(ValueError, match="requant_amax"):
+        ops.gemm_nvfp4(*args, requant=(codes, sf))
+    with pytest.raises(RuntimeError, match="residual"):
+        ops.gemm_nvfp4(*args, requant=(codes, sf), requant_amax=amax, residual=torch.zeros(128, 256, dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(ValueError, match="store_out"):
+        ops.gemm_nvfp4(*args, store_out=False)
