@@ -102,7 +102,8 @@ int llnv_quantize_nvfp4_pair(const void* x0, const void* x1, int64_t M, int64_t 
  * (utils/adaln_triton.py:36-126; call sites wan_5b/modules/causal_model.py:867-873, 908-914)
  * followed by the activation quantize of the next Linear
  * (fouroversix/src/fouroversix/model/modules/linear.py:45-46); y itself is written only when
- * y_out != NULL.
+ * y_out != NULL.  With codes == NULL and sf == NULL only y is produced (the modulated LayerNorm in front of a
+ * bf16 Linear: CausalHead.forward, wan_5b/modules/causal_model.py:950-959).
  *   x: bf16 [M, C], C % 64 == 0, C <= 4096.  scale/shift: bf16 [frames, mod_stride].
  *   add_one: 1 -> multiply by (1 + scale) (adaln_triton.py:74-78), 0 -> by scale.
  *   row_stats: caller-provided scratch of 2*M floats (mean and 1/std of every row). */

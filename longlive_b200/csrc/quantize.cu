@@ -185,11 +185,13 @@ __global__ void __launch_bounds__(256) quantize_nvfp4_kernel(const uint16_t* x, 
         yo[1] = make_uint4(cur[4], cur[5], cur[6], cur[7]);
       }
     }
+    if (codes == nullptr) continue;          // transform-only call (y_out): nothing to quantize
     uint32_t c_lo, c_hi, s;
     quant_block<RULE>(cur, qc, c_lo, c_hi, s);
     if (col_ok) *reinterpret_cast<uint2*>(codes + r * (K >> 1) + (col >> 1)) = make_uint2(c_lo, c_hi);
     my_sf |= s << (8 * i);
   }
+  if (codes == nullptr) return;
 
   // Transpose the 4x4 scale bytes of each group of four lanes: lane q ends up with the word of
   // 16-byte unit r0 that holds row (r0 + 32*q), scale columns 4*(cb/4) .. +3.
@@ -397,7 +399,8 @@ int ln_quantize_impl(int mode, const void* x, int64_t M, int64_t C, int64_t ldx,
                      int64_t mod_stride, int frame_rows, float eps, int add_one, int rule, void* codes, void* sf,
                      float* amax, void* y_out, int64_t ldy, float* row_stats, cudaStream_t stream, const char* who,
                      int64_t row_offset, int phase) {
-  LLNV_REQUIRE(x && p0 && p1 && codes && sf && amax && row_stats, "%s: null pointer", who);
+  LLNV_REQUIRE(x && p0 && p1 && amax && row_stats, "%s: null pointer", who);
+  LLNV_REQUIRE((codes && sf) || (!codes && !sf && y_out), "%s: codes and sf go together; both may be null only when y_out is wanted", who);
   LLNV_REQUIRE(mode == kAdaLN || mode == kAffineLN, "%s: unknown mode %d", who, mode);
   LLNV_REQUIRE(M >= 0 && C > 0 && C % 64 == 0 && C <= 4096, "%s: C must be a multiple of 64 and at most 4096 (got %lld)", who, (long long)C);
   LLNV_REQUIRE(ldx >= C && ldx % 8 == 0, "%s: ldx must be >= C and a multiple of 8", who);

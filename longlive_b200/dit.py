@@ -70,9 +70,13 @@ class DiTConfig:
         return self.in_channels * 4
 
 
-def rope_tables(cfg: DiTConfig, start_frame: int, device) -> tuple[torch.Tensor, torch.Tensor]:
+def rope_tables(cfg: DiTConfig, start_frame: int, device, t_scale: float = 1.0,
+                temporal_offset: float = 0.0) -> tuple[torch.Tensor, torch.Tensor]:
     """cos/sin fp32 [chunk_tokens, 64] for frames start_frame.., tokens in (f, h, w) order
-    (wan_5b/modules/model.py:29-36, wan_5b/modules/causal_model.py:156-165, 1075-1081)."""
+    (wan_5b/modules/model.py:29-36, wan_5b/modules/causal_model.py:156-165, 1075-1081).  The temporal position of
+    frame f is (start_frame + f + temporal_offset) * t_scale: ``t_scale`` < 1 compresses time, ``temporal_offset``
+    is the multi-shot offset (shot index times phi) of utils/position_embedding_utils.py:56-105; with the defaults
+    the positions are the integers the reference looks up in its 1024-entry table (:73-78)."""
     d = 128
     dims = [d - 4 * (d // 6), 2 * (d // 6), 2 * (d // 6)]
 
@@ -81,7 +85,7 @@ def rope_tables(cfg: DiTConfig, start_frame: int, device) -> tuple[torch.Tensor,
         return torch.outer(pos.to(torch.float64), inv)
 
     f, h, w = cfg.frames_per_chunk, cfg.grid_h, cfg.grid_w
-    at = ang(torch.arange(start_frame, start_frame + f), dims[0])
+    at = ang((torch.arange(start_frame, start_frame + f, dtype=torch.float64) + float(temporal_offset)) * float(t_scale), dims[0])
     ah = ang(torch.arange(h), dims[1])
     aw = ang(torch.arange(w), dims[2])
     full = torch.cat([at[:, None, None, :].expand(f, h, w, -1), ah[None, :, None, :].expand(f, h, w, -1),
@@ -311,7 +315,10 @@ class CausalDiT:
         self.g_t = torch.zeros(cfg.frames_per_chunk, dtype=torch.float32, device=dev)
         self.cos_buf = torch.empty((Sl, 64), dtype=torch.float32, device=dev)
         self.sin_buf = torch.empty((Sl, 64), dtype=torch.float32, device=dev)
-        self._rope_frame: int | None = None
+        self._rope_frame = None
+        # temporal RoPE scale and multi-shot offset of the chunks to come (set before run_chunk; the reference passes
+        # them down every forward, causal_model.py:479-486)
+        self.rope_t_scale, self.rope_temporal_offset = 1.0, 0.0
         self._graphs: dict = {}
         self._scheduler = None
         self._time_cache: dict = {}
@@ -574,13 +581,14 @@ class CausalDiT:
         return e, e0
 
     def _set_rope(self, start_frame: int) -> None:
-        if self._rope_frame == start_frame:
+        key = (start_frame, self.rope_t_scale, self.rope_temporal_offset)
+        if self._rope_frame == key:
             return
-        cos, sin = rope_tables(self.cfg, start_frame, self.device)
+        cos, sin = rope_tables(self.cfg, start_frame, self.device, self.rope_t_scale, self.rope_temporal_offset)
         lo, hi = self.rank * self.Sl, (self.rank + 1) * self.Sl
         self.cos_buf.copy_(cos[lo:hi])
         self.sin_buf.copy_(sin[lo:hi])
-        self._rope_frame = start_frame
+        self._rope_frame = key
 
     def _time_inputs(self, t: torch.Tensor, t_key):
         """(e, per-layer modulation) of the timesteps ``t``.  They depend on the timesteps and the weights
@@ -653,11 +661,10 @@ class CausalDiT:
             self._ffn_calibrated = True          # every layer's hidden amax is known from here on
         # head: LayerNorm, modulate with (head.modulation + e), project (CausalHead.forward, causal_model.py:950-959):
         # the same bf16 rounding points as a block's adaLN, so the quantizer's load-side transform produces y
-        # (its NVFP4 output goes to scratch and is not used: the head Linear stays bf16)
+        # (nothing is quantized: the head Linear stays bf16)
         hm = self.head_mod + e.unsqueeze(1)                             # [F, 2, dim]: shift, scale
-        a = self.act_c
-        _, _, _, y = ops.adaln_quantize_nvfp4(cur, hm[:, 1], hm[:, 0], cfg.frame_tokens, MSE, cfg.eps, want_y=True, codes=a.codes,
-                                              sf=a.sf, amax=a.amax, row_stats=self.row_stats, row_offset=self.rank * self.Sl)
+        _, _, _, y = ops.adaln_quantize_nvfp4(cur, hm[:, 1], hm[:, 0], cfg.frame_tokens, MSE, cfg.eps, y_only=True,
+                                              amax=self.h_amax, row_stats=self.row_stats, row_offset=self.rank * self.Sl)
         return self._edge(y, self.head_w, self.head_b)
 
     def run_chunk(self, latent_tokens: torch.Tensor, ctx: torch.Tensor, chunk_index: int,

@@ -76,8 +76,12 @@ def _materialize_quantized_weights_for_inference(model: nn.Module, target_device
 def quantize_model_with_filter(model: nn.Module, quant_config=None, filtered_modules=None, filter_profile=None,
                                use_default_filtered_modules: bool = False, cast_model_to_bf16: bool = True,
                                materialize_for_inference: bool = False, materialize_target_device=None,
-                               use_transformer_engine: bool = False, verbose: bool = True, **kwargs):
-    """Convert a model's Linear layers to NVFP4, skipping names / ``re:`` patterns (utils/quant.py:585-689)."""
+                               use_transformer_engine: bool = False, te_inference_only: bool = False,
+                               te_low_precision_weights=None, te_recipe_kwargs=None, te_module_kwargs=None,
+                               te_fallback_to_fouroversix: bool = False, verbose: bool = True, **kwargs):
+    """Convert a model's Linear layers to NVFP4, skipping names / ``re:`` patterns (utils/quant.py:585-689).
+    The ``te_*`` parameters belong to the reference's TransformerEngine path and are accepted for call
+    compatibility; asking for that path (``use_transformer_engine=True``) raises."""
     if use_transformer_engine:
         raise ValueError("the TransformerEngine linear path is not part of this package")
     if quant_config is None:

@@ -108,24 +108,30 @@ def _quant_outputs(x, m, c, codes, sf, amax):
 
 
 def adaln_quantize_nvfp4(x, scale, shift, frame_rows, rule_id, eps=1e-6, add_one=True, *, want_y=False, codes=None,
-                         sf=None, amax=None, row_stats=None, row_offset=0, phase=0):
+                         sf=None, amax=None, row_stats=None, row_offset=0, phase=0, y_only=False):
     """LayerNorm(no affine) -> (1 + scale[f]) * x + shift[f] (bf16 rounding points of the reference)
     fused with the NVFP4 quantize of the result.  x: bf16 [M, C]; scale/shift: bf16 [F, C] views
-    (row stride free).  Returns (codes, sf, amax, y or None)."""
+    (row stride free).  Returns (codes, sf, amax, y or None); with ``y_only`` nothing is quantized
+    (codes and sf are None) and only y is produced."""
     _require_cuda(x, "x")
     if x.dim() != 2 or x.dtype != torch.bfloat16 or x.stride(1) != 1:
         raise RuntimeError("adaln_quantize_nvfp4 expects a 2-D bfloat16 tensor with unit column stride")
     if scale.dim() != 2 or shift.dim() != 2 or scale.stride(1) != 1 or shift.stride(1) != 1 or scale.stride(0) != shift.stride(0):
         raise RuntimeError("scale and shift must be [frames, C] views with the same row stride")
     m, c = x.shape
-    codes, sf, amax = _quant_outputs(x, m, c, codes, sf, amax)
+    if y_only:
+        want_y, codes, sf = True, None, None
+        amax = amax if amax is not None else torch.empty(1, dtype=torch.float32, device=x.device)
+    else:
+        codes, sf, amax = _quant_outputs(x, m, c, codes, sf, amax)
     if row_stats is None:
         row_stats = torch.empty(2 * max(m, 1), dtype=torch.float32, device=x.device)
     y = torch.empty((m, c), dtype=torch.bfloat16, device=x.device) if want_y else None
     with torch.cuda.device(x.device):
         _check(_lib.lib().llnv_adaln_quantize_nvfp4_ex(
             x.data_ptr(), m, c, x.stride(0), scale.data_ptr(), shift.data_ptr(), scale.stride(0), int(frame_rows), float(eps),
-            1 if add_one else 0, rule_id, codes.data_ptr(), sf.data_ptr(), amax.data_ptr(),
+            1 if add_one else 0, rule_id, codes.data_ptr() if codes is not None else None,
+            sf.data_ptr() if sf is not None else None, amax.data_ptr(),
             y.data_ptr() if y is not None else None, c, row_stats.data_ptr(), int(row_offset), int(phase), _stream(x)))
     return codes, sf, amax, y
 

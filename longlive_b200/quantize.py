@@ -135,6 +135,9 @@ def quantize_to_fp4(x: torch.Tensor, config: QuantizationConfig | None = None, *
             raise ValueError("No backend found that supports the given parameters")
         raise ValueError(f"Backend {config.backend} does not support the given parameters")
     if x.dtype == torch.float16:
+        # The reference's CUDA backend also takes fp16 (quantize/cuda/backend.py:45-51).  The kernels here read bf16 bit
+        # patterns (block maxima and the exactness argument of the 4-over-6 decision rest on the 8-bit significand),
+        # and every tensor of the NVFP4 inference path is bf16, so fp16 is refused rather than silently converted.
         raise ValueError("Backend cuda does not support float16 inputs in this build (bfloat16 only)")
     rows, cols = x.shape
     if cols % 64 != 0:

@@ -399,7 +399,8 @@ def dequantize_kv_cache(blocks, num_heads: int, block_token_size: int, rule="mse
 # RoPE, norms, adaLN, attention
 # --------------------------------------------------------------------------------------
 
-def rope_tables(start_frame: int, frames: int, h: int, w: int, d: int = 128, theta: float = 10000.0):
+def rope_tables(start_frame: int, frames: int, h: int, w: int, d: int = 128, theta: float = 10000.0,
+                t_scale: float = 1.0, temporal_offset: float = 0.0):
     """cos/sin fp32 tables [frames*h*w, d/2] for tokens in (f, h, w) row-major order.
 
     wan_5b/modules/model.py:29-36 (``rope_params``), wan_5b/modules/causal_model.py:1075-1081
@@ -414,7 +415,7 @@ def rope_tables(start_frame: int, frames: int, h: int, w: int, d: int = 128, the
         inv = 1.0 / np.power(theta, np.arange(0, dim, 2, dtype=np.float64) / dim)
         return np.outer(pos.astype(np.float64), inv)
 
-    at = angles(np.arange(start_frame, start_frame + frames), dims[0])
+    at = angles((np.arange(start_frame, start_frame + frames, dtype=np.float64) + float(temporal_offset)) * float(t_scale), dims[0])
     ah = angles(np.arange(h), dims[1])
     aw = angles(np.arange(w), dims[2])
     full = np.concatenate([

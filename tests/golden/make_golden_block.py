@@ -143,6 +143,17 @@ def main() -> None:
         print(f"chunk {chunk}: {action}, block slot {slot}, |y| mean {y.float().abs().mean():.4f}")
     np.savez_compressed(os.path.join(HERE, "dit_block.npz"), **out)
 
+    # ---- RoPE with a temporal scale and a multi-shot offset (utils/position_embedding_utils.py:56-105) ----------
+    gen = torch.Generator().manual_seed(41)
+    F_, Hh, Ww, nh = 3, 4, 6, 2
+    xq = torch.randn(1, F_ * Hh * Ww, nh, d, generator=gen).bfloat16()
+    ro = {"x": bf16_bits(xq), "grid": np.array([F_, Hh, Ww])}
+    for tag, (start, ts, off) in {"a": (5, 0.5, 0.0), "b": (7, 1.0, 2.5), "c": (2, 0.75, 3.25)}.items():
+        yy = cm.causal_rope_apply(xq, [(F_, Hh, Ww)], freqs, start_frame=start, t_scale=ts, temporal_offset=off).type_as(xq)
+        ro[f"y_{tag}"] = bf16_bits(yy)
+        ro[f"p_{tag}"] = np.array([start, ts, off], dtype=np.float64)
+    np.savez_compressed(os.path.join(HERE, "rope_offset.npz"), **ro)
+
     # ---- NVFP4 state-dict entries as the reference's exporter writes them ---------------------------
     from utils.nvfp4_checkpoint import NVFP4_CHECKPOINT_FORMAT, NVFP4_CHECKPOINT_VERSION
     gen = torch.Generator().manual_seed(31)

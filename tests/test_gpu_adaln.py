@@ -47,6 +47,9 @@ def test_adaln_quantize(m, c, frames, rule):
     c2, s2, a2, none = ops.adaln_quantize_nvfp4(xd, scale, shift, frame_rows, rid)
     assert none is None and torch.equal(c2, codes) and torch.equal(a2, amax)
     assert torch.equal(s2.view(torch.uint8), sf.view(torch.uint8))
+    # transform only (the modulated LayerNorm in front of a bf16 Linear): the same y, nothing quantized
+    c3, s3, a3, y3 = ops.adaln_quantize_nvfp4(xd, scale, shift, frame_rows, rid, y_only=True)
+    assert c3 is None and s3 is None and torch.equal(y3, y) and torch.equal(a3, amax)
 
 
 def test_adaln_matches_reference_fixture(golden):
