@@ -595,7 +595,11 @@ def run_kernel_case(spec: str, iters: int):
     gemm:MxNxK[:tile]   quantize:MxK[:rule]   kvdequant:BLOCKSxTOKENSxHEADS   attention:LQxLKxHEADS   ropenorm:TOKENSxHEADS
     attnkv:LQxBLOCKSxTOKENSxHEADS[:twostep]  (attention over BLOCKS NVFP4 cache blocks + one bf16 chunk; twostep = dequantize, then attend)
     linear:MxNxK  (the bf16 Linear of the edge layers)
-    unipc:ELEMENTS[:f32]  (the scheduler step with order-2 corrector and predictor: 5 tensors read, 3 written)"""
+    refgemm:MxNxK  (the same NVFP4 operands through torch._scaled_mm, i.e. the vendor library's block-scaled FP4 GEMM: an
+                    anchor on the same box, not part of the product path; prints the error text if the build refuses NVFP4)
+    unipc:ELEMENTS[:f32]  (the scheduler step with order-2 corrector and predictor: 5 tensors read, 3 written)
+    forward:LAYERS  (one eager forward of a LAYERS-layer DiT at the benchmark's widths with a full window; the cache blocks are
+                     filled with quantized noise instead of running the chunks that would fill them)"""
     import torch
 
     import longlive_b200 as L
@@ -603,6 +607,33 @@ def run_kernel_case(spec: str, iters: int):
 
     lib = _lib.lib()
     kind, _, rest = spec.partition(":")
+    if kind == "forward":
+        from longlive_b200 import dit
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        cfg = dit.DiTConfig(layers=int(rest))
+        model = dit.CausalDiT(cfg, device=dev, seed=0)
+        gen = torch.Generator(device=dev).manual_seed(7)
+        ctx = model.encode_text(torch.randn(cfg.text_len, cfg.text_dim, generator=gen, device=dev).bfloat16())
+        lat = torch.randn(cfg.chunk_tokens, cfg.patch_dim, generator=gen, device=dev).bfloat16()
+        noise = torch.randn(cfg.chunk_tokens * cfg.heads, 128, generator=gen, device=dev).bfloat16()
+        for layer in range(cfg.layers):
+            for slot in range(cfg.max_blocks):
+                L.quantize_to_fp4(noise, out=model.cache.k[layer][slot])
+                L.quantize_to_fp4(noise, out=model.cache.v[layer][slot])
+        model.cache.filled = cfg.max_blocks
+        t = torch.full((cfg.frames_per_chunk,), 937.0, device=dev)
+        times = []
+        for i in range(iters + 1):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            model.forward(lat, t, ctx, 12, t_key=(937.0,) * 3)
+            e.record()
+            torch.cuda.synchronize()
+            times.append(s.elapsed_time(e))
+        ops.check_status(dev)
+        print(json.dumps({"kernel_case": spec, "iters": iters, "median_ms": statistics.median(times[1:]), "first_ms": times[0]}))
+        return
     dims, _, opt = rest.partition(":")
     d = [int(v) for v in dims.split("x")]
     dev = torch.device("cuda", 0)
@@ -616,6 +647,20 @@ def run_kernel_case(spec: str, iters: int):
         out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
         fn = lambda: ops.gemm_nvfp4(xq.values, xq.scale_factors, xq.amax, 3, wq.values, wq.scale_factors, wq.amax, 3,
                                     m, n, k, out=out, tile=int(opt or 0))
+        work, unit = 2.0 * m * n * k / 1e12, "TFLOP/s"
+    elif kind == "refgemm":
+        m, n, k = d
+        xq = L.quantize_to_fp4(torch.randn(m, k, generator=gen, device=dev).bfloat16())
+        wq = L.quantize_to_fp4((torch.randn(n, k, generator=gen, device=dev) * 0.02).bfloat16())
+        try:
+            a = xq.values.view(torch.float4_e2m1fn_x2)            # rows padded to 128, as the scale layout needs
+            b = wq.values.view(torch.float4_e2m1fn_x2).t()
+            fn = lambda: torch._scaled_mm(a, b, xq.scale_factors, wq.scale_factors, out_dtype=torch.bfloat16)
+            fn()
+            torch.cuda.synchronize()
+        except Exception as exc:          # noqa: BLE001 - the point is to record why the anchor is unavailable
+            print(json.dumps({"kernel_case": spec, "unavailable": f"{type(exc).__name__}: {str(exc)[:300]}"}))
+            return
         work, unit = 2.0 * m * n * k / 1e12, "TFLOP/s"
     elif kind == "quantize":
         m, k = d

@@ -434,8 +434,9 @@ class CausalDiT:
         return not self.cache_text_kv or all(kv is not None for kv in self._prompt(ctx)["kv"])
 
     # ---- one block ----------------------------------------------------------------------------
-    def block_forward(self, li: int, x: torch.Tensor, x_out: torch.Tensor, e: torch.Tensor, ctx, cos, sin):
-        """x: [Sl, dim] bf16 (my tokens); e: [F, 6, dim] (block modulation + time projection); returns x_out."""
+    def block_forward(self, li: int, x: torch.Tensor, x_out: torch.Tensor, e: torch.Tensor, ctx, cos, sin, write_cache: bool = True):
+        """x: [Sl, dim] bf16 (my tokens); e: [F, 6, dim] (block modulation + time projection); returns x_out.
+        ``write_cache=False`` leaves the current cache block unwritten (see ``run_chunk``)."""
         cfg, blk, cache = self.cfg, self.blocks[li], self.cache
         Sl, S, ft = self.Sl, self.S, cfg.frame_tokens
         roff = self.rank * Sl
@@ -513,7 +514,8 @@ class CausalDiT:
             # per-rank scales: the producers saw (my tokens, all heads), the cache block holds (all tokens,
             # my heads); its own amax is taken so that no value can exceed the scale's range
             kv_given = False
-        ops.quantize_nvfp4_pair(k_for_cache.reshape(S * self.Hl, 128), v_for_cache.reshape(S * self.Hl, 128), MSE, ck, cv, amax_given=kv_given)
+        if write_cache:
+            ops.quantize_nvfp4_pair(k_for_cache.reshape(S * self.Hl, 128), v_for_cache.reshape(S * self.Hl, 128), MSE, ck, cv, amax_given=kv_given)
         if self.arena is not None:
             # heads -> tokens over peer memory: rank r receives my heads of its tokens in attn_sh[my rank];
             # the quantizer reads that [source heads][my tokens] layout directly
@@ -607,8 +609,13 @@ class CausalDiT:
             hit = self._time_cache[t_key] = (e, self.modulation_all + e0.unsqueeze(0))
         return hit
 
-    def forward(self, latent_tokens: torch.Tensor, t: torch.Tensor, ctx: torch.Tensor, start_frame: int, t_key=None) -> torch.Tensor:
+    def forward(self, latent_tokens: torch.Tensor, t: torch.Tensor, ctx: torch.Tensor, start_frame: int, t_key=None,
+                write_cache: bool = True) -> torch.Tensor:
         """latent_tokens: [Sl, patch_dim] (my token shard of the patchified chunk) -> [Sl, patch_dim].
+
+        ``write_cache``: quantize this forward's rotated keys and values into the current cache block, as every
+        forward of the reference does (causal_model.py:1644-1645).  ``run_chunk`` switches it off for the denoising
+        forwards: nothing reads the current block before the chunk's clean re-cache forward overwrites it.
 
         With ``use_graphs`` the whole forward (about a thousand launches, the collectives included)
         is captured once per state of the KV block table and replayed afterwards: the launch sequence
@@ -618,24 +625,24 @@ class CausalDiT:
         set-up such as the text K/V and the communicators must not happen inside a capture)."""
         self._set_rope(start_frame)
         if not self.use_graphs:
-            return self._forward_impl(latent_tokens, t, ctx, self._time_inputs(t, t_key) if t_key is not None else None)
+            return self._forward_impl(latent_tokens, t, ctx, self._time_inputs(t, t_key) if t_key is not None else None, write_cache)
         self.g_lat.copy_(latent_tokens)
         self.g_t.copy_(t)
         tin = self._time_inputs(t, t_key) if t_key is not None else None     # outside any capture: the tensors outlive the graphs
         prompt_key = self._prompt(ctx)["serial"] if self.cache_text_kv else ctx.data_ptr()
-        key = (tuple(self.cache.order), self.cache.filled, prompt_key, t_key)
+        key = (tuple(self.cache.order), self.cache.filled, prompt_key, t_key, write_cache)
         entry = self._graphs.get(key)
         if entry is None:
             # eager when one-time set-up is still due (first forward, the text K / V of a new prompt) or
             # while the window still fills: none of that may happen inside a capture
             if not self._ran_eager or self.cache.filled < self.cfg.max_blocks or not self._text_ready(ctx):
-                return self._forward_impl(self.g_lat, self.g_t, ctx, tin)
+                return self._forward_impl(self.g_lat, self.g_t, ctx, tin, write_cache)
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
             graph = torch.cuda.CUDAGraph()
             torch.cuda.synchronize(self.device)
             with torch.cuda.graph(graph, pool=self._graph_pool, capture_error_mode="thread_local"):
-                out = self._forward_impl(self.g_lat, self.g_t, ctx, tin)
+                out = self._forward_impl(self.g_lat, self.g_t, ctx, tin, write_cache)
             entry = self._graphs[key] = (graph, out)
         entry[0].replay()
         return entry[1]
@@ -646,7 +653,8 @@ class CausalDiT:
         self._graphs.clear()
         self._graph_pool = None
 
-    def _forward_impl(self, latent_tokens: torch.Tensor, t: torch.Tensor, ctx: torch.Tensor, time_inputs=None) -> torch.Tensor:
+    def _forward_impl(self, latent_tokens: torch.Tensor, t: torch.Tensor, ctx: torch.Tensor, time_inputs=None,
+                      write_cache: bool = True) -> torch.Tensor:
         cfg = self.cfg
         self._edge(latent_tokens, self.patch_w, self.patch_b, out=self.x_a)       # patch embedding, causal_model.py:1535-1540
         e, em_all = time_inputs if time_inputs is not None else self._time_inputs(t, None)
@@ -655,7 +663,7 @@ class CausalDiT:
         self._ran_eager = True
         cur, nxt = self.x_a, self.x_b
         for li, blk in enumerate(self.blocks):
-            self.block_forward(li, cur, nxt, em_all[li], ctx, cos, sin)
+            self.block_forward(li, cur, nxt, em_all[li], ctx, cos, sin, write_cache)
             cur, nxt = nxt, cur
         if not ran_before:
             self._ffn_calibrated = True          # every layer's hidden amax is known from here on
@@ -686,7 +694,8 @@ class CausalDiT:
         x_t = latent_tokens
         for t in sched.timesteps.tolist():
             tt = torch.full((F,), float(t), device=self.device)
-            flow = self.forward(x_t, tt, ctx, start_frame, t_key=(float(t),) * F)
+            # the block these forwards would write is overwritten by the re-cache forward below before anything reads it
+            flow = self.forward(x_t, tt, ctx, start_frame, t_key=(float(t),) * F, write_cache=False)
             x_t = sched.step(flow, t, x_t, return_dict=False)[0]
         if scene_cut and clean_recache:
             self.cache.reset_keep_global()
