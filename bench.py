@@ -272,6 +272,29 @@ def sp_parity_check(dev, rank, world, group):
     return ("bit-exact" if int(flag.item()) == 1 else "mismatch"), exchange
 
 
+def fp4_mma_issue_rate(dev, k_blocks=4000, reps=5):
+    """TFLOP/s of block-scaled FP4 MMAs issued back to back on operands resident in shared memory (llnv_fp4_mma_rate): the
+    tensor-core ceiling of the W4A4 main loop on this device, measured live."""
+    import ctypes
+
+    import torch
+
+    from longlive_b200 import _lib
+    lib = _lib.lib()
+    flop = ctypes.c_double()
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    times = []
+    for i in range(reps + 2):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        _lib.check(lib.llnv_fp4_mma_rate(k_blocks, ctypes.byref(flop), stream))
+        e.record()
+        torch.cuda.synchronize(dev)
+        if i >= 2:
+            times.append(s.elapsed_time(e))
+    return flop.value / (statistics.median(times) * 1e-3) / 1e12
+
+
 def run_gemm_sweep(dev, rank, world, steps, warmup, peaks):
     """One pass over the 30 GEMMs of the DiT-block shape sweep per step (operands resident, L2 flushed between steps,
     the 30 launches replayed as one CUDA graph), on every rank independently; beside it the ten GEMMs a block runs on a
@@ -341,6 +364,7 @@ def run_gemm_sweep(dev, rank, world, steps, warmup, peaks):
     tf_all = flops_of(shapes) / (ms_all * 1e-3) / 1e12
     tf_dit = flops_of(dit_shapes) / (ms_dit * 1e-3) / 1e12
     del flush
+    mma_peak = fp4_mma_issue_rate(dev)
     return {
         "metric": "w4a4_gemm_tflops", "unit": "TFLOP/s per GPU", "value": tf_all, "ms_per_step": ms_all, "steps": steps,
         "workload": "q/k/v/o + cross q/o 3072x3072, cross k/v M=512, FFN 3072<->14336; M in {880,2640,10560}; 30 GEMMs per step, "
@@ -349,8 +373,12 @@ def run_gemm_sweep(dev, rank, world, steps, warmup, peaks):
         "roofline": {"bound": "tensor", "achieved": tf_all, "peak": fp4_peak, "unit": "TFLOP/s", "frac": tf_all / fp4_peak,
                      "traffic": dram_traffic("gemm_nvfp4_kernel", "2640x14336x3072"), "traffic_case": "M=2640 N=14336 K=3072 launch (profiles/dram_traffic.md)",
                      "peak_note": f"4 x {peaks['source']} dense bf16 burst peak ({peaks['bf16_tflops']} TFLOP/s): no FP4 entry is measured; nominal dense FP4 is 9000",
-                     "kernel": "gemm_nvfp4_kernel", "frac_of_nominal_9pf": tf_all / 9000.0},
+                     "kernel": "gemm_nvfp4_kernel", "frac_of_nominal_9pf": tf_all / 9000.0,
+                     "mma_issue_peak": mma_peak, "frac_of_mma_issue_peak": tf_all / mma_peak,
+                     "mma_issue_peak_note": "llnv_fp4_mma_rate measured in this run: every SM issues 128x256x64 block-scaled FP4 MMAs back to "
+                                            "back on operands resident in shared memory (no loads, no epilogue)"},
         "m2640_only": {"value": tf_dit, "ms_per_step": ms_dit, "frac": tf_dit / fp4_peak, "frac_of_nominal_9pf": tf_dit / 9000.0,
+                       "frac_of_mma_issue_peak": tf_dit / mma_peak,
                        "workload": "the 10 GEMMs one block runs on a 2640-token chunk (cross k/v at M=512)", "flops_per_step": flops_of(dit_shapes)},
     }
 
@@ -434,7 +462,7 @@ def run_gpu_arm(args):
     cfg = dit.DiTConfig()
     sync_amax = world > 1 and not args.per_shard_scales
     model = dit.CausalDiT(cfg, device=dev, seed=0, sp_group=group, sync_amax=sync_amax, use_graphs=not args.eager,
-                          edge_linear=os.environ.get("LLNV_EDGE_LINEAR", "own"))
+                          edge_linear=os.environ.get("LLNV_EDGE_LINEAR", "own"), ffn_requant=args.ffn_requant)
     gen = torch.Generator(device=dev).manual_seed(7)
     ctx = model.encode_text(torch.randn(cfg.text_len, cfg.text_dim, generator=gen, device=dev).bfloat16())
     sl = cfg.chunk_tokens // world
@@ -554,7 +582,7 @@ def run_gpu_arm(args):
                        "l2": "inputs larger than L2: a chunk streams 2.9 GB of NVFP4 weights five times",
                        "launches": "CUDA graph per (block-table state, timestep)" if not args.eager else "eager launches",
                        "parallelism": "single GPU" if world == 1 else f"sequence-parallel over {world} GPUs (tokens / heads), exchange: {exchange}",
-                       "amax_sync": bool(sync_amax), "latent_fps": 3.0 / (ms_per_step * 1e-3)},
+                       "amax_sync": bool(sync_amax), "ffn_requant": args.ffn_requant, "latent_fps": 3.0 / (ms_per_step * 1e-3)},
             "ms_per_chunk_p50": med, "ms_per_chunk_p10": p10, "ms_per_chunk_p90": p90,
             "clocks": clocks,
             "e2e": {"value": 12.0 / e2e_s, "unit": "frames/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
@@ -595,6 +623,8 @@ def run_kernel_case(spec: str, iters: int):
     gemm:MxNxK[:tile]   quantize:MxK[:rule]   kvdequant:BLOCKSxTOKENSxHEADS   attention:LQxLKxHEADS   ropenorm:TOKENSxHEADS
     attnkv:LQxBLOCKSxTOKENSxHEADS[:twostep]  (attention over BLOCKS NVFP4 cache blocks + one bf16 chunk; twostep = dequantize, then attend)
     linear:MxNxK  (the bf16 Linear of the edge layers)
+    fp4peak:KBLOCKS  (MMA issue only: every SM issues KBLOCKS x 4 block-scaled FP4 MMAs of 128 x 256 x 64 on operands resident
+                      in shared memory; the rate is the tensor-core ceiling of the W4A4 main loop on this device)
     refgemm:MxNxK  (the same NVFP4 operands through torch._scaled_mm, i.e. the vendor library's block-scaled FP4 GEMM: an
                     anchor on the same box, not part of the product path; prints the error text if the build refuses NVFP4)
     unipc:ELEMENTS[:f32]  (the scheduler step with order-2 corrector and predictor: 5 tensors read, 3 written)
@@ -648,6 +678,13 @@ def run_kernel_case(spec: str, iters: int):
         fn = lambda: ops.gemm_nvfp4(xq.values, xq.scale_factors, xq.amax, 3, wq.values, wq.scale_factors, wq.amax, 3,
                                     m, n, k, out=out, tile=int(opt or 0))
         work, unit = 2.0 * m * n * k / 1e12, "TFLOP/s"
+    elif kind == "fp4peak":
+        import ctypes
+        flop = ctypes.c_double()
+        stream = torch.cuda.current_stream().cuda_stream
+        fn = lambda: _lib.check(lib.llnv_fp4_mma_rate(d[0], ctypes.byref(flop), stream))
+        fn()
+        work, unit = flop.value / 1e12, "TFLOP/s"
     elif kind == "refgemm":
         m, n, k = d
         xq = L.quantize_to_fp4(torch.randn(m, k, generator=gen, device=dev).bfloat16())
@@ -772,6 +809,9 @@ def main():
     ap.add_argument("--no-gemm-sweep", action="store_true")
     ap.add_argument("--no-rollout", action="store_true")
     ap.add_argument("--rollout-chunks", type=int, default=80, help="chunks of the from-empty rollout (80 = 240 latent frames)")
+    ap.add_argument("--ffn-requant", default="two_pass", choices=["two_pass", "single_pass"],
+                    help="two_pass = the reference's rounding (default); single_pass = the FFN-up GEMM quantizes its own output under the "
+                         "previous forward's tensor amax (faster, not the reference's rounding)")
     ap.add_argument("--eager", action="store_true", help="launch every kernel eagerly instead of replaying CUDA graphs")
     ap.add_argument("--per-shard-scales", action="store_true",
                     help="N > 1: every rank quantizes its token shard with its own tensor scale (what the reference's "

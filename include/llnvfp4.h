@@ -133,8 +133,10 @@ int llnv_layernorm_quantize_nvfp4_ex(const void* x, int64_t M, int64_t C, int64_
  *     larger M fails with LLNV_E_INVALID and a message naming the limit.
  *   - All calls on a GPU share the array and it keeps the previous call's contents; nothing in it
  *     needs to start at zero.  Calls that can overlap on the same GPU race: issue them on one stream.
- *   - The first call on each device resolves the array's device address (one-time set-up outside
- *     the stream); make it at start-up, before any stream capture begins. */
+ *   - The array's device address is looked up on every call and never cached, so the entry point keeps
+ *     working after cudaDeviceReset() or a rebuilt primary context (the contents are lost then, which is
+ *     harmless).  The first call on a device may load the library's device code: make it at start-up,
+ *     before any stream capture begins. */
 int llnv_adaln_quantize_nvfp4_static(const void* x, int64_t M, int64_t C, int64_t ldx, const void* scale,
                                      const void* shift, int64_t mod_stride, int frame_rows, float eps, int add_one,
                                      int rule, void* codes, void* sf, float* amax, void* y_out, int64_t ldy,
@@ -254,8 +256,15 @@ int llnv_attention_bf16(const void* q, int64_t Lq, int64_t ldq, const void* k, c
  * out_amax (optional, device fp32) receives max |out| over the written elements: the tensor scale
  * of the quantizer that follows (utils/quant.py quantize_to_fp4 on the attention output) without
  * a separate reduction pass.
- * llnv_attention_key_splits() proposes a split count for the current device (1 when the tiles
- * already fill it); llnv_attention_workspace_bytes() is the workspace size for a split count. */
+ * key_splits = LLNV_ATTN_SPLIT_TAIL balances the other case, more tiles than SMs with a last partial
+ * wave (264 tiles on 148 SMs run two waves with 32 SMs idle in the second): the tiles of the last wave
+ * are each cut once, into a long and a short CTA sized so that the short ones fill the SMs the long
+ * ones leave free, and only those tiles go through the workspace (sized as for 2 splits) and the merge
+ * kernel.  Where it would save under 5 % it runs as key_splits = 1.  Partial results are merged in fp32, so
+ * a split or balanced call agrees with key_splits = 1 to fp32 rounding of the softmax sums, not bit for bit.
+ * llnv_attention_key_splits() proposes a value for the current device (1 when the tiles fill it evenly,
+ * LLNV_ATTN_SPLIT_TAIL or a count otherwise); llnv_attention_workspace_bytes() is the workspace for it. */
+enum { LLNV_ATTN_SPLIT_TAIL = -1 };
 int llnv_attention_bf16_ex(const void* q, int64_t Lq, int64_t ldq, const void* k, const void* v, int64_t Lk,
                            int64_t ldk, int64_t ldv, int heads, float scale, void* out, int64_t ldo,
                            int key_splits, void* workspace, int64_t workspace_bytes, float* out_amax,
@@ -343,6 +352,13 @@ int llnv_gemm_nvfp4_ex(const void* a_codes, const void* a_sf, const float* a_ama
                        const void* b_codes, const void* b_sf, const float* b_amax, int b_rule,
                        int64_t M, int64_t N, int64_t K, const llnv_epilogue_t* epilogue,
                        void* d, int64_t ldd, int tile, llnv_stream_t stream);
+
+/* Measurement aid, not part of the reference's interface: one CTA per SM issues k_blocks x 4 block-scaled FP4
+ * MMAs (128 x 256 x 64, the GEMM's instruction shape) on operands that stay in shared memory, with no loads,
+ * scale refills or epilogue.  *flop_out (may be NULL) receives the flop of the launch; time the launch with
+ * events on `stream`: flop / time is the tensor-core rate a W4A4 main loop can at most reach on this device,
+ * the denominator the GEMM's tensor roofline is quoted against. */
+int llnv_fp4_mma_rate(int k_blocks, double* flop_out, llnv_stream_t stream);
 
 /* Two or three Linears that share their input in one launch: B is the concatenation along N of
  * `groups` weight matrices of N_each rows (codes and swizzled scales concatenated, b_amax one fp32

@@ -101,7 +101,10 @@ struct AttnParams {
   unsigned int* status;
   // key splits: CTA z of a (query tile, head) handles a contiguous range of the key tiles and,
   // when there is more than one split, writes its unnormalised output and (m, l) to the workspace
-  int nsplit;
+  // tail balancing (tail_cut > 0, nsplit == 1, grid z = 2): (query tile, head) items are numbered in launch order
+  // (tile + tiles * head); items below tail_first run whole in their z = 0 CTA, the others are cut at key tile
+  // tail_cut into a z = 0 CTA and a shorter z = 1 CTA, both writing partial results
+  int nsplit, tail_first, tail_cut;
   float* part_o;               // [nsplit][Lq][heads][128] fp32
   float* part_ml;              // [nsplit][Lq][heads][2]   fp32: exponent offset m (raw score units), sum l
   float* out_amax;             // optional: max |out| over all written elements (zeroed by the host before the launch)
@@ -270,8 +273,18 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qt = blockIdx.x, head = blockIdx.y;
   const int nt_all = (int)((p.Lk + kBK - 1) / kBK);
-  const int j0 = (int)((int64_t)blockIdx.z * nt_all / p.nsplit);                  // first key tile of this split
-  const int nt = (int)((int64_t)(blockIdx.z + 1) * nt_all / p.nsplit) - j0;       // >= 1: the host keeps nsplit <= nt_all
+  int j0 = (int)((int64_t)blockIdx.z * nt_all / p.nsplit);                  // first key tile of this split
+  int nt = (int)((int64_t)(blockIdx.z + 1) * nt_all / p.nsplit) - j0;       // >= 1: the host keeps nsplit <= nt_all
+  bool partial = p.part_o != nullptr;
+  if (p.tail_cut > 0) {
+    if (qt + (int)gridDim.x * head < p.tail_first) {
+      if (blockIdx.z != 0) return;             // whole item, done by its z = 0 CTA (nothing is set up yet: the CTA just leaves)
+      partial = false;
+    } else {
+      j0 = blockIdx.z == 0 ? 0 : p.tail_cut;
+      nt = blockIdx.z == 0 ? p.tail_cut : nt_all - p.tail_cut;
+    }
+  }
   const int n_half = ((int64_t)qt * kBQ + kHQ < p.Lq) ? 2 : 1;     // the second half may lie entirely beyond Lq
   // key tiles [0, nd) of this split hold cached keys and are built by the decode warps, the rest come from TMA
   int nd = 0;
@@ -620,7 +633,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_wait(&pv_done[half], (uint32_t)((nt - 1) & 1), abort_flag, p.status, 302u);
     tc_fence_after();
     const int row0 = qt * kBQ + half * kHQ + q * 32;
-    if (p.part_o) {
+    if (partial) {
       // one of several key splits: unnormalised fp32 output and (m, l) for the combine kernel
       const int64_t grow = (int64_t)row0 + lane;
       const int64_t slot = ((int64_t)blockIdx.z * p.Lq + grow) * p.heads + head;
@@ -696,11 +709,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 // One warp per (query row, head); a lane owns four of the 128 channels.
 __global__ void __launch_bounds__(256) attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                                 int nsplit, int64_t Lq, int heads, float scale_log2,
-                                                                uint16_t* __restrict__ out, int64_t ldo, float* __restrict__ out_amax) {
+                                                                uint16_t* __restrict__ out, int64_t ldo, float* __restrict__ out_amax,
+                                                                int tail_first, int q_tiles) {
   pdl_wait();
   const int64_t unit = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);      // row * heads + head
   const int lane = threadIdx.x & 31;
   if (unit >= Lq * heads) return;
+  // tail balancing: only the items that were cut have partial results (the others wrote their output themselves)
+  if (tail_first >= 0 && (int)((unit / heads) / kBQ) + q_tiles * (int)(unit % heads) < tail_first) return;
   const int64_t stride = Lq * heads;
   float mmax = -INFINITY;
   for (int z = 0; z < nsplit; ++z) mmax = fmaxf(mmax, __ldg(part_ml + (z * stride + unit) * 2));
@@ -735,11 +751,27 @@ __global__ void __launch_bounds__(256) attention_combine_kernel(const float* __r
 
 using namespace llnv;
 
+// Tail balancing.  `items` (query tile, head) CTAs of `nt` key tiles each on `sms` SMs run floor(items / sms) full
+// waves and then r = items % sms CTAs on an otherwise idle device.  Cutting each of those r items at key tile
+// c = r * nt / sms gives r long CTAs (c tiles) and r short ones (nt - c tiles) that the hardware scheduler, which
+// hands the next CTA to whichever SM frees up, packs onto the sms - r remaining SMs: the last wave then lasts about c
+// tile times instead of nt.  Returns c, or 0 when there is no last partial wave or the saving is below 5 %.
+static int tail_cut_for(int64_t items, int64_t nt, int sms) {
+  const int64_t r = items % sms;
+  if (items <= sms || r == 0 || nt < 16) return 0;
+  int64_t c = (r * nt + sms - 1) / sms + 1;            // one extra tile pays for the second set-up of the short CTAs
+  if (c < 4) c = 4;
+  if (c > nt - 4) return 0;
+  const int64_t before = (items / sms + 1) * nt, after = (items / sms) * nt + c;
+  return (before - after) * 20 >= before ? (int)c : 0;
+}
+
 extern "C" int llnv_attention_key_splits(int64_t Lq, int64_t Lk, int heads) {
   if (Lq <= 0 || Lk <= 0 || heads <= 0) return 1;
   const int64_t ctas = ((Lq + kBQ - 1) / kBQ) * heads;
   const int64_t nt = (Lk + kBK - 1) / kBK;
   const int sms = sm_count();
+  if (sms > 0 && ctas > sms && tail_cut_for(ctas, nt, sms) > 0) return LLNV_ATTN_SPLIT_TAIL;
   if (sms <= 0 || 2 * ctas > sms) return 1;                 // the grid already fills most of the device
   int64_t splits = sms / ctas;
   // every split should still run a few key tiles, so that the set-up and the combine pass stay small
@@ -749,6 +781,7 @@ extern "C" int llnv_attention_key_splits(int64_t Lq, int64_t Lk, int heads) {
 }
 
 extern "C" int64_t llnv_attention_workspace_bytes(int64_t Lq, int heads, int key_splits) {
+  if (key_splits == LLNV_ATTN_SPLIT_TAIL) key_splits = 2;
   if (key_splits <= 1 || Lq <= 0 || heads <= 0) return 0;
   return (int64_t)key_splits * Lq * heads * (kD + 2) * (int64_t)sizeof(float);
 }
@@ -761,7 +794,17 @@ int attention_launch(const void* q, int64_t Lq, int64_t ldq, const void* k, cons
                      int heads, float scale, void* out, int64_t ldo, int key_splits, void* workspace, int64_t workspace_bytes,
                      float* out_amax, const KvTable* kv, int64_t n_cached, int block_tokens, float inv_denom, cudaStream_t stream,
                      const char* who) {
-  LLNV_REQUIRE(key_splits >= 1 && key_splits <= 64, "%s: key_splits must be in 1..64 (got %d)", who, key_splits);
+  int tail_cut = 0;
+  if (key_splits == LLNV_ATTN_SPLIT_TAIL) {
+    const int sms = sm_count();
+    if (sms > 0 && Lq > 0 && Lk > 0) tail_cut = tail_cut_for(((Lq + kBQ - 1) / kBQ) * heads, (Lk + kBK - 1) / kBK, sms);
+    if (tail_cut > 0)
+      LLNV_REQUIRE(workspace != nullptr && ((uintptr_t)workspace & 15) == 0 &&
+                       workspace_bytes >= llnv_attention_workspace_bytes(Lq, heads, LLNV_ATTN_SPLIT_TAIL),
+                   "%s: tail balancing needs a 16-byte aligned workspace of llnv_attention_workspace_bytes() bytes", who);
+    key_splits = 1;
+  }
+  LLNV_REQUIRE(key_splits >= 1 && key_splits <= 64, "%s: key_splits must be in 1..64 or LLNV_ATTN_SPLIT_TAIL (got %d)", who, key_splits);
   LLNV_REQUIRE(Lk <= 0 || key_splits <= (Lk + kBK - 1) / kBK, "%s: more key splits (%d) than key tiles of 128", who, key_splits);
   if (key_splits > 1) {
     LLNV_REQUIRE(workspace != nullptr && ((uintptr_t)workspace & 15) == 0 &&
@@ -809,10 +852,13 @@ int attention_launch(const void* q, int64_t Lq, int64_t ldq, const void* k, cons
   p.heads = heads;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = device_status_word();
+  const int zdim = tail_cut > 0 ? 2 : key_splits;     // partial-result slices in the workspace
   p.nsplit = key_splits;
-  p.part_o = key_splits > 1 ? (float*)workspace : nullptr;
-  p.part_ml = key_splits > 1 ? (float*)workspace + (int64_t)key_splits * Lq * heads * kD : nullptr;
-  p.out_amax = key_splits > 1 ? nullptr : out_amax;
+  p.tail_cut = tail_cut;
+  p.tail_first = tail_cut > 0 ? (int)((((Lq + kBQ - 1) / kBQ) * heads / sm_count()) * sm_count()) : 0;
+  p.part_o = zdim > 1 ? (float*)workspace : nullptr;
+  p.part_ml = zdim > 1 ? (float*)workspace + (int64_t)zdim * Lq * heads * kD : nullptr;
+  p.out_amax = key_splits > 1 ? nullptr : out_amax;   // with tail balancing the whole items report their own maximum
   p.n_cached = n_cached;
   p.block_tokens = block_tokens > 0 ? block_tokens : 1;
   p.inv_denom = inv_denom;
@@ -820,15 +866,15 @@ int attention_launch(const void* q, int64_t Lq, int64_t ldq, const void* k, cons
   p.v_cur = (const uint16_t*)v;
   p.ldk = ldk;
   p.ldv = ldv;
-  dim3 grid((unsigned)((Lq + kBQ - 1) / kBQ), (unsigned)heads, (unsigned)key_splits);
+  dim3 grid((unsigned)((Lq + kBQ - 1) / kBQ), (unsigned)heads, (unsigned)zdim);
   static const KvTable no_blocks = {};      // the bf16 kernel never reads it
   if (fused) launch_k(attention_kernel<true>, grid, kThreadsFused, kSmemBytesFused, stream, tmQ, tmK, tmV, tmO, p, *kv);
   else launch_k(attention_kernel<false>, grid, kThreads, kSmemBytes, stream, tmQ, tmK, tmV, tmO, p, no_blocks);
   int st = launch_status("attention_kernel");
-  if (st != LLNV_OK || key_splits == 1) return st;
+  if (st != LLNV_OK || zdim == 1) return st;
   const int64_t units = Lq * heads;
-  launch_k(attention_combine_kernel, (unsigned)((units + 7) / 8), 256, 0, stream, p.part_o, p.part_ml, key_splits, Lq, heads, p.scale_log2,
-                                                                           (uint16_t*)out, ldo, out_amax);
+  launch_k(attention_combine_kernel, (unsigned)((units + 7) / 8), 256, 0, stream, p.part_o, p.part_ml, zdim, Lq, heads, p.scale_log2,
+           (uint16_t*)out, ldo, out_amax, tail_cut > 0 ? p.tail_first : -1, (int)grid.x);
   return launch_status("attention_combine_kernel");
 }
 

@@ -15,11 +15,12 @@
 //     left there; this entry point needs no zero-initialised state (each call overwrites the
 //     statistics of rows 0..M-1 before reading them).  Two calls that may run concurrently on the
 //     same GPU (different streams) race on the array and must not be issued;
-//   * the first call on each device resolves the device address of the array with
-//     cudaGetSymbolAddress (a one-time set-up that is not a stream operation); make that first
-//     call during start-up, before any stream capture begins.
-#include <mutex>
-
+//   * the device address of the array is looked up with cudaGetSymbolAddress on every call (a host-side table
+//     lookup once the library's device code is loaded, no stream operation) and never cached: a cached address
+//     would dangle after cudaDeviceReset() or any other teardown of the primary context, whereas the lookup
+//     follows the context that is current.  The array's contents do not survive such a teardown and need not.
+//     The first call on each device may load the device code; make it during start-up, before any stream
+//     capture begins.
 #include "common.cuh"
 
 namespace llnv {
@@ -31,24 +32,13 @@ constexpr int64_t kStaticMaxRows = 16384;
 // address: the address kernels receive comes from cudaGetSymbolAddress below.
 static __device__ __align__(256) float g_static_row_stats[2 * kStaticMaxRows];
 
-constexpr int kMaxDevices = 64;
-float* g_row_stats_addr[kMaxDevices] = {};
-std::mutex g_addr_mu;
-
-// Device address of the scratch array on the current device (resolved once per device).
+// Device address of the scratch array in the current context.
 int static_row_stats(float** out) {
-  int dev = 0;
-  LLNV_CUDA(cudaGetDevice(&dev));
-  LLNV_REQUIRE(dev >= 0 && dev < kMaxDevices, "static scratch: device ordinal %d out of range", dev);
-  std::lock_guard<std::mutex> lock(g_addr_mu);
-  if (!g_row_stats_addr[dev]) {
-    float* p = nullptr;
-    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_row_stats);
-    if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_static_row_stats)");
-    LLNV_REQUIRE(p != nullptr, "static scratch: cudaGetSymbolAddress returned a null address");
-    g_row_stats_addr[dev] = p;
-  }
-  *out = g_row_stats_addr[dev];
+  float* p = nullptr;
+  cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_row_stats);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_static_row_stats)");
+  LLNV_REQUIRE(p != nullptr, "static scratch: cudaGetSymbolAddress returned a null address");
+  *out = p;
   return LLNV_OK;
 }
 

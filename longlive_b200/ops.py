@@ -318,6 +318,9 @@ def peer_allreduce_max(vals, slot_ptrs, signal_ptrs, rank, epoch):
                                                   len(signal_ptrs), epoch.data_ptr(), _stream(vals)))
 
 
+SPLIT_TAIL = -1          # LLNV_ATTN_SPLIT_TAIL: cut the tiles of the last partial wave once (see include/llnvfp4.h)
+
+
 def attention_bf16(q, k, v, heads, scale=None, out=None, key_splits=None, out_amax=None):
     """softmax(q k^T * scale) v per head, non-causal.  q: bf16 [Lq, heads*128]; k, v: bf16 [Lk, heads*128]
     (row strides free, unit column stride).  Returns bf16 [Lq, heads*128].  ``key_splits`` > 1 splits
@@ -338,7 +341,7 @@ def attention_bf16(q, k, v, heads, scale=None, out=None, key_splits=None, out_am
         if key_splits is None:
             key_splits = lib.llnv_attention_key_splits(q.shape[0], k.shape[0], heads)
         ws, ws_bytes = None, 0
-        if key_splits > 1:
+        if key_splits > 1 or key_splits == SPLIT_TAIL:
             ws_bytes = lib.llnv_attention_workspace_bytes(q.shape[0], heads, key_splits)
             ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
         _check(lib.llnv_attention_bf16_ex(q.data_ptr(), q.shape[0], q.stride(0), k.data_ptr(), v.data_ptr(), k.shape[0],
@@ -387,7 +390,7 @@ def attention_nvfp4kv(q, k_blocks, v_blocks, block_tokens, k_cur, v_cur, heads, 
         if key_splits is None:
             key_splits = lib.llnv_attention_key_splits(q.shape[0], lk, heads)
         ws, ws_bytes = None, 0
-        if key_splits > 1:
+        if key_splits > 1 or key_splits == SPLIT_TAIL:
             ws_bytes = lib.llnv_attention_workspace_bytes(q.shape[0], heads, key_splits)
             ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
         _check(lib.llnv_attention_nvfp4kv(

@@ -114,8 +114,43 @@ def test_attention_key_split_arguments():
     assert lib.llnv_attention_workspace_bytes(2640, 3, 1) == 0
     assert lib.llnv_attention_workspace_bytes(2640, 3, 4) == 4 * 2640 * 3 * 130 * 4
     # the full-size single-GPU call fills the device by itself; an 8-way head shard of it does not
-    assert lib.llnv_attention_key_splits(2640, 13200, 24) == 1
     assert lib.llnv_attention_key_splits(2640, 13200, 3) > 1
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    if sms == 148:
+        # 264 tiles on 148 SMs: a last wave of 116 tiles, which tail balancing cuts; 296 tiles fill two waves exactly
+        assert lib.llnv_attention_key_splits(2640, 13200, 24) == ops.SPLIT_TAIL
+        assert lib.llnv_attention_key_splits(256 * 37, 13200, 8) == 1
+    assert lib.llnv_attention_workspace_bytes(2640, 24, ops.SPLIT_TAIL) == 2 * 2640 * 24 * 130 * 4
+
+
+def test_attention_tail_balancing():
+    """More (query tile, head) items than SMs with a last partial wave: the items of that wave are cut once and merged in
+    fp32.  The result agrees with the uncut call to bf16 rounding, its amax is exact, the NVFP4-window kernel cut the same
+    way is bit-identical to dequantize-then-attend, and a call that needs the workspace refuses to run without it."""
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    heads, T, blocks = 8, 1024, 3
+    lq = 256 * ((sms + sms // 2) // heads) + 40            # about 1.5 waves of items, ragged last query tile
+    g = torch.Generator(device="cuda").manual_seed(77)
+    kq, vq = _cache_blocks(blocks, T, heads, g), _cache_blocks(blocks, T, heads, g, scale=2.0)
+    q = torch.randn(lq, heads * 128, generator=g, device="cuda").bfloat16()
+    k_cur = torch.randn(T, heads * 128, generator=g, device="cuda").bfloat16()
+    v_cur = torch.randn(T, heads * 128, generator=g, device="cuda").bfloat16()
+    lib = _lib.lib()
+    assert lib.llnv_attention_key_splits(lq, (blocks + 1) * T, heads) == ops.SPLIT_TAIL
+    am = [torch.full((1,), 9.0, device="cuda") for _ in range(3)]
+    whole = _dequant_then_attention(q, kq, vq, T, k_cur, v_cur, heads, key_splits=1, out_amax=am[0])
+    ref = _dequant_then_attention(q, kq, vq, T, k_cur, v_cur, heads, key_splits=ops.SPLIT_TAIL, out_amax=am[1])
+    out = ops.attention_nvfp4kv(q, kq, vq, T, k_cur, v_cur, heads, key_splits=ops.SPLIT_TAIL, out_amax=am[2])
+    torch.cuda.synchronize()
+    assert lib.llnv_check_status(None) == 0, lib.llnv_last_error()
+    assert torch.equal(out, ref) and torch.equal(am[1], am[2])
+    assert float(am[2].item()) == float(out.float().abs().max().item())
+    assert not torch.equal(out, whole)                         # the cut items went through the merge
+    d = (out.float() - whole.float()).abs()
+    assert float(d.max()) <= 2.0 ** -7 * float(whole.float().abs().max()) and float((d > 0).float().mean()) < 0.2
+    with pytest.raises(RuntimeError, match="workspace"):
+        ops._check(lib.llnv_attention_bf16_ex(q.data_ptr(), lq, q.stride(0), k_cur.data_ptr(), v_cur.data_ptr(), 4 * T, heads * 128, heads * 128, heads,
+                                              0.1, out.data_ptr(), out.stride(0), ops.SPLIT_TAIL, None, 0, None, None))
 
 
 @pytest.mark.parametrize("lq,splits", [(300, 1), (300, 3), (256, 1)])
