@@ -630,6 +630,8 @@ def run_kernel_case(spec: str, iters: int):
                       in shared memory; the rate is the tensor-core ceiling of the W4A4 main loop on this device)
     refgemm:MxNxK  (the same NVFP4 operands through torch._scaled_mm, i.e. the vendor library's block-scaled FP4 GEMM: an
                     anchor on the same box, not part of the product path; prints the error text if the build refuses NVFP4)
+    adalnq:MxC[:PHASE]  (adaLN on load + quantize of an M x C activation with 880-row frames; PHASE 1 = row statistics + amax only,
+                         2 = quantize only, default both)
     unipc:ELEMENTS[:f32]  (the scheduler step with order-2 corrector and predictor: 5 tensors read, 3 written)
     forward:LAYERS  (one eager forward of a LAYERS-layer DiT at the benchmark's widths with a full window; the cache blocks are
                      filled with quantized noise instead of running the chunks that would fill them)"""
@@ -767,6 +769,25 @@ def run_kernel_case(spec: str, iters: int):
         out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
         fn = lambda: ops.linear_bf16(x, w, b, out=out)
         work, unit = 2.0 * m * n * k / 1e12, "TFLOP/s"
+    elif kind == "adalnq":
+        import ctypes
+        m, c = d
+        frames = max(1, m // 880)
+        x = torch.randn(m, c, generator=gen, device=dev).bfloat16()
+        mod = (torch.randn(frames, 6, c, generator=gen, device=dev) * 0.2).bfloat16()
+        mp = ops.padded_rows(m)
+        codes = torch.empty(mp, c // 2, dtype=torch.uint8, device=dev)
+        sf = torch.empty(mp * c // 16, dtype=torch.uint8, device=dev)
+        amax = torch.zeros(1, dtype=torch.float32, device=dev)
+        stats = torch.empty(2 * m, dtype=torch.float32, device=dev)
+        stream = torch.cuda.current_stream().cuda_stream
+        phase = int(opt or 0)
+        call = lambda ph: _lib.check(lib.llnv_adaln_quantize_nvfp4_ex(
+            x.data_ptr(), m, c, x.stride(0), mod[:, 1].data_ptr(), mod[:, 0].data_ptr(), mod.stride(0), (m + frames - 1) // frames,
+            ctypes.c_float(1e-6), 1, 3, codes.data_ptr(), sf.data_ptr(), amax.data_ptr(), None, 0, stats.data_ptr(), 0, ph, stream))
+        call(0)
+        fn = lambda: call(phase)
+        work, unit = (2.0 if phase == 1 else 2.5625) * m * c / 1e9, "GB/s"
     elif kind == "unipc":
         import ctypes
         from longlive_b200.scheduler import FlowUniPCMultistepScheduler

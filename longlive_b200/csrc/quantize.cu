@@ -217,7 +217,7 @@ __global__ void __launch_bounds__(256) quantize_nvfp4_kernel(const uint16_t* x, 
 // WPR warps share one row (each takes C / WPR channels): with one warp per row a chunk of 2640
 // tokens is only 2640 warps and the kernel is bound by the latency of each warp's dependent steps.
 template <int MODE, int WPR>
-__global__ void __launch_bounds__(256) ln_stats_amax_kernel(const uint16_t* __restrict__ x, int64_t M, int64_t C, int64_t ldx,
+__global__ void __launch_bounds__(256, WPR > 1 ? 8 : 1) ln_stats_amax_kernel(const uint16_t* __restrict__ x, int64_t M, int64_t C, int64_t ldx,
                                                             float eps, Prologue pr, float* __restrict__ row_stats,
                                                             float* __restrict__ amax) {
   pdl_wait();
@@ -252,19 +252,18 @@ __global__ void __launch_bounds__(256) ln_stats_amax_kernel(const uint16_t* __re
     }
   }
   const bool live = row < M;
-  uint4 v[kVec], pa[kVec], pb[kVec];
+  uint4 v[kVec];
   float sum = 0.f;
+  // parameter row of this token (WPR > 1: its vectors are fetched where they are used, after the statistics; the few
+  // rows of a frame are shared by hundreds of tokens and stay in L1 / L2, and not holding them across the two
+  // reductions keeps the kernel at 40 registers, i.e. half as many waves of CTAs)
+  const int64_t prow = (MODE == kAdaLN && live) ? ((row + pr.row_offset) / pr.frame_rows) * pr.stride : 0;
   if (live) {
-    const int64_t prow = MODE == kAdaLN ? ((row + pr.row_offset) / pr.frame_rows) * pr.stride : 0;
 #pragma unroll
     for (int i = 0; i < kVec; ++i) {
       const int li = lane + 32 * i;
       if (li < pvec) {
         v[i] = __ldg(reinterpret_cast<const uint4*>(x + row * ldx) + vbase + li);
-        if (WPR > 1) {
-          pa[i] = __ldg(reinterpret_cast<const uint4*>(pr.p0 + prow) + vbase + li);
-          pb[i] = __ldg(reinterpret_cast<const uint4*>(pr.p1 + prow) + vbase + li);
-        }
         sum += bf16_lo(v[i].x) + bf16_hi(v[i].x) + bf16_lo(v[i].y) + bf16_hi(v[i].y) + bf16_lo(v[i].z) + bf16_hi(v[i].z) +
                bf16_lo(v[i].w) + bf16_hi(v[i].w);
       }
@@ -312,8 +311,8 @@ __global__ void __launch_bounds__(256) ln_stats_amax_kernel(const uint16_t* __re
       const int li = lane + 32 * i;
       if (li < pvec) {
         const int idx = vbase + li;
-        const uint4 a4 = WPR > 1 ? pa[i] : pa_sh[fsel][idx];
-        const uint4 b4 = WPR > 1 ? pb[i] : pb_sh[fsel][idx];
+        const uint4 a4 = WPR > 1 ? __ldg(reinterpret_cast<const uint4*>(pr.p0 + prow) + idx) : pa_sh[fsel][idx];
+        const uint4 b4 = WPR > 1 ? __ldg(reinterpret_cast<const uint4*>(pr.p1 + prow) + idx) : pb_sh[fsel][idx];
         const uint32_t ws[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
         const uint32_t aw[4] = {a4.x, a4.y, a4.z, a4.w};
         const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w};
