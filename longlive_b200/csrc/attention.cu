@@ -821,7 +821,7 @@ int attention_launch(const void* q, int64_t Lq, int64_t ldq, const void* k, cons
   LLNV_REQUIRE(((uintptr_t)q & 15) == 0 && ((uintptr_t)k & 15) == 0 && ((uintptr_t)v & 15) == 0 && ((uintptr_t)out & 15) == 0,
                "%s: pointers must be 16-byte aligned", who);
   LLNV_REQUIRE(heads <= 65535, "%s: too many heads", who);
-  if (out_amax) LLNV_CUDA(cudaMemsetAsync(out_amax, 0, sizeof(float), stream));
+  if (out_amax && !amax_accumulate(1)) LLNV_CUDA(cudaMemsetAsync(out_amax, 0, sizeof(float), stream));
   if (Lq == 0) return LLNV_OK;
   CUtensorMap tmQ, tmK, tmV, tmO;
   int rc = cached_tensor_map(&tmQ, 1, q, (uint64_t)Lq, (uint64_t)C, (uint64_t)ldq, 128, 64, 3);

@@ -57,6 +57,7 @@ int sm_count();
 // pdl_wait() returns at once.
 bool pdl_enabled();                    // llnv_set_pdl / environment LLNV_PDL=0 turn the attribute off
 void count_launch();                   // llnv_launch_count(): kernels launched by the library since it was loaded
+bool amax_accumulate(int which);       // llnv_set_amax_accumulate: bit 1 attention + LN quantizers, bit 2 grouped GEMM + RoPE
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {

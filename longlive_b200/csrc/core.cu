@@ -58,8 +58,11 @@ std::atomic<unsigned long long> g_launches{0};
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 namespace {
+thread_local int g_amax_accumulate = 0;
 int g_pdl = -1;                        // -1: not decided yet (environment LLNV_PDL=1 turns it on; default off)
 }
+
+bool amax_accumulate(int which) { return (g_amax_accumulate & which) != 0; }
 
 bool pdl_enabled() {
   if (g_pdl < 0) {
@@ -74,6 +77,12 @@ bool pdl_enabled() {
 extern "C" int llnv_set_pdl(int on) {
   const int before = llnv::pdl_enabled() ? 1 : 0;
   llnv::g_pdl = on ? 1 : 0;
+  return before;
+}
+
+extern "C" int llnv_set_amax_accumulate(int on) {
+  const int before = llnv::g_amax_accumulate;
+  llnv::g_amax_accumulate = on & 3;
   return before;
 }
 

@@ -577,7 +577,7 @@ extern "C" int llnv_gemm_nvfp4_grouped(const void* a_codes, const void* a_sf, co
                              "llnv_gemm_nvfp4_grouped: residual, gate, alpha and out_amax belong to the single-matrix call");
   if (out_amax) {
     for (int g = 0; g < groups; ++g)
-      if (out_amax[g]) LLNV_CUDA(cudaMemsetAsync(out_amax[g], 0, sizeof(float), (cudaStream_t)stream));
+      if (out_amax[g] && !amax_accumulate(2)) LLNV_CUDA(cudaMemsetAsync(out_amax[g], 0, sizeof(float), (cudaStream_t)stream));
   }
   return gemm_run(a_codes, a_sf, a_amax, a_rule, b_codes, b_sf, b_amax, b_rule, M, N_each * groups, K, epilogue, d[0], ldd[0],
                   (cudaStream_t)stream, groups, d, ldd, out_amax, LLNV_GEMM_TILE_AUTO);

@@ -410,7 +410,7 @@ int ln_quantize_impl(int mode, const void* x, int64_t M, int64_t C, int64_t ldx,
   if (mode == kAdaLN) LLNV_REQUIRE(frame_rows > 0 && mod_stride >= C && mod_stride % 8 == 0, "%s: frame_rows must be positive and the modulation stride a multiple of 8 that is >= C", who);
   if (y_out) LLNV_REQUIRE(ldy >= C && ldy % 8 == 0 && ((uintptr_t)y_out & 15) == 0, "%s: y_out must be 16-byte aligned with ldy a multiple of 8", who);
   LLNV_REQUIRE(phase >= 0 && phase <= 2 && row_offset >= 0, "%s: phase must be 0, 1 or 2 and row_offset non-negative", who);
-  if (phase != 2) LLNV_CUDA(cudaMemsetAsync(amax, 0, sizeof(float), stream));
+  if (phase != 2 && !amax_accumulate(1)) LLNV_CUDA(cudaMemsetAsync(amax, 0, sizeof(float), stream));
   if (M == 0) return LLNV_OK;
   Prologue pr = {};                 // every field the mode does not use stays zero (shard_cols = 0: plain input)
   pr.row_stats = row_stats;

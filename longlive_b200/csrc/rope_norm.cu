@@ -222,7 +222,7 @@ int rope_launch_jobs(const RopeJobs& jobs, int njobs, int64_t S, int64_t C, floa
   for (int j = 0; j < njobs; ++j) {
     int rc = check_job(jobs.job[j], C, shards);
     if (rc != LLNV_OK) return rc;
-    if (jobs.job[j].amax_out) LLNV_CUDA(cudaMemsetAsync(jobs.job[j].amax_out, 0, sizeof(float), stream));
+    if (jobs.job[j].amax_out && !amax_accumulate(2)) LLNV_CUDA(cudaMemsetAsync(jobs.job[j].amax_out, 0, sizeof(float), stream));
   }
   if (S == 0) return LLNV_OK;
   const int sv = shards > 1 ? (int)(C / shards / 8) : 0;

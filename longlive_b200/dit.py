@@ -27,7 +27,7 @@ from dataclasses import dataclass
 
 import torch
 
-from . import ops, sp
+from . import _lib, ops, sp
 from .enums import ScaleRule
 from .quantize import QuantizationConfig, QuantizedTensor, quantize_to_fp4
 from .scheduler import FlowUniPCMultistepScheduler
@@ -151,11 +151,14 @@ class KVCache:
     def __init__(self, cfg: DiTConfig, local_heads: int, device):
         rows = cfg.chunk_tokens * local_heads
         mp = ops.padded_rows(rows)
-        mk = lambda: QuantizedTensor(torch.zeros((mp, 64), dtype=torch.uint8, device=device),
-                                     torch.zeros(mp * 8, dtype=torch.float8_e4m3fn, device=device),
-                                     torch.zeros(1, dtype=torch.float32, device=device), "nvfp4", (rows, 128), "mse", (mp, 128))
-        self.k = [[mk() for _ in range(cfg.max_blocks)] for _ in range(cfg.layers)]
-        self.v = [[mk() for _ in range(cfg.max_blocks)] for _ in range(cfg.layers)]
+        # the tensor amax of every block lives in one array [layer, slot, K / V], so that a forward can clear the scalars of
+        # the block it is about to write for all layers with one fill
+        self.amax_pool = torch.zeros((cfg.layers, cfg.max_blocks, 2), dtype=torch.float32, device=device)
+        mk = lambda l, s, kv: QuantizedTensor(torch.zeros((mp, 64), dtype=torch.uint8, device=device),
+                                              torch.zeros(mp * 8, dtype=torch.float8_e4m3fn, device=device),
+                                              self.amax_pool[l, s, kv:kv + 1], "nvfp4", (rows, 128), "mse", (mp, 128))
+        self.k = [[mk(l, s, 0) for s in range(cfg.max_blocks)] for l in range(cfg.layers)]
+        self.v = [[mk(l, s, 1) for s in range(cfg.max_blocks)] for l in range(cfg.layers)]
         self.order = list(range(cfg.max_blocks))
         self.filled = 0                       # number of valid blocks, current chunk included
         self.version = 0                      # bumped whenever the set of past blocks changes
@@ -262,6 +265,10 @@ class CausalDiT:
         dev = self.device
         bf = lambda *shape: torch.empty(shape, dtype=torch.bfloat16, device=dev)
         self.act_c = _Act(Sl, c, dev)            # activations with `dim` columns
+        # One amax scalar per (layer, producer) for the six activation amax values a block produces, so that a forward
+        # clears all of them with one fill instead of one 4-byte memset per producer (llnv_set_amax_accumulate).
+        self.amax_pool = torch.zeros(cfg.layers * 6, dtype=torch.float32, device=dev)
+        self._amax_prezeroed = False             # True while _forward_impl runs the blocks with accumulate mode on
         self.act_f = _Act(Sl, cfg.ffn_dim, dev)  # FFN hidden
         self.act_t = _Act(cfg.text_len, c, dev)  # text context
         self.row_stats = torch.empty(2 * Sl, dtype=torch.float32, device=dev)
@@ -440,7 +447,10 @@ class CausalDiT:
         cfg, blk, cache = self.cfg, self.blocks[li], self.cache
         Sl, S, ft = self.Sl, self.S, cfg.frame_tokens
         roff = self.rank * Sl
+        am = self.amax_pool[li * 6:(li + 1) * 6]          # this layer's amax scalars, one per producer below
+        act_amax = lambda i: am[i:i + 1]
         # -- self attention
+        self.act_c.amax = act_amax(0)
         self._adaln_quantize(x, e[:, 1], e[:, 0], self.act_c)
         T = cfg.chunk_tokens
         cur_k, cur_v = self.cur_k, self.cur_v
@@ -500,6 +510,7 @@ class CausalDiT:
         # after the exchange only once it is MAX-reduced: the peer-memory barrier after the exchange
         # does that for free; with the NCCL exchange it is used only under sync_amax.
         fused_amax = self.P == 1 or self.sync_amax or self.arena is not None
+        self.act_c.amax = act_amax(1)
         ops.attention_nvfp4kv(q_h, [cache.k[li][s] for s in past], [cache.v[li][s] for s in past], T, cur_k, cur_v, self.Hl,
                               out=self.attn_out, out_amax=self.act_c.amax if fused_amax else None)
         # cache write: rotated (un-smoothed) keys and values of the chunk, straight into the slot
@@ -532,14 +543,17 @@ class CausalDiT:
         x1, x2 = self.x1, self.x2
         self._gemm(self.act_c, Sl, blk.o, x1, residual=x, gate=e[:, 2], frame_rows=ft, row_offset=roff)
         # -- cross attention
+        self.act_c.amax = act_amax(2)
         self._ln_quantize(x1, blk.norm3_w, blk.norm3_b, self.act_c)
         self._gemm(self.act_c, Sl, blk.cq, self.cq_buf)
         ops.rmsnorm_rope(self.cq_buf, blk.cnorm_q, eps=cfg.eps, out=self.cq_n)
         kn, v = self._text_kv(li, blk, ctx)
+        self.act_c.amax = act_amax(3)
         ops.attention_bf16(self.cq_n, kn, v, cfg.heads, out=self.cattn, out_amax=self.act_c.amax)
         self._quantize(self.cattn, self.act_c, have_local_amax=True)
         self._gemm(self.act_c, Sl, blk.co, x2, residual=x1)
         # -- FFN
+        self.act_c.amax = act_amax(4)
         self._adaln_quantize(x2, e[:, 4], e[:, 3], self.act_c)
         if self.ffn_requant == "single_pass" and self._ffn_calibrated:
             # The GEMM epilogue quantizes the GELU output itself: the 75.7 MB bf16 hidden is neither written nor re-read
@@ -560,7 +574,9 @@ class CausalDiT:
                 self._allreduce_max(new)
             use.copy_(new)
             return x_out
-        self.act_f.amax.zero_()
+        self.act_f.amax = act_amax(5)
+        if not self._amax_prezeroed:
+            self.act_f.amax.zero_()
         self._gemm(self.act_c, Sl, blk.ffn0, self.hidden, act=1, out_amax=self.act_f.amax)
         if self.sync_amax:
             self._allreduce_max(self.act_f.amax)
@@ -662,9 +678,25 @@ class CausalDiT:
         ran_before = self._ran_eager
         self._ran_eager = True
         cur, nxt = self.x_a, self.x_b
-        for li, blk in enumerate(self.blocks):
-            self.block_forward(li, cur, nxt, em_all[li], ctx, cos, sin, write_cache)
-            cur, nxt = nxt, cur
+        # every activation amax of the forward cleared by one fill; the attention and LN-quantize entry points then
+        # accumulate into their scalars instead of clearing them one by one
+        self.amax_pool.zero_()
+        lib = _lib.lib()
+        mode = 1
+        if self.P == 1:
+            # on one GPU the V GEMM and the RoPE kernel write the amax of the cache block in place: clear the current
+            # block's scalars of all layers at once as well
+            self.cache.amax_pool[:, self.cache.current_slot()].zero_()
+            mode = 3
+        before = lib.llnv_set_amax_accumulate(mode)
+        self._amax_prezeroed = True
+        try:
+            for li, blk in enumerate(self.blocks):
+                self.block_forward(li, cur, nxt, em_all[li], ctx, cos, sin, write_cache)
+                cur, nxt = nxt, cur
+        finally:
+            self._amax_prezeroed = False
+            lib.llnv_set_amax_accumulate(before)
         if not ran_before:
             self._ffn_calibrated = True          # every layer's hidden amax is known from here on
         # head: LayerNorm, modulate with (head.modulation + e), project (CausalHead.forward, causal_model.py:950-959):
