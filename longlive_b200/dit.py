@@ -305,8 +305,6 @@ class CausalDiT:
         # of the layer in its load stage and reads the current chunk's smoothed keys / values from cur_k /
         # cur_v ([all chunk tokens, my heads], one pair shared by all layers; the reference dequantizes every
         # block into a bf16 window per layer and forward, causal_model.py:557-600).
-        self.kv_amax = torch.zeros(2, dtype=torch.float32, device=dev)      # [k, v]: reduced with one collective
-        self.k_amax, self.v_amax = self.kv_amax[0:1], self.kv_amax[1:2]
         self.h_amax = torch.zeros(1, dtype=torch.float32, device=dev)
         # single-pass FFN requantization: per layer the amax the epilogue scales the hidden with (that of the layer's
         # previous forward) and the amax this forward measures
@@ -457,7 +455,10 @@ class CausalDiT:
         ck, cv = cache.k[li][cache.current_slot()], cache.v[li][cache.current_slot()]
         # q, k and v projections in one grouped launch; V lands in cur_v (one GPU) or in v_buf, with its amax
         v_out = cur_v if self.P == 1 else self.v_buf
-        v_am = cv.amax if self.P == 1 else self.v_amax
+        # K / V amax of the chunk: the producers (RoPE kernel, V GEMM epilogue) write them straight into the cache block's
+        # scalars, [k, v] adjacent in the cache's amax array, where a sequence-parallel group reduces them in place
+        kv_amax = cache.amax_pool[li, cache.current_slot()]
+        k_amax, v_am = ck.amax, cv.amax
         if blk.qkv_ok:
             a = self.act_c
             ops.gemm_nvfp4_grouped(a.codes, a.sf, a.amax, MSE, blk.qkv_codes, blk.qkv_sf, blk.qkv_amax, blk.qkv_rule.cuda_id(), Sl, cfg.dim,
@@ -481,11 +482,11 @@ class CausalDiT:
             ar, Cl = self.arena, self.Cl
             row_off = self.rank * Sl * Cl * 2                   # my token block inside an [S, Cl] buffer
             ops.rmsnorm_rope_qk(self.q_buf, blk.norm_q, ar.ptrs("q_h", row_off), Cl, self.k_buf, blk.norm_k, ar.ptrs("kr_h", row_off), Cl,
-                                ar.ptrs("cur_k", row_off), Cl, self.k_amax, cos, sin, cfg.eps)
+                                ar.ptrs("cur_k", row_off), Cl, k_amax, cos, sin, cfg.eps)
             ops.scatter_2d(self.v_buf, Cl * 2, ar.ptrs("cur_v", row_off), Cl * 2, Sl, Cl * 2)
             # the barrier that publishes the stores above also carries the K / V amax: its group maximum
             # is the tensor scale of every rank's cache block (and the one a single GPU would use)
-            ar.allreduce_max_(self.kv_amax)
+            ar.allreduce_max_(kv_amax)
             q_h, k_for_cache, v_for_cache = self.q_h, self.kr_h, cur_v
         else:
             P_, grp = self.P, self.group
@@ -494,13 +495,13 @@ class CausalDiT:
             ops.rmsnorm_rope(x=self.q_buf, weight=blk.norm_q, cos=cos, sin=sin, eps=cfg.eps, out=self.q_sh, shards=P_)
             w_q = sp.exchange(self.q_sh, self.q_h, grp, async_op=True)
             ops.rmsnorm_rope(x=self.k_buf, weight=blk.norm_k, cos=cos, sin=sin, eps=cfg.eps, out=self.kr_sh, out_smooth=self.ks_sh,
-                             amax_out=self.k_amax, shards=P_)
+                             amax_out=k_amax, shards=P_)
             w_ks = sp.exchange(self.ks_sh, cur_k, grp, async_op=True)
             w_kr = sp.exchange(self.kr_sh, self.kr_h, grp, async_op=True)
             self.v_sh.copy_(self.v_buf.view(Sl, P_, self.Cl).permute(1, 0, 2))
             w_v = sp.exchange(self.v_sh, cur_v, grp, async_op=True)
             if self.sync_amax:
-                sp.allreduce_max_(self.kv_amax, grp)
+                sp.allreduce_max_(kv_amax, grp)
             for w in (w_q, w_ks, w_kr, w_v):
                 w.wait()
             q_h, k_for_cache, v_for_cache = self.q_h, self.kr_h, cur_v
@@ -517,9 +518,7 @@ class CausalDiT:
         if self.P == 1:
             kv_given = True
         elif self.sync_amax or self.arena is not None:
-            # k_amax / v_amax (RoPE kernel, V GEMM epilogue), MAX-reduced over the group, are the amax of the cached tensors
-            ck.amax.copy_(self.k_amax)
-            cv.amax.copy_(self.v_amax)
+            # the producers' amax values, MAX-reduced over the group in place, are the amax of the cached tensors
             kv_given = True
         else:
             # per-rank scales: the producers saw (my tokens, all heads), the cache block holds (all tokens,
@@ -682,13 +681,10 @@ class CausalDiT:
         # accumulate into their scalars instead of clearing them one by one
         self.amax_pool.zero_()
         lib = _lib.lib()
-        mode = 1
-        if self.P == 1:
-            # on one GPU the V GEMM and the RoPE kernel write the amax of the cache block in place: clear the current
-            # block's scalars of all layers at once as well
-            self.cache.amax_pool[:, self.cache.current_slot()].zero_()
-            mode = 3
-        before = lib.llnv_set_amax_accumulate(mode)
+        # the V GEMM and the RoPE kernel write the amax of the cache block in place: clear the current block's scalars of
+        # all layers at once as well
+        self.cache.amax_pool[:, self.cache.current_slot()].zero_()
+        before = lib.llnv_set_amax_accumulate(3)
         self._amax_prezeroed = True
         try:
             for li, blk in enumerate(self.blocks):
