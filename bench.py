@@ -213,14 +213,17 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 2))
+    steps = max(1, min(args.steps, 10))              # one step = one bounded sample (about 11 s of host time)
+    warm = 1 if args.warmup > 0 else 0
+    for _ in range(warm):
+        cpu_chunk_fps(1)
     vals = [cpu_chunk_fps(1) for _ in range(steps)]
     value = statistics.mean(v[0] for v in vals)
     chunk_s = statistics.mean(v[2] for v in vals)
     cores = os.cpu_count() or 1
     line = {
         "impl": "reference", "metric": "dit_chunk_video_fps", "value": value, "unit": "frames/s", "n_gpus": args.gpus,
-        "steps": steps, "warmup": 0, "ms_per_step": chunk_s * 1e3, "higher_is_better": True, "scaling": "strong",
+        "steps": steps, "warmup": warm, "ms_per_step": chunk_s * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "nvfp4 fake-quant (dequantized to f32 on the CPU)", "data": "synthetic",
         "config": {"workload": "30-layer Wan2.2-5B-shaped causal DiT, one AR chunk (3 latent frames, 5 forwards), 15-frame window; "
                                "the CPU arm times a bounded sample and extrapolates", "l2": "n/a (CPU)"},

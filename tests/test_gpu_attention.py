@@ -299,3 +299,27 @@ def test_config3_window_attention_full_size_vs_oracle():
     ref = O.attention(q_rot.float().cpu().numpy().reshape(T, heads, 128)[:, sel], kw, vw)
     got = out.view(T, heads, 128)[:, sel]
     check(got, ref)
+
+
+def test_amax_accumulate_mode_keeps_the_larger_value():
+    """llnv_set_amax_accumulate(1): the attention entry points no longer clear out_amax themselves, so the scalar ends up as
+    max(what it held, max |out|); with the mode off (the default) it is overwritten.  The previous mask is returned."""
+    lib = _lib.lib()
+    g = torch.Generator(device="cuda").manual_seed(5)
+    q = torch.randn(200, 256, generator=g, device="cuda").bfloat16()
+    k = torch.randn(300, 256, generator=g, device="cuda").bfloat16()
+    v = torch.randn(300, 256, generator=g, device="cuda").bfloat16()
+    amax = torch.full((1,), 1.0e6, device="cuda")
+    out = ops.attention_bf16(q, k, v, 2, out_amax=amax)
+    true_max = float(out.float().abs().max().item())
+    assert float(amax.item()) == true_max                     # default: overwritten
+    assert lib.llnv_set_amax_accumulate(1) == 0
+    try:
+        amax.fill_(1.0e6)
+        ops.attention_bf16(q, k, v, 2, out_amax=amax)
+        assert float(amax.item()) == 1.0e6                    # kept: larger than anything the call produces
+        amax.zero_()
+        ops.attention_bf16(q, k, v, 2, out_amax=amax)
+        assert float(amax.item()) == true_max                 # cleared by the caller: the call's own maximum
+    finally:
+        assert lib.llnv_set_amax_accumulate(0) == 1

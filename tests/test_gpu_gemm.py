@@ -327,3 +327,18 @@ def test_gemm_requant_argument_checks():
         ops.gemm_nvfp4(*args, requant=(codes, sf), requant_amax=amax, residual=torch.zeros(128, 256, dtype=torch.bfloat16, device="cuda"))
     with pytest.raises(ValueError, match="store_out"):
         ops.gemm_nvfp4(*args, store_out=False)
+
+
+def test_fp4_mma_rate_probe_runs_and_reports_its_flop():
+    """The MMA issue-rate probe launches (bounded wait inside), leaves the status word clean and reports
+    2 * 128 * 256 * 256 flop per K block and SM."""
+    import ctypes
+    lib = _lib.lib()
+    flop = ctypes.c_double()
+    _lib.check(lib.llnv_fp4_mma_rate(64, ctypes.byref(flop), torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert lib.llnv_check_status(None) == 0, lib.llnv_last_error()
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert flop.value == 2.0 * 128 * 256 * 256 * 64 * sms
+    with pytest.raises(Exception):
+        _lib.check(lib.llnv_fp4_mma_rate(0, None, None))
