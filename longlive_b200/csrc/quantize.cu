@@ -92,6 +92,30 @@ struct Prologue {
   uint8_t* sf2;
 };
 
+// y of two adjacent channels (packed bf16 in, packed bf16 out) with the rounding points listed at Prologue.  Packed
+// two-lane fp32 instructions: every lane rounds as the scalar instruction does, at half the issue slots.
+__device__ __forceinline__ void round_f2(F2& v) { round_bf16x2(v.x, v.y); }
+template <int MODE>
+__device__ __forceinline__ uint32_t ln_pair(uint32_t xw, uint32_t aw, uint32_t bw, F2 mean2, F2 rstd2, int add_one) {
+  F2 xn = f2_mul(f2_sub(F2{bf16_lo(xw), bf16_hi(xw)}, mean2), rstd2);
+  const F2 a = {bf16_lo(aw), bf16_hi(aw)}, b = {bf16_lo(bw), bf16_hi(bw)};
+  F2 y;
+  if (MODE == kAdaLN) {
+    F2 sc = a;
+    if (add_one) {
+      sc = f2_add(a, f2_splat(1.f));
+      round_f2(sc);
+    }
+    round_f2(xn);
+    F2 m = f2_mul(xn, sc);
+    round_f2(m);
+    y = f2_add(m, b);
+  } else {
+    y = f2_fma(xn, a, b);
+  }
+  return pack_bf16x2(y.x, y.y);
+}
+
 template <int MODE>
 __device__ __forceinline__ void transform_block(uint32_t (&w)[8], const Prologue& pr, int64_t row, int64_t col) {
   if (MODE == kPlain) return;
@@ -102,31 +126,9 @@ __device__ __forceinline__ void transform_block(uint32_t (&w)[8], const Prologue
   const uint4 a0 = __ldg(a4), a1 = __ldg(a4 + 1), b0 = __ldg(b4), b1 = __ldg(b4 + 1);
   const uint32_t aw[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
   const uint32_t bw[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+  const F2 mean2 = f2_splat(mean), rstd2 = f2_splat(rstd);
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    float y[2];
-    const float a0f = bf16_lo(aw[j]), a1f = bf16_hi(aw[j]);
-    const float b0f = bf16_lo(bw[j]), b1f = bf16_hi(bw[j]);
-    float xn0 = __fmul_rn(__fsub_rn(bf16_lo(w[j]), mean), rstd);
-    float xn1 = __fmul_rn(__fsub_rn(bf16_hi(w[j]), mean), rstd);
-    if (MODE == kAdaLN) {
-      float s0 = a0f, s1 = a1f;
-      if (pr.add_one) {
-        s0 = __fadd_rn(a0f, 1.f);
-        s1 = __fadd_rn(a1f, 1.f);
-        round_bf16x2(s0, s1);
-      }
-      round_bf16x2(xn0, xn1);
-      float m0 = __fmul_rn(xn0, s0), m1 = __fmul_rn(xn1, s1);
-      round_bf16x2(m0, m1);
-      y[0] = __fadd_rn(m0, b0f);
-      y[1] = __fadd_rn(m1, b1f);
-    } else {
-      y[0] = __fmaf_rn(xn0, a0f, b0f);
-      y[1] = __fmaf_rn(xn1, a1f, b1f);
-    }
-    w[j] = pack_bf16x2(y[0], y[1]);
-  }
+  for (int j = 0; j < 8; ++j) w[j] = ln_pair<MODE>(w[j], aw[j], bw[j], mean2, rstd2, pr.add_one);
 }
 
 template <int RULE, int MODE>
@@ -306,6 +308,8 @@ __global__ void __launch_bounds__(256, WPR > 1 ? 8 : 1) ln_stats_amax_kernel(con
       row_stats[2 * row + 1] = rstd;
     }
     const int fsel = (MODE == kAdaLN && (row + pr.row_offset) / pr.frame_rows != f0) ? 1 : 0;
+    const F2 mean2 = f2_splat(mean), rstd2 = f2_splat(rstd);
+    uint32_t ymax2 = 0u;                       // packed running maximum of |y| (two bf16 magnitudes)
 #pragma unroll
     for (int i = 0; i < kVec; ++i) {
       const int li = lane + 32 * i;
@@ -317,33 +321,10 @@ __global__ void __launch_bounds__(256, WPR > 1 ? 8 : 1) ln_stats_amax_kernel(con
         const uint32_t aw[4] = {a4.x, a4.y, a4.z, a4.w};
         const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float a0f = bf16_lo(aw[j]), a1f = bf16_hi(aw[j]);
-          const float b0f = bf16_lo(bw[j]), b1f = bf16_hi(bw[j]);
-          float xn0 = __fmul_rn(__fsub_rn(bf16_lo(ws[j]), mean), rstd);
-          float xn1 = __fmul_rn(__fsub_rn(bf16_hi(ws[j]), mean), rstd);
-          float y0, y1;
-          if (MODE == kAdaLN) {
-            float s0 = a0f, s1 = a1f;
-            if (pr.add_one) {
-              s0 = __fadd_rn(a0f, 1.f);
-              s1 = __fadd_rn(a1f, 1.f);
-              round_bf16x2(s0, s1);
-            }
-            round_bf16x2(xn0, xn1);
-            float m0 = __fmul_rn(xn0, s0), m1 = __fmul_rn(xn1, s1);
-            round_bf16x2(m0, m1);
-            y0 = __fadd_rn(m0, b0f);
-            y1 = __fadd_rn(m1, b1f);
-          } else {
-            y0 = __fmaf_rn(xn0, a0f, b0f);
-            y1 = __fmaf_rn(xn1, a1f, b1f);
-          }
-          round_bf16x2(y0, y1);
-          wmax = fmaxf(wmax, fmaxf(fabsf(y0), fabsf(y1)));
-        }
+        for (int j = 0; j < 4; ++j) ymax2 = __vmaxu2(ymax2, ln_pair<MODE>(ws[j], aw[j], bw[j], mean2, rstd2, pr.add_one) & 0x7FFF7FFFu);
       }
     }
+    wmax = __uint_as_float(max(ymax2 & 0xFFFFu, ymax2 >> 16) << 16);      // bf16 magnitudes order as integers
   }
   wmax = warp_max(wmax);
   __shared__ float smax[8];

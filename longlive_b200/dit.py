@@ -358,9 +358,9 @@ class CausalDiT:
                 amax_given = True
         ops.quantize_nvfp4(x, MSE, act.amax, act.codes, act.sf, amax_given=amax_given)
 
-    def _adaln_quantize(self, x, scale, shift, act: _Act):
+    def _adaln_quantize(self, x, scale, shift, act: _Act, add_one: bool = True):
         cfg = self.cfg
-        kw = dict(codes=act.codes, sf=act.sf, amax=act.amax, row_stats=self.row_stats, row_offset=self.rank * self.Sl)
+        kw = dict(codes=act.codes, sf=act.sf, amax=act.amax, row_stats=self.row_stats, row_offset=self.rank * self.Sl, add_one=add_one)
         if self.sync_amax:
             ops.adaln_quantize_nvfp4(x, scale, shift, cfg.frame_tokens, MSE, cfg.eps, phase=1, **kw)
             self._allreduce_max(act.amax)
@@ -439,9 +439,11 @@ class CausalDiT:
         return not self.cache_text_kv or all(kv is not None for kv in self._prompt(ctx)["kv"])
 
     # ---- one block ----------------------------------------------------------------------------
-    def block_forward(self, li: int, x: torch.Tensor, x_out: torch.Tensor, e: torch.Tensor, ctx, cos, sin, write_cache: bool = True):
+    def block_forward(self, li: int, x: torch.Tensor, x_out: torch.Tensor, e: torch.Tensor, ctx, cos, sin, write_cache: bool = True,
+                      scales_folded: bool = False):
         """x: [Sl, dim] bf16 (my tokens); e: [F, 6, dim] (block modulation + time projection); returns x_out.
-        ``write_cache=False`` leaves the current cache block unwritten (see ``run_chunk``)."""
+        ``write_cache=False`` leaves the current cache block unwritten (see ``run_chunk``).  ``scales_folded``: rows 1 and 4
+        of ``e`` already hold bf16(1 + scale) (``_fold_scales``)."""
         cfg, blk, cache = self.cfg, self.blocks[li], self.cache
         Sl, S, ft = self.Sl, self.S, cfg.frame_tokens
         roff = self.rank * Sl
@@ -449,7 +451,7 @@ class CausalDiT:
         act_amax = lambda i: am[i:i + 1]
         # -- self attention
         self.act_c.amax = act_amax(0)
-        self._adaln_quantize(x, e[:, 1], e[:, 0], self.act_c)
+        self._adaln_quantize(x, e[:, 1], e[:, 0], self.act_c, add_one=not scales_folded)
         T = cfg.chunk_tokens
         cur_k, cur_v = self.cur_k, self.cur_v
         ck, cv = cache.k[li][cache.current_slot()], cache.v[li][cache.current_slot()]
@@ -553,7 +555,7 @@ class CausalDiT:
         self._gemm(self.act_c, Sl, blk.co, x2, residual=x1)
         # -- FFN
         self.act_c.amax = act_amax(4)
-        self._adaln_quantize(x2, e[:, 4], e[:, 3], self.act_c)
+        self._adaln_quantize(x2, e[:, 4], e[:, 3], self.act_c, add_one=not scales_folded)
         if self.ffn_requant == "single_pass" and self._ffn_calibrated:
             # The GEMM epilogue quantizes the GELU output itself: the 75.7 MB bf16 hidden is neither written nor re-read
             # and one launch goes away.  A quantizer needs the tensor amax before its first block; it is taken from this
@@ -607,6 +609,16 @@ class CausalDiT:
         self.sin_buf.copy_(sin[lo:hi])
         self._rope_frame = key
 
+    @staticmethod
+    def _fold_scales(em: torch.Tensor) -> torch.Tensor:
+        """The two adaLN scale rows of every block's modulation as bf16(1 + scale), which is what the modulation
+        multiplies with (utils/adaln_triton.py:62-86 forms it per element in every call): formed once per timestep
+        vector here, so that the kernels run with add_one = 0.  Shifts and gates are untouched."""
+        em = em.clone()
+        em[:, :, 1] = (em[:, :, 1].float() + 1.0).to(em.dtype)
+        em[:, :, 4] = (em[:, :, 4].float() + 1.0).to(em.dtype)
+        return em
+
     def _time_inputs(self, t: torch.Tensor, t_key):
         """(e, per-layer modulation) of the timesteps ``t``.  They depend on the timesteps and the weights
         only, and a video runs the same few timesteps in every chunk, so with a host-side key for ``t``
@@ -614,14 +626,14 @@ class CausalDiT:
         the time MLP and the time projection in every forward (causal_model.py:1561-1564)."""
         if t_key is None:
             e, e0 = self.time_embed(t)
-            return e, self.modulation_all + e0.unsqueeze(0)     # [layers, F, 6, dim], causal_model.py:863 for every block at once
+            return e, self._fold_scales(self.modulation_all + e0.unsqueeze(0))     # [layers, F, 6, dim], causal_model.py:863 for every block at once
         hit = self._time_cache.get(t_key)
         if hit is None:
             if len(self._time_cache) >= 64:
                 self._time_cache.clear()
                 self._graphs.clear()                             # captured graphs read the dropped tensors
             e, e0 = self.time_embed(t)
-            hit = self._time_cache[t_key] = (e, self.modulation_all + e0.unsqueeze(0))
+            hit = self._time_cache[t_key] = (e, self._fold_scales(self.modulation_all + e0.unsqueeze(0)))
         return hit
 
     def forward(self, latent_tokens: torch.Tensor, t: torch.Tensor, ctx: torch.Tensor, start_frame: int, t_key=None,
@@ -688,7 +700,7 @@ class CausalDiT:
         self._amax_prezeroed = True
         try:
             for li, blk in enumerate(self.blocks):
-                self.block_forward(li, cur, nxt, em_all[li], ctx, cos, sin, write_cache)
+                self.block_forward(li, cur, nxt, em_all[li], ctx, cos, sin, write_cache, scales_folded=True)
                 cur, nxt = nxt, cur
         finally:
             self._amax_prezeroed = False
