@@ -275,6 +275,11 @@ class CausalDiT:
         self.q_buf, self.k_buf, self.v_buf = bf(Sl, c), bf(Sl, c), bf(Sl, c)
         self.q_rot, self.k_rot, self.k_smooth = bf(Sl, c), bf(Sl, c), bf(Sl, c)
         self.attn_out = bf(S, self.Cl)
+        # partial results of a split or tail-balanced self-attention call (none when the call is not split)
+        # (sized for every window length the cache passes through while it fills)
+        with torch.cuda.device(dev):
+            ws_bytes = max(ops.attention_workspace_bytes(S, n * cfg.chunk_tokens, self.Hl) for n in range(1, cfg.max_blocks + 1))
+        self.attn_ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
         self.arena = None
         self.check_peer_status = True         # run_chunk raises ops.DeviceTimeout when a peer barrier gave up
         if self.P > 1:
@@ -515,7 +520,7 @@ class CausalDiT:
         fused_amax = self.P == 1 or self.sync_amax or self.arena is not None
         self.act_c.amax = act_amax(1)
         ops.attention_nvfp4kv(q_h, [cache.k[li][s] for s in past], [cache.v[li][s] for s in past], T, cur_k, cur_v, self.Hl,
-                              out=self.attn_out, out_amax=self.act_c.amax if fused_amax else None)
+                              out=self.attn_out, out_amax=self.act_c.amax if fused_amax else None, workspace=self.attn_ws)
         # cache write: rotated (un-smoothed) keys and values of the chunk, straight into the slot
         if self.P == 1:
             kv_given = True

@@ -321,11 +321,35 @@ def peer_allreduce_max(vals, slot_ptrs, signal_ptrs, rank, epoch):
 SPLIT_TAIL = -1          # LLNV_ATTN_SPLIT_TAIL: cut the tiles of the last partial wave once (see include/llnvfp4.h)
 
 
-def attention_bf16(q, k, v, heads, scale=None, out=None, key_splits=None, out_amax=None):
+def _attention_workspace(lib, lq, heads, key_splits, workspace, device):
+    """(tensor, bytes) of the partial-result workspace a split or tail-balanced call needs: the caller's ``workspace``
+    (uint8, at least llnv_attention_workspace_bytes) or a fresh allocation."""
+    if not (key_splits > 1 or key_splits == SPLIT_TAIL):
+        return None, 0
+    ws_bytes = lib.llnv_attention_workspace_bytes(lq, heads, key_splits)
+    if workspace is not None:
+        if workspace.dtype != torch.uint8 or not workspace.is_contiguous() or workspace.numel() < ws_bytes or workspace.device != device:
+            raise RuntimeError(f"attention workspace must be a contiguous uint8 tensor of at least {ws_bytes} bytes on the device of q")
+        return workspace, workspace.numel()
+    return torch.empty(ws_bytes, dtype=torch.uint8, device=device), ws_bytes
+
+
+def attention_workspace_bytes(lq, lk, heads, key_splits=None):
+    """Bytes of workspace ``attention_bf16`` / ``attention_nvfp4kv`` use for this shape (0 when the call is not split);
+    ``key_splits`` None = what the library proposes for the current device."""
+    lib = _lib.lib()
+    if key_splits is None:
+        key_splits = lib.llnv_attention_key_splits(lq, lk, heads)
+    return int(lib.llnv_attention_workspace_bytes(lq, heads, key_splits)) if (key_splits > 1 or key_splits == SPLIT_TAIL) else 0
+
+
+def attention_bf16(q, k, v, heads, scale=None, out=None, key_splits=None, out_amax=None, workspace=None):
     """softmax(q k^T * scale) v per head, non-causal.  q: bf16 [Lq, heads*128]; k, v: bf16 [Lk, heads*128]
     (row strides free, unit column stride).  Returns bf16 [Lq, heads*128].  ``key_splits`` > 1 splits
     the key window over several CTAs per query tile (default: what the library proposes for the
-    device, 1 unless the tiles alone leave most SMs idle).  ``out_amax`` (fp32 [1]) receives max |out|."""
+    device, 1 unless the tiles alone leave most SMs idle).  ``out_amax`` (fp32 [1]) receives max |out|.
+    ``workspace``: a uint8 tensor for the partial results of a split call (``attention_workspace_bytes``); allocated
+    per call when omitted."""
     _require_cuda(q, "q")
     for name, t in (("q", q), ("k", k), ("v", v)):
         if t.dim() != 2 or t.dtype != torch.bfloat16 or t.stride(1) != 1 or t.shape[1] != heads * 128:
@@ -340,10 +364,7 @@ def attention_bf16(q, k, v, heads, scale=None, out=None, key_splits=None, out_am
     with torch.cuda.device(q.device):
         if key_splits is None:
             key_splits = lib.llnv_attention_key_splits(q.shape[0], k.shape[0], heads)
-        ws, ws_bytes = None, 0
-        if key_splits > 1 or key_splits == SPLIT_TAIL:
-            ws_bytes = lib.llnv_attention_workspace_bytes(q.shape[0], heads, key_splits)
-            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+        ws, ws_bytes = _attention_workspace(lib, q.shape[0], heads, key_splits, workspace, q.device)
         _check(lib.llnv_attention_bf16_ex(q.data_ptr(), q.shape[0], q.stride(0), k.data_ptr(), v.data_ptr(), k.shape[0],
                                           k.stride(0), v.stride(0), heads, float(scale), out.data_ptr(), out.stride(0),
                                           int(key_splits), ws.data_ptr() if ws is not None else None, ws_bytes,
@@ -352,7 +373,7 @@ def attention_bf16(q, k, v, heads, scale=None, out=None, key_splits=None, out_am
 
 
 def attention_nvfp4kv(q, k_blocks, v_blocks, block_tokens, k_cur, v_cur, heads, scale=None, out=None, key_splits=None,
-                      out_amax=None, e2m1_max=6.0, e4m3_max=256.0):
+                      out_amax=None, e2m1_max=6.0, e4m3_max=256.0, workspace=None):
     """Chunk attention over [cached NVFP4 blocks ... | current chunk (bf16)] without dequantizing the cache to
     memory (``llnv_attention_nvfp4kv``).  ``k_blocks`` / ``v_blocks``: cache blocks oldest first, each with
     ``values`` (uint8 [rows_padded, 64]), ``scale_factors`` and ``amax`` (a ``QuantizedTensor`` of
@@ -389,10 +410,7 @@ def attention_nvfp4kv(q, k_blocks, v_blocks, block_tokens, k_cur, v_cur, heads, 
     with torch.cuda.device(q.device):
         if key_splits is None:
             key_splits = lib.llnv_attention_key_splits(q.shape[0], lk, heads)
-        ws, ws_bytes = None, 0
-        if key_splits > 1 or key_splits == SPLIT_TAIL:
-            ws_bytes = lib.llnv_attention_workspace_bytes(q.shape[0], heads, key_splits)
-            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+        ws, ws_bytes = _attention_workspace(lib, q.shape[0], heads, key_splits, workspace, q.device)
         _check(lib.llnv_attention_nvfp4kv(
             q.data_ptr(), q.shape[0], q.stride(0),
             tab(k_blocks, lambda b: b.values), tab(k_blocks, lambda b: b.scale_factors), tab(k_blocks, lambda b: b.amax),

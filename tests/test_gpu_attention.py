@@ -323,3 +323,20 @@ def test_amax_accumulate_mode_keeps_the_larger_value():
         assert float(amax.item()) == true_max                 # cleared by the caller: the call's own maximum
     finally:
         assert lib.llnv_set_amax_accumulate(0) == 1
+
+
+def test_attention_caller_owned_workspace():
+    """A split call uses the caller's workspace when one is given (same result as with a per-call allocation) and refuses
+    one that is too small."""
+    g = torch.Generator(device="cuda").manual_seed(3)
+    q = torch.randn(300, 256, generator=g, device="cuda").bfloat16()
+    k = torch.randn(1024, 256, generator=g, device="cuda").bfloat16()
+    v = torch.randn(1024, 256, generator=g, device="cuda").bfloat16()
+    need = ops.attention_workspace_bytes(300, 1024, 2, key_splits=4)
+    assert need == 4 * 300 * 2 * 130 * 4 and ops.attention_workspace_bytes(300, 1024, 2, key_splits=1) == 0
+    ws = torch.empty(need + 64, dtype=torch.uint8, device="cuda")
+    a = ops.attention_bf16(q, k, v, 2, key_splits=4, workspace=ws)
+    b = ops.attention_bf16(q, k, v, 2, key_splits=4)
+    assert torch.equal(a, b)
+    with pytest.raises(RuntimeError, match="workspace"):
+        ops.attention_bf16(q, k, v, 2, key_splits=4, workspace=ws[: need - 16])
