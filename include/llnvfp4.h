@@ -218,6 +218,29 @@ int llnv_set_peer_poll_limit(unsigned int max_polls);
 int llnv_peer_allreduce_max(float* vals, int n, void* const* slot_ptrs, void* const* signal_ptrs, int rank, int world,
                             void* epoch, llnv_stream_t stream);
 
+/* Quantizers of a sequence-parallel group that reduce their tensor amax themselves.  Bit-identity with the single-GPU
+ * run needs the MAX of every tensor amax over the ranks before the first block is quantized.  These forms take this
+ * rank's amax in *amax (llnv_quantize_nvfp4_group: written by the producer's epilogue; the adaLN / LayerNorm forms
+ * compute it in their statistics pass) and do the exchange inside the quantize kernel - its first CTA publishes the
+ * value into every rank's slot area and raises this rank's flag, one thread of every CTA waits (bounded by
+ * llnv_set_peer_poll_limit) for all flags and takes the maximum - instead of a separate all-reduce launch in front
+ * of it.  On return *amax holds the group maximum.  slot_ptrs / signal_ptrs / rank / world as in
+ * llnv_peer_allreduce_max; epoch points to TWO zero-initialised device uint32 of this rank (the epoch that
+ * llnv_peer_barrier and llnv_peer_allreduce_max also use, and a counter of finished CTAs).  Every call counts as one
+ * barrier of the group's sequence, so all ranks must issue the same sequence of barrier / all-reduce / group calls.
+ * M must be positive on every rank.  A wait that gives up records LLNV_E_TIMEOUT for llnv_check_status. */
+int llnv_quantize_nvfp4_group(const void* x, int64_t M, int64_t K, int64_t ldx, int rule, void* codes, void* sf, float* amax,
+                              int shards, const void* const* slot_ptrs, const void* const* signal_ptrs, int rank, int world,
+                              void* epoch, llnv_stream_t stream);
+int llnv_adaln_quantize_nvfp4_group(const void* x, int64_t M, int64_t C, int64_t ldx, const void* scale, const void* shift,
+                                    int64_t mod_stride, int frame_rows, float eps, int add_one, int rule, void* codes, void* sf,
+                                    float* amax, float* row_stats, int64_t row_offset, const void* const* slot_ptrs,
+                                    const void* const* signal_ptrs, int rank, int world, void* epoch, llnv_stream_t stream);
+int llnv_layernorm_quantize_nvfp4_group(const void* x, int64_t M, int64_t C, int64_t ldx, const void* weight, const void* bias,
+                                        float eps, int rule, void* codes, void* sf, float* amax, float* row_stats,
+                                        const void* const* slot_ptrs, const void* const* signal_ptrs, int rank, int world,
+                                        void* epoch, llnv_stream_t stream);
+
 /* Dequantize `num_blocks` KV-cache blocks, each an NVFP4 matrix [rows_padded, 128] holding
  * block_token_size*num_heads logical rows (token-major, head-minor), into one contiguous
  * tensor [1, num_blocks*block_token_size, num_heads, 128] of dtype_code.

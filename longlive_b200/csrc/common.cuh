@@ -75,14 +75,34 @@ inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// ---- group maximum over NVLink peer memory, for kernels that consume a tensor amax --------------
+// A sequence-parallel group that wants the single-GPU codes needs the MAX of every tensor amax over its ranks before the
+// quantizer's first block.  Instead of a separate one-warp all-reduce kernel in front of it, the quantize kernel does the
+// exchange itself (quantize.cu): its first CTA publishes this rank's value into every rank's slot array and raises this
+// rank's flag there, thread 0 of every CTA waits (bounded) until all ranks' flags show the current epoch, and takes the
+// maximum of the slots.  Flags, slots and the epoch counter are those of llnv_peer_barrier / llnv_peer_allreduce_max
+// (peer.cu), so the fused form counts as one barrier of the same sequence.  epoch[1] counts the CTAs that are done:
+// the last one stores the group maximum back to the amax scalar, resets the counter and advances the epoch.
+constexpr int kMaxPeers = 8;
+struct PeerReduce {
+  void* slots[kMaxPeers];
+  void* signals[kMaxPeers];
+  int rank, world;             // world <= 1: no exchange
+  unsigned int* epoch;         // [2] device words of this rank: epoch, finished-CTA counter
+  unsigned int max_polls;
+  unsigned int* status;
+};
+unsigned int peer_poll_limit();        // llnv_set_peer_poll_limit
+
 // LayerNorm-family transform fused into the quantizer (quantize.cu).  mode: 1 = adaLN modulation,
 // 2 = affine LayerNorm.  row_stats is a scratch array of 2*M floats; nothing is allocated.
 // row_offset shifts the frame lookup (token shards); phase 0 = statistics + amax + quantize,
 // 1 = statistics + amax only, 2 = quantize only (amax and row_stats as left by phase 1).
+// peer (phase 0 only): MAX-reduce the tensor amax over a sequence-parallel group inside the quantize kernel.
 int ln_quantize_impl(int mode, const void* x, int64_t M, int64_t C, int64_t ldx, const void* p0, const void* p1,
                      int64_t mod_stride, int frame_rows, float eps, int add_one, int rule, void* codes, void* sf,
                      float* amax, void* y_out, int64_t ldy, float* row_stats, cudaStream_t stream, const char* who,
-                     int64_t row_offset, int phase);
+                     int64_t row_offset, int phase, const struct PeerReduce* peer = nullptr);
 
 // ---- scale rule constants -----------------------------------------------------------------
 __host__ __device__ inline float rule_e2m1_max(int rule) { return rule == LLNV_RULE_STATIC_4 ? 4.f : 6.f; }
@@ -98,6 +118,49 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+
+// See PeerReduce.  Called by ONE thread per CTA; `publish` is true in exactly one CTA of the grid.
+__device__ inline float peer_group_max(const PeerReduce& pr, float local, bool publish, unsigned int* epoch_out) {
+  const unsigned int e = *reinterpret_cast<volatile unsigned int*>(pr.epoch) + 1u;
+  *epoch_out = e;
+  const int par = (int)(e & 1u);
+  if (publish) {
+    for (int r = 0; r < pr.world; ++r) {
+      float* theirs = reinterpret_cast<float*>(pr.slots[r]) + ((int64_t)par * kMaxPeers + pr.rank) * 32;
+      asm volatile("st.relaxed.sys.global.f32 [%0], %1;" ::"l"(theirs), "f"(local) : "memory");
+      unsigned int* flag = reinterpret_cast<unsigned int*>(pr.signals[r]) + pr.rank;
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(e) : "memory");
+    }
+  }
+  bool ok = true;
+  for (int r = 0; r < pr.world && ok; ++r) {
+    const unsigned int* mine = reinterpret_cast<const unsigned int*>(pr.signals[pr.rank]) + r;
+    ok = false;
+    for (unsigned int i = 0; i < pr.max_polls; ++i) {
+      unsigned int v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+      if ((int)(v - e) >= 0) {
+        ok = true;
+        break;
+      }
+      // another CTA (or an earlier kernel) has already recorded a failed wait: do not wait it out again
+      if ((i & 1023u) == 1023u && pr.status && *reinterpret_cast<volatile unsigned int*>(pr.status) != 0u) break;
+    }
+    if (!ok && pr.status && atomicCAS(pr.status, 0u, 3u) == 0u) {
+      pr.status[1] = 702u;
+      pr.status[2] = (unsigned int)r;
+      pr.status[3] = e;
+    }
+  }
+  const float* slots = reinterpret_cast<const float*>(pr.slots[pr.rank]) + (int64_t)par * kMaxPeers * 32;
+  float m = local;
+  for (int q = 0; q < pr.world; ++q) {
+    float v;
+    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(slots + q * 32) : "memory");
+    m = fmaxf(m, v);
+  }
+  return m;
+}
 
 // fp32 -> bf16 bits, round to nearest even (finite inputs).
 __device__ __forceinline__ uint32_t f2bf(float f) {

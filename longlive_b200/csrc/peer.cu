@@ -29,7 +29,6 @@ namespace llnv {
 namespace {
 
 constexpr uint32_t kDefaultPeerPolls = 1u << 22;     // a few seconds of polling before giving up
-constexpr int kMaxPeers = 8;
 uint32_t g_peer_polls = kDefaultPeerPolls;
 
 struct PeerPtrs {
@@ -137,6 +136,8 @@ __global__ void __launch_bounds__(256) scatter_2d_kernel(const uint8_t* __restri
 }
 
 }  // namespace
+
+unsigned int peer_poll_limit() { return g_peer_polls; }
 }  // namespace llnv
 
 using namespace llnv;

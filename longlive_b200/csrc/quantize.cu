@@ -90,6 +90,9 @@ struct Prologue {
   const float* amax2;
   uint8_t* codes2;
   uint8_t* sf2;
+  // sequence-parallel group whose ranks' amax values are MAX-reduced inside the quantize kernel before its first block
+  // (world <= 1: none): on entry *amax is this rank's value, on return the group's
+  PeerReduce peer;
 };
 
 // y of two adjacent channels (packed bf16 in, packed bf16 out) with the rounding points listed at Prologue.  Packed
@@ -143,7 +146,17 @@ __global__ void __launch_bounds__(256) quantize_nvfp4_kernel(const uint16_t* x, 
     codes = pr.codes2;
     sf = pr.sf2;
   }
-  const QuantConsts qc = make_consts<RULE>(*amax_ptr);
+  float amax_val = *amax_ptr;
+  unsigned int peer_epoch = 0u;
+  if (pr.peer.world > 1) {
+    __shared__ float amax_sh;
+    __shared__ unsigned int epoch_sh;
+    if (threadIdx.x == 0) amax_sh = peer_group_max(pr.peer, amax_val, (blockIdx.x | blockIdx.y | blockIdx.z) == 0u, &epoch_sh);
+    __syncthreads();
+    amax_val = amax_sh;
+    peer_epoch = epoch_sh;
+  }
+  const QuantConsts qc = make_consts<RULE>(amax_val);
 
   // 256 threads cover 128 x 128 elements, 128 threads 128 x 64 (one scale atom): the narrower CTA
   // is launched for small tensors, whose few wide CTAs would spread unevenly over the SMs
@@ -210,6 +223,18 @@ __global__ void __launch_bounds__(256) quantize_nvfp4_kernel(const uint16_t* x, 
     const int64_t sc = col >> 4;                                   // global scale column
     const int64_t atom = (int64_t)blockIdx.y * (K >> 6) + (sc >> 2);
     *reinterpret_cast<uint32_t*>(sf + atom * 512 + r0 * 16 + q * 4) = word;
+  }
+  if (pr.peer.world > 1 && threadIdx.x == 0) {
+    // The last CTA to get here closes the exchange: every CTA has read the epoch and this rank's value by now, so the
+    // scalar can take the group maximum (the GEMM that consumes this tensor scales with it) and the epoch can advance.
+    const unsigned int total = gridDim.x * gridDim.y * gridDim.z;
+    __threadfence();
+    if (atomicAdd(pr.peer.epoch + 1, 1u) == total - 1u) {
+      *const_cast<float*>(amax_ptr) = amax_val;
+      pr.peer.epoch[1] = 0u;
+      __threadfence();
+      pr.peer.epoch[0] = peer_epoch;
+    }
   }
 }
 
@@ -378,8 +403,9 @@ int launch_quantize(int rule, dim3 grid, cudaStream_t stream, const uint16_t* x,
 int ln_quantize_impl(int mode, const void* x, int64_t M, int64_t C, int64_t ldx, const void* p0, const void* p1,
                      int64_t mod_stride, int frame_rows, float eps, int add_one, int rule, void* codes, void* sf,
                      float* amax, void* y_out, int64_t ldy, float* row_stats, cudaStream_t stream, const char* who,
-                     int64_t row_offset, int phase) {
+                     int64_t row_offset, int phase, const PeerReduce* peer) {
   LLNV_REQUIRE(x && p0 && p1 && amax && row_stats, "%s: null pointer", who);
+  if (peer) LLNV_REQUIRE(phase == 0 && codes && M > 0, "%s: the group form runs both passes on a non-empty shard and writes codes", who);
   LLNV_REQUIRE((codes && sf) || (!codes && !sf && y_out), "%s: codes and sf go together; both may be null only when y_out is wanted", who);
   LLNV_REQUIRE(mode == kAdaLN || mode == kAffineLN, "%s: unknown mode %d", who, mode);
   LLNV_REQUIRE(M >= 0 && C > 0 && C % 64 == 0 && C <= 4096, "%s: C must be a multiple of 64 and at most 4096 (got %lld)", who, (long long)C);
@@ -413,6 +439,7 @@ int ln_quantize_impl(int mode, const void* x, int64_t M, int64_t C, int64_t ldx,
     if (rc != LLNV_OK) return rc;
   }
   if (phase == 1) return LLNV_OK;
+  if (peer) pr.peer = *peer;
   const int64_t mp = (M + 127) / 128 * 128;
   LLNV_REQUIRE(mp / 128 <= 65535, "%s: too many rows (%lld)", who, (long long)M);
   dim3 grid((unsigned)((C + 127) / 128), (unsigned)(mp / 128));
@@ -547,4 +574,72 @@ extern "C" int llnv_selftest_div_const(int divisor, uint32_t first_bits, uint64_
   if (divisor == 6) launch_k(div_const_selftest_kernel<6>, blocks, 256, 0, stream, first_bits, count, mismatches);
   else launch_k(div_const_selftest_kernel<1536>, blocks, 256, 0, stream, first_bits, count, mismatches);
   return launch_status("div_const_selftest_kernel");
+}
+
+namespace {
+// Group description of the C ABI -> PeerReduce.
+int fill_peer(PeerReduce* out, const void* const* slot_ptrs, const void* const* signal_ptrs, int rank, int world, void* epoch, const char* who) {
+  LLNV_REQUIRE(slot_ptrs && signal_ptrs && epoch, "%s: null group pointer", who);
+  LLNV_REQUIRE(world >= 2 && world <= kMaxPeers && rank >= 0 && rank < world, "%s: need 2 <= world <= 8 and 0 <= rank < world", who);
+  LLNV_REQUIRE(((uintptr_t)epoch & 7) == 0, "%s: epoch must be an 8-byte aligned pair of device words", who);
+  *out = PeerReduce{};
+  for (int r = 0; r < world; ++r) {
+    LLNV_REQUIRE(slot_ptrs[r] && signal_ptrs[r] && ((uintptr_t)slot_ptrs[r] & 3) == 0 && ((uintptr_t)signal_ptrs[r] & 3) == 0, "%s: bad pointer of rank %d", who, r);
+    out->slots[r] = const_cast<void*>(slot_ptrs[r]);
+    out->signals[r] = const_cast<void*>(signal_ptrs[r]);
+  }
+  out->rank = rank;
+  out->world = world;
+  out->epoch = (unsigned int*)epoch;
+  out->max_polls = peer_poll_limit();
+  out->status = device_status_word();
+  return LLNV_OK;
+}
+}  // namespace
+
+extern "C" int llnv_quantize_nvfp4_group(const void* x, int64_t M, int64_t K, int64_t ldx, int rule, void* codes, void* sf, float* amax,
+                                         int shards, const void* const* slot_ptrs, const void* const* signal_ptrs, int rank, int world,
+                                         void* epoch, llnv_stream_t stream_) {
+  const char* who = "llnv_quantize_nvfp4_group";
+  cudaStream_t stream = (cudaStream_t)stream_;
+  LLNV_REQUIRE(x && codes && sf && amax, "%s: null pointer", who);
+  LLNV_REQUIRE(M > 0 && K > 0 && K % 64 == 0, "%s: M must be positive and K a positive multiple of 64", who);
+  LLNV_REQUIRE(shards >= 1 && K % shards == 0 && (K / shards) % 16 == 0, "%s: shards must divide K into multiples of 16 columns", who);
+  const int64_t Ks = K / shards;
+  LLNV_REQUIRE(ldx >= Ks && ldx % 8 == 0, "%s: ldx must be >= K / shards and a multiple of 8", who);
+  LLNV_REQUIRE(rule >= 0 && rule <= 4, "%s: unknown scale rule %d", who, rule);
+  LLNV_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)codes & 7) == 0 && ((uintptr_t)sf & 3) == 0, "%s: x must be 16-byte, codes 8-byte, sf 4-byte aligned", who);
+  const int64_t mp = (M + 127) / 128 * 128;
+  LLNV_REQUIRE(mp / 128 <= 65535, "%s: too many rows (%lld)", who, (long long)M);
+  Prologue pr = {};
+  if (shards > 1) {
+    pr.shard_cols = Ks;
+    pr.shard_stride = M * ldx;
+  }
+  const int rc = fill_peer(&pr.peer, slot_ptrs, signal_ptrs, rank, world, epoch, who);
+  if (rc != LLNV_OK) return rc;
+  dim3 grid((unsigned)((K + 127) / 128), (unsigned)(mp / 128));
+  return launch_quantize<kPlain>(rule, grid, stream, (const uint16_t*)x, M, K, ldx, amax, (uint8_t*)codes, (uint8_t*)sf, pr, nullptr, 0);
+}
+
+extern "C" int llnv_adaln_quantize_nvfp4_group(const void* x, int64_t M, int64_t C, int64_t ldx, const void* scale, const void* shift,
+                                               int64_t mod_stride, int frame_rows, float eps, int add_one, int rule, void* codes, void* sf,
+                                               float* amax, float* row_stats, int64_t row_offset, const void* const* slot_ptrs,
+                                               const void* const* signal_ptrs, int rank, int world, void* epoch, llnv_stream_t stream) {
+  PeerReduce peer;
+  const int rc = fill_peer(&peer, slot_ptrs, signal_ptrs, rank, world, epoch, "llnv_adaln_quantize_nvfp4_group");
+  if (rc != LLNV_OK) return rc;
+  return ln_quantize_impl(kAdaLN, x, M, C, ldx, scale, shift, mod_stride, frame_rows, eps, add_one, rule, codes, sf, amax, nullptr, 0,
+                          row_stats, (cudaStream_t)stream, "llnv_adaln_quantize_nvfp4_group", row_offset, 0, &peer);
+}
+
+extern "C" int llnv_layernorm_quantize_nvfp4_group(const void* x, int64_t M, int64_t C, int64_t ldx, const void* weight, const void* bias,
+                                                   float eps, int rule, void* codes, void* sf, float* amax, float* row_stats,
+                                                   const void* const* slot_ptrs, const void* const* signal_ptrs, int rank, int world,
+                                                   void* epoch, llnv_stream_t stream) {
+  PeerReduce peer;
+  const int rc = fill_peer(&peer, slot_ptrs, signal_ptrs, rank, world, epoch, "llnv_layernorm_quantize_nvfp4_group");
+  if (rc != LLNV_OK) return rc;
+  return ln_quantize_impl(kAffineLN, x, M, C, ldx, weight, bias, 0, 1, eps, 0, rule, codes, sf, amax, nullptr, 0, row_stats,
+                          (cudaStream_t)stream, "llnv_layernorm_quantize_nvfp4_group", 0, 0, &peer);
 }

@@ -357,6 +357,10 @@ class CausalDiT:
             if self.sync_amax:
                 if not have_local_amax:
                     ops.amax_bf16(x if x.dim() == 2 else x.view(-1, x.shape[-1]), act.amax)
+                if self.arena is not None:
+                    # the quantize kernel reduces the amax over the group itself (no separate all-reduce launch)
+                    ops.quantize_nvfp4(x, MSE, act.amax, act.codes, act.sf, amax_given=True, group=self.arena)
+                    return
                 self._allreduce_max(act.amax)
                 amax_given = True
             elif have_local_amax:
@@ -366,7 +370,9 @@ class CausalDiT:
     def _adaln_quantize(self, x, scale, shift, act: _Act, add_one: bool = True):
         cfg = self.cfg
         kw = dict(codes=act.codes, sf=act.sf, amax=act.amax, row_stats=self.row_stats, row_offset=self.rank * self.Sl, add_one=add_one)
-        if self.sync_amax:
+        if self.sync_amax and self.arena is not None:
+            ops.adaln_quantize_nvfp4(x, scale, shift, cfg.frame_tokens, MSE, cfg.eps, group=self.arena, **kw)
+        elif self.sync_amax:
             ops.adaln_quantize_nvfp4(x, scale, shift, cfg.frame_tokens, MSE, cfg.eps, phase=1, **kw)
             self._allreduce_max(act.amax)
             ops.adaln_quantize_nvfp4(x, scale, shift, cfg.frame_tokens, MSE, cfg.eps, phase=2, **kw)
@@ -375,7 +381,9 @@ class CausalDiT:
 
     def _ln_quantize(self, x, w, b, act: _Act):
         kw = dict(codes=act.codes, sf=act.sf, amax=act.amax, row_stats=self.row_stats)
-        if self.sync_amax:
+        if self.sync_amax and self.arena is not None:
+            ops.layernorm_quantize_nvfp4(x, w, b, MSE, self.cfg.eps, group=self.arena, **kw)
+        elif self.sync_amax:
             ops.layernorm_quantize_nvfp4(x, w, b, MSE, self.cfg.eps, phase=1, **kw)
             self._allreduce_max(act.amax)
             ops.layernorm_quantize_nvfp4(x, w, b, MSE, self.cfg.eps, phase=2, **kw)
@@ -584,9 +592,10 @@ class CausalDiT:
         if not self._amax_prezeroed:
             self.act_f.amax.zero_()
         self._gemm(self.act_c, Sl, blk.ffn0, self.hidden, act=1, out_amax=self.act_f.amax)
-        if self.sync_amax:
+        group = self.arena if self.sync_amax else None
+        if self.sync_amax and group is None:
             self._allreduce_max(self.act_f.amax)
-        ops.quantize_nvfp4(self.hidden, MSE, self.act_f.amax, self.act_f.codes, self.act_f.sf, amax_given=True)
+        ops.quantize_nvfp4(self.hidden, MSE, self.act_f.amax, self.act_f.codes, self.act_f.sf, amax_given=True, group=group)
         self._gemm(self.act_f, Sl, blk.ffn2, x_out, residual=x2, gate=e[:, 5], frame_rows=ft, row_offset=roff)
         if self.ffn_requant == "single_pass":
             self.ffn_amax_use[li:li + 1].copy_(self.act_f.amax)      # calibration: the first forward runs the two-pass form

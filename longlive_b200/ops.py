@@ -57,8 +57,14 @@ def amax_bf16(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     return out
 
 
+def _group_args(group):
+    """(slot pointer table, signal pointer table, rank, world, epoch pointer) of a peer arena (``sp.PeerArena``)."""
+    return (_ptr_table([b + group.SIGNAL_BYTES for b in group.base]), _ptr_table(group.base), group.rank, group.world,
+            group.epoch.data_ptr())
+
+
 def quantize_nvfp4(x: torch.Tensor, rule_id: int, amax: torch.Tensor | None = None, codes=None, sf=None,
-                   amax_given: bool | None = None):
+                   amax_given: bool | None = None, group=None):
     """bf16 [M, K] (K % 64 == 0, unit column stride) -> (codes [Mp, K/2] u8, sf [Mp*K/16] e4m3, amax [1] f32).
 
     A contiguous 3-D ``x`` [shards, M, K / shards] is read as the column-sharded form of the [M, K]
@@ -67,6 +73,8 @@ def quantize_nvfp4(x: torch.Tensor, rule_id: int, amax: torch.Tensor | None = No
     ``amax`` is the fp32 tensor-scale buffer.  With ``amax_given`` (default: true when a buffer is
     passed) it is read as the scale; otherwise it is computed on the device into that buffer (or a
     new one).  ``codes`` / ``sf`` may be preallocated slot buffers (KV cache) written in place.
+    ``group`` (a ``sp.PeerArena``): ``amax`` holds this rank's amax of its shard; the quantize kernel MAX-reduces it over
+    the group before its first block and leaves the group maximum in ``amax`` (``llnv_quantize_nvfp4_group``).
     """
     _require_cuda(x, "x")
     shards = 1
@@ -91,8 +99,14 @@ def quantize_nvfp4(x: torch.Tensor, rule_id: int, amax: torch.Tensor | None = No
             raise ValueError("amax_given needs an amax tensor")
         amax = torch.empty(1, dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
-        _check(_lib.lib().llnv_quantize_nvfp4_ex(x.data_ptr(), m, k, ldx, rule_id, codes.data_ptr(), sf.data_ptr(),
-                                                 amax.data_ptr(), 1 if given else 0, shards, _stream(x)))
+        if group is not None:
+            if not given:
+                raise ValueError("the group form needs this rank's amax in `amax`")
+            _check(_lib.lib().llnv_quantize_nvfp4_group(x.data_ptr(), m, k, ldx, rule_id, codes.data_ptr(), sf.data_ptr(),
+                                                        amax.data_ptr(), shards, *_group_args(group), _stream(x)))
+        else:
+            _check(_lib.lib().llnv_quantize_nvfp4_ex(x.data_ptr(), m, k, ldx, rule_id, codes.data_ptr(), sf.data_ptr(),
+                                                     amax.data_ptr(), 1 if given else 0, shards, _stream(x)))
     return codes, sf, amax
 
 
@@ -108,11 +122,12 @@ def _quant_outputs(x, m, c, codes, sf, amax):
 
 
 def adaln_quantize_nvfp4(x, scale, shift, frame_rows, rule_id, eps=1e-6, add_one=True, *, want_y=False, codes=None,
-                         sf=None, amax=None, row_stats=None, row_offset=0, phase=0, y_only=False):
+                         sf=None, amax=None, row_stats=None, row_offset=0, phase=0, y_only=False, group=None):
     """LayerNorm(no affine) -> (1 + scale[f]) * x + shift[f] (bf16 rounding points of the reference)
     fused with the NVFP4 quantize of the result.  x: bf16 [M, C]; scale/shift: bf16 [F, C] views
     (row stride free).  Returns (codes, sf, amax, y or None); with ``y_only`` nothing is quantized
-    (codes and sf are None) and only y is produced."""
+    (codes and sf are None) and only y is produced.  ``group`` (a ``sp.PeerArena``): the tensor amax is MAX-reduced
+    over the group inside the quantize kernel (``llnv_adaln_quantize_nvfp4_group``)."""
     _require_cuda(x, "x")
     if x.dim() != 2 or x.dtype != torch.bfloat16 or x.stride(1) != 1:
         raise RuntimeError("adaln_quantize_nvfp4 expects a 2-D bfloat16 tensor with unit column stride")
@@ -127,6 +142,15 @@ def adaln_quantize_nvfp4(x, scale, shift, frame_rows, rule_id, eps=1e-6, add_one
     if row_stats is None:
         row_stats = torch.empty(2 * max(m, 1), dtype=torch.float32, device=x.device)
     y = torch.empty((m, c), dtype=torch.bfloat16, device=x.device) if want_y else None
+    if group is not None:
+        if want_y or phase != 0:
+            raise ValueError("the group form runs both passes and produces no y")
+        with torch.cuda.device(x.device):
+            _check(_lib.lib().llnv_adaln_quantize_nvfp4_group(
+                x.data_ptr(), m, c, x.stride(0), scale.data_ptr(), shift.data_ptr(), scale.stride(0), int(frame_rows), float(eps),
+                1 if add_one else 0, rule_id, codes.data_ptr(), sf.data_ptr(), amax.data_ptr(), row_stats.data_ptr(), int(row_offset),
+                *_group_args(group), _stream(x)))
+        return codes, sf, amax, None
     with torch.cuda.device(x.device):
         _check(_lib.lib().llnv_adaln_quantize_nvfp4_ex(
             x.data_ptr(), m, c, x.stride(0), scale.data_ptr(), shift.data_ptr(), scale.stride(0), int(frame_rows), float(eps),
@@ -137,8 +161,9 @@ def adaln_quantize_nvfp4(x, scale, shift, frame_rows, rule_id, eps=1e-6, add_one
 
 
 def layernorm_quantize_nvfp4(x, weight, bias, rule_id, eps=1e-6, *, want_y=False, codes=None, sf=None, amax=None,
-                             row_stats=None, phase=0):
-    """Affine LayerNorm fused with the NVFP4 quantize of its output.  Returns (codes, sf, amax, y or None)."""
+                             row_stats=None, phase=0, group=None):
+    """Affine LayerNorm fused with the NVFP4 quantize of its output.  Returns (codes, sf, amax, y or None).
+    ``group`` (a ``sp.PeerArena``): the tensor amax is MAX-reduced over the group inside the quantize kernel."""
     _require_cuda(x, "x")
     if x.dim() != 2 or x.dtype != torch.bfloat16 or x.stride(1) != 1:
         raise RuntimeError("layernorm_quantize_nvfp4 expects a 2-D bfloat16 tensor with unit column stride")
@@ -147,6 +172,14 @@ def layernorm_quantize_nvfp4(x, weight, bias, rule_id, eps=1e-6, *, want_y=False
     if row_stats is None:
         row_stats = torch.empty(2 * max(m, 1), dtype=torch.float32, device=x.device)
     y = torch.empty((m, c), dtype=torch.bfloat16, device=x.device) if want_y else None
+    if group is not None:
+        if want_y or phase != 0:
+            raise ValueError("the group form runs both passes and produces no y")
+        with torch.cuda.device(x.device):
+            _check(_lib.lib().llnv_layernorm_quantize_nvfp4_group(
+                x.data_ptr(), m, c, x.stride(0), weight.data_ptr(), bias.data_ptr(), float(eps), rule_id, codes.data_ptr(),
+                sf.data_ptr(), amax.data_ptr(), row_stats.data_ptr(), *_group_args(group), _stream(x)))
+        return codes, sf, amax, None
     with torch.cuda.device(x.device):
         _check(_lib.lib().llnv_layernorm_quantize_nvfp4_ex(
             x.data_ptr(), m, c, x.stride(0), weight.data_ptr(), bias.data_ptr(), float(eps), rule_id, codes.data_ptr(),

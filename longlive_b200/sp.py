@@ -123,7 +123,7 @@ class PeerArena:
         self.buf.zero_()
         self.handle = symm_mem.rendezvous(self.buf, group.group_name)
         self.base = [int(p) for p in self.handle.buffer_ptrs]
-        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        self.epoch = torch.zeros(2, dtype=torch.int32, device=device)      # [epoch, finished-CTA counter of the group quantizers]
         torch.cuda.synchronize(device)
         dist.barrier(group)                     # every rank's flags are zero before anyone signals
 

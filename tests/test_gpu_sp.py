@@ -120,3 +120,55 @@ def test_peer_barrier_gives_up_and_reports_timeout():
     ops.peer_barrier([mine.data_ptr()], 0, epoch)
     ops.check_status(dev)
     assert torch.equal(torch.ones(4, device=dev) * 2, torch.full((4,), 2.0, device=dev))
+
+
+class _FakeArena:
+    """What ``ops._group_args`` reads of a ``sp.PeerArena``, on local buffers: ``base[r]`` is rank r's area, the signal
+    flags first, the value slots ``SIGNAL_BYTES`` further."""
+    SIGNAL_BYTES = 256
+
+    def __init__(self, areas, rank, epoch):
+        self.base = [a.data_ptr() for a in areas]
+        self.rank, self.world, self.epoch = rank, len(areas), epoch
+
+
+def test_group_quantizer_on_one_gpu_with_a_played_peer_and_with_a_missing_one():
+    """llnv_quantize_nvfp4_group on one GPU.  (1) World of two in which the test plays rank 1 beforehand: it stores rank 1's
+    amax into rank 0's slot and raises rank 1's flag for the coming epoch, so rank 0's kernel finds the exchange complete:
+    codes and scales must be those of the standalone quantizer under max(own, peer) amax, the amax scalar must hold that
+    maximum afterwards, the epoch must have advanced and the CTA counter be back at zero.  (2) Nobody plays rank 1 and the
+    poll limit is short: the kernel returns by itself and the status word reports the timeout (where 702)."""
+    from longlive_b200 import _lib, ops
+    lib = _lib.lib()
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(11)
+    x = torch.randn(300, 512, generator=g, device=dev).bfloat16()
+    own = x.float().abs().max().reshape(1)
+    area0 = torch.zeros(256 // 4 + 2 * 8 * 32, dtype=torch.float32, device=dev)      # flags (as int32 bits) + slots
+    area1 = torch.zeros_like(area0)
+    epoch = torch.zeros(2, dtype=torch.int32, device=dev)
+    arena = _FakeArena([area0, area1], 0, epoch)
+    ops.check_status(dev)
+    for peer_amax in (float(own.item()) * 2.0, float(own.item()) * 0.5):
+        e = int(epoch[0].item()) + 1
+        area0[64 + ((e & 1) * 8 + 1) * 32] = peer_amax                 # slot [parity][rank 1][0] of rank 0's area
+        area0.view(torch.int32)[1] = e                                # rank 1's flag in rank 0's signal area
+        amax = own.clone()
+        codes, sf, _ = ops.quantize_nvfp4(x, 3, amax, amax_given=True, group=arena)
+        torch.cuda.synchronize()
+        ops.check_status(dev)
+        want = torch.tensor([max(float(own.item()), peer_amax)], device=dev)
+        ref_codes, ref_sf, _ = ops.quantize_nvfp4(x, 3, want.clone(), amax_given=True)
+        assert torch.equal(amax, want) and torch.equal(codes, ref_codes) and torch.equal(sf.view(torch.uint8), ref_sf.view(torch.uint8))
+        assert epoch.tolist() == [e, 0]
+        assert int(area1.view(torch.int32)[0].item()) == e            # rank 0 raised its flag in rank 1's area ...
+        assert float(area1[64 + ((e & 1) * 8 + 0) * 32].item()) == float(own.item())     # ... after publishing its value there
+    lib.llnv_set_peer_poll_limit(20000)
+    try:
+        amax = own.clone()
+        ops.quantize_nvfp4(x, 3, amax, amax_given=True, group=arena)
+        with pytest.raises(ops.DeviceTimeout, match="code=3 where=702"):
+            ops.check_status(dev)
+        ops.check_status(dev)
+    finally:
+        lib.llnv_set_peer_poll_limit(0)
