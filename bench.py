@@ -80,6 +80,29 @@ def load_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
+_REAL_STDOUT = None
+
+
+def quiet_stdout():
+    """Point file descriptor 1 at stderr for the rest of the run, so that whatever libraries print on their own (NCCL's
+    version banner, for one) cannot get between the caller and the ONE JSON line; `emit` writes that line to the real stdout."""
+    global _REAL_STDOUT
+    if _REAL_STDOUT is None:
+        sys.stdout.flush()
+        _REAL_STDOUT = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    text = (json.dumps(line) + "\n").encode()
+    if _REAL_STDOUT is None:
+        sys.stdout.write(text.decode())
+        sys.stdout.flush()
+    else:
+        sys.stdout.flush()
+        os.write(_REAL_STDOUT, text)
+
+
 def dram_traffic(kernel: str, shape: str):
     """DRAM read+write bytes per launch from the committed ncu summaries (profiles/dram_traffic.md: one row per
     captured kernel and shape).  None when no capture of that shape is committed."""
@@ -231,7 +254,7 @@ def run_reference_arm(args):
                          "sample": vals[0][3] + f"; {vals[0][1]:.1f} s per block call"},
         "e2e": {"value": value, "unit": "frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -618,7 +641,7 @@ def run_gpu_arm(args):
             fps, dt, chunk_s, desc = cpu_chunk_fps(1)
             line["cpu_baseline"] = {"value": fps, "unit": "frames/s", "cores": os.cpu_count() or 1, "kind": "port",
                                     "sample": desc + f"; {dt:.1f} s per block call -> {chunk_s:.0f} s per chunk"}
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -838,7 +861,7 @@ def main():
     ap.add_argument("--rollout-chunks", type=int, default=80, help="chunks of the from-empty rollout (80 = 240 latent frames)")
     ap.add_argument("--ffn-requant", default="two_pass", choices=["two_pass", "single_pass"],
                     help="two_pass = the reference's rounding (default); single_pass = the FFN-up GEMM quantizes its own output under the "
-                         "previous forward's tensor amax (faster, not the reference's rounding)")
+                         "previous forward's tensor amax (not the reference's rounding, and measured slower)")
     ap.add_argument("--eager", action="store_true", help="launch every kernel eagerly instead of replaying CUDA graphs")
     ap.add_argument("--per-shard-scales", action="store_true",
                     help="N > 1: every rank quantizes its token shard with its own tensor scale (what the reference's "
@@ -847,6 +870,7 @@ def main():
     if args.kernel_case:
         run_kernel_case(args.kernel_case, args.iters)
         return
+    quiet_stdout()
     if args.impl == "reference":
         run_reference_arm(args)
     else:
