@@ -79,8 +79,8 @@ inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
 // A sequence-parallel group that wants the single-GPU codes needs the MAX of every tensor amax over its ranks before the
 // quantizer's first block.  Instead of a separate one-warp all-reduce kernel in front of it, the quantize kernel does the
 // exchange itself (quantize.cu): its first CTA publishes this rank's value into every rank's slot array and raises this
-// rank's flag there, thread 0 of every CTA waits (bounded) until all ranks' flags show the current epoch, and takes the
-// maximum of the slots.  Flags, slots and the epoch counter are those of llnv_peer_barrier / llnv_peer_allreduce_max
+// rank's flag there, one warp of every CTA waits (bounded; lane r on rank r's flag) until all ranks' flags show the current
+// epoch, and takes the maximum of the slots.  Flags, slots and the epoch counter are those of llnv_peer_barrier / llnv_peer_allreduce_max
 // (peer.cu), so the fused form counts as one barrier of the same sequence.  epoch[1] counts the CTAs that are done:
 // the last one stores the group maximum back to the amax scalar, resets the counter and advances the epoch.
 constexpr int kMaxPeers = 8;
@@ -119,23 +119,24 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
 
-// See PeerReduce.  Called by ONE thread per CTA; `publish` is true in exactly one CTA of the grid.
+// See PeerReduce.  Called by the 32 lanes of ONE warp per CTA (lane r talks to rank r, so that the waits on the `world`
+// flags overlap instead of queueing behind one another); `publish` is true in exactly one CTA of the grid.  Every lane
+// returns the group maximum; lane 0 also returns the epoch of the exchange through epoch_out.
 __device__ inline float peer_group_max(const PeerReduce& pr, float local, bool publish, unsigned int* epoch_out) {
+  const int r = (int)(threadIdx.x & 31u);
   const unsigned int e = *reinterpret_cast<volatile unsigned int*>(pr.epoch) + 1u;
-  *epoch_out = e;
+  if (r == 0) *epoch_out = e;
   const int par = (int)(e & 1u);
-  if (publish) {
-    for (int r = 0; r < pr.world; ++r) {
+  float m = local;
+  if (r < pr.world) {
+    if (publish) {
       float* theirs = reinterpret_cast<float*>(pr.slots[r]) + ((int64_t)par * kMaxPeers + pr.rank) * 32;
       asm volatile("st.relaxed.sys.global.f32 [%0], %1;" ::"l"(theirs), "f"(local) : "memory");
       unsigned int* flag = reinterpret_cast<unsigned int*>(pr.signals[r]) + pr.rank;
       asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(e) : "memory");
     }
-  }
-  bool ok = true;
-  for (int r = 0; r < pr.world && ok; ++r) {
     const unsigned int* mine = reinterpret_cast<const unsigned int*>(pr.signals[pr.rank]) + r;
-    ok = false;
+    bool ok = false;
     for (unsigned int i = 0; i < pr.max_polls; ++i) {
       unsigned int v;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
@@ -151,14 +152,14 @@ __device__ inline float peer_group_max(const PeerReduce& pr, float local, bool p
       pr.status[2] = (unsigned int)r;
       pr.status[3] = e;
     }
-  }
-  const float* slots = reinterpret_cast<const float*>(pr.slots[pr.rank]) + (int64_t)par * kMaxPeers * 32;
-  float m = local;
-  for (int q = 0; q < pr.world; ++q) {
+    // rank r's value in my slot area (its flag, acquired above, was raised after the value was stored)
+    const float* slot = reinterpret_cast<const float*>(pr.slots[pr.rank]) + ((int64_t)par * kMaxPeers + r) * 32;
     float v;
-    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(slots + q * 32) : "memory");
+    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(slot) : "memory");
     m = fmaxf(m, v);
   }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
   return m;
 }
 

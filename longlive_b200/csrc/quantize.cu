@@ -151,7 +151,10 @@ __global__ void __launch_bounds__(256) quantize_nvfp4_kernel(const uint16_t* x, 
   if (pr.peer.world > 1) {
     __shared__ float amax_sh;
     __shared__ unsigned int epoch_sh;
-    if (threadIdx.x == 0) amax_sh = peer_group_max(pr.peer, amax_val, (blockIdx.x | blockIdx.y | blockIdx.z) == 0u, &epoch_sh);
+    if (threadIdx.x < 32) {
+      const float m = peer_group_max(pr.peer, amax_val, (blockIdx.x | blockIdx.y | blockIdx.z) == 0u, &epoch_sh);
+      if (threadIdx.x == 0) amax_sh = m;
+    }
     __syncthreads();
     amax_val = amax_sh;
     peer_epoch = epoch_sh;
