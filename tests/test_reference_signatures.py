@@ -9,7 +9,9 @@ import sys
 
 import pytest
 
-REF = os.environ.get("LONGLIVE_REFERENCE", "/root/reference")
+# the reference checkout: $LONGLIVE_REFERENCE, else a directory "reference" beside this repository
+REF = os.environ.get("LONGLIVE_REFERENCE") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "fouroversix", "src")), reason="reference checkout not mounted")
 
 
