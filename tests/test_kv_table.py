@@ -132,3 +132,41 @@ def test_versions_and_errors():
     with pytest.raises(ValueError):
         KVCache(DiTConfig(dim=128, ffn_dim=256, heads=1, layers=1, grid_h=2, grid_w=2, frames_per_chunk=3, window_frames=9,
                           sink_frames=2, in_channels=4), 1, torch.device("cpu"))
+
+
+def test_block_amax_scalars_are_views_of_one_array():
+    """Every cache block's tensor amax lives in KVCache.amax_pool[layer, slot, K / V]: writing a block's scalar shows in the
+    array, and clearing one slot column of the array clears exactly that slot's K and V scalars of every layer (what a
+    forward does with one fill before the producers accumulate into them)."""
+    cfg = DiTConfig(dim=256, ffn_dim=256, heads=2, layers=3, text_len=128, grid_h=6, grid_w=8, frames_per_chunk=3, window_frames=9,
+                    sink_frames=3, in_channels=4)
+    cache = KVCache(cfg, local_heads=2, device="cpu")
+    assert tuple(cache.amax_pool.shape) == (3, 3, 2)
+    for layer in range(3):
+        for slot in range(3):
+            cache.k[layer][slot].amax.fill_(10 * layer + slot + 0.25)
+            cache.v[layer][slot].amax.fill_(10 * layer + slot + 0.5)
+            assert cache.k[layer][slot].amax.shape == (1,) and cache.v[layer][slot].amax.shape == (1,)
+    assert float(cache.amax_pool[2, 1, 0]) == 21.25 and float(cache.amax_pool[1, 2, 1]) == 12.5
+    cache.amax_pool[:, 1].zero_()
+    for layer in range(3):
+        assert float(cache.k[layer][1].amax) == 0.0 and float(cache.v[layer][1].amax) == 0.0
+        assert float(cache.k[layer][0].amax) == 10 * layer + 0.25 and float(cache.v[layer][2].amax) == 10 * layer + 2.5
+    # [k, v] of one block are adjacent: the pair a sequence-parallel group reduces in place
+    pair = cache.amax_pool[1, 0]
+    assert pair.is_contiguous() and pair.data_ptr() == cache.k[1][0].amax.data_ptr() and pair.data_ptr() + 4 == cache.v[1][0].amax.data_ptr()
+
+
+def test_fold_scales_forms_one_plus_scale_once():
+    """CausalDiT._fold_scales: rows 1 and 4 of every block's modulation become bf16(1 + scale) (fp32 add, one rounding, as the
+    adaLN kernel forms it per element with add_one = 1); shifts and gates are untouched and the input is not modified."""
+    from longlive_b200.dit import CausalDiT
+    g = torch.Generator().manual_seed(1)
+    em = (torch.randn(2, 3, 6, 64, generator=g) * 0.3).bfloat16()
+    keep = em.clone()
+    out = CausalDiT._fold_scales(em)
+    assert torch.equal(em, keep)
+    for row in (1, 4):
+        assert torch.equal(out[:, :, row], (keep[:, :, row].float() + 1.0).bfloat16())
+    for row in (0, 2, 3, 5):
+        assert torch.equal(out[:, :, row], keep[:, :, row])
