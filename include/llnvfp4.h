@@ -388,6 +388,14 @@ int llnv_gemm_nvfp4_ex(const void* a_codes, const void* a_sf, const float* a_ama
  * llnv_amax_bf16 and llnv_quantize_nvfp4 (amax_given = 0) always clear theirs. */
 int llnv_set_amax_accumulate(int on);
 
+/* llnv_quantize_nvfp4 for fp16 input (x: IEEE half, row stride ldx elements): the reference's CUDA backend takes fp16
+ * activations beside bf16 (fouroversix/src/fouroversix/quantize/cuda/backend.py:45-51, csrc/quantize/fp4_quant.cu:205-227).
+ * Same outputs, layouts and bit-exactness against the reference's PyTorch quantizer on the values widened to fp32; every
+ * block is evaluated with the reference's fp32 arithmetic one operation at a time (no packed fast path), so it is the
+ * slower of the two.  The DiT path is bf16 throughout. */
+int llnv_quantize_nvfp4_f16(const void* x, int64_t M, int64_t K, int64_t ldx, int rule, void* codes, void* sf,
+                            float* amax, int amax_given, llnv_stream_t stream);
+
 /* Measurement aid, not part of the reference's interface: one CTA per SM issues k_blocks x 4 block-scaled FP4
  * MMAs (128 x 256 x 64, the GEMM's instruction shape) on operands that stay in shared memory, with no loads,
  * scale refills or epilogue.  *flop_out (may be NULL) receives the flop of the launch; time the launch with

@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(_PKG, "libllnvfp4.so")
 EXPORTS = [
     "llnv_version", "llnv_last_error", "llnv_check_status", "llnv_amax_bf16", "llnv_quantize_nvfp4",
     "llnv_kv_dequant", "llnv_dequantize_nvfp4", "llnv_gemm_nvfp4", "llnv_gemm_nvfp4_grouped", "llnv_adaln_quantize_nvfp4",
-    "llnv_layernorm_quantize_nvfp4", "llnv_gemm_nvfp4_ex", "llnv_attention_nvfp4kv", "llnv_init_device", "llnv_launch_count", "llnv_set_peer_poll_limit", "llnv_selftest_div_const", "llnv_fp4_mma_rate", "llnv_set_amax_accumulate", "llnv_quantize_nvfp4_group", "llnv_adaln_quantize_nvfp4_group", "llnv_layernorm_quantize_nvfp4_group",
+    "llnv_layernorm_quantize_nvfp4", "llnv_gemm_nvfp4_ex", "llnv_attention_nvfp4kv", "llnv_init_device", "llnv_launch_count", "llnv_set_peer_poll_limit", "llnv_selftest_div_const", "llnv_fp4_mma_rate", "llnv_set_amax_accumulate", "llnv_quantize_nvfp4_f16", "llnv_quantize_nvfp4_group", "llnv_adaln_quantize_nvfp4_group", "llnv_layernorm_quantize_nvfp4_group",
     "llnv_adaln_quantize_nvfp4_static", "llnv_static_max_rows", "llnv_rmsnorm_rope", "llnv_attention_bf16", "llnv_attention_bf16_ex", "llnv_quantize_nvfp4_ex", "llnv_quantize_nvfp4_pair", "llnv_rmsnorm_rope_ex", "llnv_rmsnorm_rope_scatter", "llnv_rmsnorm_rope_qk", "llnv_scatter_2d", "llnv_peer_barrier", "llnv_peer_allreduce_max", "llnv_attention_key_splits", "llnv_attention_workspace_bytes", "llnv_adaln_quantize_nvfp4_ex", "llnv_layernorm_quantize_nvfp4_ex", "llnv_unipc_step", "llnv_set_pdl", "llnv_linear_bf16", "llnv_patchify", "llnv_unpatchify",
 ]
 
@@ -62,6 +62,7 @@ def lib() -> C.CDLL:
         l.llnv_layernorm_quantize_nvfp4.argtypes = [p, i64, i64, i64, p, p, f32, i32, p, p, p, p, i64, p, p]
         l.llnv_fp4_mma_rate.argtypes = [i32, p, p]
         l.llnv_set_amax_accumulate.argtypes = [i32]
+        l.llnv_quantize_nvfp4_f16.argtypes = [p, i64, i64, i64, i32, p, p, p, i32, p]
         l.llnv_quantize_nvfp4_group.argtypes = [p, i64, i64, i64, i32, p, p, p, i32, p, p, i32, i32, p, p]
         l.llnv_adaln_quantize_nvfp4_group.argtypes = [p, i64, i64, i64, p, p, i64, i32, f32, i32, i32, p, p, p, p, i64, p, p, i32, i32, p, p]
         l.llnv_layernorm_quantize_nvfp4_group.argtypes = [p, i64, i64, i64, p, p, f32, i32, p, p, p, p, p, p, i32, i32, p, p]

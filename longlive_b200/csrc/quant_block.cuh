@@ -6,6 +6,7 @@
 #pragma once
 
 #include <cuda_fp4.h>
+#include <cuda_fp16.h>
 
 #include "common.cuh"
 
@@ -103,17 +104,10 @@ __device__ __noinline__ void candidate_slow(const float (&x)[16], float s, float
   }
 }
 
-// x[16] is indexed with run-time i in candidate_slow: keep it out of the fast path's registers
+// The reference's arithmetic on 16 fp32 values (whatever type they were loaded from), operation by operation.
 template <int RULE>
-__device__ __noinline__ void quant_block_slow(const uint32_t (&w)[8], const QuantConsts& qc, float hp, uint32_t& c_lo,
-                                              uint32_t& c_hi, uint32_t& sf_out) {
-  float x[16];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    x[2 * j] = bf16_lo(w[j]);
-    x[2 * j + 1] = bf16_hi(w[j]);
-  }
-  // regroup so that x[i] / x[i+8] pair up as in the error sum: element order is preserved
+__device__ __forceinline__ void quant_block_slow_f(const float (&x)[16], const QuantConsts& qc, float hp, uint32_t& c_lo,
+                                                   uint32_t& c_hi, uint32_t& sf_out) {
   const uint32_t sc6 = float_to_e4m3(hp);
   const float s6 = e4m3_to_float(sc6);
   const float inv6 = s6 != 0.f ? __fdiv_rn(1.f, __fmul_rn(qc.dec, s6)) : 0.f;
@@ -134,6 +128,40 @@ __device__ __noinline__ void quant_block_slow(const uint32_t (&w)[8], const Quan
   c_lo = sel4 ? l4 : l6;
   c_hi = sel4 ? h4 : h6;
   sf_out = sel4 ? sc4 : sc6;
+}
+
+// x[16] is indexed with run-time i in candidate_slow: keep it out of the fast path's registers
+template <int RULE>
+__device__ __noinline__ void quant_block_slow(const uint32_t (&w)[8], const QuantConsts& qc, float hp, uint32_t& c_lo,
+                                              uint32_t& c_hi, uint32_t& sf_out) {
+  float x[16];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    x[2 * j] = bf16_lo(w[j]);
+    x[2 * j + 1] = bf16_hi(w[j]);
+  }
+  quant_block_slow_f<RULE>(x, qc, hp, c_lo, c_hi, sf_out);
+}
+
+// One 16-element block of fp16 input (w: 8 words of packed halves): the values go through the reference's arithmetic as
+// fp32, one operation at a time (the packed fast path below relies on bf16 inputs: a tensor amax of at most 8 significant
+// bits makes several of its products exact, which an fp16 tensor does not give).  The reference's CUDA backend takes
+// fp16 activations as well as bf16 (fouroversix/src/fouroversix/quantize/cuda/backend.py:45-51).
+template <int RULE>
+__device__ __noinline__ void quant_block_f16(const uint32_t (&w)[8], const QuantConsts& qc, uint32_t& c_lo, uint32_t& c_hi,
+                                             uint32_t& sf_out) {
+  float x[16];
+  float bmax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+    x[2 * j] = f.x;
+    x[2 * j + 1] = f.y;
+    bmax = fmaxf(bmax, fmaxf(fabsf(f.x), fabsf(f.y)));
+  }
+  if (bmax == 0.f || qc.amax == 0.f) { c_lo = c_hi = 0u; sf_out = 0u; return; }
+  const float hp = RULE == LLNV_RULE_STATIC_4 ? __fmul_rn(__fmul_rn(bmax, 0.25f), qc.enc) : __fmul_rn(__fdiv_rn(bmax, 6.f), qc.enc);
+  quant_block_slow_f<RULE>(x, qc, hp, c_lo, c_hi, sf_out);
 }
 
 // One 16-element block.  w: 8 words of packed bf16 (element 2j in the low half of w[j]).

@@ -39,8 +39,10 @@ namespace {
 using namespace quant;
 
 // ---- tensor amax ----------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) amax_bf16_kernel(const uint16_t* __restrict__ x, int64_t M, int64_t K,
-                                                        int64_t ldx, float* __restrict__ amax) {
+// (F16: the 16-bit values are fp16; their magnitudes order as integers too, only the final conversion differs)
+template <bool F16>
+__global__ void __launch_bounds__(256) amax_16bit_kernel(const uint16_t* __restrict__ x, int64_t M, int64_t K,
+                                                         int64_t ldx, float* __restrict__ amax) {
   pdl_wait();
   const int64_t vec_per_row = K >> 3;
   const int64_t total = M * vec_per_row;
@@ -63,7 +65,10 @@ __global__ void __launch_bounds__(256) amax_bf16_kernel(const uint16_t* __restri
     mm = threadIdx.x < (blockDim.x >> 5) ? s[threadIdx.x] : 0u;
 #pragma unroll
     for (int o = 4; o > 0; o >>= 1) mm = max(mm, __shfl_xor_sync(0xFFFFFFFFu, mm, o));
-    if (threadIdx.x == 0 && mm != 0) atomicMax(reinterpret_cast<int*>(amax), (int)(mm << 16));
+    if (threadIdx.x == 0 && mm != 0) {
+      const int bits = F16 ? __float_as_int(__half2float(__ushort_as_half((unsigned short)mm))) : (int)(mm << 16);
+      atomicMax(reinterpret_cast<int*>(amax), bits);
+    }
   }
 }
 
@@ -134,7 +139,7 @@ __device__ __forceinline__ void transform_block(uint32_t (&w)[8], const Prologue
   for (int j = 0; j < 8; ++j) w[j] = ln_pair<MODE>(w[j], aw[j], bw[j], mean2, rstd2, pr.add_one);
 }
 
-template <int RULE, int MODE>
+template <int RULE, int MODE, bool F16 = false>
 __global__ void __launch_bounds__(256) quantize_nvfp4_kernel(const uint16_t* x, int64_t M, int64_t K,
                                                              int64_t ldx, const float* amax_ptr,
                                                              uint8_t* codes, uint8_t* sf,
@@ -205,7 +210,8 @@ __global__ void __launch_bounds__(256) quantize_nvfp4_kernel(const uint16_t* x, 
     }
     if (codes == nullptr) continue;          // transform-only call (y_out): nothing to quantize
     uint32_t c_lo, c_hi, s;
-    quant_block<RULE>(cur, qc, c_lo, c_hi, s);
+    if (F16) quant_block_f16<RULE>(cur, qc, c_lo, c_hi, s);      // the words hold fp16 values
+    else quant_block<RULE>(cur, qc, c_lo, c_hi, s);
     if (col_ok) *reinterpret_cast<uint2*>(codes + r * (K >> 1) + (col >> 1)) = make_uint2(c_lo, c_hi);
     my_sf |= s << (8 * i);
   }
@@ -467,7 +473,7 @@ extern "C" int llnv_amax_bf16(const void* x, int64_t M, int64_t K, int64_t ldx, 
   int64_t blocks = (total + 256 * 4 - 1) / (256 * 4);
   const int64_t cap = (int64_t)sm_count() * 8;
   if (blocks > cap) blocks = cap;
-  launch_k(amax_bf16_kernel, (unsigned)blocks, 256, 0, stream, (const uint16_t*)x, M, K, ldx, amax);
+  launch_k(amax_16bit_kernel<false>, (unsigned)blocks, 256, 0, stream, (const uint16_t*)x, M, K, ldx, amax);
   return launch_status("amax_bf16_kernel");
 }
 
@@ -645,4 +651,44 @@ extern "C" int llnv_layernorm_quantize_nvfp4_group(const void* x, int64_t M, int
   if (rc != LLNV_OK) return rc;
   return ln_quantize_impl(kAffineLN, x, M, C, ldx, weight, bias, 0, 1, eps, 0, rule, codes, sf, amax, nullptr, 0, row_stats,
                           (cudaStream_t)stream, "llnv_layernorm_quantize_nvfp4_group", 0, 0, &peer);
+}
+
+// fp16 input (the reference's CUDA backend accepts it beside bf16, fouroversix/src/fouroversix/quantize/cuda/backend.py:45-51):
+// same outputs and layouts; every block goes through the reference's fp32 arithmetic one operation at a time.
+extern "C" int llnv_quantize_nvfp4_f16(const void* x, int64_t M, int64_t K, int64_t ldx, int rule, void* codes, void* sf,
+                                       float* amax, int amax_given, llnv_stream_t stream_) {
+  const char* who = "llnv_quantize_nvfp4_f16";
+  cudaStream_t stream = (cudaStream_t)stream_;
+  LLNV_REQUIRE(x && codes && sf && amax, "%s: null pointer", who);
+  LLNV_REQUIRE(M >= 0 && K > 0 && K % 64 == 0, "%s: K must be a positive multiple of 64 (got %lld)", who, (long long)K);
+  LLNV_REQUIRE(ldx >= K && ldx % 8 == 0, "%s: ldx must be >= K and a multiple of 8 (got %lld)", who, (long long)ldx);
+  LLNV_REQUIRE(rule >= 0 && rule <= 4, "%s: unknown scale rule %d", who, rule);
+  LLNV_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)codes & 7) == 0 && ((uintptr_t)sf & 3) == 0, "%s: x must be 16-byte, codes 8-byte, sf 4-byte aligned", who);
+  if (!amax_given) LLNV_CUDA(cudaMemsetAsync(amax, 0, sizeof(float), stream));
+  if (M == 0) return LLNV_OK;
+  if (!amax_given) {
+    int64_t blocks = (M * (K / 8) + 256 * 4 - 1) / (256 * 4);
+    const int64_t cap = (int64_t)sm_count() * 8;
+    if (blocks > cap) blocks = cap;
+    launch_k(amax_16bit_kernel<true>, (unsigned)blocks, 256, 0, stream, (const uint16_t*)x, M, K, ldx, amax);
+    const int rc = launch_status("amax_f16_kernel");
+    if (rc != LLNV_OK) return rc;
+  }
+  const int64_t mp = (M + 127) / 128 * 128;
+  LLNV_REQUIRE(mp / 128 <= 65535, "%s: too many rows (%lld)", who, (long long)M);
+  dim3 grid((unsigned)((K + 63) / 64), (unsigned)(mp / 128));          // 128 threads per CTA: 128 rows x 64 columns
+  const Prologue pr = {};
+  const uint16_t* xp = (const uint16_t*)x;
+  uint8_t* cp = (uint8_t*)codes;
+  uint8_t* sp = (uint8_t*)sf;
+  uint16_t* none = nullptr;
+  const int64_t zero = 0;
+  switch (rule) {
+    case LLNV_RULE_STATIC_6: launch_k(quantize_nvfp4_kernel<LLNV_RULE_STATIC_6, kPlain, true>, grid, 128, 0, stream, xp, M, K, ldx, amax, cp, sp, pr, none, zero); break;
+    case LLNV_RULE_STATIC_4: launch_k(quantize_nvfp4_kernel<LLNV_RULE_STATIC_4, kPlain, true>, grid, 128, 0, stream, xp, M, K, ldx, amax, cp, sp, pr, none, zero); break;
+    case LLNV_RULE_MAE: launch_k(quantize_nvfp4_kernel<LLNV_RULE_MAE, kPlain, true>, grid, 128, 0, stream, xp, M, K, ldx, amax, cp, sp, pr, none, zero); break;
+    case LLNV_RULE_MSE: launch_k(quantize_nvfp4_kernel<LLNV_RULE_MSE, kPlain, true>, grid, 128, 0, stream, xp, M, K, ldx, amax, cp, sp, pr, none, zero); break;
+    default: launch_k(quantize_nvfp4_kernel<LLNV_RULE_ABS_MAX, kPlain, true>, grid, 128, 0, stream, xp, M, K, ldx, amax, cp, sp, pr, none, zero); break;
+  }
+  return launch_status("quantize_nvfp4_kernel<f16>");
 }

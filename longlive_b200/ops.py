@@ -81,8 +81,8 @@ def quantize_nvfp4(x: torch.Tensor, rule_id: int, amax: torch.Tensor | None = No
     if x.dim() == 3 and x.dtype == torch.bfloat16 and x.is_contiguous():
         shards, m, ks = x.shape
         k, ldx = shards * ks, ks
-    elif x.dim() != 2 or x.dtype != torch.bfloat16:
-        raise RuntimeError("quantize_nvfp4 expects a 2-D bfloat16 tensor (or a contiguous [shards, M, K/shards] one)")
+    elif x.dim() != 2 or x.dtype not in (torch.bfloat16, torch.float16):
+        raise RuntimeError("quantize_nvfp4 expects a 2-D bfloat16 or float16 tensor (or a contiguous bfloat16 [shards, M, K/shards] one)")
     else:
         if x.stride(1) != 1:
             x = x.contiguous()
@@ -98,6 +98,13 @@ def quantize_nvfp4(x: torch.Tensor, rule_id: int, amax: torch.Tensor | None = No
         if given:
             raise ValueError("amax_given needs an amax tensor")
         amax = torch.empty(1, dtype=torch.float32, device=x.device)
+    if x.dtype == torch.float16:
+        if group is not None:
+            raise ValueError("the group form takes bfloat16 input")
+        with torch.cuda.device(x.device):
+            _check(_lib.lib().llnv_quantize_nvfp4_f16(x.data_ptr(), m, k, ldx, rule_id, codes.data_ptr(), sf.data_ptr(),
+                                                      amax.data_ptr(), 1 if given else 0, _stream(x)))
+        return codes, sf, amax
     with torch.cuda.device(x.device):
         if group is not None:
             if not given:

@@ -134,11 +134,8 @@ def quantize_to_fp4(x: torch.Tensor, config: QuantizationConfig | None = None, *
         if config.backend is None:
             raise ValueError("No backend found that supports the given parameters")
         raise ValueError(f"Backend {config.backend} does not support the given parameters")
-    if x.dtype == torch.float16:
-        # The reference's CUDA backend also takes fp16 (quantize/cuda/backend.py:45-51).  The kernels here read bf16 bit
-        # patterns (block maxima and the exactness argument of the 4-over-6 decision rest on the 8-bit significand),
-        # and every tensor of the NVFP4 inference path is bf16, so fp16 is refused rather than silently converted.
-        raise ValueError("Backend cuda does not support float16 inputs in this build (bfloat16 only)")
+    # fp16 input, which the reference's CUDA backend takes beside bf16 (quantize/cuda/backend.py:45-51), goes through
+    # llnv_quantize_nvfp4_f16: same result layout, the reference's fp32 arithmetic block by block (ops.quantize_nvfp4).
     rows, cols = x.shape
     if cols % 64 != 0:
         x = F.pad(x, (0, (-cols) % 64))

@@ -34,8 +34,8 @@ def quantize_to_fp4(x: torch.Tensor, is_nvfp4: bool, is_rtn: bool, is_rht: bool,
                     selection_rule: int, rbits: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     if not is_nvfp4 or not is_rtn or is_rht or is_2d or is_transpose:
         raise RuntimeError("llnvfp4::quantize_to_fp4 supports NVFP4 with round-to-nearest, 1-D block scales, no RHT, no transpose")
-    if x.dim() != 2 or x.dtype != torch.bfloat16 or x.shape[1] % 64 != 0:
-        raise RuntimeError("llnvfp4::quantize_to_fp4 expects a 2-D bfloat16 tensor whose column count is a multiple of 64")
+    if x.dim() != 2 or x.dtype not in (torch.bfloat16, torch.float16) or x.shape[1] % 64 != 0:
+        raise RuntimeError("llnvfp4::quantize_to_fp4 expects a 2-D bfloat16 or float16 tensor whose column count is a multiple of 64")
     codes, sf, amax = ops.quantize_nvfp4(x.contiguous(), int(selection_rule))
     return codes, sf, amax
 

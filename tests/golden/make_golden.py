@@ -94,6 +94,7 @@ def edge_case_tensor(gen: torch.Generator) -> torch.Tensor:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the NVlabs/LongLive checkout")
+    ap.add_argument("--only", default="all", choices=["all", "fp16"], help="fp16: write quantize_fp16.npz and nothing else")
     args = ap.parse_args()
     _setup(args.reference)
 
@@ -101,6 +102,23 @@ def main() -> None:
     from fouroversix.quantize.quantized_tensor import from_blocked
 
     rules = ["static_6", "static_4", "mae", "mse", "abs_max"]
+
+    # ---- 0. quantizer on fp16 input (the reference widens to fp32; 11-bit significands, fp16 subnormals) ----------
+    gen16 = torch.Generator().manual_seed(4321)
+    x16 = (torch.randn(200, 192, generator=gen16) * 2).half()
+    x16[3] = 0
+    x16[5, 0:16] = torch.tensor([6.1e-5, -3.0e-5, 5.96e-8, 0.0] * 4).half()          # around the smallest normal / subnormal halves
+    x16[7, 16:32] = torch.tensor([60000.0, -65504.0] + [1.0] * 14).half()            # the largest halves set the tensor amax
+    x16[9, 32:48] = -0.0
+    out16 = {"x": x16.view(torch.int16).numpy().view(np.uint16)}
+    for rule in rules:
+        q = quantize_to_fp4(x16, QuantizationConfig(backend="pytorch", scale_rule=rule))
+        out16[f"{rule}_codes"] = q.values.numpy()
+        out16[f"{rule}_sf"] = u8(q.scale_factors)
+        out16[f"{rule}_amax"] = np.float32(q.amax.item())
+    np.savez_compressed(os.path.join(HERE, "quantize_fp16.npz"), **out16)
+    if args.only == "fp16":
+        return
 
     # ---- 1. quantizer, all rules, edge-case tensor + plain randn + all-zero ----------
     gen = torch.Generator().manual_seed(1234)

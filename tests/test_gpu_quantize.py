@@ -207,3 +207,28 @@ def test_quantize_two_tensors_in_one_launch():
         for r, q in ((ra, qa), (rb, qb)):
             assert torch.equal(r.values, q.values) and torch.equal(r.amax, q.amax)
             assert torch.equal(r.scale_factors.view(torch.uint8), q.scale_factors.view(torch.uint8))
+
+
+@pytest.mark.parametrize("rule", RULES)
+def test_quantize_fp16_input(golden, rule):
+    """fp16 activations (accepted by the reference's CUDA backend beside bf16): codes, scales and amax equal the
+    reference's PyTorch quantizer on the fixture tensor and the oracle on a larger seeded one, with and without a given
+    amax; the custom op takes fp16 as well."""
+    g = golden("quantize_fp16.npz")
+    x = torch.from_numpy(g["x"].view(np.int16).copy()).view(torch.float16)
+    q = L.quantize_to_fp4(x.cuda(), L.QuantizationConfig(scale_rule=rule))
+    assert q.original_shape == tuple(x.shape) and float(q.amax.item()) == float(g[f"{rule}_amax"])
+    assert np.array_equal(util.u8(q.scale_factors), g[f"{rule}_sf"]) and np.array_equal(q.values.cpu().numpy(), g[f"{rule}_codes"])
+    gen = torch.Generator().manual_seed(77)
+    big = (torch.randn(520, 1024, generator=gen) * 3)
+    big = torch.where(torch.rand(520, 1024, generator=gen) < 0.002, big * 50, big).half()
+    oc, osf, oamax = O.quantize_nvfp4(big.float().numpy(), rule)
+    qb = L.quantize_to_fp4(big.cuda(), L.QuantizationConfig(scale_rule=rule))
+    assert float(qb.amax.item()) == float(oamax) and np.array_equal(util.u8(qb.scale_factors), osf)
+    assert np.array_equal(qb.values.cpu().numpy(), oc)
+    q2 = L.quantize_to_fp4(big.cuda(), L.QuantizationConfig(scale_rule=rule), amax=qb.amax.clone())
+    assert torch.equal(q2.values, qb.values) and torch.equal(q2.scale_factors.view(torch.uint8), qb.scale_factors.view(torch.uint8))
+    if rule == "mse":
+        import longlive_b200.torch_ops  # noqa: F401  (registers torch.ops.llnvfp4)
+        v, s, a = torch.ops.llnvfp4.quantize_to_fp4(big.cuda(), True, True, False, False, False, 3, 0)
+        assert torch.equal(v, qb.values) and torch.equal(s.view(torch.uint8), qb.scale_factors.view(torch.uint8)) and torch.equal(a, qb.amax)
