@@ -10,6 +10,8 @@ and stores small input/output vectors as ``.npz`` files.  The fixtures travel wi
 repository; the reference itself does not, so nothing else reads the reference at run time.
 
 bf16 tensors are stored as uint16 bit patterns, e4m3 scales as uint8 bit patterns.
+``--only fp16`` writes just ``quantize_fp16.npz`` (the quantizer on an fp16 tensor, stored as uint16 bit patterns of
+the halves) and leaves the other files as they are.
 """
 from __future__ import annotations
 
