@@ -44,8 +44,15 @@
 // lookups, the sign bits, four interleaves.  No conversion or multiply runs per element, so the
 // decode stays off the special-function pipe the softmax's exp2 lives on.  A tile that holds the
 // last cached keys and the first keys of the current chunk is also built by these warps (they copy
-// the bf16 rows); tiles that lie entirely in the current chunk come from TMA as before.  With 16 warps the register file is re-divided after
-// start-up (setmaxnreg): load/MMA warpgroup 56, decode warpgroup 104, softmax warpgroups 176.
+// the bf16 rows); tiles that lie entirely in the current chunk come from TMA as before.
+// Warp roles of this instantiation (16 warps): 0 = Q and K loads (code tiles or bf16 tiles), 1 = MMA issuer, 2 = V loads,
+// 3 idle, 4-7 / 8-11 = softmax of half a / b, 12-15 = decode.  The register file is re-divided at the top of each role's
+// branch (setmaxnreg): load / MMA warpgroup 56, decode warpgroup 104, softmax warpgroups 176.
+//
+// Work split.  blockIdx.z = key split: with nsplit > 1 every (query tile, head) item is cut into nsplit equal ranges of key
+// tiles, each CTA writes unnormalised fp32 partials and (m, l), and attention_combine_kernel merges them (head shards with
+// too few items to fill the device).  Tail balancing (tail_cut > 0) cuts only the items of the last partial wave, once, into a
+// long and a short CTA, so that the short ones fill the SMs the long ones leave free (see tail_cut_for).
 #include <cuda.h>
 #include <cuda_fp4.h>
 
