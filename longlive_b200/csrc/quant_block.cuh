@@ -205,7 +205,7 @@ __device__ __forceinline__ void quant_block(const uint32_t (&w)[8], const QuantC
   }
   const float inv4 = __frcp_rn(__fmul_rn(qc.dec, s4));
   const float sa6 = __fmul_rn(s6, qc.amax), sa4 = __fmul_rn(s4, qc.amax);        // exact (4 + 8 significant bits)
-  uint32_t lo6 = 0, hi6 = 0, lo4 = 0, hi4 = 0;
+  uint32_t pa[4], pb[4];
   float e6 = 0.f, e4 = 0.f;
   // pair j holds elements (2j, 2j+1) in w[j] and (2j+8, 2j+9) in w[j+4]; the error sum adds
   // element i to element i+8 first, then the eight lane sums left to right
@@ -221,8 +221,9 @@ __device__ __forceinline__ void quant_block(const uint32_t (&w)[8], const QuantC
     const uint32_t cb6 = cvt_e2m1x2(sb6v.x, sb6v.y);
     const uint32_t ca4 = cvt_e2m1x2(sa4v.x, sa4v.y);
     const uint32_t cb4 = cvt_e2m1x2(sb4v.x, sb4v.y);
-    lo6 |= ca6 << (8 * j); hi6 |= cb6 << (8 * j);
-    lo4 |= ca4 << (8 * j); hi4 |= cb4 << (8 * j);
+    // candidate-6 and candidate-4 code bytes of this pair side by side; the selected ones are gathered at the end
+    pa[j] = __byte_perm(ca6, ca4, 0x0040);
+    pb[j] = __byte_perm(cb6, cb4, 0x0040);
     const float2 qa6 = e2m1x2_to_float2(ca6), qb6 = e2m1x2_to_float2(cb6);
     const float2 qa4 = e2m1x2_to_float2(ca4), qb4 = e2m1x2_to_float2(cb4);
     // dequantized candidates minus x, two elements per packed instruction (every lane rounds as the scalar op does)
@@ -257,8 +258,10 @@ __device__ __forceinline__ void quant_block(const uint32_t (&w)[8], const QuantC
     }
   }
   const bool sel4 = e4 < e6;
-  c_lo = sel4 ? lo4 : lo6;
-  c_hi = sel4 ? hi4 : hi6;
+  // bytes (c6_0, c4_0, c6_1, c4_1) | (c6_2, c4_2, c6_3, c4_3): one permute picks the even (6) or the odd (4) bytes
+  const uint32_t pick = sel4 ? 0x7531u : 0x6420u;
+  c_lo = __byte_perm(__byte_perm(pa[0], pa[1], 0x5410), __byte_perm(pa[2], pa[3], 0x5410), pick);
+  c_hi = __byte_perm(__byte_perm(pb[0], pb[1], 0x5410), __byte_perm(pb[2], pb[3], 0x5410), pick);
   sf_out = sel4 ? (sc >> 8) : (sc & 0xFFu);
 }
 
