@@ -89,3 +89,20 @@ def test_quantize_model_filter_and_registry():
     assert model["blocks"][0].q.quantized_weight_values.shape == (64, 32)
     with pytest.raises(ValueError):
         L.QuantizedModule.register(nn.Linear)(object)
+
+
+def test_documented_python_seam_names_exist():
+    """Every name the integration notes rebind on the reference's utils.quant (and the scheduler class) is importable from
+    this package, so the documented aliasing snippet cannot rot."""
+    import longlive_b200
+    import longlive_b200.kv_cache
+    import longlive_b200.scheduler
+    for name in ("quantize_to_fp4", "dequantize_kv_cache", "copy_quantized_into", "clone_quantized_tensor", "k_smooth",
+                 "quantize_model_with_filter", "_materialize_quantized_weights_for_inference", "LongLiveQuantizationConfig"):
+        obj = getattr(longlive_b200, name, None) or getattr(longlive_b200.kv_cache, name, None)
+        assert obj is not None, name
+    for name in ("DataType", "ModelQuantizationConfig", "QuantizationConfig", "QuantizedTensor", "RoundStyle", "ScaleRule",
+                 "quantize_model", "quantize_to_fp4", "fp4_matmul", "FourOverSixLinear"):
+        assert hasattr(longlive_b200, name), name
+    sched = longlive_b200.scheduler.FlowUniPCMultistepScheduler
+    assert all(hasattr(sched, m) for m in ("set_timesteps", "step"))
